@@ -1,0 +1,69 @@
+"""ctypes binding of libbitnet_b200.so (the C ABI in include/bitnet_b200.h).
+
+There is no CPU or PyTorch fallback: if the shared library is missing, importing this
+module raises, and every wrapper raises on a non-zero status from the library.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libbitnet_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m bitnet_b200.build` "
+        "(needs nvcc; there is no fallback implementation)"
+    )
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i, _i64, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+# every symbol include/bitnet_b200.h declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "bitnet_last_status": (_i, []),
+    "bitnet_status_string": (ctypes.c_char_p, [_i]),
+    "bitnet_last_cuda_error": (ctypes.c_char_p, []),
+    "bitlinear_int8xint2": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "bitnet_linear_w2a8": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _vp]),
+    "bitnet_quant_input": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
+    "bitnet_w2t_bytes": (ctypes.c_size_t, [_i, _i]),
+    "bitnet_pack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),
+    "bitnet_pack_from_i2s": (_i, [_vp, _vp, _i, _i, _vp]),
+    "bitnet_pack_from_ref_int2": (_i, [_vp, _vp, _i, _i, _vp]),
+    "bitnet_unpack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),
+    "quantize_i2_s": (ctypes.c_size_t, [_vp, _vp, _i64, _i64, _vp]),
+    "ggml_vec_dot_i2_i8_s": (None, [_i, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _i]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)          # AttributeError here = the library lacks a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class BitnetError(RuntimeError):
+    pass
+
+
+def check(status: int | None = None) -> None:
+    """Raises BitnetError unless the library's last status (or `status`) is 0."""
+    st = lib.bitnet_last_status() if status is None else status
+    if st != 0:
+        msg = lib.bitnet_status_string(st).decode()
+        if st == 3:
+            msg += ": " + lib.bitnet_last_cuda_error().decode()
+        raise BitnetError(f"libbitnet_b200: {msg} (status {st})")
+
+
+def ptr(t) -> ctypes.c_void_p:
+    """Device (or host) address of a torch tensor, NULL for None."""
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    import torch
+
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)

@@ -1,0 +1,50 @@
+// Host-side launchers shared between the translation units of libbitnet_b200.so.
+#pragma once
+#include "common.cuh"
+
+namespace bitnet {
+
+// One BitLinear call: out[M,N] = ((y[M,K] . W[N,K]^T) / a[m]) * ws[segment(n)].
+struct LinearArgs {
+    const void* w2t = nullptr;          // W2T packed weights (device)
+    const int8_t* y = nullptr;          // int8 activations [M, ldy] (device)
+    int64_t ldy = 0;
+    const int32_t* ysum = nullptr;      // optional [M]
+    int32_t* acc_out = nullptr;         // optional int32 [M, N]
+    __nv_bfloat16* out = nullptr;       // optional bf16 [M, ldo]
+    int64_t ldo = 0;
+    const float* a_f32 = nullptr;       // activation scale per token (one of the two)
+    const __nv_bfloat16* a_bf16 = nullptr;
+    int a_stride = 1;
+    const float* ws_f32 = nullptr;      // weight scale per segment (one of the two)
+    const __nv_bfloat16* ws_bf16 = nullptr;
+    ScaleSegments seg{1, {0, 0, 0, 0, 0, 0, 0, 0}};
+    int M = 0, N = 0, K = 0;
+};
+
+int w2a8_gemv(const LinearArgs& a, cudaStream_t stream);
+
+// Packers (all buffers on the device).
+int pack_ternary_to_w2t(const int8_t* q, void* w2t, int N, int K, cudaStream_t stream);
+int pack_i2s_to_w2t(const uint8_t* i2s, void* w2t, int N, int K, cudaStream_t stream);
+int pack_refgpu_to_w2t(const int8_t* packed, void* w2t, int N, int K, cudaStream_t stream);
+int unpack_w2t_to_ternary(const void* w2t, int8_t* q, int N, int K, cudaStream_t stream);
+int i2s_quantize(const float* src, uint8_t* dst, int64_t n_total, uint32_t* absmax_bits_scratch, cudaStream_t stream);
+
+// Activation prologue: optional RMSNorm, then per-token absmax int8 quantisation.
+struct QuantArgs {
+    const __nv_bfloat16* x_bf16 = nullptr;   // one of x_bf16 / x_f32
+    const float* x_f32 = nullptr;
+    int64_t ldx = 0;
+    const __nv_bfloat16* gamma = nullptr;    // RMSNorm weight [K] or null (no norm)
+    float eps = 1e-5f;
+    int8_t* y = nullptr;
+    int64_t ldy = 0;                         // >= K; bytes [K, ldy) are zero-filled
+    float* a_f32 = nullptr;                  // optional [M]
+    __nv_bfloat16* a_bf16 = nullptr;         // optional [M]
+    int32_t* ysum = nullptr;                 // optional [M]
+    int M = 0, K = 0;
+};
+int act_quant(const QuantArgs& a, cudaStream_t stream);
+
+}  // namespace bitnet

@@ -1,0 +1,64 @@
+"""Python entry points of the W2A8 BitLinear path (thin wrappers over the C ABI)."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+
+def bitnet_int8xint2_linear(input0: torch.Tensor, input1: torch.Tensor, s: torch.Tensor, ws: torch.Tensor,
+                            ret: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Same call as the reference's gpu/model.py:21-37 (and gpu/test.py:15-29 when `ret` is
+    given): int8 activations [.., K] x packed weights [N, K/4] -> bf16 [.., N] through the
+    `bitlinear_int8xint2` symbol, on the current stream."""
+    out_shape = list(input0.shape)
+    out_shape[-1] = input1.shape[0]
+    m = input0.shape[0]
+    if len(out_shape) == 3:
+        m *= input0.shape[1]
+    n = input1.shape[0]
+    k = input1.shape[1] * 4
+    if ret is None:
+        ret = torch.empty(*out_shape, dtype=torch.bfloat16, device=input0.device)
+    _lib.lib.bitlinear_int8xint2(_lib.ptr(input0), _lib.ptr(input1), _lib.ptr(ret), _lib.ptr(s), _lib.ptr(ws),
+                                 m, n, k, _lib.stream_ptr())
+    _lib.check()
+    return ret
+
+
+def quant_input(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 1e-5, pad_to: int = 128):
+    """(Optional RMSNorm, then) per-token absmax int8 quantisation of bf16 x [.., K]
+    (BitLinearKernel.quant_input, gpu/model.py:68-71).  Returns (y int8 [M, K_pad],
+    act_scale f32 [M], ysum int32 [M]); K_pad = K rounded up to `pad_to`, zero filled."""
+    assert x.dtype == torch.bfloat16 and x.is_cuda
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    m = x2.shape[0]
+    k_pad = (k + pad_to - 1) // pad_to * pad_to
+    y = torch.empty((m, k_pad), dtype=torch.int8, device=x.device)
+    a = torch.empty((m,), dtype=torch.float32, device=x.device)
+    ysum = torch.empty((m,), dtype=torch.int32, device=x.device)
+    _lib.check(_lib.lib.bitnet_quant_input(_lib.ptr(x2), x2.stride(0), _lib.ptr(gamma), eps, _lib.ptr(y), k_pad,
+                                           _lib.ptr(a), None, _lib.ptr(ysum), m, k, _lib.stream_ptr()))
+    return y, a, ysum
+
+
+def linear_w2a8(y: torch.Tensor, act_scale: torch.Tensor, ysum: Optional[torch.Tensor], weight: torch.Tensor,
+                w_scale: torch.Tensor, seg_end: Sequence[int], n: int, k: int,
+                want_acc: bool = False, want_out: bool = True):
+    """int8 y [M, ldy] x packed weight -> bf16 [M, N] (and/or the exact int32 sums)."""
+    m = y.shape[0]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=y.device) if want_out else None
+    acc = torch.empty((m, n), dtype=torch.int32, device=y.device) if want_acc else None
+    seg = (ctypes.c_int * len(seg_end))(*seg_end)
+    _lib.check(_lib.lib.bitnet_linear_w2a8(_lib.ptr(y), y.stride(0), _lib.ptr(weight), _lib.ptr(out), n, _lib.ptr(acc),
+                                           _lib.ptr(act_scale), _lib.ptr(ysum), _lib.ptr(w_scale), seg, len(seg_end),
+                                           m, n, k, _lib.stream_ptr()))
+    if want_acc and want_out:
+        return out, acc
+    return acc if want_acc else out

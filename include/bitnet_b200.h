@@ -1,0 +1,112 @@
+/* C ABI of libbitnet_b200.so: the W2A8 BitLinear hot path of microsoft/BitNet on NVIDIA
+ * B200 (sm_100a).  Plain pointers and sizes only.  Unless a function says "host", every
+ * buffer pointer is a device pointer owned by the caller; the library keeps none of them.
+ * `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Functions that
+ * return int return 0 on success or one of the BITNET_STATUS_* codes; all functions also
+ * record that code for bitnet_last_status().  No function aborts, traps or prints.
+ *
+ * Paths in the comments are relative to the microsoft/BitNet checkout. */
+#ifndef BITNET_B200_H
+#define BITNET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BITNET_STATUS_OK            0
+#define BITNET_STATUS_BAD_ARGUMENT  1
+#define BITNET_STATUS_UNSUPPORTED   2
+#define BITNET_STATUS_CUDA_ERROR    3
+#define BITNET_STATUS_TOO_LARGE     4
+
+/* Status of the calling thread's most recent library call.  The reference reports nothing
+ * (void return, a message on stdout for an unknown shape,
+ * gpu/bitnet_kernels/bitnet_kernels.cu:34-36); this is the queryable replacement. */
+int bitnet_last_status(void);
+const char* bitnet_status_string(int status);
+/* cudaGetErrorString of the last failing CUDA call on this thread ("" if none). */
+const char* bitnet_last_cuda_error(void);
+
+/* ---- the reference's GPU entry point --------------------------------------------------
+ * Replaces bitlinear_int8xint2 of gpu/bitnet_kernels/bitnet_kernels.cu:3-37, which
+ * gpu/model.py:21-37 and gpu/test.py:15-29 call through ctypes with exactly these
+ * arguments.
+ *   input0  int8 [M,K] activations         input1  packed weights, viewed int8 [N,K/4]
+ *   output0 bf16 [M,N]                     s       bf16 [M] activation scales 127/absmax
+ *   ws      bf16 weight scales, one per row segment
+ * output0[m,n] = bf16( float(sum_k input0[m,k]*w[n,k]) / s[m] * ws[segment(n)] ).
+ * Differences from the reference: any M >= 1 and any N, K with N % 16 == 0 and
+ * K % 128 == 0 are accepted (the reference takes M == 1 and ten fixed shapes); s is read
+ * per token (the reference reads s[0], its only token); input1 must be in this library's
+ * W2T layout, as bitnet_pack_ternary / bitnet_pack_from_ref_int2 produce it (same byte
+ * count and [N,K/4] shape as the reference's layout).  Row segments follow the
+ * reference's shape ladder: N/ws_num equal parts with ws_num = 3 for (N,K)=(3840,2560),
+ * 2 for (13824,2560) and (20480,3200), 6 for (4800,3200), else 1
+ * (gpu/bitnet_kernels/bitnet_kernels.cu:4-33, bitnet_kernels.h:80-82).
+ * Asynchronous on `stream`; allocates nothing; may be captured in a CUDA graph. */
+void bitlinear_int8xint2(int8_t* input0, int8_t* input1, void* output0, void* s, void* ws,
+                         int M, int N, int K, void* stream);
+
+/* ---- the same operation with explicit arguments ---------------------------------------
+ * Serves gpu/model.py:54-75 (BitLinearKernel.forward) with the row segments stated by the
+ * caller instead of guessed from the shape (for the fused wqkv the segments are the q, k
+ * and v row ranges that gpu/convert_checkpoint.py:41-52 quantised separately).
+ *   y        int8 [M, ldy], ldy >= K         w2t     W2T packed weights (bitnet_w2t_bytes)
+ *   out_bf16 bf16 [M, ldo] or NULL           acc_out int32 [M, N] or NULL: the exact
+ *                                                    sum_k y[m,k]*w[n,k]
+ *   act_scale f32 [M]                        ysum    int32 [M] = sum_k y[m,k], or NULL
+ *                                                    (then computed inside the kernel)
+ *   w_scale  f32 [n_seg]                     seg_end host int[n_seg], seg_end[i] = first
+ *                                                    row after segment i; n_seg <= 8
+ * Any M >= 1, N >= 1, K >= 1 (rows beyond N and columns beyond K are padding in w2t). */
+int bitnet_linear_w2a8(const int8_t* y, int64_t ldy, const void* w2t, void* out_bf16, int64_t ldo,
+                       int32_t* acc_out, const float* act_scale, const int32_t* ysum,
+                       const float* w_scale, const int* seg_end, int n_seg,
+                       int M, int N, int K, void* stream);
+
+/* Activation prologue: optional RMSNorm (gamma_bf16 != NULL; gpu/model.py:159-160,
+ * 195-196, 237-242) followed by BitLinearKernel.quant_input (gpu/model.py:68-71):
+ * a = 127 / max(absmax, 1e-5), y = clamp(round_half_even(x*a), -128, 127).
+ *   x_bf16 bf16 [M, ldx]      y int8 [M, ldy] (bytes K..ldy-1 of each row are zeroed)
+ *   act_scale f32 [M] or NULL, s_bf16 bf16 [M] or NULL (the reference's `s`),
+ *   ysum int32 [M] or NULL. */
+int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, float eps,
+                       int8_t* y, int64_t ldy, float* act_scale, void* s_bf16, int32_t* ysum,
+                       int M, int K, void* stream);
+
+/* ---- weight layout conversion ----------------------------------------------------------
+ * Size in bytes of a W2T buffer for an [N,K] matrix: ceil16(N) * ceil128(K) / 4. */
+size_t bitnet_w2t_bytes(int N, int K);
+/* ternary int8 [N,K] in {-1,0,+1} (gpu/convert_checkpoint.py:23-27) -> W2T.  Replaces
+ * convert_weight_int8_to_int2 of gpu/pack_weight.py:76-98. */
+int bitnet_pack_ternary(const int8_t* q, void* w2t, int N, int K, void* stream);
+/* I2_S bytes (src/ggml-bitnet-mad.cpp:80-88; N*K % 128 == 0) -> W2T. */
+int bitnet_pack_from_i2s(const uint8_t* i2s, void* w2t, int N, int K, void* stream);
+/* The reference's GPU int2 bytes (gpu/pack_weight.py:76-98; N % 16 == 0, K % 32 == 0), as
+ * stored in its model_state_int2.pt checkpoints -> W2T. */
+int bitnet_pack_from_ref_int2(const int8_t* packed, void* w2t, int N, int K, void* stream);
+/* W2T -> ternary int8 [N,K]. */
+int bitnet_unpack_ternary(const void* w2t, int8_t* q, int N, int K, void* stream);
+
+/* ---- the reference's CPU I2_S entry points, backed by the GPU (HOST pointers) ----------
+ * quantize_i2_s of src/ggml-bitnet-mad.cpp:51-96: f32 (zero or +-scale) -> I2_S bytes plus
+ * the f32 scale at byte nrow*n_per_row/4; returns nrow*n_per_row/4 + 32, or 0 on failure.
+ * Byte-identical to the reference's x86 ACT_PARALLEL output.  quant_weights is ignored,
+ * as in the reference. */
+size_t quantize_i2_s(const float* src, void* dst, int64_t nrow, int64_t n_per_row, const float* quant_weights);
+/* ggml_vec_dot_i2_i8_s of src/ggml-bitnet-mad.cpp:1043-1056.  As in the reference:
+ * if nrc % 4 == 0, one weight row vx against nrc activation rows (stride by bytes),
+ * s[j*bs] = sum_k code_k * y_j[k]; otherwise nrc weight rows (stride bx/4 bytes) against
+ * the one activation row vy, s[row] = sum.  Codes are {0,1,2,3} taken literally, no
+ * offset and no scale; sums are exact (the reference's int16 lanes can wrap on extreme
+ * inputs, this cannot). */
+void ggml_vec_dot_i2_i8_s(int n, float* s, size_t bs, const void* vx, size_t bx,
+                          const void* vy, size_t by, int nrc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITNET_B200_H */
