@@ -255,6 +255,7 @@ def run_ours(a, args_model):
 
     # ---- the BitLinear kernel alone: every BitLinear of the model, once per step ----------
     lins = [m for m in model.modules() if isinstance(m, BitLinearKernel)]
+    fused = gen.fused is not None
     inputs = {}
     for lin in lins:
         if lin.in_features not in inputs:
@@ -264,6 +265,9 @@ def run_ours(a, args_model):
     weight_bytes = sum(l.out_features * l.in_features // 4 for l in lins)
 
     def linears_once():
+        if fused:                      # the fused BitLinear kernels (prologue + matmul), chained
+            gen.fused.bench_linears(gen.tokens)
+            return
         for lin in lins:
             y, sc, ys = inputs[lin.in_features]
             ops.linear_w2a8(y, sc, ys, lin.weight, lin.scale_f32, lin.seg_end, lin.out_features, lin.in_features)
@@ -316,10 +320,11 @@ def run_ours(a, args_model):
                          % (weight_bytes / 1e6)},
         "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
                 "d2h_bytes_per_step": 8 * B},
-        "gpu_launches": 2 * n_lin * K,
+        "gpu_launches": (gen.fused.kernels_per_step if fused else 2 * n_lin) * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": "measured" if peaks else "fallback",
-                     "kernel": "w2a8_gemv_kernel", "launches_per_step": n_lin,
+                     "kernel": "fused_linear_kernel (prologue + W2A8 matmul, PDL chain)" if fused else "w2a8_gemv_kernel",
+                     "launches_per_step": n_lin,
                      "bytes_per_launch": weight_bytes / n_lin, "us_per_launch": 1e3 * ms_lin / n_lin},
         "cpu_baseline": cpu, "clocks": clocks,
     }

@@ -29,6 +29,12 @@ SIGNATURES = {
     "bitlinear_int8xint2": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bitnet_linear_w2a8": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _vp]),
     "bitnet_quant_input": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
+    "bitnet_decoder_create": (_vp, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "bitnet_decoder_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "bitnet_decoder_bench_linears": (_i, [_vp, _vp, _vp]),
+    "bitnet_decoder_error_flag": (_i, [_vp]),
+    "bitnet_decoder_kernels_per_step": (_i, [_vp]),
+    "bitnet_decoder_destroy": (None, [_vp]),
     "bitnet_w2t_bytes": (ctypes.c_size_t, [_i, _i]),
     "bitnet_pack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),
     "bitnet_pack_from_i2s": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -1,0 +1,721 @@
+// One decode step of the BitNet decoder (batch <= 8, one new token per sequence) as a chain
+// of seven kernel types launched with programmatic dependent launch:
+//
+//   per layer:  wqkv -> attention -> wo -> w13 -> w2          then:  output head -> argmax
+//
+// A BitLinear at batch 1 moves 1.6-8.8 MB of packed weights: about a microsecond of HBM
+// time, less than a kernel boundary costs.  The chain therefore hides the boundaries
+// instead of paying them: every kernel lets its successor start at once
+// (griddepcontrol.launch_dependents as its first instruction); the successor's CTAs bring
+// their whole share of the weight matrix into shared memory with bulk asynchronous copies
+// - the weights do not depend on the predecessor - and only then wait for the predecessor
+// (griddepcontrol.wait) to read the activations.  Each BitLinear kernel fuses, in front of
+// the matmul, everything between the previous matmul and this one (rescale of the previous
+// int32 sums to bf16, residual add, squared-ReLU gate, attention split combine, RMSNorm,
+// absmax, int8 quantisation), following gpu/model.py:121-162, 192-197, 231-243, and leaves
+// exact int32 sums for its successor.
+//
+// Work split of a BitLinear: the matrix is a flat sequence of 16x128 tiles (row-group
+// major); CTA c of G takes a contiguous range of total/G tiles, so the load is even for
+// every shape.  Ranges cut through row groups, so each CTA reduces its sums in shared
+// memory and adds them to the int32 output with red.global.add; integer addition makes the
+// result independent of order.  The output buffers are zeroed by a later kernel of the
+// chain after their last reader has finished (see `zero_buf`).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "decode_fused.h"
+
+namespace bitnet {
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kStageTiles = 32;
+constexpr int kStageBytes = kStageTiles * kTileBytes;     // 16 KB
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kLinearThreads = kConsumerThreads + 32;     // + one producer warp
+constexpr long long kWaitCycles = 2000000000LL;           // about one second: then give up
+
+// ---------------------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and the caller abandons the kernel) after about a second.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitCycles) return false;
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads) : "memory"); }
+
+// bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
+__device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
+
+// Sum / max over the 256 consumer threads (two named-barrier syncs).
+__device__ __forceinline__ float consumer_reduce(float v, bool is_max, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, t) : v + t;
+    }
+    consumer_sync();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    consumer_sync();
+    float r = scratch[0];
+#pragma unroll
+    for (int i = 1; i < kConsumerWarps; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+    return r;
+}
+
+__device__ __forceinline__ void zero_duty(int32_t* buf, int count, int cta, int n_cta, int tid, int n_thr) {
+    if (!buf) return;
+    for (int i = cta * n_thr + tid; i < count; i += n_cta * n_thr) buf[i] = 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// The value of element k of token m of the vector that enters the norm, by source kind.
+// ---------------------------------------------------------------------------------------
+template <int SRC>
+__device__ __forceinline__ float source_value(const FusedLinearParams& p, int m, int k) {
+    if (SRC == kSrcEmbedding) {
+        return __bfloat162float(p.emb[p.tokens[m] * (int64_t)p.K + k]);
+    } else if (SRC == kSrcResidual) {
+        const float lin = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + k], p.a_in[m], p.ws_in[0]);
+        return bf16_round(__bfloat162float(p.h_in[(int64_t)m * p.K + k]) + lin);
+    } else if (SRC == kSrcGlu) {
+        const float a = p.a_in[m];
+        const float x1 = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + k], a, p.ws_in[0]);
+        const float x3 = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + p.K + k], a, p.ws_in[1]);
+        const float r = fmaxf(x1, 0.f);
+        return bf16_round(bf16_round(r * r) * x3);
+    } else {   // kSrcAttention: combine the KV splits of head k / D
+        const int h = k / p.D, d = k - h * p.D;
+        const float* ml = p.part_ml + ((int64_t)(m * p.H + h) * p.S) * 2;
+        const float* po = p.part_o + ((int64_t)(m * p.H + h) * p.S) * p.D + d;
+        float mx = -INFINITY;
+        for (int s = 0; s < p.S; ++s) mx = fmaxf(mx, ml[2 * s]);
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < p.S; ++s) {
+            const float l = ml[2 * s + 1];
+            if (l > 0.f) {
+                const float w = __expf(ml[2 * s] - mx) * l;
+                num += w * po[(int64_t)s * p.D];
+                den += w;
+            }
+        }
+        return bf16_round(den > 0.f ? num / den : 0.f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Fused BitLinear: prologue (source -> RMSNorm -> int8) + W2A8 matmul over this CTA's tiles
+// ---------------------------------------------------------------------------------------
+template <int SRC>
+__global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const FusedLinearParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 8 floats
+    int* ysum_s = reinterpret_cast<int*>(scratch + 8);                         // 8 ints
+    float* a_s = reinterpret_cast<float*>(ysum_s + 8);                         // 8 floats
+    int* sacc = reinterpret_cast<int*>(a_s + 8);                               // [r_max][16][8]
+    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [M][K]
+    const int y_stride = p.k_tiles * kTileCols + 16;
+    int8_t* ys = reinterpret_cast<int8_t*>(xv + (size_t)p.M * p.K_even);        // [M][y_stride]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, n_cta = gridDim.x;
+
+    // this CTA's tile range
+    const int t0 = cta * p.tiles_base + min(cta, p.tiles_rem);
+    const int n_tiles = p.tiles_base + (cta < p.tiles_rem ? 1 : 0);
+    const int n_chunks = (n_tiles + kStageTiles - 1) / kStageTiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kConsumerWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kConsumerWarps) {
+        // ---- producer: streams the weight tiles; independent of the predecessor kernel ----
+        if (lane == 0) {
+            const uint8_t* src = p.w2t + (int64_t)t0 * kTileBytes;
+            for (int c = 0; c < n_chunks; ++c) {
+                const int s = c % kStages;
+                if (c >= kStages && !mbar_wait(&empty_bar[s], ((c / kStages) - 1) & 1)) {
+                    atomicExch(p.error_flag, 1);
+                    break;
+                }
+                const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
+                mbar_expect_tx(&full_bar[s], tiles * kTileBytes);
+                bulk_g2s(ring + s * kStageBytes, src + (int64_t)c * kStageBytes, tiles * kTileBytes, &full_bar[s]);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ---------------------------------------------------------------------
+    for (int i = tid; i < p.r_max * 128; i += kConsumerThreads) sacc[i] = 0;
+
+    pdl_wait();   // the predecessor's results are visible from here on
+
+    zero_duty(p.zero_buf, p.zero_count, cta, n_cta, tid, kConsumerThreads);
+
+    // prologue, one token at a time: v -> RMSNorm -> bf16 -> absmax -> int8
+    for (int m = 0; m < p.M; ++m) {
+        __nv_bfloat16* xm = xv + (size_t)m * p.K_even;
+        float ss = 0.f;
+        for (int k = tid; k < p.K; k += kConsumerThreads) {
+            const float v = source_value<SRC>(p, m, k);
+            xm[k] = __float2bfloat16_rn(v);
+            ss += v * v;
+        }
+        if ((SRC == kSrcEmbedding || SRC == kSrcResidual) && p.h_out) {
+            // the new residual stream: each CTA stores its slice
+            consumer_sync();
+            const int lo = (int)((int64_t)p.K * cta / n_cta), hi = (int)((int64_t)p.K * (cta + 1) / n_cta);
+            for (int k = lo + tid; k < hi; k += kConsumerThreads) p.h_out[(int64_t)m * p.K + k] = xm[k];
+        }
+        ss = consumer_reduce(ss, false, scratch);
+        const float rinv = rsqrtf(ss / (float)p.K + p.eps);
+        float mx = 0.f;
+        for (int k = tid; k < p.K; k += kConsumerThreads) {
+            const float xn = bf16_round(__bfloat162float(xm[k]) * rinv * __bfloat162float(p.gamma[k]));
+            xm[k] = __float2bfloat16_rn(xn);
+            mx = fmaxf(mx, fabsf(xn));
+        }
+        mx = consumer_reduce(mx, true, scratch);
+        const float a = 127.0f / fmaxf(mx, 1e-5f);
+        int8_t* ym = ys + (size_t)m * y_stride;
+        float sy = 0.f;
+        for (int k = tid; k < p.k_tiles * kTileCols; k += kConsumerThreads) {
+            float f = 0.f;
+            if (k < p.K) {
+                f = rintf(__bfloat162float(xm[k]) * a);
+                f = fminf(fmaxf(f, -128.f), 127.f);
+            }
+            ym[k] = (int8_t)(int)f;
+            sy += f;
+        }
+        sy = consumer_reduce(sy, false, scratch);   // exact: |sum| < 2^24
+        if (tid == 0) {
+            ysum_s[m] = (int)sy;
+            a_s[m] = a;
+            if (cta == 0) p.a_out[m] = a;
+        }
+    }
+    consumer_sync();
+
+    // ---- matmul over the staged tiles ----------------------------------------------------
+    const int g = lane >> 2, q = lane & 3;
+    const int rg_first = t0 / p.k_tiles;
+    int cur_rg = -1;
+    int acc[4][4];
+    auto flush = [&]() {
+        if (cur_rg < 0) return;
+        int* dst = sacc + (cur_rg - rg_first) * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int tok = 2 * q + (i & 1);
+            if (tok < p.M) {
+                const int v = acc[0][i] + (acc[1][i] >> 2) + (acc[2][i] >> 4) + (acc[3][i] >> 6);
+                atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
+            }
+        }
+    };
+    bool ok = true;
+    for (int c = 0; c < n_chunks && ok; ++c) {
+        const int s = c % kStages;
+        if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) {
+            if (lane == 0) atomicExch(p.error_flag, 2);
+            ok = false;
+            break;
+        }
+        const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
+        const uint8_t* stage = ring + s * kStageBytes;
+#pragma unroll
+        for (int u = 0; u < kStageTiles / kConsumerWarps; ++u) {
+            const int i = warp * (kStageTiles / kConsumerWarps) + u;
+            if (i >= tiles) break;
+            const int t = t0 + c * kStageTiles + i;
+            const int rg = t / p.k_tiles, kt = t - rg * p.k_tiles;
+            if (rg != cur_rg) {
+                flush();
+                cur_rg = rg;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[j][e] = 0;
+            }
+            const uint4 wv = *reinterpret_cast<const uint4*>(stage + i * kTileBytes + lane * 16);
+            const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t b[8];
+            if (g < p.M) {
+                const uint4* yp = reinterpret_cast<const uint4*>(ys + (size_t)g * y_stride + kt * kTileCols + 32 * q);
+                const uint4 v0 = yp[0], v1 = yp[1];
+                b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
+                b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b[e] = 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t msk = 0x03030303u << (2 * j);
+                mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
+            }
+            if (kt == 0) {   // fields hold weight + 1: take sum(y) off once per row
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int tok = 2 * q + (e & 1);
+                    if (tok < p.M) acc[0][e] -= ysum_s[tok];
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    flush();
+    consumer_sync();
+    if (!ok) return;
+
+    // ---- add this CTA's sums to the int32 output ----------------------------------------
+    const int n_rg = n_tiles > 0 ? (t0 + n_tiles - 1) / p.k_tiles - rg_first + 1 : 0;
+    for (int idx = tid; idx < n_rg * 16 * p.M; idx += kConsumerThreads) {
+        const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);      // consecutive threads -> consecutive rows
+        const int row = rg_first * 16 + rem;
+        if (row < p.N) atomicAdd(&p.acc_out[(int64_t)m * p.N + row], sacc[rem * 8 + m]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Attention for one new token per sequence: rescale q/k/v, RoPE, append to the KV cache,
+// softmax(q k^T) v over one slice of the cache per CTA (flash-decoding split).
+// grid (n_kv_heads * S, batch), 128 threads; one warp walks keys, a lane owns 4 dims.
+// ---------------------------------------------------------------------------------------
+template <int GMAX>
+__global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int D = p.D, G = p.H / p.Hkv;
+    float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
+    float* knew = q_s + G * D;                             // [D]
+    float* vnew = knew + D;                                // [D]
+    float* red_m = vnew + D;                               // [4][GMAX]
+    float* red_l = red_m + 4 * GMAX;                       // [4][GMAX]
+    float* red_o = red_l + 4 * GMAX;                       // [4][G][D]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.y, kvh = blockIdx.x / p.S, split = blockIdx.x % p.S;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    zero_duty(p.zero_buf, p.zero_count, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, tid, 128);
+
+    const int P = (int)p.pos[b];                           // keys already in the cache
+    const float a = p.a_in[b];
+    const int32_t* acc = p.acc_qkv + (int64_t)b * p.ld_acc;
+    const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
+    const float qscale = rsqrtf((float)D);
+    // vectors: G query heads, then k, then v; pairs (2i, 2i+1) rotate together
+    for (int idx = tid; idx < (G + 2) * (D / 2); idx += 128) {
+        const int vec = idx / (D / 2), i = idx - vec * (D / 2);
+        int col;
+        float ws;
+        if (vec < G) { col = (kvh * G + vec) * D; ws = p.ws_q; }
+        else if (vec == G) { col = p.H * D + kvh * D; ws = p.ws_k; }
+        else { col = (p.H + p.Hkv) * D + kvh * D; ws = p.ws_v; }
+        float x0 = lin_out(acc[col + 2 * i], a, ws), x1 = lin_out(acc[col + 2 * i + 1], a, ws);
+        if (vec <= G) {
+            const float cs = rope[2 * i], sn = rope[2 * i + 1];
+            const float r0 = bf16_round(x0 * cs - x1 * sn), r1 = bf16_round(x0 * sn + x1 * cs);
+            x0 = r0; x1 = r1;
+        }
+        if (vec < G) { q_s[vec * D + 2 * i] = x0 * qscale; q_s[vec * D + 2 * i + 1] = x1 * qscale; }
+        else {
+            float* dst = vec == G ? knew : vnew;
+            dst[2 * i] = x0; dst[2 * i + 1] = x1;
+            if (split == 0) {
+                __nv_bfloat16* c = (vec == G ? p.cache_k : p.cache_v) + (((int64_t)b * p.L + P) * p.Hkv + kvh) * D;
+                c[2 * i] = __float2bfloat16_rn(x0);
+                c[2 * i + 1] = __float2bfloat16_rn(x1);
+            }
+        }
+    }
+    __syncthreads();
+
+    const int lo = (int)((int64_t)P * split / p.S), hi = (int)((int64_t)P * (split + 1) / p.S);
+    const int d0 = 4 * lane;
+    const bool live = d0 < D;
+    float m_h[GMAX], l_h[GMAX], o_h[GMAX][4];
+#pragma unroll
+    for (int h = 0; h < GMAX; ++h) {
+        m_h[h] = -INFINITY; l_h[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o_h[h][e] = 0.f;
+    }
+    auto visit = [&](const float (&kf)[4], const float (&vf)[4]) {
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h) {
+            if (h < G) {
+                float s = 0.f;
+                if (live) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q_s + h * D + d0);
+                    s = qv.x * kf[0] + qv.y * kf[1] + qv.z * kf[2] + qv.w * kf[3];
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                const float mn = fmaxf(m_h[h], s);
+                const float corr = __expf(m_h[h] - mn), pr = __expf(s - mn);
+                l_h[h] = l_h[h] * corr + pr;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + pr * vf[e];
+                m_h[h] = mn;
+            }
+        }
+    };
+    const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
+    const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
+    const int64_t key_stride = (int64_t)p.Hkv * D;
+    constexpr int U = 4;
+    for (int j0 = lo + warp * U; j0 < hi; j0 += 4 * U) {
+        uint2 kr[U], vr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            kr[u] = make_uint2(0, 0); vr[u] = make_uint2(0, 0);
+            if (j0 + u < hi && live) {
+                kr[u] = *reinterpret_cast<const uint2*>(ck + (j0 + u) * key_stride);
+                vr[u] = *reinterpret_cast<const uint2*>(cv + (j0 + u) * key_stride);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (j0 + u >= hi) break;
+            float kf[4], vf[4];
+            const __nv_bfloat162 k01 = *reinterpret_cast<const __nv_bfloat162*>(&kr[u].x);
+            const __nv_bfloat162 k23 = *reinterpret_cast<const __nv_bfloat162*>(&kr[u].y);
+            const __nv_bfloat162 v01 = *reinterpret_cast<const __nv_bfloat162*>(&vr[u].x);
+            const __nv_bfloat162 v23 = *reinterpret_cast<const __nv_bfloat162*>(&vr[u].y);
+            kf[0] = __low2float(k01); kf[1] = __high2float(k01); kf[2] = __low2float(k23); kf[3] = __high2float(k23);
+            vf[0] = __low2float(v01); vf[1] = __high2float(v01); vf[2] = __low2float(v23); vf[3] = __high2float(v23);
+            visit(kf, vf);
+        }
+    }
+    if (split == p.S - 1 && warp == 0) {   // the new token attends to itself
+        float kf[4] = {0, 0, 0, 0}, vf[4] = {0, 0, 0, 0};
+        if (live) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { kf[e] = knew[d0 + e]; vf[e] = vnew[d0 + e]; }
+        }
+        visit(kf, vf);
+    }
+    // combine the four warps
+#pragma unroll
+    for (int h = 0; h < GMAX; ++h) {
+        if (h < G) {
+            if (lane == 0) { red_m[warp * GMAX + h] = m_h[h]; red_l[warp * GMAX + h] = l_h[h]; }
+            if (live) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) red_o[(warp * G + h) * D + d0 + e] = o_h[h][e];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += 128) {
+        const int h = idx / D, d = idx - h * D;
+        float mx = -INFINITY;
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_m[w * GMAX + h]);
+        float l = 0.f, o = 0.f;
+        for (int w = 0; w < 4; ++w) {
+            const float lw = red_l[w * GMAX + h];
+            if (lw > 0.f) {
+                const float f = __expf(red_m[w * GMAX + h] - mx);
+                l += lw * f;
+                o += red_o[(w * G + h) * D + d] * f;
+            }
+        }
+        const int64_t slot = ((int64_t)b * p.H + kvh * G + h) * p.S + split;
+        p.part_o[slot * D + d] = l > 0.f ? o / l : 0.f;
+        if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Output head: final residual + RMSNorm, then logits = x . E^T over this CTA's slice of the
+// vocabulary (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281)
+// and the slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
+// ---------------------------------------------------------------------------------------
+constexpr int kHeadThreads = 512;
+constexpr int kHeadMaxLoads = 16;   // 16-byte loads per lane per row: K <= 4096 per pass
+
+__global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const HeadParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    float* xs = reinterpret_cast<float*>(smem);                 // [M][K]
+    float* scratch = xs + (size_t)p.M * p.K;                    // [16]
+    float* best_v = scratch + 16;                               // [16 warps][8]
+    int* best_i = reinterpret_cast<int*>(best_v + 16 * 8);      // [16 warps][8]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, n_cta = gridDim.x;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    zero_duty(p.zero_buf, p.zero_count, cta, n_cta, tid, kHeadThreads);
+
+    for (int m = 0; m < p.M; ++m) {
+        float ss = 0.f;
+        for (int k = tid; k < p.K; k += kHeadThreads) {
+            const float lin = lin_out(p.acc_in[(int64_t)m * p.K + k], p.a_in[m], p.ws_in);
+            const float v = bf16_round(__bfloat162float(p.h_in[(int64_t)m * p.K + k]) + lin);
+            xs[(size_t)m * p.K + k] = v;
+            ss += v * v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int i = 0; i < kHeadThreads / 32; ++i) tot += scratch[i];
+        const float rinv = rsqrtf(tot / (float)p.K + p.eps);
+        for (int k = tid; k < p.K; k += kHeadThreads)
+            xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * rinv * __bfloat162float(p.gamma[k]));
+    }
+    __syncthreads();
+
+    const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
+    float bv[8];
+    int bi[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) { bv[m] = -INFINITY; bi[m] = 0x7fffffff; }
+    const int vec_per_row = p.K / 8;     // 16-byte pieces
+    for (int row = r0 + warp; row < r1; row += kHeadThreads / 32) {
+        const uint4* wr = reinterpret_cast<const uint4*>(p.w + (int64_t)row * p.K);
+        float dot[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) dot[m] = 0.f;
+        for (int base = 0; base < vec_per_row; base += 32 * kHeadMaxLoads) {
+            uint4 wv[kHeadMaxLoads];
+#pragma unroll
+            for (int u = 0; u < kHeadMaxLoads; ++u) {
+                const int v = base + u * 32 + lane;
+                if (v < vec_per_row) wv[u] = ldg_stream(wr + v);
+            }
+#pragma unroll
+            for (int u = 0; u < kHeadMaxLoads; ++u) {
+                const int v = base + u * 32 + lane;
+                if (v < vec_per_row) {
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
+                    float wf[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { wf[2 * e] = __low2float(h2[e]); wf[2 * e + 1] = __high2float(h2[e]); }
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        if (m < p.M) {
+                            const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8);
+                            const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8 + 4);
+                            dot[m] += wf[0] * x0.x + wf[1] * x0.y + wf[2] * x0.z + wf[3] * x0.w + wf[4] * x1.x +
+                                      wf[5] * x1.y + wf[6] * x1.z + wf[7] * x1.w;
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            if (m < p.M) {
+                float d = dot[m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                d = bf16_round(d);
+                if (lane == 0 && p.logits) p.logits[(int64_t)m * p.V + row] = d;
+                if (d > bv[m]) { bv[m] = d; bi[m] = row; }     // rows ascend: first maximum wins
+            }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < 8; ++m) { best_v[warp * 8 + m] = bv[m]; best_i[warp * 8 + m] = bi[m]; }
+    }
+    __syncthreads();
+    if (tid < p.M) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int w = 0; w < kHeadThreads / 32; ++w) {
+            const float wv = best_v[w * 8 + tid];
+            const int wi = best_i[w * 8 + tid];
+            if (wv > v || (wv == v && wi < i)) { v = wv; i = wi; }
+        }
+        p.part_val[cta * 8 + tid] = v;
+        p.part_idx[cta * 8 + tid] = i;
+    }
+}
+
+// Greedy choice over the per-CTA maxima; writes the chosen ids, feeds them back as the next
+// input and advances the positions.
+__global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int m = 0; m < p.M; ++m) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int c = threadIdx.x; c < p.n_part; c += 256) {
+            const float cv = p.part_val[c * 8 + m];
+            const int ci = p.part_idx[c * 8 + m];
+            if (cv > v || (cv == v && ci < i)) { v = cv; i = ci; }
+        }
+        sv[threadIdx.x] = v; si[threadIdx.x] = i;
+        __syncthreads();
+        for (int s = 128; s > 0; s >>= 1) {
+            if (threadIdx.x < s) {
+                const float ov = sv[threadIdx.x + s];
+                const int oi = si[threadIdx.x + s];
+                if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+                    sv[threadIdx.x] = ov; si[threadIdx.x] = oi;
+                }
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            p.out[m] = si[0];
+            p.tokens[m] = si[0];
+            p.pos[m] += 1;
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// launch helpers
+// ---------------------------------------------------------------------------------------
+template <class Params>
+cudaError_t launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Params& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+size_t linear_smem_bytes(const FusedLinearParams& p) {
+    const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
+    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 3 + (size_t)p.r_max * 128 * 4 +
+           (size_t)p.M * p.K_even * 2 + (size_t)p.M * y_stride + 128;
+}
+
+}  // namespace
+
+void plan_linear(FusedLinearParams& p, int n_sm) {
+    p.k_tiles = (p.K + kTileCols - 1) / kTileCols;
+    p.K_even = (p.K + 7) / 8 * 8;
+    const int total = ((p.N + 15) / 16) * p.k_tiles;
+    p.grid = total < n_sm ? total : n_sm;
+    p.tiles_base = total / p.grid;
+    p.tiles_rem = total % p.grid;
+    p.r_max = (p.tiles_base + 1 + p.k_tiles - 1) / p.k_tiles + 1;
+}
+
+size_t fused_linear_smem(const FusedLinearParams& p) { return linear_smem_bytes(p); }
+
+int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {
+    cudaError_t e;
+#define SET_SMEM(k, n)                                                                          \
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
+    if (e != cudaSuccess) return check_cuda(e);
+    SET_SMEM(fused_linear_kernel<kSrcEmbedding>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcResidual>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcGlu>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcAttention>, max_linear_smem)
+    SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
+    SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
+    SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
+    SET_SMEM(output_head_kernel, max_head_smem)
+#undef SET_SMEM
+    return kOk;
+}
+
+int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream) {
+    const size_t smem = linear_smem_bytes(p);
+    cudaError_t e;
+    switch (p.src) {
+        case kSrcEmbedding: e = launch_pdl(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p); break;
+        case kSrcResidual: e = launch_pdl(fused_linear_kernel<kSrcResidual>, p.grid, kLinearThreads, smem, stream, p); break;
+        case kSrcGlu: e = launch_pdl(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p); break;
+        default: e = launch_pdl(fused_linear_kernel<kSrcAttention>, p.grid, kLinearThreads, smem, stream, p); break;
+    }
+    return check_cuda(e);
+}
+
+size_t attention_smem(const AttentionParams& p) {
+    const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
+    return sizeof(float) * ((size_t)(G + 2) * p.D + 8 * gmax + 4 * (size_t)G * p.D) + 64;
+}
+
+int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream) {
+    const int G = p.H / p.Hkv;
+    const dim3 grid(p.Hkv * p.S, batch);
+    const size_t smem = attention_smem(p);
+    cudaError_t e;
+    if (G <= 4) e = launch_pdl(attention_decode_kernel<4>, grid, 128, smem, stream, p);
+    else if (G <= 8) e = launch_pdl(attention_decode_kernel<8>, grid, 128, smem, stream, p);
+    else e = launch_pdl(attention_decode_kernel<16>, grid, 128, smem, stream, p);
+    return check_cuda(e);
+}
+
+size_t head_smem(const HeadParams& p) { return sizeof(float) * ((size_t)p.M * p.K + 16 + 16 * 8 * 2) + 64; }
+
+int launch_head(const HeadParams& p, int grid, cudaStream_t stream) {
+    return check_cuda(launch_pdl(output_head_kernel, grid, kHeadThreads, head_smem(p), stream, p));
+}
+
+int launch_argmax(const ArgmaxParams& p, cudaStream_t stream) {
+    return check_cuda(launch_pdl(argmax_kernel, 1, 256, 0, stream, p));
+}
+
+}  // namespace bitnet

@@ -6,15 +6,91 @@ the prompt, then one graph replay per generated token.  The reference keeps two 
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional
 
 import torch
 
-from .model import Transformer, make_cache
+from . import _lib
+from .model import BitLinearKernel, Transformer, make_cache
+
+
+class _DecoderConfig(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("dim", "n_layers", "n_heads", "n_kv_heads", "head_dim", "ffn_dim",
+                                            "vocab_size")] + [("norm_eps", ctypes.c_float), ("batch", ctypes.c_int),
+                                                              ("max_seq_len", ctypes.c_int)]
+
+
+class _DecoderLayer(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("wqkv", "wo", "w13", "w2")] +
+                [(n, ctypes.c_float) for n in ("s_q", "s_k", "s_v", "s_o", "s_1", "s_3", "s_2")] +
+                [(n, ctypes.c_void_p) for n in ("attention_norm", "attn_sub_norm", "ffn_norm", "ffn_sub_norm",
+                                                "cache_k", "cache_v")])
+
+
+class FusedDecoder:
+    """One decode step for a batch of at most 8 through `bitnet_decoder_step`: the whole
+    step is a chain of fused kernels inside the library (see include/bitnet_b200.h)."""
+
+    MAX_BATCH = 8
+
+    def __init__(self, model: Transformer, cache, batch: int, max_seq_len: int):
+        a = model.args
+        assert a.use_kernel and 1 <= batch <= self.MAX_BATCH
+        assert model.rope is not None and model.rope.shape[0] >= max_seq_len
+        cfg = _DecoderConfig(a.dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_dim, a.ffn_dim, a.vocab_size,
+                             a.norm_eps, batch, max_seq_len)
+        layers = (_DecoderLayer * a.n_layers)()
+        self._keep = [model, cache]
+        for i, (layer, (ck, cv)) in enumerate(zip(model.layers, cache)):
+            att, ff = layer.attention, layer.feed_forward
+            for lin in (att.wqkv, att.wo, ff.w13, ff.w2):
+                assert isinstance(lin, BitLinearKernel)
+            assert ck.is_contiguous() and cv.is_contiguous() and tuple(ck.shape) == (batch, max_seq_len, a.n_kv_heads,
+                                                                                   a.head_dim)
+            sq, sk, sv = (float(x) for x in att.wqkv.scale_f32.tolist())
+            s1, s3 = (float(x) for x in ff.w13.scale_f32.tolist())
+            L = layers[i]
+            L.wqkv, L.wo, L.w13, L.w2 = (att.wqkv.weight.data_ptr(), att.wo.weight.data_ptr(),
+                                         ff.w13.weight.data_ptr(), ff.w2.weight.data_ptr())
+            L.s_q, L.s_k, L.s_v, L.s_o, L.s_1, L.s_3, L.s_2 = (sq, sk, sv, float(att.wo.scale_f32[0]), s1, s3,
+                                                                float(ff.w2.scale_f32[0]))
+            L.attention_norm = layer.attention_norm.weight.data_ptr()
+            L.attn_sub_norm = att.attn_sub_norm.weight.data_ptr()
+            L.ffn_norm = layer.ffn_norm.weight.data_ptr()
+            L.ffn_sub_norm = ff.ffn_sub_norm.weight.data_ptr()
+            L.cache_k, L.cache_v = ck.data_ptr(), cv.data_ptr()
+        self.rope = model.rope[:max_seq_len].contiguous()
+        self.handle = _lib.lib.bitnet_decoder_create(ctypes.byref(cfg), layers, model.tok_embeddings.weight.data_ptr(),
+                                                     model.norm.weight.data_ptr(), model.output.weight.data_ptr(),
+                                                     self.rope.data_ptr())
+        if not self.handle:
+            _lib.check()
+            raise _lib.BitnetError("bitnet_decoder_create failed")
+        self.kernels_per_step = _lib.lib.bitnet_decoder_kernels_per_step(self.handle)
+
+    def step(self, tokens: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, logits: Optional[torch.Tensor] = None):
+        """tokens int64 [B] (or [B,1]), pos int64 [B], out int64 [B] on the device; enqueued on the current stream."""
+        _lib.check(_lib.lib.bitnet_decoder_step(self.handle, _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(out),
+                                                _lib.ptr(logits), _lib.stream_ptr()))
+
+    def bench_linears(self, tokens: torch.Tensor):
+        """Enqueues only the fused BitLinear kernels of every layer (a measurement aid)."""
+        _lib.check(_lib.lib.bitnet_decoder_bench_linears(self.handle, _lib.ptr(tokens), _lib.stream_ptr()))
+
+    def error_flag(self) -> int:
+        return _lib.lib.bitnet_decoder_error_flag(self.handle)
+
+    def __del__(self):
+        h, self.handle = getattr(self, "handle", None), None
+        if h:
+            _lib.lib.bitnet_decoder_destroy(h)
 
 
 class Generator:
-    def __init__(self, model: Transformer, batch: int, max_seq_len: int, use_cuda_graph: bool = True):
+    def __init__(self, model: Transformer, batch: int, max_seq_len: int, use_cuda_graph: bool = True,
+                 fused: Optional[bool] = None):
+        """fused=None picks the fused kernel chain whenever it applies (kernel model, batch <= 8)."""
         self.model, self.batch, self.max_seq_len = model, batch, max_seq_len
         dev = model.tok_embeddings.weight.device
         self.device = dev
@@ -27,8 +103,21 @@ class Generator:
         self.use_cuda_graph = use_cuda_graph
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.stream = torch.cuda.Stream(device=dev)
+        can_fuse = model.args.use_kernel and batch <= FusedDecoder.MAX_BATCH
+        if fused and not can_fuse:
+            raise ValueError("the fused decode chain needs the kernel model and batch <= 8")
+        self.fused: Optional[FusedDecoder] = None
+        if can_fuse and fused is not False:
+            if model.rope is None or model.rope.shape[0] < max_seq_len:
+                from .model import rope_table
+                model.rope = rope_table(model.args.head_dim, max(max_seq_len, model.max_seq_len),
+                                        model.args.rope_theta, dev)
+            self.fused = FusedDecoder(model, self.cache, batch, max_seq_len)
 
     def _step(self):
+        if self.fused is not None:
+            self.fused.step(self.tokens, self.pos, self.out)
+            return
         logits = self.model(self.tokens, self.pos, self.cache)
         nxt = logits[:, -1].argmax(-1)
         self.out.copy_(nxt)

@@ -131,23 +131,33 @@ class BitLinearKernel(nn.Module):
 
 
 class BitLinear(nn.Linear):
-    """gpu/model.py:77-85: the bf16 fake-quantised form (dequantised ternary weight,
-    activations quantised and dequantised in place).  Library GEMM; kept as the
-    floating-point reference that the kernel path is compared with."""
+    """The BitLinear arithmetic in plain PyTorch: per-token absmax int8 quantisation
+    (gpu/model.py:78-81), an exact integer product with the ternary weight, then the rescale
+    in the order the reference's GPU kernel applies it (gpu/bitnet_kernels/bitnet_kernels.h:82:
+    divide by the activation scale, multiply by the weight scale, round to bf16).  Library
+    matmul in f32, exact because every partial sum is an integer below 2^24.  It is the
+    floating-point reference that the kernel path is compared with; `weight` holds the
+    dequantised ternary weight (as the reference's bf16 prefill model does), `ternary` and
+    `row_scale` its two factors."""
 
     def __init__(self, in_features: int, out_features: int, segments: Optional[Sequence[int]] = None):
         super().__init__(in_features, out_features, bias=False, dtype=torch.bfloat16)
         self.weight.requires_grad_(False)
+        self.register_buffer("ternary", torch.zeros(out_features, in_features, dtype=torch.float32), persistent=False)
+        self.register_buffer("row_scale", torch.ones(out_features, dtype=torch.float32), persistent=False)
 
-    def quant_input(self, x: torch.Tensor) -> torch.Tensor:
+    def quant_input(self, x: torch.Tensor):
         xf = x.float()
         s = 127.0 / xf.abs().max(dim=-1, keepdim=True).values.clamp_(min=1e-5)
-        return ((xf * s).round().clamp(-128, 127) / s)
+        return (xf * s).round().clamp(-128, 127), s
 
     def forward(self, x: torch.Tensor, norm: Optional[RMSNorm] = None) -> torch.Tensor:
         if norm is not None:
             x = norm(x)
-        return F.linear(self.quant_input(x), self.weight.float()).to(torch.bfloat16)
+        y, s = self.quant_input(x)
+        assert self.in_features * 128 < (1 << 24)
+        acc = F.linear(y, self.ternary)
+        return (acc / s * self.row_scale).to(torch.bfloat16)
 
 
 def rope_table(head_dim: int, max_len: int, theta: float, device) -> torch.Tensor:
@@ -302,6 +312,8 @@ def build_synthetic(args: ModelArgs, seed: int = 0, device="cuda", max_seq_len: 
             lin.load_ternary(parts, scales)
         else:
             lin.weight.data = torch.cat([p.to(torch.bfloat16) * s for p, s in zip(parts, scales)], dim=0)
+            lin.ternary = torch.cat(parts, dim=0).float()
+            lin.row_scale = torch.cat([s.float().expand(p.shape[0]) for p, s in zip(parts, scales)])
 
     gen.manual_seed(seed * 1000003 + 1)
     model.tok_embeddings.weight.data = torch.randn((args.vocab_size, args.dim), generator=gen, device=device,

@@ -77,6 +77,49 @@ int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, 
                        int8_t* y, int64_t ldy, float* act_scale, void* s_bf16, int32_t* ysum,
                        int M, int K, void* stream);
 
+/* ---- one decode step of the whole decoder (batch <= 8) --------------------------------
+ * Counterpart of the decode model that the reference captures in a CUDA graph
+ * (gpu/generate.py:159-213) around Transformer.forward_with_attn_bias (gpu/model.py:269-282):
+ * one call enqueues, for every layer, wqkv -> attention -> wo -> w13 -> w2 (each BitLinear
+ * fused with the rescale, residual, gate, RMSNorm and int8 quantisation in front of it),
+ * then the bf16 output projection and the greedy choice.  Kernels are chained with
+ * programmatic dependent launch; the call allocates nothing and may be captured in a
+ * CUDA graph.  All pointers in the structs are device pointers that must stay valid for
+ * the decoder's lifetime. */
+typedef struct bitnet_decoder_config {
+    int dim, n_layers, n_heads, n_kv_heads, head_dim, ffn_dim, vocab_size;
+    float norm_eps;
+    int batch;          /* sequences decoded together, 1..8 */
+    int max_seq_len;    /* length of the KV cache */
+} bitnet_decoder_config;
+
+typedef struct bitnet_decoder_layer {
+    const void *wqkv, *wo, *w13, *w2;                  /* W2T packed weights */
+    float s_q, s_k, s_v, s_o, s_1, s_3, s_2;           /* weight scales (gpu/convert_checkpoint.py:41-83) */
+    const void *attention_norm, *attn_sub_norm, *ffn_norm, *ffn_sub_norm;   /* bf16 RMSNorm weights */
+    void *cache_k, *cache_v;                           /* bf16 [batch, max_seq_len, n_kv_heads, head_dim] */
+} bitnet_decoder_layer;
+
+/* tok_embeddings bf16 [vocab, dim]; norm bf16 [dim]; output bf16 [vocab, dim]; rope f32
+ * [max_seq_len, head_dim/2, 2] (cos, sin).  Allocates the decoder's scratch buffers (the
+ * only allocation; do it outside stream capture).  Returns NULL on failure (see
+ * bitnet_last_status). */
+void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
+                            const void* tok_embeddings, const void* norm, const void* output, const float* rope);
+/* tokens int64 [batch]: ids to feed (overwritten with the chosen ids, so that the next
+ * call continues the sequence); pos int64 [batch]: tokens already in the cache (incremented);
+ * out int64 [batch]: chosen ids; logits f32 [batch, vocab] or NULL. */
+int bitnet_decoder_step(void* decoder, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream);
+/* Measurement aid: enqueues only the four fused BitLinear kernels of every layer (no
+ * attention, no output head), so that the BitLinear kernel can be timed alone on the
+ * model's real weights.  The activations it leaves behind are meaningless. */
+int bitnet_decoder_bench_linears(void* decoder, int64_t* tokens, void* stream);
+/* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
+int bitnet_decoder_error_flag(void* decoder);
+/* Number of kernels one step launches. */
+int bitnet_decoder_kernels_per_step(void* decoder);
+void bitnet_decoder_destroy(void* decoder);
+
 /* ---- weight layout conversion ----------------------------------------------------------
  * Size in bytes of a W2T buffer for an [N,K] matrix: ceil16(N) * ceil128(K) / 4. */
 size_t bitnet_w2t_bytes(int N, int K);
