@@ -116,6 +116,7 @@ int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, 
                        float* act_scale, void* s_bf16, int32_t* ysum, int M, int K, void* stream) {
     g_status = kOk;
     if (!x_bf16 || !y || M < 1 || K < 1 || ldx < K || ldy < K) return fail(kBadArgument);
+    if (ldy % 8 != 0 || (reinterpret_cast<uintptr_t>(y) & 7) != 0) return fail(kBadArgument);
     QuantArgs q;
     q.x_bf16 = static_cast<const __nv_bfloat16*>(x_bf16); q.ldx = ldx;
     q.gamma = static_cast<const __nv_bfloat16*>(gamma_bf16); q.eps = eps;

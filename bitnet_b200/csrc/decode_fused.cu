@@ -1,30 +1,35 @@
-// One decode step of the BitNet decoder (batch <= 8, one new token per sequence) as a chain
-// of seven kernel types launched with programmatic dependent launch:
+// Fused decode kernels for batches of at most 8 tokens, and the chain that makes one
+// decode step of the BitNet decoder out of them:
 //
 //   per layer:  wqkv -> attention -> wo -> w13 -> w2          then:  output head -> argmax
 //
 // A BitLinear at batch 1 moves 1.6-8.8 MB of packed weights: about a microsecond of HBM
 // time, less than a kernel boundary costs.  The chain therefore hides the boundaries
-// instead of paying them: every kernel lets its successor start at once
-// (griddepcontrol.launch_dependents as its first instruction); the successor's CTAs bring
-// their whole share of the weight matrix into shared memory with bulk asynchronous copies
-// - the weights do not depend on the predecessor - and only then wait for the predecessor
-// (griddepcontrol.wait) to read the activations.  Each BitLinear kernel fuses, in front of
-// the matmul, everything between the previous matmul and this one (rescale of the previous
-// int32 sums to bf16, residual add, squared-ReLU gate, attention split combine, RMSNorm,
-// absmax, int8 quantisation), following gpu/model.py:121-162, 192-197, 231-243, and leaves
-// exact int32 sums for its successor.
+// instead of paying them: with programmatic dependent launch every kernel lets its
+// successor start at once (griddepcontrol.launch_dependents as its first instruction); the
+// successor's CTAs bring their share of the weight matrix into shared memory with bulk
+// asynchronous copies - the weights do not depend on the predecessor - and only then wait
+// for the predecessor (griddepcontrol.wait) to read the activations.
 //
-// Work split of a BitLinear: the matrix is a flat sequence of 16x128 tiles (row-group
-// major); CTA c of G takes a contiguous range of total/G tiles, so the load is even for
-// every shape.  Ranges cut through row groups, so each CTA reduces its sums in shared
-// memory and adds them to the int32 output with red.global.add; integer addition makes the
-// result independent of order.  The output buffers are zeroed by a later kernel of the
-// chain after their last reader has finished (see `zero_buf`).
+// fused_linear_kernel = prologue + W2A8 matmul + epilogue:
+//  * prologue (every CTA, redundantly; the vector is a few KB): source vector -> RMSNorm ->
+//    bf16 -> absmax -> int8 (prologue.cuh), following gpu/model.py:68-71, 159-160, 192-197,
+//    237-243;
+//  * matmul: the matrix is a flat sequence of 16x128 tiles (row-group major); CTA c of G
+//    takes a contiguous range of total/G tiles, so the load is even for every shape.  A
+//    producer warp streams the range through a ring of 16 KB stages with cp.async.bulk; eight
+//    consumer warps unpack with masks only and multiply with mma.sync m16n8k32 (u8 x s8);
+//  * epilogue: ranges cut through row groups, so a CTA that holds only part of a row
+//    group's K range adds its int32 sums to a scratch buffer (red.global.add; integer
+//    addition is order independent) and takes a ticket from the row group's counter; the
+//    CTA that draws the last ticket rescales the finished sums to bf16 (and adds the
+//    residual), then clears scratch and counter for the next launch.  Nobody waits.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "decode_fused.h"
+#include "prologue.cuh"
 
 namespace bitnet {
 
@@ -85,64 +90,17 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\
 // bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
 __device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
 
-// Sum / max over the 256 consumer threads (two named-barrier syncs).
-__device__ __forceinline__ float consumer_reduce(float v, bool is_max, float* scratch) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float t = __shfl_xor_sync(0xffffffffu, v, o);
-        v = is_max ? fmaxf(v, t) : v + t;
-    }
-    consumer_sync();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    consumer_sync();
-    float r = scratch[0];
-#pragma unroll
-    for (int i = 1; i < kConsumerWarps; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
-    return r;
-}
 
-__device__ __forceinline__ void zero_duty(int32_t* buf, int count, int cta, int n_cta, int tid, int n_thr) {
-    if (!buf) return;
-    for (int i = cta * n_thr + tid; i < count; i += n_cta * n_thr) buf[i] = 0;
+__device__ __forceinline__ void consumer_sync_fn() { consumer_sync(); }
+
+// CTA that owns tile t under the even split (tiles_base + 1 tiles for the first tiles_rem CTAs).
+__device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
+    const int big = p.tiles_rem * (p.tiles_base + 1);
+    return t < big ? t / (p.tiles_base + 1) : p.tiles_rem + (t - big) / p.tiles_base;
 }
 
 // ---------------------------------------------------------------------------------------
-// The value of element k of token m of the vector that enters the norm, by source kind.
-// ---------------------------------------------------------------------------------------
-template <int SRC>
-__device__ __forceinline__ float source_value(const FusedLinearParams& p, int m, int k) {
-    if (SRC == kSrcEmbedding) {
-        return __bfloat162float(p.emb[p.tokens[m] * (int64_t)p.K + k]);
-    } else if (SRC == kSrcResidual) {
-        const float lin = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + k], p.a_in[m], p.ws_in[0]);
-        return bf16_round(__bfloat162float(p.h_in[(int64_t)m * p.K + k]) + lin);
-    } else if (SRC == kSrcGlu) {
-        const float a = p.a_in[m];
-        const float x1 = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + k], a, p.ws_in[0]);
-        const float x3 = lin_out(p.acc_in[(int64_t)m * p.ld_acc_in + p.K + k], a, p.ws_in[1]);
-        const float r = fmaxf(x1, 0.f);
-        return bf16_round(bf16_round(r * r) * x3);
-    } else {   // kSrcAttention: combine the KV splits of head k / D
-        const int h = k / p.D, d = k - h * p.D;
-        const float* ml = p.part_ml + ((int64_t)(m * p.H + h) * p.S) * 2;
-        const float* po = p.part_o + ((int64_t)(m * p.H + h) * p.S) * p.D + d;
-        float mx = -INFINITY;
-        for (int s = 0; s < p.S; ++s) mx = fmaxf(mx, ml[2 * s]);
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < p.S; ++s) {
-            const float l = ml[2 * s + 1];
-            if (l > 0.f) {
-                const float w = __expf(ml[2 * s] - mx) * l;
-                num += w * po[(int64_t)s * p.D];
-                den += w;
-            }
-        }
-        return bf16_round(den > 0.f ? num / den : 0.f);
-    }
-}
-
-// ---------------------------------------------------------------------------------------
-// Fused BitLinear: prologue (source -> RMSNorm -> int8) + W2A8 matmul over this CTA's tiles
+// Fused BitLinear
 // ---------------------------------------------------------------------------------------
 template <int SRC>
 __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const FusedLinearParams p) {
@@ -153,15 +111,16 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
     float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 8 floats
     int* ysum_s = reinterpret_cast<int*>(scratch + 8);                         // 8 ints
     float* a_s = reinterpret_cast<float*>(ysum_s + 8);                         // 8 floats
-    int* sacc = reinterpret_cast<int*>(a_s + 8);                               // [r_max][16][8]
-    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [M][K]
-    const int y_stride = p.k_tiles * kTileCols + 16;
-    int8_t* ys = reinterpret_cast<int8_t*>(xv + (size_t)p.M * p.K_even);        // [M][y_stride]
+    int* last_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (2 used)
+    int* sacc = last_s + 8;                                                    // [r_max][16][8]
+    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even]
+    const int k_pad = p.k_tiles * kTileCols;
+    const int y_stride = k_pad + 16;
+    int8_t* ys = reinterpret_cast<int8_t*>(xv + p.K_even);                      // [M][y_stride]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cta = blockIdx.x, n_cta = gridDim.x;
+    const int cta = blockIdx.x;
 
-    // this CTA's tile range
     const int t0 = cta * p.tiles_base + min(cta, p.tiles_rem);
     const int n_tiles = p.tiles_base + (cta < p.tiles_rem ? 1 : 0);
     const int n_chunks = (n_tiles + kStageTiles - 1) / kStageTiles;
@@ -199,52 +158,74 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
 
     pdl_wait();   // the predecessor's results are visible from here on
 
-    zero_duty(p.zero_buf, p.zero_count, cta, n_cta, tid, kConsumerThreads);
-
-    // prologue, one token at a time: v -> RMSNorm -> bf16 -> absmax -> int8
+    // prologue: the int8 activations of every token, in shared memory
     for (int m = 0; m < p.M; ++m) {
-        __nv_bfloat16* xm = xv + (size_t)m * p.K_even;
-        float ss = 0.f;
-        for (int k = tid; k < p.K; k += kConsumerThreads) {
-            const float v = source_value<SRC>(p, m, k);
-            xm[k] = __float2bfloat16_rn(v);
-            ss += v * v;
-        }
-        if ((SRC == kSrcEmbedding || SRC == kSrcResidual) && p.h_out) {
-            // the new residual stream: each CTA stores its slice
-            consumer_sync();
-            const int lo = (int)((int64_t)p.K * cta / n_cta), hi = (int)((int64_t)p.K * (cta + 1) / n_cta);
-            for (int k = lo + tid; k < hi; k += kConsumerThreads) p.h_out[(int64_t)m * p.K + k] = xm[k];
-        }
-        ss = consumer_reduce(ss, false, scratch);
-        const float rinv = rsqrtf(ss / (float)p.K + p.eps);
-        float mx = 0.f;
-        for (int k = tid; k < p.K; k += kConsumerThreads) {
-            const float xn = bf16_round(__bfloat162float(xm[k]) * rinv * __bfloat162float(p.gamma[k]));
-            xm[k] = __float2bfloat16_rn(xn);
-            mx = fmaxf(mx, fabsf(xn));
-        }
-        mx = consumer_reduce(mx, true, scratch);
-        const float a = 127.0f / fmaxf(mx, 1e-5f);
         int8_t* ym = ys + (size_t)m * y_stride;
-        float sy = 0.f;
-        for (int k = tid; k < p.k_tiles * kTileCols; k += kConsumerThreads) {
-            float f = 0.f;
-            if (k < p.K) {
-                f = rintf(__bfloat162float(xm[k]) * a);
-                f = fminf(fmaxf(f, -128.f), 127.f);
+        float a;
+        int ysum;
+        if (SRC == kSrcQuantized) {
+            const int8_t* row = p.yq + (int64_t)m * p.ldy;
+            const bool vec_ok = aligned16(p.yq, p.ldy, 1);
+            float sy = 0.f;
+            for (int v = tid; v < k_pad / 16; v += kConsumerThreads) {
+                uint4 u = make_uint4(0, 0, 0, 0);
+                const int k = v * 16;
+                if (vec_ok && k + 16 <= p.K) {
+                    u = *reinterpret_cast<const uint4*>(row + k);
+                } else {
+                    uint32_t w[4] = {0, 0, 0, 0};
+                    for (int e = 0; e < 16; ++e)
+                        if (k + e < p.K) w[e >> 2] |= (uint32_t)(uint8_t)row[k + e] << (8 * (e & 3));
+                    u = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                *reinterpret_cast<uint4*>(ym + k) = u;
+                if (!p.ysum_q)
+                    sy += (float)(__dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) +
+                                  __dp4a((int)u.z, 0x01010101, 0) + __dp4a((int)u.w, 0x01010101, 0));
             }
-            ym[k] = (int8_t)(int)f;
-            sy += f;
+            if (!p.ysum_q) sy = reduce_256(sy, false, scratch, tid, consumer_sync_fn);
+            ysum = p.ysum_q ? p.ysum_q[m] : (int)sy;
+            a = p.a_q ? p.a_q[m] : (p.a_q_bf16 ? __bfloat162float(p.a_q_bf16[m]) : 1.f);
+        } else if (SRC == kSrcEmbedding) {
+            const __nv_bfloat16* row = p.emb + p.tokens[m] * (int64_t)p.K;
+            const bool vec_ok = aligned16(p.emb, p.K, 2);
+            const int K = p.K;
+            norm_quant_token([&](int k) {
+                    const Vec8 x = load_bf16x8(row, k, K, vec_ok);
+                    if (cta == 0 && p.h_copy) {   // the residual stream starts as the embedding row
+                        for (int e = 0; e < 8; ++e)
+                            if (k + e < K) p.h_copy[(int64_t)m * K + k + e] = __float2bfloat16_rn(x.v[e]);
+                    }
+                    return x;
+                }, K, k_pad, p.gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
+        } else if (SRC == kSrcGlu) {
+            const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
+            const bool vec_ok = aligned16(p.x, p.ldx, 2) && (p.K % 8 == 0);
+            const int K = p.K;
+            norm_quant_token([&](int k) {
+                    const Vec8 x1 = load_bf16x8(row, k, K, vec_ok), x3 = load_bf16x8(row + K, k, K, vec_ok);
+                    Vec8 r;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float t = fmaxf(x1.v[e], 0.f);
+                        r.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
+                    }
+                    return r;
+                }, K, k_pad, p.gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
+        } else {
+            const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
+            const bool vec_ok = aligned16(p.x, p.ldx, 2);
+            const int K = p.K;
+            norm_quant_token([&](int k) { return load_bf16x8(row, k, K, vec_ok); }, K, k_pad, p.gamma, p.eps, xv, ym,
+                             scratch, tid, consumer_sync_fn, a, ysum);
         }
-        sy = consumer_reduce(sy, false, scratch);   // exact: |sum| < 2^24
         if (tid == 0) {
-            ysum_s[m] = (int)sy;
+            ysum_s[m] = ysum;
             a_s[m] = a;
-            if (cta == 0) p.a_out[m] = a;
+            last_s[4] = 0;
         }
+        consumer_sync();   // xv is reused by the next token
     }
-    consumer_sync();
 
     // ---- matmul over the staged tiles ----------------------------------------------------
     const int g = lane >> 2, q = lane & 3;
@@ -263,12 +244,13 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
             }
         }
     };
-    bool ok = true;
-    for (int c = 0; c < n_chunks && ok; ++c) {
+    for (int c = 0; c < n_chunks; ++c) {
         const int s = c % kStages;
-        if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) {
-            if (lane == 0) atomicExch(p.error_flag, 2);
-            ok = false;
+        if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) {   // gave up: flag it, leave together below
+            if (lane == 0) {
+                atomicExch(p.error_flag, 2);
+                last_s[4] = 1;
+            }
             break;
         }
         const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
@@ -317,21 +299,79 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
     }
     flush();
     consumer_sync();
-    if (!ok) return;
+    if (last_s[4] || n_tiles == 0) return;
 
-    // ---- add this CTA's sums to the int32 output ----------------------------------------
-    const int n_rg = n_tiles > 0 ? (t0 + n_tiles - 1) / p.k_tiles - rg_first + 1 : 0;
+    // ---- epilogue --------------------------------------------------------------------------
+    const int n_rg = (t0 + n_tiles - 1) / p.k_tiles - rg_first + 1;
+    const int rg_last = rg_first + n_rg - 1;
+    // only the first and the last row group of the range can be partial
+    const bool part_first = t0 > rg_first * p.k_tiles || (t0 + n_tiles) < (rg_first + 1) * p.k_tiles;
+    const bool part_last = n_rg > 1 && (t0 + n_tiles) < (rg_last + 1) * p.k_tiles;
+    if (part_first || part_last) {
+        const int n_val = 16 * p.M;
+        for (int idx = tid; idx < 2 * n_val; idx += kConsumerThreads) {
+            const int which = idx / n_val, rem = idx - which * n_val;
+            if ((which == 0 && !part_first) || (which == 1 && !part_last)) continue;
+            const int li = which == 0 ? 0 : n_rg - 1;
+            const int r = rem % 16, m = rem / 16;
+            atomicAdd(&p.acc_scratch[(int64_t)(rg_first + li) * 128 + r * 8 + m], sacc[li * 128 + r * 8 + m]);
+        }
+        __threadfence();
+        consumer_sync();
+        if (tid < 2) {
+            const bool mine = tid == 0 ? part_first : part_last;
+            int last = 0;
+            if (mine) {
+                const int rg = tid == 0 ? rg_first : rg_last;
+                const int lo_t = rg * p.k_tiles, hi_t = min(lo_t + p.k_tiles, p.total_tiles) - 1;
+                const int expected = cta_of_tile(p, hi_t) - cta_of_tile(p, lo_t) + 1;
+                const int ticket = atomicAdd(&p.counters[rg], 1);
+                if (ticket == expected - 1) {
+                    last = 1;
+                    p.counters[rg] = 0;   // every contributor has arrived: ready for the next launch
+                }
+            }
+            last_s[tid] = last;
+        }
+        consumer_sync();
+        if (last_s[0] || last_s[1]) __threadfence();
+    } else if (tid < 2) {
+        last_s[tid] = 0;
+    }
+    if (!(part_first || part_last)) consumer_sync();
+
     for (int idx = tid; idx < n_rg * 16 * p.M; idx += kConsumerThreads) {
         const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);      // consecutive threads -> consecutive rows
-        const int row = rg_first * 16 + rem;
-        if (row < p.N) atomicAdd(&p.acc_out[(int64_t)m * p.N + row], sacc[rem * 8 + m]);
+        const int li = rem >> 4, r = rem & 15;
+        const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
+        int v;
+        if (!partial) {
+            v = sacc[rem * 8 + m];
+        } else {
+            if (!last_s[li == 0 ? 0 : 1]) continue;
+            int32_t* src = &p.acc_scratch[(int64_t)(rg_first + li) * 128 + r * 8 + m];
+            v = __ldcg(src);
+            *src = 0;
+        }
+        const int row = (rg_first + li) * 16 + r;
+        if (row >= p.N) continue;
+        if (p.acc_out) p.acc_out[(int64_t)m * p.N + row] = v;
+        if (p.out) {
+            const int sg = segment_of(p.seg, row);
+            const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg]
+                                          : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : p.ws[sg]);
+            const float lin = lin_out(v, a_s[m], ws);
+            __nv_bfloat16* o = p.out + (int64_t)m * p.ldo + row;
+            *o = __float2bfloat16_rn(p.out_kind == kOutResidual ? __bfloat162float(*o) + lin : lin);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------------------
-// Attention for one new token per sequence: rescale q/k/v, RoPE, append to the KV cache,
-// softmax(q k^T) v over one slice of the cache per CTA (flash-decoding split).
-// grid (n_kv_heads * S, batch), 128 threads; one warp walks keys, a lane owns 4 dims.
+// Attention for one new token per sequence: RoPE on q and k, append k, v to the cache,
+// softmax(q k^T) v over one slice of the cache per CTA (flash-decoding split); the CTA that
+// finishes a (sequence, kv head) last combines the slices.  grid (n_kv_heads * S, batch),
+// 128 threads; a warp walks keys, a lane owns 4 dims.
 // ---------------------------------------------------------------------------------------
 template <int GMAX>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionParams p) {
@@ -343,31 +383,30 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     float* red_m = vnew + D;                               // [4][GMAX]
     float* red_l = red_m + 4 * GMAX;                       // [4][GMAX]
     float* red_o = red_l + 4 * GMAX;                       // [4][G][D]
+    __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.y, kvh = blockIdx.x / p.S, split = blockIdx.x % p.S;
 
     pdl_launch_dependents();
     pdl_wait();
-    zero_duty(p.zero_buf, p.zero_count, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, tid, 128);
 
     const int P = (int)p.pos[b];                           // keys already in the cache
-    const float a = p.a_in[b];
-    const int32_t* acc = p.acc_qkv + (int64_t)b * p.ld_acc;
+    const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
     // vectors: G query heads, then k, then v; pairs (2i, 2i+1) rotate together
     for (int idx = tid; idx < (G + 2) * (D / 2); idx += 128) {
         const int vec = idx / (D / 2), i = idx - vec * (D / 2);
         int col;
-        float ws;
-        if (vec < G) { col = (kvh * G + vec) * D; ws = p.ws_q; }
-        else if (vec == G) { col = p.H * D + kvh * D; ws = p.ws_k; }
-        else { col = (p.H + p.Hkv) * D + kvh * D; ws = p.ws_v; }
-        float x0 = lin_out(acc[col + 2 * i], a, ws), x1 = lin_out(acc[col + 2 * i + 1], a, ws);
+        if (vec < G) col = (kvh * G + vec) * D;
+        else if (vec == G) col = p.H * D + kvh * D;
+        else col = (p.H + p.Hkv) * D + kvh * D;
+        float x0 = __bfloat162float(x[col + 2 * i]), x1 = __bfloat162float(x[col + 2 * i + 1]);
         if (vec <= G) {
             const float cs = rope[2 * i], sn = rope[2 * i + 1];
-            const float r0 = bf16_round(x0 * cs - x1 * sn), r1 = bf16_round(x0 * sn + x1 * cs);
+            const float r0 = bf16_round(__fmul_rn(x0, cs) - __fmul_rn(x1, sn));
+            const float r1 = bf16_round(__fmul_rn(x0, sn) + __fmul_rn(x1, cs));
             x0 = r0; x1 = r1;
         }
         if (vec < G) { q_s[vec * D + 2 * i] = x0 * qscale; q_s[vec * D + 2 * i + 1] = x1 * qscale; }
@@ -477,15 +516,43 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         p.part_o[slot * D + d] = l > 0.f ? o / l : 0.f;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
+    // the last slice of this (sequence, kv head) to finish combines all of them
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* ctr = &p.counters[b * p.Hkv + kvh];
+        const int ticket = atomicAdd(ctr, 1);
+        is_last = ticket == p.S - 1;
+        if (is_last) *ctr = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * D; idx += 128) {
+        const int h = idx / D, d = idx - h * D;
+        const int64_t slot0 = ((int64_t)b * p.H + kvh * G + h) * p.S;
+        float mx = -INFINITY;
+        for (int s = 0; s < p.S; ++s) mx = fmaxf(mx, __ldcg(&p.part_ml[(slot0 + s) * 2]));
+        float num = 0.f, den = 0.f;
+        for (int s = 0; s < p.S; ++s) {
+            const float l = __ldcg(&p.part_ml[(slot0 + s) * 2 + 1]);
+            if (l > 0.f) {
+                const float w = __expf(__ldcg(&p.part_ml[(slot0 + s) * 2]) - mx) * l;
+                num += w * __ldcg(&p.part_o[(slot0 + s) * D + d]);
+                den += w;
+            }
+        }
+        p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
-// Output head: final residual + RMSNorm, then logits = x . E^T over this CTA's slice of the
-// vocabulary (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281)
-// and the slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
+// Output head: final RMSNorm, then logits = x . E^T over this CTA's slice of the vocabulary
+// (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281) and the
+// slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
 // ---------------------------------------------------------------------------------------
 constexpr int kHeadThreads = 512;
-constexpr int kHeadMaxLoads = 16;   // 16-byte loads per lane per row: K <= 4096 per pass
+constexpr int kHeadMaxLoads = 10;   // 16-byte loads per lane per pass over a row
 
 __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const HeadParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -498,13 +565,11 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const Head
 
     pdl_launch_dependents();
     pdl_wait();
-    zero_duty(p.zero_buf, p.zero_count, cta, n_cta, tid, kHeadThreads);
 
     for (int m = 0; m < p.M; ++m) {
         float ss = 0.f;
         for (int k = tid; k < p.K; k += kHeadThreads) {
-            const float lin = lin_out(p.acc_in[(int64_t)m * p.K + k], p.a_in[m], p.ws_in);
-            const float v = bf16_round(__bfloat162float(p.h_in[(int64_t)m * p.K + k]) + lin);
+            const float v = __bfloat162float(p.h[(int64_t)m * p.K + k]);
             xs[(size_t)m * p.K + k] = v;
             ss += v * v;
         }
@@ -543,17 +608,14 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const Head
             for (int u = 0; u < kHeadMaxLoads; ++u) {
                 const int v = base + u * 32 + lane;
                 if (v < vec_per_row) {
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u]);
-                    float wf[8];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) { wf[2 * e] = __low2float(h2[e]); wf[2 * e + 1] = __high2float(h2[e]); }
+                    const Vec8 wf = unpack_bf16x8(wv[u]);
 #pragma unroll
                     for (int m = 0; m < 8; ++m) {
                         if (m < p.M) {
                             const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8);
                             const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8 + 4);
-                            dot[m] += wf[0] * x0.x + wf[1] * x0.y + wf[2] * x0.z + wf[3] * x0.w + wf[4] * x1.x +
-                                      wf[5] * x1.y + wf[6] * x1.z + wf[7] * x1.w;
+                            dot[m] += wf.v[0] * x0.x + wf.v[1] * x0.y + wf.v[2] * x0.z + wf.v[3] * x0.w +
+                                      wf.v[4] * x1.x + wf.v[5] * x1.y + wf.v[6] * x1.z + wf.v[7] * x1.w;
                         }
                     }
                 }
@@ -629,7 +691,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
 // launch helpers
 // ---------------------------------------------------------------------------------------
 template <class Params>
-cudaError_t launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Params& p) {
+cudaError_t launch_k(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Params& p,
+                     bool pdl) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -639,14 +702,10 @@ cudaError_t launch_pdl(void (*kernel)(Params), dim3 grid, dim3 block, size_t sme
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    // BITNET_NO_PDL=1 launches everything with ordinary stream ordering (for measurements)
+    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
+    cfg.numAttrs = (pdl && !no_pdl) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, p);
-}
-
-size_t linear_smem_bytes(const FusedLinearParams& p) {
-    const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
-    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 3 + (size_t)p.r_max * 128 * 4 +
-           (size_t)p.M * p.K_even * 2 + (size_t)p.M * y_stride + 128;
 }
 
 }  // namespace
@@ -654,24 +713,30 @@ size_t linear_smem_bytes(const FusedLinearParams& p) {
 void plan_linear(FusedLinearParams& p, int n_sm) {
     p.k_tiles = (p.K + kTileCols - 1) / kTileCols;
     p.K_even = (p.K + 7) / 8 * 8;
-    const int total = ((p.N + 15) / 16) * p.k_tiles;
-    p.grid = total < n_sm ? total : n_sm;
-    p.tiles_base = total / p.grid;
-    p.tiles_rem = total % p.grid;
+    p.total_tiles = ((p.N + 15) / 16) * p.k_tiles;
+    p.grid = p.total_tiles < n_sm ? p.total_tiles : n_sm;
+    p.tiles_base = p.total_tiles / p.grid;
+    p.tiles_rem = p.total_tiles % p.grid;
     p.r_max = (p.tiles_base + 1 + p.k_tiles - 1) / p.k_tiles + 1;
 }
 
-size_t fused_linear_smem(const FusedLinearParams& p) { return linear_smem_bytes(p); }
+size_t fused_linear_smem(const FusedLinearParams& p) {
+    const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
+    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 4 + (size_t)p.r_max * 128 * 4 +
+           (size_t)p.K_even * 2 + (size_t)p.M * y_stride + 128;
+}
 
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {
     cudaError_t e;
-#define SET_SMEM(k, n)                                                                          \
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
-    if (e != cudaSuccess) return check_cuda(e);
+#define SET_SMEM(k, n)                                                                              \
+    if ((n) > 0) {                                                                                  \
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
+        if (e != cudaSuccess) return check_cuda(e);                                                 \
+    }
+    SET_SMEM(fused_linear_kernel<kSrcVector>, max_linear_smem)
     SET_SMEM(fused_linear_kernel<kSrcEmbedding>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcResidual>, max_linear_smem)
     SET_SMEM(fused_linear_kernel<kSrcGlu>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcAttention>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcQuantized>, max_linear_smem)
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
@@ -680,14 +745,14 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     return kOk;
 }
 
-int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream) {
-    const size_t smem = linear_smem_bytes(p);
+int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pdl) {
+    const size_t smem = fused_linear_smem(p);
     cudaError_t e;
     switch (p.src) {
-        case kSrcEmbedding: e = launch_pdl(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p); break;
-        case kSrcResidual: e = launch_pdl(fused_linear_kernel<kSrcResidual>, p.grid, kLinearThreads, smem, stream, p); break;
-        case kSrcGlu: e = launch_pdl(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p); break;
-        default: e = launch_pdl(fused_linear_kernel<kSrcAttention>, p.grid, kLinearThreads, smem, stream, p); break;
+        case kSrcEmbedding: e = launch_k(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        case kSrcGlu: e = launch_k(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        case kSrcQuantized: e = launch_k(fused_linear_kernel<kSrcQuantized>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        default: e = launch_k(fused_linear_kernel<kSrcVector>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
     }
     return check_cuda(e);
 }
@@ -697,25 +762,25 @@ size_t attention_smem(const AttentionParams& p) {
     return sizeof(float) * ((size_t)(G + 2) * p.D + 8 * gmax + 4 * (size_t)G * p.D) + 64;
 }
 
-int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream) {
+int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl) {
     const int G = p.H / p.Hkv;
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (G <= 4) e = launch_pdl(attention_decode_kernel<4>, grid, 128, smem, stream, p);
-    else if (G <= 8) e = launch_pdl(attention_decode_kernel<8>, grid, 128, smem, stream, p);
-    else e = launch_pdl(attention_decode_kernel<16>, grid, 128, smem, stream, p);
+    if (G <= 4) e = launch_k(attention_decode_kernel<4>, grid, 128, smem, stream, p, pdl);
+    else if (G <= 8) e = launch_k(attention_decode_kernel<8>, grid, 128, smem, stream, p, pdl);
+    else e = launch_k(attention_decode_kernel<16>, grid, 128, smem, stream, p, pdl);
     return check_cuda(e);
 }
 
 size_t head_smem(const HeadParams& p) { return sizeof(float) * ((size_t)p.M * p.K + 16 + 16 * 8 * 2) + 64; }
 
-int launch_head(const HeadParams& p, int grid, cudaStream_t stream) {
-    return check_cuda(launch_pdl(output_head_kernel, grid, kHeadThreads, head_smem(p), stream, p));
+int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl) {
+    return check_cuda(launch_k(output_head_kernel, grid, kHeadThreads, head_smem(p), stream, p, pdl));
 }
 
-int launch_argmax(const ArgmaxParams& p, cudaStream_t stream) {
-    return check_cuda(launch_pdl(argmax_kernel, 1, 256, 0, stream, p));
+int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl) {
+    return check_cuda(launch_k(argmax_kernel, 1, 256, 0, stream, p, pdl));
 }
 
 }  // namespace bitnet

@@ -1,14 +1,84 @@
-// The decode-step object behind bitnet_decoder_create / _step / _destroy: owns the scratch
-// buffers of the fused kernel chain (decode_fused.cu) and enqueues one step - five kernels
-// per layer, then the output head and the greedy choice - on the caller's stream.
+// Host side of the fused decode kernels: the per-device workspace behind the stand-alone
+// entry points, and the decode-step object behind bitnet_decoder_create / _step / _destroy,
+// which owns its scratch and enqueues one step - five kernels per layer, then the output
+// head and the greedy choice - on the caller's stream.
+#include <mutex>
 #include <new>
 #include <vector>
 
 #include "../../include/bitnet_b200.h"
 #include "common.cuh"
 #include "decode_fused.h"
+#include "kernels.h"
 
 namespace bitnet {
+
+// ---------------------------------------------------------------------------------------
+// Per-device workspace of the stand-alone fused kernels.  Allocated on first use on a
+// device (bitnet_init does it explicitly); the first use must therefore happen outside
+// stream capture.  Calls that share it must be ordered on one stream.
+// ---------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+constexpr int kWsRowGroups = 1 << 15;             // BitLinear outputs up to 524288 rows
+
+struct Workspace {
+    bool ready = false;
+    int n_sm = 0;
+    size_t smem_optin = 0;
+    int32_t* acc_scratch = nullptr;               // [kWsRowGroups][16][8]
+    int* counters = nullptr;                      // [kWsRowGroups]
+    int* error_flag = nullptr;
+    float* attn_part = nullptr;                   // attention split partials, grown on demand
+    size_t attn_part_bytes = 0;
+    int* attn_counters = nullptr;                 // [4096]
+};
+
+static Workspace g_ws[kMaxDevices];
+static std::mutex g_ws_mutex;
+
+Workspace* workspace() {
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev))) return nullptr;
+    if (dev < 0 || dev >= kMaxDevices) return set_status(kUnsupported), nullptr;
+    Workspace& w = g_ws[dev];
+    if (w.ready) return &w;
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if (w.ready) return &w;
+    cudaDeviceProp prop;
+    if (check_cuda(cudaGetDeviceProperties(&prop, dev))) return nullptr;
+    w.n_sm = prop.multiProcessorCount;
+    w.smem_optin = prop.sharedMemPerBlockOptin;
+    const size_t acc_bytes = (size_t)kWsRowGroups * 128 * 4, ctr_bytes = (size_t)kWsRowGroups * 4;
+    uint8_t* base = nullptr;
+    const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256;
+    if (check_cuda(cudaMalloc(&base, total)) || check_cuda(cudaMemset(base, 0, total))) return nullptr;
+    w.acc_scratch = reinterpret_cast<int32_t*>(base);
+    w.counters = reinterpret_cast<int*>(base + acc_bytes);
+    w.attn_counters = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes);
+    w.error_flag = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes + 4096 * 4);
+    if (prepare_fused_kernels(w.smem_optin, 96 * 1024, w.smem_optin)) return nullptr;
+    w.ready = true;
+    return &w;
+}
+
+// BitLinear on caller-quantised activations through the fused kernel (M <= 8).
+int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream) {
+    Workspace* w = workspace();
+    if (!w) return bitnet_last_status();
+    if ((a.N + 15) / 16 > kWsRowGroups) return set_status(kTooLarge), kTooLarge;
+    FusedLinearParams p{};
+    p.w2t = static_cast<const uint8_t*>(a.w2t);
+    p.N = a.N; p.K = a.K; p.M = a.M;
+    p.src = kSrcQuantized; p.out_kind = kOutBf16;
+    plan_linear(p, w->n_sm);
+    p.yq = a.y; p.ldy = a.ldy; p.a_q = a.a_f32; p.a_q_bf16 = a.a_bf16; p.ysum_q = a.ysum;
+    p.out = a.out; p.ldo = a.ldo; p.acc_out = a.acc_out;
+    p.seg = a.seg;
+    if (fused_linear_smem(p) > w->smem_optin) return set_status(kTooLarge), kTooLarge;
+    p.ws_dev_f32 = a.ws_f32; p.ws_dev_bf16 = a.ws_bf16;
+    p.acc_scratch = w->acc_scratch; p.counters = w->counters; p.error_flag = w->error_flag;
+    return launch_fused_linear(p, stream, false);
+}
 
 struct Decoder {
     bitnet_decoder_config cfg{};
@@ -18,14 +88,11 @@ struct Decoder {
     const __nv_bfloat16* output = nullptr;
     const float* rope = nullptr;
     int device = 0, n_sm = 0, kv_splits = 1, head_grid = 0;
-    // scratch (one allocation)
     void* scratch = nullptr;
-    int32_t *acc_qkv = nullptr, *acc_o = nullptr, *acc_13 = nullptr, *acc_2 = nullptr;
-    float *a_qkv = nullptr, *a_o = nullptr, *a_13 = nullptr, *a_2 = nullptr;
-    __nv_bfloat16 *h_a = nullptr, *h_b = nullptr;
+    int32_t* acc_scratch = nullptr;
+    int *counters = nullptr, *attn_counters = nullptr, *error_flag = nullptr, *part_idx = nullptr;
+    __nv_bfloat16 *h = nullptr, *xqkv = nullptr, *attn_out = nullptr, *x13 = nullptr;
     float *part_o = nullptr, *part_ml = nullptr, *part_val = nullptr;
-    int* part_idx = nullptr;
-    int* error_flag = nullptr;
     FusedLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
 };
 
@@ -37,13 +104,18 @@ using namespace bitnet;
 
 extern "C" {
 
+int bitnet_init(void) {
+    set_status(kOk);
+    return workspace() ? kOk : bitnet_last_status();
+}
+
 void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
                             const void* tok_embeddings, const void* norm, const void* output, const float* rope) {
     set_status(kOk);
     if (!cfg || !layers || !tok_embeddings || !norm || !output || !rope) return set_status(kBadArgument), nullptr;
     const int B = cfg->batch, D = cfg->head_dim, H = cfg->n_heads, Hkv = cfg->n_kv_heads;
     if (B < 1 || B > 8 || cfg->n_layers < 1 || H < 1 || Hkv < 1 || H % Hkv != 0 || H / Hkv > 16 || D % 4 != 0 ||
-        D > 128 || cfg->dim % 8 != 0 || cfg->dim != H * D || cfg->max_seq_len < 2)
+        D > 128 || cfg->dim % 8 != 0 || cfg->dim != H * D || cfg->ffn_dim % 8 != 0 || cfg->max_seq_len < 2)
         return set_status(kUnsupported), nullptr;
     Decoder* d = new (std::nothrow) Decoder();
     if (!d) return set_status(kBadArgument), nullptr;
@@ -64,15 +136,15 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->head_grid = d->n_sm;
 
     const int dim = cfg->dim, F = cfg->ffn_dim, Nqkv = (H + 2 * Hkv) * D;
-    auto plan = [&](FusedLinearParams& p, int N, int K, int src) {
+    auto plan = [&](FusedLinearParams& p, int N, int K, int src, int out_kind) {
         p = FusedLinearParams{};
-        p.N = N; p.K = K; p.src = src; p.M = B; p.eps = cfg->norm_eps;
+        p.N = N; p.K = K; p.src = src; p.out_kind = out_kind; p.M = B; p.eps = cfg->norm_eps;
         plan_linear(p, d->n_sm);
     };
-    plan(d->plan_qkv, Nqkv, dim, kSrcResidual);
-    plan(d->plan_o, dim, dim, kSrcAttention);
-    plan(d->plan_13, 2 * F, dim, kSrcResidual);
-    plan(d->plan_2, dim, F, kSrcGlu);
+    plan(d->plan_qkv, Nqkv, dim, kSrcVector, kOutBf16);
+    plan(d->plan_o, dim, dim, kSrcVector, kOutResidual);
+    plan(d->plan_13, 2 * F, dim, kSrcVector, kOutBf16);
+    plan(d->plan_2, dim, F, kSrcGlu, kOutResidual);
 
     AttentionParams ap{};
     ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.S = d->kv_splits;
@@ -86,37 +158,38 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         delete d;
         return set_status(kTooLarge), nullptr;
     }
-    if (prepare_fused_kernels(lin_smem, attention_smem(ap), head_smem(hp))) {
+    if (!workspace()) {   // also sets the kernels' shared memory limits for this device
         delete d;
         return nullptr;
     }
 
     // one zero-initialised scratch allocation
+    const int max_rg = ((2 * F > Nqkv ? 2 * F : Nqkv) + 15) / 16;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return o; };
-    const size_t o_qkv = take((size_t)B * Nqkv * 4), o_o = take((size_t)B * dim * 4), o_13 = take((size_t)B * 2 * F * 4),
-                 o_2 = take((size_t)B * dim * 4), o_a = take(4 * 8 * 4), o_ha = take((size_t)B * dim * 2),
-                 o_hb = take((size_t)B * dim * 2), o_po = take((size_t)B * H * d->kv_splits * D * 4),
+    const size_t o_acc = take((size_t)max_rg * 128 * 4), o_ctr = take((size_t)max_rg * 4),
+                 o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_h = take((size_t)B * dim * 2),
+                 o_qkv = take((size_t)B * Nqkv * 2), o_att = take((size_t)B * dim * 2),
+                 o_13 = take((size_t)B * 2 * F * 2), o_po = take((size_t)B * H * d->kv_splits * D * 4),
                  o_pml = take((size_t)B * H * d->kv_splits * 2 * 4), o_pv = take((size_t)d->head_grid * 8 * 4),
-                 o_pi = take((size_t)d->head_grid * 8 * 4), o_err = take(4);
+                 o_pi = take((size_t)d->head_grid * 8 * 4);
     if (check_cuda(cudaMalloc(&d->scratch, off)) || check_cuda(cudaMemset(d->scratch, 0, off))) {
         delete d;
         return nullptr;
     }
     uint8_t* base = static_cast<uint8_t*>(d->scratch);
-    d->acc_qkv = reinterpret_cast<int32_t*>(base + o_qkv);
-    d->acc_o = reinterpret_cast<int32_t*>(base + o_o);
-    d->acc_13 = reinterpret_cast<int32_t*>(base + o_13);
-    d->acc_2 = reinterpret_cast<int32_t*>(base + o_2);
-    float* a = reinterpret_cast<float*>(base + o_a);
-    d->a_qkv = a; d->a_o = a + 8; d->a_13 = a + 16; d->a_2 = a + 24;
-    d->h_a = reinterpret_cast<__nv_bfloat16*>(base + o_ha);
-    d->h_b = reinterpret_cast<__nv_bfloat16*>(base + o_hb);
+    d->acc_scratch = reinterpret_cast<int32_t*>(base + o_acc);
+    d->counters = reinterpret_cast<int*>(base + o_ctr);
+    d->attn_counters = reinterpret_cast<int*>(base + o_actr);
+    d->error_flag = reinterpret_cast<int*>(base + o_err);
+    d->h = reinterpret_cast<__nv_bfloat16*>(base + o_h);
+    d->xqkv = reinterpret_cast<__nv_bfloat16*>(base + o_qkv);
+    d->attn_out = reinterpret_cast<__nv_bfloat16*>(base + o_att);
+    d->x13 = reinterpret_cast<__nv_bfloat16*>(base + o_13);
     d->part_o = reinterpret_cast<float*>(base + o_po);
     d->part_ml = reinterpret_cast<float*>(base + o_pml);
     d->part_val = reinterpret_cast<float*>(base + o_pv);
     d->part_idx = reinterpret_cast<int*>(base + o_pi);
-    d->error_flag = reinterpret_cast<int*>(base + o_err);
     return d;
 }
 
@@ -125,78 +198,70 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
     const bitnet_decoder_config& c = d->cfg;
     const int B = c.batch, D = c.head_dim, H = c.n_heads, Hkv = c.n_kv_heads, dim = c.dim, F = c.ffn_dim;
     const int Nqkv = (H + 2 * Hkv) * D;
+    auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
+        p.w2t = static_cast<const uint8_t*>(w);
+        p.gamma = static_cast<const __nv_bfloat16*>(gamma);
+        p.acc_scratch = d->acc_scratch; p.counters = d->counters; p.error_flag = d->error_flag;
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         const bitnet_decoder_layer& L = d->layers[l];
-        // wqkv: residual (or embedding) -> attention_norm -> wqkv
+        // wqkv: (embedding ->) h -> attention_norm -> wqkv -> xqkv
         FusedLinearParams p = d->plan_qkv;
-        p.w2t = static_cast<const uint8_t*>(L.wqkv);
-        p.gamma = static_cast<const __nv_bfloat16*>(L.attention_norm);
-        p.acc_out = d->acc_qkv; p.a_out = d->a_qkv;
-        p.zero_buf = d->acc_13; p.zero_count = B * 2 * F;
-        p.error_flag = d->error_flag;
-        p.h_out = d->h_a;
+        common(p, L.wqkv, L.attention_norm);
         if (l == 0) {
             p.src = kSrcEmbedding;
-            p.tokens = tokens; p.emb = d->emb;
+            p.tokens = tokens; p.emb = d->emb; p.h_copy = d->h;
         } else {
-            p.src = kSrcResidual;
-            p.h_in = d->h_b; p.acc_in = d->acc_2; p.ld_acc_in = dim; p.a_in = d->a_2;
-            p.ws_in[0] = d->layers[l - 1].s_2;
+            p.x = d->h; p.ldx = dim;
         }
-        if (launch_fused_linear(p, stream)) return bitnet_last_status();
+        p.out = d->xqkv; p.ldo = Nqkv;
+        p.seg.n_seg = 3; p.seg.end[0] = H * D; p.seg.end[1] = (H + Hkv) * D; p.seg.end[2] = Nqkv;
+        p.ws[0] = L.s_q; p.ws[1] = L.s_k; p.ws[2] = L.s_v;
+        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
 
-        AttentionParams ap{};
-        ap.acc_qkv = d->acc_qkv; ap.ld_acc = Nqkv; ap.a_in = d->a_qkv;
-        ap.ws_q = L.s_q; ap.ws_k = L.s_k; ap.ws_v = L.s_v;
-        ap.pos = pos; ap.rope = d->rope;
-        ap.cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
-        ap.part_o = d->part_o; ap.part_ml = d->part_ml;
-        ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.L = c.max_seq_len; ap.S = d->kv_splits;
-        ap.zero_buf = d->acc_2; ap.zero_count = B * dim;
-        if (!linears_only && launch_attention(ap, B, stream)) return bitnet_last_status();
+        if (!linears_only) {
+            AttentionParams ap{};
+            ap.xqkv = d->xqkv; ap.ld_qkv = Nqkv; ap.pos = pos; ap.rope = d->rope;
+            ap.cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
+            ap.out = d->attn_out; ap.part_o = d->part_o; ap.part_ml = d->part_ml; ap.counters = d->attn_counters;
+            ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.L = c.max_seq_len; ap.S = d->kv_splits;
+            if (launch_attention(ap, B, stream, true)) return bitnet_last_status();
+        }
 
-        // wo: attention output -> attn_sub_norm -> wo
+        // wo: attention output -> attn_sub_norm -> wo -> h += ...
         p = d->plan_o;
-        p.w2t = static_cast<const uint8_t*>(L.wo);
-        p.gamma = static_cast<const __nv_bfloat16*>(L.attn_sub_norm);
-        p.acc_out = d->acc_o; p.a_out = d->a_o;
-        p.zero_buf = d->acc_qkv; p.zero_count = B * Nqkv;
-        p.error_flag = d->error_flag;
-        p.part_o = d->part_o; p.part_ml = d->part_ml; p.S = d->kv_splits; p.H = H; p.D = D;
-        if (launch_fused_linear(p, stream)) return bitnet_last_status();
+        common(p, L.wo, L.attn_sub_norm);
+        p.x = d->attn_out; p.ldx = dim;
+        p.out = d->h; p.ldo = dim;
+        p.seg.n_seg = 1; p.seg.end[0] = dim; p.ws[0] = L.s_o;
+        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
 
-        // w13: residual -> ffn_norm -> w13
+        // w13: h -> ffn_norm -> w13 -> x13
         p = d->plan_13;
-        p.w2t = static_cast<const uint8_t*>(L.w13);
-        p.gamma = static_cast<const __nv_bfloat16*>(L.ffn_norm);
-        p.acc_out = d->acc_13; p.a_out = d->a_13;
-        p.error_flag = d->error_flag;
-        p.h_in = d->h_a; p.h_out = d->h_b; p.acc_in = d->acc_o; p.ld_acc_in = dim; p.a_in = d->a_o;
-        p.ws_in[0] = L.s_o;
-        if (launch_fused_linear(p, stream)) return bitnet_last_status();
+        common(p, L.w13, L.ffn_norm);
+        p.x = d->h; p.ldx = dim;
+        p.out = d->x13; p.ldo = 2 * F;
+        p.seg.n_seg = 2; p.seg.end[0] = F; p.seg.end[1] = 2 * F; p.ws[0] = L.s_1; p.ws[1] = L.s_3;
+        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
 
-        // w2: relu(x1)^2 * x3 -> ffn_sub_norm -> w2
+        // w2: relu(x1)^2 * x3 -> ffn_sub_norm -> w2 -> h += ...
         p = d->plan_2;
-        p.w2t = static_cast<const uint8_t*>(L.w2);
-        p.gamma = static_cast<const __nv_bfloat16*>(L.ffn_sub_norm);
-        p.acc_out = d->acc_2; p.a_out = d->a_2;
-        p.zero_buf = d->acc_o; p.zero_count = B * dim;
-        p.error_flag = d->error_flag;
-        p.acc_in = d->acc_13; p.ld_acc_in = 2 * F; p.a_in = d->a_13;
-        p.ws_in[0] = L.s_1; p.ws_in[1] = L.s_3;
-        if (launch_fused_linear(p, stream)) return bitnet_last_status();
+        common(p, L.w2, L.ffn_sub_norm);
+        p.x = d->x13; p.ldx = 2 * F;
+        p.out = d->h; p.ldo = dim;
+        p.seg.n_seg = 1; p.seg.end[0] = dim; p.ws[0] = L.s_2;
+        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
     }
     if (linears_only) return kOk;
     HeadParams hp{};
     hp.w = d->output; hp.gamma = d->final_norm; hp.eps = c.norm_eps;
-    hp.h_in = d->h_b; hp.acc_in = d->acc_2; hp.a_in = d->a_2; hp.ws_in = d->layers[c.n_layers - 1].s_2;
-    hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
+    hp.h = d->h; hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
     hp.M = B; hp.K = dim; hp.V = c.vocab_size;
-    if (launch_head(hp, d->head_grid, stream)) return bitnet_last_status();
+    if (launch_head(hp, d->head_grid, stream, true)) return bitnet_last_status();
     ArgmaxParams am{};
     am.part_val = d->part_val; am.part_idx = d->part_idx; am.n_part = d->head_grid; am.M = B;
     am.out = out; am.tokens = tokens; am.pos = pos;
-    return launch_argmax(am, stream);
+    return launch_argmax(am, stream, true);
 }
 
 int bitnet_decoder_step(void* dec, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream) {
@@ -231,6 +296,40 @@ void bitnet_decoder_destroy(void* dec) {
     if (!d) return;
     if (d->scratch) cudaFree(d->scratch);
     delete d;
+}
+
+int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos, const float* rope, void* cache_k,
+                            void* cache_v, void* out, int batch, int n_heads, int n_kv_heads, int head_dim,
+                            int max_seq_len, void* stream) {
+    set_status(kOk);
+    if (!xqkv || !pos || !rope || !cache_k || !cache_v || !out || batch < 1) return set_status(kBadArgument), kBadArgument;
+    if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || n_heads / n_kv_heads > 16 || head_dim % 4 != 0 ||
+        head_dim > 128 || batch * n_kv_heads > 4096)
+        return set_status(kUnsupported), kUnsupported;
+    Workspace* w = workspace();
+    if (!w) return bitnet_last_status();
+    int s = w->n_sm / (n_kv_heads * batch);
+    s = s < 1 ? 1 : (s > 16 ? 16 : s);
+    const size_t need = (size_t)batch * n_heads * s * (head_dim + 2) * sizeof(float);
+    if (need > w->attn_part_bytes) {      // grows outside stream capture only (cudaMalloc)
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        if (need > w->attn_part_bytes) {
+            float* nb = nullptr;
+            if (check_cuda(cudaMalloc(&nb, need))) return bitnet_last_status();
+            w->attn_part = nb;            // the old buffer may still be in use by enqueued work: it is kept
+            w->attn_part_bytes = need;
+        }
+    }
+    AttentionParams ap{};
+    ap.xqkv = static_cast<const __nv_bfloat16*>(xqkv); ap.ld_qkv = ld_qkv; ap.pos = pos; ap.rope = rope;
+    ap.cache_k = static_cast<__nv_bfloat16*>(cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(cache_v);
+    ap.out = static_cast<__nv_bfloat16*>(out);
+    ap.part_o = w->attn_part;
+    ap.part_ml = w->attn_part + (size_t)batch * n_heads * s * head_dim;
+    ap.counters = w->attn_counters;
+    ap.H = n_heads; ap.Hkv = n_kv_heads; ap.D = head_dim; ap.L = max_seq_len; ap.S = s;
+    if (attention_smem(ap) > 96 * 1024) return set_status(kTooLarge), kTooLarge;
+    return launch_attention(ap, batch, static_cast<cudaStream_t>(stream), false);
 }
 
 }  // extern "C"

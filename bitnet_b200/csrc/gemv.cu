@@ -8,6 +8,8 @@
 // (mma.sync m16n8k32 u8 x s8): the four 2-bit fields of a byte are separated by masks
 // only, without shifts, by accumulating field j in its own accumulator (which then holds
 // 4^j times the true sum) and folding the four with exact arithmetic shifts at the end.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -177,6 +179,10 @@ cudaError_t launch(const GemvParams& p, cudaStream_t stream) {
 }  // namespace
 
 int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
+    // Decode-sized batches go through the fused kernel; BITNET_GEMV_DIRECT=1 keeps them on
+    // the direct-load kernel below (for comparisons).
+    static const bool direct = getenv("BITNET_GEMV_DIRECT") != nullptr;
+    if (a.M <= 8 && !direct && a.K % 8 == 0) return fused_linear_quantized(a, stream);
     GemvParams p;
     p.w = reinterpret_cast<const uint4*>(a.w2t);
     p.y = a.y; p.ldy = a.ldy; p.ysum = a.ysum;

@@ -23,6 +23,9 @@ struct LinearArgs {
 };
 
 int w2a8_gemv(const LinearArgs& a, cudaStream_t stream);
+// The same for M <= 8 through the fused decode kernel (bulk-copy weight staging, even
+// tile split); uses the per-device workspace.
+int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream);
 
 // Packers (all buffers on the device).
 int pack_ternary_to_w2t(const int8_t* q, void* w2t, int N, int K, cudaStream_t stream);
@@ -33,13 +36,12 @@ int i2s_quantize(const float* src, uint8_t* dst, int64_t n_total, uint32_t* absm
 
 // Activation prologue: optional RMSNorm, then per-token absmax int8 quantisation.
 struct QuantArgs {
-    const __nv_bfloat16* x_bf16 = nullptr;   // one of x_bf16 / x_f32
-    const float* x_f32 = nullptr;
+    const __nv_bfloat16* x_bf16 = nullptr;
     int64_t ldx = 0;
     const __nv_bfloat16* gamma = nullptr;    // RMSNorm weight [K] or null (no norm)
     float eps = 1e-5f;
     int8_t* y = nullptr;
-    int64_t ldy = 0;                         // >= K; bytes [K, ldy) are zero-filled
+    int64_t ldy = 0;                         // >= K, multiple of 8; bytes [K, ldy) are zero-filled
     float* a_f32 = nullptr;                  // optional [M]
     __nv_bfloat16* a_bf16 = nullptr;         // optional [M]
     int32_t* ysum = nullptr;                 // optional [M]

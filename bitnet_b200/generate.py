@@ -83,7 +83,7 @@ class FusedDecoder:
 
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
-        if h:
+        if h and _lib is not None and getattr(_lib, "lib", None) is not None:   # may run at interpreter exit
             _lib.lib.bitnet_decoder_destroy(h)
 
 

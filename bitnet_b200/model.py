@@ -189,12 +189,17 @@ class Attention(nn.Module):
                            segments=[n_heads * head_dim, n_kv_heads * head_dim, n_kv_heads * head_dim])
         self.wo = Linear(n_heads * head_dim, dim)
         self.attn_sub_norm = RMSNorm(dim, norm_eps)
+        self.kernel_attention = True   # False: PyTorch attention for single-token steps too
 
     def forward(self, x, norm, cache: LayerCache, pos: torch.Tensor, rope: torch.Tensor,
                 kv_len: Optional[int] = None) -> torch.Tensor:
         B, T, _ = x.shape
         H, Hkv, D = self.n_local_heads, self.n_local_kv_heads, self.head_dim
         xqkv = self.wqkv(x, norm)
+        if T == 1 and kv_len is None and isinstance(self.wqkv, BitLinearKernel) and self.kernel_attention:
+            # decode: the library's attention kernel (RoPE + cache append + split attention)
+            out = ops.attention_decode(xqkv.view(B, -1), pos, rope, cache[0], cache[1], H, Hkv, D)
+            return self.wo(out.view(B, 1, H * D), self.attn_sub_norm)
         xq = xqkv[..., : H * D].view(B, T, H, D)
         xk = xqkv[..., H * D: (H + Hkv) * D].view(B, T, Hkv, D)
         xv = xqkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)

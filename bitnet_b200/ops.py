@@ -62,3 +62,19 @@ def linear_w2a8(y: torch.Tensor, act_scale: torch.Tensor, ysum: Optional[torch.T
     if want_acc and want_out:
         return out, acc
     return acc if want_acc else out
+
+
+def attention_decode(xqkv: torch.Tensor, pos: torch.Tensor, rope: torch.Tensor, cache_k: torch.Tensor,
+                     cache_v: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """One new token per sequence: RoPE, append to the KV cache, attention over the cache.
+    xqkv bf16 [B, (H + 2 Hkv) D]; pos int64 [B]; rope f32 [L', D/2, 2]; caches bf16
+    [B, L, Hkv, D] (updated in place).  Returns bf16 [B, H D]."""
+    assert xqkv.dtype == torch.bfloat16 and xqkv.dim() == 2 and xqkv.stride(1) == 1
+    assert cache_k.is_contiguous() and cache_v.is_contiguous() and rope.is_contiguous()
+    b, length = cache_k.shape[0], cache_k.shape[1]
+    assert rope.shape[0] >= length and pos.dtype == torch.int64
+    out = torch.empty((b, n_heads * head_dim), dtype=torch.bfloat16, device=xqkv.device)
+    _lib.check(_lib.lib.bitnet_attention_decode(_lib.ptr(xqkv), xqkv.stride(0), _lib.ptr(pos), _lib.ptr(rope),
+                                                _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.ptr(out), b, n_heads,
+                                                n_kv_heads, head_dim, length, _lib.stream_ptr()))
+    return out

@@ -30,6 +30,12 @@ const char* bitnet_status_string(int status);
 /* cudaGetErrorString of the last failing CUDA call on this thread ("" if none). */
 const char* bitnet_last_cuda_error(void);
 
+/* Allocates the calling thread's current device's workspace (a few MB: the scratch of the
+ * split-K epilogue and of the attention splits).  Entry points that need it allocate it on
+ * first use, which must then happen outside stream capture; calling this first removes
+ * that constraint.  Calls that use the workspace must be ordered on one stream per device. */
+int bitnet_init(void);
+
 /* ---- the reference's GPU entry point --------------------------------------------------
  * Replaces bitlinear_int8xint2 of gpu/bitnet_kernels/bitnet_kernels.cu:3-37, which
  * gpu/model.py:21-37 and gpu/test.py:15-29 call through ctypes with exactly these
@@ -70,7 +76,8 @@ int bitnet_linear_w2a8(const int8_t* y, int64_t ldy, const void* w2t, void* out_
 /* Activation prologue: optional RMSNorm (gamma_bf16 != NULL; gpu/model.py:159-160,
  * 195-196, 237-242) followed by BitLinearKernel.quant_input (gpu/model.py:68-71):
  * a = 127 / max(absmax, 1e-5), y = clamp(round_half_even(x*a), -128, 127).
- *   x_bf16 bf16 [M, ldx]      y int8 [M, ldy] (bytes K..ldy-1 of each row are zeroed)
+ *   x_bf16 bf16 [M, ldx]      y int8 [M, ldy], 8-byte aligned, ldy % 8 == 0 (bytes K..ldy-1
+ *                             of each row are zeroed)
  *   act_scale f32 [M] or NULL, s_bf16 bf16 [M] or NULL (the reference's `s`),
  *   ysum int32 [M] or NULL. */
 int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, float eps,
@@ -114,6 +121,17 @@ int bitnet_decoder_step(void* decoder, int64_t* tokens, int64_t* pos, int64_t* o
  * attention, no output head), so that the BitLinear kernel can be timed alone on the
  * model's real weights.  The activations it leaves behind are meaningless. */
 int bitnet_decoder_bench_linears(void* decoder, int64_t* tokens, void* stream);
+/* The attention step of that chain on its own (batch sequences, one new token each), for
+ * callers that run the decoder op by op: RoPE on q and k (adjacent pairs, as the
+ * interleaved rope of gpu/model.py:144-152), append k and v to the cache at pos[b], then
+ * softmax(q k^T / sqrt(head_dim)) v over keys 0..pos[b] (gpu/model.py:154-158).
+ *   xqkv bf16 [batch, ld_qkv]: q heads, k heads, v heads of the new token
+ *   pos int64 [batch]; rope f32 [max_seq_len, head_dim/2, 2]
+ *   cache_k, cache_v bf16 [batch, max_seq_len, n_kv_heads, head_dim]; out bf16 [batch, n_heads*head_dim]
+ * Uses the workspace (see bitnet_init). */
+int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos, const float* rope, void* cache_k,
+                            void* cache_v, void* out, int batch, int n_heads, int n_kv_heads, int head_dim,
+                            int max_seq_len, void* stream);
 /* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
 int bitnet_decoder_error_flag(void* decoder);
 /* Number of kernels one step launches. */

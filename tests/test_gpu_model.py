@@ -15,24 +15,62 @@ def models():
     return args, kern, ref
 
 
-def test_kernel_model_matches_fake_quant_reference(models):
-    """Same ternary weights, same arithmetic up to bf16 rounding: logits within 1e-2
-    relative (of the logit scale) and the same greedy token."""
+def test_kernel_layers_match_torch_reference_layer_by_layer(models):
+    """Each decoder layer on the kernels against the same layer in plain PyTorch, both fed
+    the PyTorch model's layer input.  The two differ only by f32 rounding order and by the
+    int8 values that a last-bit difference pushes across a rounding boundary (a quantiser
+    amplifies such differences, so the comparison is per layer, not end to end): bf16
+    outputs within 1e-2 relative for 90 % of the tokens, 5e-2 for all."""
     from bitnet_b200.model import make_cache
 
     args, kern, ref = models
     B, T = 2, 12
     toks = torch.randint(0, args.vocab_size, (B, T), device="cuda", generator=torch.Generator("cuda").manual_seed(1))
     pos = torch.zeros(B, dtype=torch.int64, device="cuda")
-    lk = kern(toks, pos, make_cache(args, B, 128, "cuda"), kv_len=T)
-    lr = ref(toks, pos, make_cache(args, B, 128, "cuda"), kv_len=T)
-    scale = lr.abs().max()
-    err = (lk - lr).abs().amax(-1) / scale                    # per token
-    # bf16 outputs within 1e-2 relative; a rare int8 rounding flip (the fused norm uses
-    # rsqrtf) may push single tokens of a random-weight model past it, so the bound is on
-    # the 90th percentile, with the worst token bounded loosely
-    assert torch.quantile(err.flatten(), 0.9) <= 1e-2 and err.max() <= 1e-1
-    assert (lk.argmax(-1) == lr.argmax(-1)).float().mean() >= 0.95
+    cache_k, cache_r = make_cache(args, B, 128, "cuda"), make_cache(args, B, 128, "cuda")
+    h = ref.tok_embeddings(toks)
+    assert torch.equal(h, kern.tok_embeddings(toks))
+    for lk, lr, ck, cr in zip(kern.layers, ref.layers, cache_k, cache_r):
+        out_r = lr(h, cr, pos, ref.rope, T)
+        out_k = lk(h, ck, pos, kern.rope, T)
+        err = (out_k.float() - out_r.float()).abs().amax(-1) / out_r.float().abs().amax(-1)
+        assert torch.quantile(err.flatten(), 0.9) <= 1e-2 and err.max() <= 5e-2
+        h = out_r
+
+
+def test_attention_kernel_matches_pytorch_attention(models):
+    """The stand-alone decode attention (RoPE, cache append, split softmax) against
+    apply_rope + scaled_dot_product_attention, bf16 outputs within 1e-2 relative."""
+    from bitnet_b200 import ops
+    from bitnet_b200.model import apply_rope, rope_table
+
+    for B, H, Hkv, D, L, P in [(1, 20, 5, 128, 256, 200), (3, 8, 2, 64, 64, 5), (2, 32, 32, 100, 96, 37),
+                               (2, 80, 8, 128, 128, 0), (64, 8, 8, 128, 64, 33)]:
+        g = torch.Generator("cuda").manual_seed(B * 100 + H)
+        xqkv = torch.randn((B, (H + 2 * Hkv) * D), device="cuda", generator=g).bfloat16()
+        ck = torch.randn((B, L, Hkv, D), device="cuda", generator=g).bfloat16()
+        cv = torch.randn((B, L, Hkv, D), device="cuda", generator=g).bfloat16()
+        pos = torch.full((B,), P, dtype=torch.int64, device="cuda")
+        pos[0] = max(P - 3, 0)
+        rope = rope_table(D, L, 500000.0, "cuda")
+        ck2, cv2 = ck.clone(), cv.clone()
+        out = ops.attention_decode(xqkv, pos, rope, ck2, cv2, H, Hkv, D)
+        # reference
+        q = xqkv[:, : H * D].view(B, 1, H, D)
+        k = xqkv[:, H * D: (H + Hkv) * D].view(B, 1, Hkv, D)
+        v = xqkv[:, (H + Hkv) * D:].view(B, 1, Hkv, D)
+        cs = rope[pos[:, None]]
+        q, k = apply_rope(q, cs), apply_rope(k, cs)
+        bidx = torch.arange(B, device="cuda")
+        ck[bidx, pos] = k[:, 0]
+        cv[bidx, pos] = v[:, 0]
+        assert torch.equal(ck, ck2) and torch.equal(cv, cv2)               # cache append is exact
+        mask = torch.arange(L, device="cuda")[None, None, None, :] <= pos[:, None, None, None]
+        ref = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2).float(), ck.transpose(1, 2).float(), cv.transpose(1, 2).float(), attn_mask=mask,
+            enable_gqa=True).transpose(1, 2).reshape(B, H * D)
+        err = (out.float() - ref).abs().max() / ref.abs().max()
+        assert err <= 1e-2, (B, H, Hkv, D, float(err))
 
 
 def test_graph_decode_equals_eager_decode(models):
@@ -94,10 +132,13 @@ def _teacher_forced_agreement(model, args, batch, n_steps, prompt_len, max_seq, 
 
 
 def test_fused_chain_matches_op_by_op_tiny(models):
+    """The chain and the op-by-op path run the same arithmetic kernel for kernel (shared
+    prologue code, same attention kernel); only the bf16 output projection differs (own
+    kernel vs library GEMM)."""
     args, kern, _ = models
     agree, rel = _teacher_forced_agreement(kern, args, batch=2, n_steps=100, prompt_len=9, max_seq=128, seed=11)
     assert sum(agree) / len(agree) >= 0.99
-    assert sorted(rel)[int(0.9 * len(rel))] <= 1e-2
+    assert max(rel) <= 1e-2
 
 
 @pytest.mark.parametrize("batch", [1, 3])
@@ -110,7 +151,7 @@ def test_fused_chain_2b_shapes_256_greedy_steps(batch):
     model = build_synthetic(args, seed=21, device="cuda", max_seq_len=384)
     agree, rel = _teacher_forced_agreement(model, args, batch=batch, n_steps=256, prompt_len=17, max_seq=384, seed=12)
     assert sum(agree) / len(agree) >= 0.99
-    assert sorted(rel)[int(0.9 * len(rel))] <= 1e-2
+    assert max(rel) <= 1e-2
 
 
 def test_fused_chain_in_cuda_graph_equals_eager(models):
@@ -130,5 +171,5 @@ def test_fused_chain_odd_head_dim():
     args = preset("3b", n_layers=2, vocab_size=2048)
     model = build_synthetic(args, seed=22, device="cuda", max_seq_len=128)
     agree, rel = _teacher_forced_agreement(model, args, batch=2, n_steps=64, prompt_len=5, max_seq=128, seed=13)
-    assert sum(agree) / len(agree) >= 0.98
-    assert sorted(rel)[int(0.9 * len(rel))] <= 1e-2
+    assert sum(agree) / len(agree) >= 0.99
+    assert max(rel) <= 1e-2
