@@ -103,7 +103,7 @@ __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
 // Fused BitLinear
 // ---------------------------------------------------------------------------------------
 template <int SRC>
-__global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const FusedLinearParams p) {
+__global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const FusedLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -114,9 +114,10 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
     int* last_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (2 used)
     int* sacc = last_s + 8;                                                    // [r_max][16][8]
     __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even]
+    __nv_bfloat16* gs = xv + p.K_even;                                          // [K_even] RMSNorm weight
     const int k_pad = p.k_tiles * kTileCols;
     const int y_stride = k_pad + 16;
-    int8_t* ys = reinterpret_cast<int8_t*>(xv + p.K_even);                      // [M][y_stride]
+    int8_t* ys = reinterpret_cast<int8_t*>(gs + p.K_even);                      // [M][y_stride]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
@@ -155,6 +156,13 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
 
     // ---- consumers ---------------------------------------------------------------------
     for (int i = tid; i < p.r_max * 128; i += kConsumerThreads) sacc[i] = 0;
+    const __nv_bfloat16* gamma = nullptr;
+    if (SRC != kSrcQuantized && p.gamma) {   // the norm weight is a constant: stage it before the wait
+        const bool g_vec = aligned16(p.gamma, 8, 2);
+        for (int v = tid; v < p.K_even / 8; v += kConsumerThreads)
+            *reinterpret_cast<uint4*>(gs + v * 8) = pack_bf16x8(load_bf16x8(p.gamma, v * 8, p.K, g_vec));
+        gamma = gs;
+    }
 
     pdl_wait();   // the predecessor's results are visible from here on
 
@@ -197,7 +205,7 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
                             if (k + e < K) p.h_copy[(int64_t)m * K + k + e] = __float2bfloat16_rn(x.v[e]);
                     }
                     return x;
-                }, K, k_pad, p.gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
+                }, K, k_pad, gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
         } else if (SRC == kSrcGlu) {
             const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
             const bool vec_ok = aligned16(p.x, p.ldx, 2) && (p.K % 8 == 0);
@@ -211,12 +219,12 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
                         r.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
                     }
                     return r;
-                }, K, k_pad, p.gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
+                }, K, k_pad, gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
         } else {
             const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
             const bool vec_ok = aligned16(p.x, p.ldx, 2);
             const int K = p.K;
-            norm_quant_token([&](int k) { return load_bf16x8(row, k, K, vec_ok); }, K, k_pad, p.gamma, p.eps, xv, ym,
+            norm_quant_token([&](int k) { return load_bf16x8(row, k, K, vec_ok); }, K, k_pad, gamma, p.eps, xv, ym,
                              scratch, tid, consumer_sync_fn, a, ysum);
         }
         if (tid == 0) {
@@ -307,63 +315,42 @@ __global__ void __launch_bounds__(kLinearThreads, 1) fused_linear_kernel(const F
     // only the first and the last row group of the range can be partial
     const bool part_first = t0 > rg_first * p.k_tiles || (t0 + n_tiles) < (rg_first + 1) * p.k_tiles;
     const bool part_last = n_rg > 1 && (t0 + n_tiles) < (rg_last + 1) * p.k_tiles;
-    if (part_first || part_last) {
-        const int n_val = 16 * p.M;
-        for (int idx = tid; idx < 2 * n_val; idx += kConsumerThreads) {
-            const int which = idx / n_val, rem = idx - which * n_val;
-            if ((which == 0 && !part_first) || (which == 1 && !part_last)) continue;
-            const int li = which == 0 ? 0 : n_rg - 1;
-            const int r = rem % 16, m = rem / 16;
-            atomicAdd(&p.acc_scratch[(int64_t)(rg_first + li) * 128 + r * 8 + m], sacc[li * 128 + r * 8 + m]);
-        }
-        __threadfence();
-        consumer_sync();
-        if (tid < 2) {
-            const bool mine = tid == 0 ? part_first : part_last;
-            int last = 0;
-            if (mine) {
-                const int rg = tid == 0 ? rg_first : rg_last;
-                const int lo_t = rg * p.k_tiles, hi_t = min(lo_t + p.k_tiles, p.total_tiles) - 1;
-                const int expected = cta_of_tile(p, hi_t) - cta_of_tile(p, lo_t) + 1;
-                const int ticket = atomicAdd(&p.counters[rg], 1);
-                if (ticket == expected - 1) {
-                    last = 1;
-                    p.counters[rg] = 0;   // every contributor has arrived: ready for the next launch
-                }
-            }
-            last_s[tid] = last;
-        }
-        consumer_sync();
-        if (last_s[0] || last_s[1]) __threadfence();
-    } else if (tid < 2) {
-        last_s[tid] = 0;
-    }
-    if (!(part_first || part_last)) consumer_sync();
 
-    for (int idx = tid; idx < n_rg * 16 * p.M; idx += kConsumerThreads) {
-        const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);      // consecutive threads -> consecutive rows
-        const int li = rem >> 4, r = rem & 15;
-        const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
-        int v;
-        if (!partial) {
-            v = sacc[rem * 8 + m];
-        } else {
-            if (!last_s[li == 0 ? 0 : 1]) continue;
-            int32_t* src = &p.acc_scratch[(int64_t)(rg_first + li) * 128 + r * 8 + m];
-            v = __ldcg(src);
-            *src = 0;
-        }
-        const int row = (rg_first + li) * 16 + r;
-        if (row >= p.N) continue;
+    auto finalize = [&](int m, int row, int v, float h_old) {
         if (p.acc_out) p.acc_out[(int64_t)m * p.N + row] = v;
         if (p.out) {
             const int sg = segment_of(p.seg, row);
             const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg]
                                           : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : p.ws[sg]);
             const float lin = lin_out(v, a_s[m], ws);
-            __nv_bfloat16* o = p.out + (int64_t)m * p.ldo + row;
-            *o = __float2bfloat16_rn(p.out_kind == kOutResidual ? __bfloat162float(*o) + lin : lin);
+            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(p.out_kind == kOutResidual ? h_old + lin : lin);
         }
+    };
+    for (int idx = tid; idx < n_rg * 16 * p.M; idx += kConsumerThreads) {
+        const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);      // consecutive threads -> consecutive rows
+        const int li = rem >> 4, r = rem & 15;
+        const int rg = rg_first + li, row = rg * 16 + r;
+        const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
+        if (row >= p.N && !partial) continue;
+        float h_old = 0.f;
+        if (p.out && p.out_kind == kOutResidual && row < p.N) h_old = __bfloat162float(p.out[(int64_t)m * p.ldo + row]);
+        int v = sacc[rem * 8 + m];
+        if (partial) {
+            // Row group shared with other CTAs: add this CTA's sum and a ticket to the 64-bit
+            // slot in one atomic (sum in the low 40 bits, tickets above).  The contributor
+            // whose atomic completes the ticket count sees the finished sum in the returned
+            // value, finalises the element and clears the slot.  Nobody waits.
+            const int lo_t = rg * p.k_tiles, hi_t = lo_t + p.k_tiles - 1;
+            const long long expected = cta_of_tile(p, hi_t) - cta_of_tile(p, lo_t) + 1;
+            unsigned long long* slot = &p.acc_scratch[(int64_t)rg * 128 + r * 8 + m];
+            const unsigned long long add = (unsigned long long)((long long)v + (1LL << 40));
+            const long long tot = (long long)(atomicAdd(slot, add) + add);
+            const long long cnt = (tot + (1LL << 39)) >> 40;
+            if (cnt != expected) continue;
+            v = (int)(tot - (cnt << 40));
+            *slot = 0ull;
+        }
+        if (row < p.N) finalize(m, row, v, h_old);
     }
 }
 
@@ -392,6 +379,9 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     pdl_wait();
 
     const int P = (int)p.pos[b];                           // keys already in the cache
+    // Short contexts use fewer slices (at least 64 keys each); the surplus CTAs leave at once.
+    const int S = min(p.S, max(1, (P + 64) / 64));
+    if (split >= S) return;
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
@@ -422,7 +412,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     }
     __syncthreads();
 
-    const int lo = (int)((int64_t)P * split / p.S), hi = (int)((int64_t)P * (split + 1) / p.S);
+    const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
     const int d0 = 4 * lane;
     const bool live = d0 < D;
     float m_h[GMAX], l_h[GMAX], o_h[GMAX][4];
@@ -479,7 +469,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
             visit(kf, vf);
         }
     }
-    if (split == p.S - 1 && warp == 0) {   // the new token attends to itself
+    if (split == S - 1 && warp == 0) {   // the new token attends to itself
         float kf[4] = {0, 0, 0, 0}, vf[4] = {0, 0, 0, 0};
         if (live) {
 #pragma unroll
@@ -512,17 +502,23 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
                 o += red_o[(w * G + h) * D + d] * f;
             }
         }
+        const float on = l > 0.f ? o / l : 0.f;
+        if (S == 1) {                       // a single slice: this is the result
+            p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(on);
+            continue;
+        }
         const int64_t slot = ((int64_t)b * p.H + kvh * G + h) * p.S + split;
-        p.part_o[slot * D + d] = l > 0.f ? o / l : 0.f;
+        p.part_o[slot * D + d] = on;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
+    if (S == 1) return;
     // the last slice of this (sequence, kv head) to finish combines all of them
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         int* ctr = &p.counters[b * p.Hkv + kvh];
         const int ticket = atomicAdd(ctr, 1);
-        is_last = ticket == p.S - 1;
+        is_last = ticket == S - 1;
         if (is_last) *ctr = 0;
     }
     __syncthreads();
@@ -532,9 +528,9 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         const int h = idx / D, d = idx - h * D;
         const int64_t slot0 = ((int64_t)b * p.H + kvh * G + h) * p.S;
         float mx = -INFINITY;
-        for (int s = 0; s < p.S; ++s) mx = fmaxf(mx, __ldcg(&p.part_ml[(slot0 + s) * 2]));
+        for (int s = 0; s < S; ++s) mx = fmaxf(mx, __ldcg(&p.part_ml[(slot0 + s) * 2]));
         float num = 0.f, den = 0.f;
-        for (int s = 0; s < p.S; ++s) {
+        for (int s = 0; s < S; ++s) {
             const float l = __ldcg(&p.part_ml[(slot0 + s) * 2 + 1]);
             if (l > 0.f) {
                 const float w = __expf(__ldcg(&p.part_ml[(slot0 + s) * 2]) - mx) * l;
@@ -723,7 +719,7 @@ void plan_linear(FusedLinearParams& p, int n_sm) {
 size_t fused_linear_smem(const FusedLinearParams& p) {
     const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
     return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 4 + (size_t)p.r_max * 128 * 4 +
-           (size_t)p.K_even * 2 + (size_t)p.M * y_stride + 128;
+           (size_t)p.K_even * 4 + (size_t)p.M * y_stride + 128;
 }
 
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {

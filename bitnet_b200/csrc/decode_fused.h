@@ -44,8 +44,7 @@ struct FusedLinearParams {
     const float* ws_dev_f32;         //   device array of f32 scales
     const __nv_bfloat16* ws_dev_bf16;  // device array of bf16 scales
     // scratch owned by the caller of the launcher
-    int32_t* acc_scratch;            // [ceil16(N)/16][16][8] int32, zero between launches
-    int* counters;                   // [ceil16(N)/16], zero between launches
+    unsigned long long* acc_scratch; // [ceil16(N)/16][16][8] 64-bit slots (sum + tickets), zero between launches
     int* error_flag;
 };
 

@@ -25,8 +25,7 @@ struct Workspace {
     bool ready = false;
     int n_sm = 0;
     size_t smem_optin = 0;
-    int32_t* acc_scratch = nullptr;               // [kWsRowGroups][16][8]
-    int* counters = nullptr;                      // [kWsRowGroups]
+    unsigned long long* acc_scratch = nullptr;    // [kWsRowGroups][16][8]
     int* error_flag = nullptr;
     float* attn_part = nullptr;                   // attention split partials, grown on demand
     size_t attn_part_bytes = 0;
@@ -48,12 +47,11 @@ Workspace* workspace() {
     if (check_cuda(cudaGetDeviceProperties(&prop, dev))) return nullptr;
     w.n_sm = prop.multiProcessorCount;
     w.smem_optin = prop.sharedMemPerBlockOptin;
-    const size_t acc_bytes = (size_t)kWsRowGroups * 128 * 4, ctr_bytes = (size_t)kWsRowGroups * 4;
+    const size_t acc_bytes = (size_t)kWsRowGroups * 128 * 8, ctr_bytes = 0;
     uint8_t* base = nullptr;
     const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256;
     if (check_cuda(cudaMalloc(&base, total)) || check_cuda(cudaMemset(base, 0, total))) return nullptr;
-    w.acc_scratch = reinterpret_cast<int32_t*>(base);
-    w.counters = reinterpret_cast<int*>(base + acc_bytes);
+    w.acc_scratch = reinterpret_cast<unsigned long long*>(base);
     w.attn_counters = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes);
     w.error_flag = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes + 4096 * 4);
     if (prepare_fused_kernels(w.smem_optin, 96 * 1024, w.smem_optin)) return nullptr;
@@ -76,7 +74,7 @@ int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream) {
     p.seg = a.seg;
     if (fused_linear_smem(p) > w->smem_optin) return set_status(kTooLarge), kTooLarge;
     p.ws_dev_f32 = a.ws_f32; p.ws_dev_bf16 = a.ws_bf16;
-    p.acc_scratch = w->acc_scratch; p.counters = w->counters; p.error_flag = w->error_flag;
+    p.acc_scratch = w->acc_scratch; p.error_flag = w->error_flag;
     return launch_fused_linear(p, stream, false);
 }
 
@@ -89,8 +87,8 @@ struct Decoder {
     const float* rope = nullptr;
     int device = 0, n_sm = 0, kv_splits = 1, head_grid = 0;
     void* scratch = nullptr;
-    int32_t* acc_scratch = nullptr;
-    int *counters = nullptr, *attn_counters = nullptr, *error_flag = nullptr, *part_idx = nullptr;
+    unsigned long long* acc_scratch = nullptr;
+    int *attn_counters = nullptr, *error_flag = nullptr, *part_idx = nullptr;
     __nv_bfloat16 *h = nullptr, *xqkv = nullptr, *attn_out = nullptr, *x13 = nullptr;
     float *part_o = nullptr, *part_ml = nullptr, *part_val = nullptr;
     FusedLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
@@ -167,7 +165,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     const int max_rg = ((2 * F > Nqkv ? 2 * F : Nqkv) + 15) / 16;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return o; };
-    const size_t o_acc = take((size_t)max_rg * 128 * 4), o_ctr = take((size_t)max_rg * 4),
+    const size_t o_acc = take((size_t)max_rg * 128 * 8),
                  o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_h = take((size_t)B * dim * 2),
                  o_qkv = take((size_t)B * Nqkv * 2), o_att = take((size_t)B * dim * 2),
                  o_13 = take((size_t)B * 2 * F * 2), o_po = take((size_t)B * H * d->kv_splits * D * 4),
@@ -178,8 +176,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         return nullptr;
     }
     uint8_t* base = static_cast<uint8_t*>(d->scratch);
-    d->acc_scratch = reinterpret_cast<int32_t*>(base + o_acc);
-    d->counters = reinterpret_cast<int*>(base + o_ctr);
+    d->acc_scratch = reinterpret_cast<unsigned long long*>(base + o_acc);
     d->attn_counters = reinterpret_cast<int*>(base + o_actr);
     d->error_flag = reinterpret_cast<int*>(base + o_err);
     d->h = reinterpret_cast<__nv_bfloat16*>(base + o_h);
@@ -201,7 +198,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
     auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
         p.w2t = static_cast<const uint8_t*>(w);
         p.gamma = static_cast<const __nv_bfloat16*>(gamma);
-        p.acc_scratch = d->acc_scratch; p.counters = d->counters; p.error_flag = d->error_flag;
+        p.acc_scratch = d->acc_scratch; p.error_flag = d->error_flag;
     };
     for (int l = 0; l < c.n_layers; ++l) {
         const bitnet_decoder_layer& L = d->layers[l];
