@@ -34,6 +34,7 @@ SIGNATURES = {
     "bitnet_decoder_create": (_vp, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_bench_linears": (_i, [_vp, _vp, _vp]),
+    "bitnet_decoder_read_trace": (_i, [_vp, _vp, _i]),
     "bitnet_decoder_error_flag": (_i, [_vp]),
     "bitnet_decoder_kernels_per_step": (_i, [_vp]),
     "bitnet_decoder_destroy": (None, [_vp]),

@@ -50,6 +50,13 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// d = c + sum_i a.u8[i] * b.s8[i]
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // Streaming 16-byte load that does not allocate in L1 (weights are read exactly once).
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     uint4 v;

@@ -102,8 +102,8 @@ __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
 // ---------------------------------------------------------------------------------------
 // Fused BitLinear
 // ---------------------------------------------------------------------------------------
-template <int SRC>
-__global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const FusedLinearParams p) {
+template <int SRC, int MT>
+__global__ void __launch_bounds__(kLinearThreads, (MT <= 4 ? 2 : 1)) fused_linear_kernel(const FusedLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -114,13 +114,22 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     int* last_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (2 used)
     int* sacc = last_s + 8;                                                    // [r_max][16][8]
     __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even]
-    __nv_bfloat16* gs = xv + p.K_even;                                          // [K_even] RMSNorm weight
+    const int k_stage = SRC == kSrcQuantized ? 0 : p.K_even;                    // no staging rows needed
+    __nv_bfloat16* gs = xv + k_stage;                                           // [K_even] RMSNorm weight
     const int k_pad = p.k_tiles * kTileCols;
     const int y_stride = k_pad + 16;
-    int8_t* ys = reinterpret_cast<int8_t*>(gs + p.K_even);                      // [M][y_stride]
+    int8_t* ys = reinterpret_cast<int8_t*>(gs + k_stage);                       // [M][y_stride]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
+    auto stamp = [&](int i) {   // optional phase timestamps of CTA 0 (a measurement aid)
+        if (p.trace && cta == 0 && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[i] = t;
+        }
+    };
+    stamp(0);
 
     const int t0 = cta * p.tiles_base + min(cta, p.tiles_rem);
     const int n_tiles = p.tiles_base + (cta < p.tiles_rem ? 1 : 0);
@@ -164,7 +173,9 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         gamma = gs;
     }
 
+    stamp(1);
     pdl_wait();   // the predecessor's results are visible from here on
+    stamp(2);
 
     // prologue: the int8 activations of every token, in shared memory
     for (int m = 0; m < p.M; ++m) {
@@ -235,20 +246,31 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         consumer_sync();   // xv is reused by the next token
     }
 
+    stamp(3);
     // ---- matmul over the staged tiles ----------------------------------------------------
+    // Per tile a lane holds rows g and g+8 and the 32 columns [32q, 32q+32): each of its four
+    // words is split into its four 2-bit fields by AND masks alone (field j stays scaled by
+    // 4^j and has its own accumulator) and multiplied with dp4a.  Integer tensor-core MMA
+    // (mma.sync) was measured at about 120 cycles per m16n8k32 on this part and is not used.
     const int g = lane >> 2, q = lane & 3;
     const int rg_first = t0 / p.k_tiles;
     int cur_rg = -1;
-    int acc[4][4];
+    bool had_kt0 = false;
+    int acc[MT][2][4];
     auto flush = [&]() {
         if (cur_rg < 0) return;
         int* dst = sacc + (cur_rg - rg_first) * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int tok = 2 * q + (i & 1);
-            if (tok < p.M) {
-                const int v = acc[0][i] + (acc[1][i] >> 2) + (acc[2][i] >> 4) + (acc[3][i] >> 6);
-                atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int rs = 0; rs < 2; ++rs) {
+                int v = acc[m][rs][0] + (acc[m][rs][1] >> 2) + (acc[m][rs][2] >> 4) + (acc[m][rs][3] >> 6);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (q == 0 && m < p.M) {
+                    if (had_kt0) v -= ysum_s[m];   // fields hold weight + 1: take sum(y) off once per row
+                    atomicAdd(&dst[(g + 8 * rs) * 8 + m], v);
+                }
             }
         }
     };
@@ -272,33 +294,31 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             if (rg != cur_rg) {
                 flush();
                 cur_rg = rg;
+                had_kt0 = false;
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int m = 0; m < MT; ++m)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[j][e] = 0;
+                    for (int e = 0; e < 8; ++e) acc[m][e >> 2][e & 3] = 0;
             }
+            had_kt0 = had_kt0 || kt == 0;
             const uint4 wv = *reinterpret_cast<const uint4*>(stage + i * kTileBytes + lane * 16);
             const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
-            uint32_t b[8];
-            if (g < p.M) {
-                const uint4* yp = reinterpret_cast<const uint4*>(ys + (size_t)g * y_stride + kt * kTileCols + 32 * q);
-                const uint4 v0 = yp[0], v1 = yp[1];
-                b[0] = v0.x; b[1] = v0.y; b[2] = v0.z; b[3] = v0.w;
-                b[4] = v1.x; b[5] = v1.y; b[6] = v1.z; b[7] = v1.w;
-            } else {
+            uint32_t a[4][4];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) b[e] = 0;
-            }
+            for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t msk = 0x03030303u << (2 * j);
-                mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
-            }
-            if (kt == 0) {   // fields hold weight + 1: take sum(y) off once per row
+                for (int j = 0; j < 4; ++j) a[r][j] = w[r] & (0x03030303u << (2 * j));
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int tok = 2 * q + (e & 1);
-                    if (tok < p.M) acc[0][e] -= ysum_s[tok];
+            for (int m = 0; m < MT; ++m) {
+                if (m < p.M) {
+                    const uint4* yp = reinterpret_cast<const uint4*>(ys + (size_t)m * y_stride + kt * kTileCols + 32 * q);
+                    const uint4 v0 = yp[0], v1 = yp[1];
+                    const uint32_t b[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            acc[m][r & 1][j] = dp4a_u8s8(a[r][j], b[2 * j + (r >> 1)], acc[m][r & 1][j]);
                 }
             }
         }
@@ -307,6 +327,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     }
     flush();
     consumer_sync();
+    stamp(4);
     if (last_s[4] || n_tiles == 0) return;
 
     // ---- epilogue --------------------------------------------------------------------------
@@ -352,6 +373,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         }
         if (row < p.N) finalize(m, row, v, h_old);
     }
+    stamp(5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -374,9 +396,17 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.y, kvh = blockIdx.x / p.S, split = blockIdx.x % p.S;
-
+    auto stamp = [&](int i) {   // optional phase timestamps of CTA (0, 0) (a measurement aid)
+        if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[i] = t;
+        }
+    };
+    stamp(0);
     pdl_launch_dependents();
     pdl_wait();
+    stamp(1);
 
     const int P = (int)p.pos[b];                           // keys already in the cache
     // Short contexts use fewer slices (at least 64 keys each); the surplus CTAs leave at once.
@@ -411,41 +441,70 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         }
     }
     __syncthreads();
+    stamp(2);
 
     const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
     const int d0 = 4 * lane;
     const bool live = d0 < D;
-    float m_h[GMAX], l_h[GMAX], o_h[GMAX][4];
+    // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
+    float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
         m_h[h] = -INFINITY; l_h[h] = 0.f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o_h[h][e] = 0.f;
+        for (int e = 0; e < 4; ++e) {
+            o_h[h][e] = 0.f;
+            q_r[h][e] = (h < G && live) ? q_s[h * D + d0 + e] : 0.f;
+        }
     }
-    auto visit = [&](const float (&kf)[4], const float (&vf)[4]) {
+    constexpr int U = 4;   // keys per step: their scores are reduced together, then one softmax update
+    auto visit = [&](const float (&kf)[U][4], const float (&vf)[U][4], int n) {
+        float sc[GMAX][U];
+#pragma unroll
+        for (int h = 0; h < GMAX; ++h)
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                sc[h][u] = q_r[h][0] * kf[u][0] + q_r[h][1] * kf[u][1] + q_r[h][2] * kf[u][2] + q_r[h][3] * kf[u][3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h)
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (h < G) sc[h][u] += __shfl_xor_sync(0xffffffffu, sc[h][u], o);
 #pragma unroll
         for (int h = 0; h < GMAX; ++h) {
             if (h < G) {
-                float s = 0.f;
-                if (live) {
-                    const float4 qv = *reinterpret_cast<const float4*>(q_s + h * D + d0);
-                    s = qv.x * kf[0] + qv.y * kf[1] + qv.z * kf[2] + qv.w * kf[3];
+                float mn = m_h[h];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (u < n) mn = fmaxf(mn, sc[h][u]);
+                const float corr = __expf(m_h[h] - mn);
+                float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (u < n) {
+                        const float pr = __expf(sc[h][u] - mn);
+                        ps += pr;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ov[e] += pr * vf[u][e];
+                    }
                 }
+                l_h[h] = l_h[h] * corr + ps;
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                const float mn = fmaxf(m_h[h], s);
-                const float corr = __expf(m_h[h] - mn), pr = __expf(s - mn);
-                l_h[h] = l_h[h] * corr + pr;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + pr * vf[e];
+                for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
                 m_h[h] = mn;
             }
         }
     };
+    auto unpack4 = [](const uint2& r, float (&f)[4]) {
+        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        f[0] = __low2float(lo2); f[1] = __high2float(lo2); f[2] = __low2float(hi2); f[3] = __high2float(hi2);
+    };
     const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const int64_t key_stride = (int64_t)p.Hkv * D;
-    constexpr int U = 4;
     for (int j0 = lo + warp * U; j0 < hi; j0 += 4 * U) {
         uint2 kr[U], vr[U];
 #pragma unroll
@@ -456,27 +515,23 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
                 vr[u] = *reinterpret_cast<const uint2*>(cv + (j0 + u) * key_stride);
             }
         }
+        float kf[U][4], vf[U][4];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (j0 + u >= hi) break;
-            float kf[4], vf[4];
-            const __nv_bfloat162 k01 = *reinterpret_cast<const __nv_bfloat162*>(&kr[u].x);
-            const __nv_bfloat162 k23 = *reinterpret_cast<const __nv_bfloat162*>(&kr[u].y);
-            const __nv_bfloat162 v01 = *reinterpret_cast<const __nv_bfloat162*>(&vr[u].x);
-            const __nv_bfloat162 v23 = *reinterpret_cast<const __nv_bfloat162*>(&vr[u].y);
-            kf[0] = __low2float(k01); kf[1] = __high2float(k01); kf[2] = __low2float(k23); kf[3] = __high2float(k23);
-            vf[0] = __low2float(v01); vf[1] = __high2float(v01); vf[2] = __low2float(v23); vf[3] = __high2float(v23);
-            visit(kf, vf);
-        }
+        for (int u = 0; u < U; ++u) { unpack4(kr[u], kf[u]); unpack4(vr[u], vf[u]); }
+        visit(kf, vf, min(U, hi - j0));
     }
     if (split == S - 1 && warp == 0) {   // the new token attends to itself
-        float kf[4] = {0, 0, 0, 0}, vf[4] = {0, 0, 0, 0};
-        if (live) {
+        float kf[U][4], vf[U][4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { kf[e] = knew[d0 + e]; vf[e] = vnew[d0 + e]; }
-        }
-        visit(kf, vf);
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                kf[u][e] = (u == 0 && live) ? knew[d0 + e] : 0.f;
+                vf[u][e] = (u == 0 && live) ? vnew[d0 + e] : 0.f;
+            }
+        visit(kf, vf, 1);
     }
+    stamp(3);
     // combine the four warps
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
@@ -511,6 +566,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         p.part_o[slot * D + d] = on;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
+    stamp(4);
     if (S == 1) return;
     // the last slice of this (sequence, kv head) to finish combines all of them
     __threadfence();
@@ -524,22 +580,37 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // weights of the slices per head, then one pass over the partial outputs
+    float* sl_m = red_o;                  // [G][S] max, then weight
+    float* sl_l = red_o + G * p.S;        // [G][S] sum
+    const int64_t head0 = (int64_t)b * p.H + kvh * G;
+    for (int idx = tid; idx < G * S; idx += 128) {
+        const int h = idx / S, sidx = idx - h * S;
+        sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
+        sl_l[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2 + 1]);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float mx = -INFINITY, den = 0.f;
+        for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, sl_m[tid * p.S + sidx]);
+        for (int sidx = 0; sidx < S; ++sidx) {
+            const float l = sl_l[tid * p.S + sidx];
+            const float w = l > 0.f ? __expf(sl_m[tid * p.S + sidx] - mx) * l : 0.f;
+            sl_m[tid * p.S + sidx] = w;
+            den += w;
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        for (int sidx = 0; sidx < S; ++sidx) sl_m[tid * p.S + sidx] *= inv;
+    }
+    __syncthreads();
     for (int idx = tid; idx < G * D; idx += 128) {
         const int h = idx / D, d = idx - h * D;
-        const int64_t slot0 = ((int64_t)b * p.H + kvh * G + h) * p.S;
-        float mx = -INFINITY;
-        for (int s = 0; s < S; ++s) mx = fmaxf(mx, __ldcg(&p.part_ml[(slot0 + s) * 2]));
-        float num = 0.f, den = 0.f;
-        for (int s = 0; s < S; ++s) {
-            const float l = __ldcg(&p.part_ml[(slot0 + s) * 2 + 1]);
-            if (l > 0.f) {
-                const float w = __expf(__ldcg(&p.part_ml[(slot0 + s) * 2]) - mx) * l;
-                num += w * __ldcg(&p.part_o[(slot0 + s) * D + d]);
-                den += w;
-            }
-        }
-        p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        const float* po = p.part_o + (head0 + h) * p.S * D + d;
+        float num = 0.f;
+        for (int sidx = 0; sidx < S; ++sidx) num += sl_m[h * p.S + sidx] * __ldcg(po + (int64_t)sidx * D);
+        p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(num);
     }
+    stamp(5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -719,7 +790,7 @@ void plan_linear(FusedLinearParams& p, int n_sm) {
 size_t fused_linear_smem(const FusedLinearParams& p) {
     const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
     return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 4 + (size_t)p.r_max * 128 * 4 +
-           (size_t)p.K_even * 4 + (size_t)p.M * y_stride + 128;
+           (p.src == kSrcQuantized ? 0 : (size_t)p.K_even * 4) + (size_t)p.M * y_stride + 128;
 }
 
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {
@@ -729,10 +800,16 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
         if (e != cudaSuccess) return check_cuda(e);                                                 \
     }
-    SET_SMEM(fused_linear_kernel<kSrcVector>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcEmbedding>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcGlu>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcQuantized>, max_linear_smem)
+#define SET_SMEM_SRC(src)                                      \
+    SET_SMEM((fused_linear_kernel<src, 1>), max_linear_smem)   \
+    SET_SMEM((fused_linear_kernel<src, 2>), max_linear_smem)   \
+    SET_SMEM((fused_linear_kernel<src, 4>), max_linear_smem)   \
+    SET_SMEM((fused_linear_kernel<src, 8>), max_linear_smem)
+    SET_SMEM_SRC(kSrcVector)
+    SET_SMEM_SRC(kSrcEmbedding)
+    SET_SMEM_SRC(kSrcGlu)
+    SET_SMEM_SRC(kSrcQuantized)
+#undef SET_SMEM_SRC
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
@@ -741,14 +818,22 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     return kOk;
 }
 
+template <int SRC>
+static cudaError_t launch_linear_src(const FusedLinearParams& p, size_t smem, cudaStream_t stream, bool pdl) {
+    if (p.M <= 1) return launch_k(fused_linear_kernel<SRC, 1>, p.grid, kLinearThreads, smem, stream, p, pdl);
+    if (p.M <= 2) return launch_k(fused_linear_kernel<SRC, 2>, p.grid, kLinearThreads, smem, stream, p, pdl);
+    if (p.M <= 4) return launch_k(fused_linear_kernel<SRC, 4>, p.grid, kLinearThreads, smem, stream, p, pdl);
+    return launch_k(fused_linear_kernel<SRC, 8>, p.grid, kLinearThreads, smem, stream, p, pdl);
+}
+
 int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pdl) {
     const size_t smem = fused_linear_smem(p);
     cudaError_t e;
     switch (p.src) {
-        case kSrcEmbedding: e = launch_k(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        case kSrcGlu: e = launch_k(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        case kSrcQuantized: e = launch_k(fused_linear_kernel<kSrcQuantized>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        default: e = launch_k(fused_linear_kernel<kSrcVector>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        case kSrcEmbedding: e = launch_linear_src<kSrcEmbedding>(p, smem, stream, pdl); break;
+        case kSrcGlu: e = launch_linear_src<kSrcGlu>(p, smem, stream, pdl); break;
+        case kSrcQuantized: e = launch_linear_src<kSrcQuantized>(p, smem, stream, pdl); break;
+        default: e = launch_linear_src<kSrcVector>(p, smem, stream, pdl); break;
     }
     return check_cuda(e);
 }

@@ -46,6 +46,7 @@ struct FusedLinearParams {
     // scratch owned by the caller of the launcher
     unsigned long long* acc_scratch; // [ceil16(N)/16][16][8] 64-bit slots (sum + tickets), zero between launches
     int* error_flag;
+    unsigned long long* trace;       // optional: 8 phase timestamps written by CTA 0
 };
 
 struct AttentionParams {
@@ -60,6 +61,7 @@ struct AttentionParams {
     float* part_ml;                  // [B, H, S, 2]
     int* counters;                   // [B, Hkv], zero between launches
     int H, Hkv, D, L, S;
+    unsigned long long* trace;       // optional: 8 phase timestamps written by CTA (0, 0)
 };
 
 struct HeadParams {

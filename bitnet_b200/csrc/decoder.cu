@@ -2,6 +2,8 @@
 // entry points, and the decode-step object behind bitnet_decoder_create / _step / _destroy,
 // which owns its scratch and enqueues one step - five kernels per layer, then the output
 // head and the greedy choice - on the caller's stream.
+#include <stdlib.h>
+
 #include <mutex>
 #include <new>
 #include <vector>
@@ -91,6 +93,7 @@ struct Decoder {
     int *attn_counters = nullptr, *error_flag = nullptr, *part_idx = nullptr;
     __nv_bfloat16 *h = nullptr, *xqkv = nullptr, *attn_out = nullptr, *x13 = nullptr;
     float *part_o = nullptr, *part_ml = nullptr, *part_val = nullptr;
+    unsigned long long* trace = nullptr;          // [n_layers * 4][8] phase timestamps (measurement aid)
     FusedLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
 };
 
@@ -170,7 +173,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
                  o_qkv = take((size_t)B * Nqkv * 2), o_att = take((size_t)B * dim * 2),
                  o_13 = take((size_t)B * 2 * F * 2), o_po = take((size_t)B * H * d->kv_splits * D * 4),
                  o_pml = take((size_t)B * H * d->kv_splits * 2 * 4), o_pv = take((size_t)d->head_grid * 8 * 4),
-                 o_pi = take((size_t)d->head_grid * 8 * 4);
+                 o_pi = take((size_t)d->head_grid * 8 * 4), o_tr = take((size_t)cfg->n_layers * 5 * 8 * 8);
     if (check_cuda(cudaMalloc(&d->scratch, off)) || check_cuda(cudaMemset(d->scratch, 0, off))) {
         delete d;
         return nullptr;
@@ -187,6 +190,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->part_ml = reinterpret_cast<float*>(base + o_pml);
     d->part_val = reinterpret_cast<float*>(base + o_pv);
     d->part_idx = reinterpret_cast<int*>(base + o_pi);
+    if (getenv("BITNET_TRACE")) d->trace = reinterpret_cast<unsigned long long*>(base + o_tr);
     return d;
 }
 
@@ -195,7 +199,10 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
     const bitnet_decoder_config& c = d->cfg;
     const int B = c.batch, D = c.head_dim, H = c.n_heads, Hkv = c.n_kv_heads, dim = c.dim, F = c.ffn_dim;
     const int Nqkv = (H + 2 * Hkv) * D;
+    int launch_no = 0;
     auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
+        p.trace = d->trace ? d->trace + 8 * launch_no : nullptr;
+        ++launch_no;
         p.w2t = static_cast<const uint8_t*>(w);
         p.gamma = static_cast<const __nv_bfloat16*>(gamma);
         p.acc_scratch = d->acc_scratch; p.error_flag = d->error_flag;
@@ -222,6 +229,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
             ap.cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
             ap.out = d->attn_out; ap.part_o = d->part_o; ap.part_ml = d->part_ml; ap.counters = d->attn_counters;
             ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.L = c.max_seq_len; ap.S = d->kv_splits;
+            ap.trace = d->trace ? d->trace + 8 * (c.n_layers * 4 + l) : nullptr;
             if (launch_attention(ap, B, stream, true)) return bitnet_last_status();
         }
 
@@ -281,6 +289,14 @@ int bitnet_decoder_error_flag(void* dec) {
     int v = -1;
     if (check_cuda(cudaMemcpy(&v, d->error_flag, sizeof(int), cudaMemcpyDeviceToHost))) return -1;
     return v;
+}
+
+int bitnet_decoder_read_trace(void* dec, unsigned long long* host_out, int n_values) {
+    Decoder* d = static_cast<Decoder*>(dec);
+    if (!d || !d->trace || !host_out) return set_status(kBadArgument), kBadArgument;
+    const int have = d->cfg.n_layers * 5 * 8;
+    return check_cuda(cudaMemcpy(host_out, d->trace, sizeof(unsigned long long) * (n_values < have ? n_values : have),
+                                 cudaMemcpyDeviceToHost));
 }
 
 int bitnet_decoder_kernels_per_step(void* dec) {

@@ -75,13 +75,25 @@ __device__ __forceinline__ void norm_quant_token(Load8 load8, int K, int k_pad, 
     const int n_vec = (K + 7) / 8;
     const bool g_vec = gamma && aligned16(gamma, 8, 2);
     float ss = 0.f, mx = 0.f;
-    for (int v = tid; v < n_vec; v += kPrologueThreads) {
-        const Vec8 x = load8(v * 8);
-        *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x);
+    constexpr int U = 4;   // source loads in flight per thread
+    for (int base = 0; base < n_vec; base += kPrologueThreads * U) {
+        Vec8 x[U];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            ss += x.v[e] * x.v[e];
-            mx = fmaxf(mx, fabsf(x.v[e]));
+        for (int u = 0; u < U; ++u) {
+            const int v = base + u * kPrologueThreads + tid;
+            if (v < n_vec) x[u] = load8(v * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int v = base + u * kPrologueThreads + tid;
+            if (v < n_vec) {
+                *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x[u]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    ss += x[u].v[e] * x[u].v[e];
+                    mx = fmaxf(mx, fabsf(x[u].v[e]));
+                }
+            }
         }
     }
     if (gamma) {

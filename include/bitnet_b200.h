@@ -132,6 +132,12 @@ int bitnet_decoder_bench_linears(void* decoder, int64_t* tokens, void* stream);
 int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos, const float* rope, void* cache_k,
                             void* cache_v, void* out, int batch, int n_heads, int n_kv_heads, int head_dim,
                             int max_seq_len, void* stream);
+/* Measurement aid: when the decoder was created with the environment variable BITNET_TRACE
+ * set, CTA 0 of every fused BitLinear launch records six %globaltimer stamps (start, weights
+ * requested, dependency resolved, activations quantised, matmul done, results stored);
+ * this copies them out, eight 64-bit values per launch: first the 4 BitLinear launches of
+ * every layer, then one attention launch per layer. */
+int bitnet_decoder_read_trace(void* decoder, unsigned long long* host_out, int n_values);
 /* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
 int bitnet_decoder_error_flag(void* decoder);
 /* Number of kernels one step launches. */
