@@ -102,8 +102,8 @@ __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
 // ---------------------------------------------------------------------------------------
 // Fused BitLinear
 // ---------------------------------------------------------------------------------------
-template <int SRC, int MT>
-__global__ void __launch_bounds__(kLinearThreads, (MT <= 4 ? 2 : 1)) fused_linear_kernel(const FusedLinearParams p) {
+template <int SRC>
+__global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const FusedLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -248,32 +248,32 @@ __global__ void __launch_bounds__(kLinearThreads, (MT <= 4 ? 2 : 1)) fused_linea
 
     stamp(3);
     // ---- matmul over the staged tiles ----------------------------------------------------
-    // Per tile a lane holds rows g and g+8 and the 32 columns [32q, 32q+32): each of its four
-    // words is split into its four 2-bit fields by AND masks alone (field j stays scaled by
-    // 4^j and has its own accumulator) and multiplied with dp4a.  Integer tensor-core MMA
-    // (mma.sync) was measured at about 120 cycles per m16n8k32 on this part and is not used.
+    // Per tile a lane holds the A fragments of rows g, g+8 for four m16n8k32 MMAs: each of its
+    // four words is split into its four 2-bit fields by AND masks alone (field j stays scaled
+    // by 4^j and has its own accumulator).  Tokens are the MMA's 8 columns, so any M <= 8
+    // costs the same.  Measured on B200: 0.52 such MMAs per clock per SM, against 2 integer
+    // warp-instructions per clock, so the 16 ANDs per tile, not the MMAs, bound the loop.
     const int g = lane >> 2, q = lane & 3;
     const int rg_first = t0 / p.k_tiles;
+    constexpr int kTilesPerWarp = kStageTiles / kConsumerWarps;
+    // (row group, K tile) of this warp's next tile, advanced without divisions
+    int rg = (t0 + warp * kTilesPerWarp) / p.k_tiles;
+    int kt = (t0 + warp * kTilesPerWarp) - rg * p.k_tiles;
     int cur_rg = -1;
-    bool had_kt0 = false;
-    int acc[MT][2][4];
+    int acc[4][4];
     auto flush = [&]() {
         if (cur_rg < 0) return;
         int* dst = sacc + (cur_rg - rg_first) * 128;
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-#pragma unroll
-            for (int rs = 0; rs < 2; ++rs) {
-                int v = acc[m][rs][0] + (acc[m][rs][1] >> 2) + (acc[m][rs][2] >> 4) + (acc[m][rs][3] >> 6);
-                v += __shfl_xor_sync(0xffffffffu, v, 1);
-                v += __shfl_xor_sync(0xffffffffu, v, 2);
-                if (q == 0 && m < p.M) {
-                    if (had_kt0) v -= ysum_s[m];   // fields hold weight + 1: take sum(y) off once per row
-                    atomicAdd(&dst[(g + 8 * rs) * 8 + m], v);
-                }
+        for (int i = 0; i < 4; ++i) {
+            const int tok = 2 * q + (i & 1);
+            if (tok < p.M) {
+                const int v = acc[0][i] + (acc[1][i] >> 2) + (acc[2][i] >> 4) + (acc[3][i] >> 6);
+                atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
             }
         }
     };
+    const int8_t* y_lane = ys + (size_t)(g < p.M ? g : 0) * y_stride + 32 * q;
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % kStages;
         if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) {   // gave up: flag it, leave together below
@@ -283,44 +283,57 @@ __global__ void __launch_bounds__(kLinearThreads, (MT <= 4 ? 2 : 1)) fused_linea
             }
             break;
         }
+        if (c == 0) stamp(6);
+        if (c == n_chunks - 1) stamp(7);
         const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
-        const uint8_t* stage = ring + s * kStageBytes;
+        const int mine = max(0, min(kTilesPerWarp, tiles - warp * kTilesPerWarp));
+        const uint8_t* stage = ring + s * kStageBytes + (warp * kTilesPerWarp) * kTileBytes + lane * 16;
+        uint4 wv[kTilesPerWarp];
 #pragma unroll
-        for (int u = 0; u < kStageTiles / kConsumerWarps; ++u) {
-            const int i = warp * (kStageTiles / kConsumerWarps) + u;
-            if (i >= tiles) break;
-            const int t = t0 + c * kStageTiles + i;
-            const int rg = t / p.k_tiles, kt = t - rg * p.k_tiles;
-            if (rg != cur_rg) {
-                flush();
-                cur_rg = rg;
-                had_kt0 = false;
+        for (int u = 0; u < kTilesPerWarp; ++u)
+            if (u < mine) wv[u] = *reinterpret_cast<const uint4*>(stage + u * kTileBytes);
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
+        for (int u = 0; u < kTilesPerWarp; ++u) {
+            if (u < mine) {
+                if (rg != cur_rg) {
+                    flush();
+                    cur_rg = rg;
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[m][e >> 2][e & 3] = 0;
-            }
-            had_kt0 = had_kt0 || kt == 0;
-            const uint4 wv = *reinterpret_cast<const uint4*>(stage + i * kTileBytes + lane * 16);
-            const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
-            uint32_t a[4][4];
+                    for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
+                        for (int e = 0; e < 4; ++e) acc[j][e] = 0;
+                }
+                uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+                if (g < p.M) {
+                    const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
+                    v0 = yp[0];
+                    v1 = yp[1];
+                }
+                const uint32_t b[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                const uint32_t w[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) a[r][j] = w[r] & (0x03030303u << (2 * j));
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t msk = 0x03030303u << (2 * j);
+                    mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
+                }
+                if (kt == 0) {   // fields hold weight + 1: take sum(y) off once per row
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m < p.M) {
-                    const uint4* yp = reinterpret_cast<const uint4*>(ys + (size_t)m * y_stride + kt * kTileCols + 32 * q);
-                    const uint4 v0 = yp[0], v1 = yp[1];
-                    const uint32_t b[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-#pragma unroll
-                    for (int r = 0; r < 4; ++r)
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            acc[m][r & 1][j] = dp4a_u8s8(a[r][j], b[2 * j + (r >> 1)], acc[m][r & 1][j]);
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = 2 * q + (e & 1);
+                        if (tok < p.M) acc[0][e] -= ysum_s[tok];
+                    }
+                }
+                if (++kt == p.k_tiles) {
+                    kt = 0;
+                    ++rg;
                 }
             }
+        }
+        // on to this warp's first tile of the next chunk
+        kt += kStageTiles - mine;
+        while (kt >= p.k_tiles) {
+            kt -= p.k_tiles;
+            ++rg;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -380,18 +393,25 @@ __global__ void __launch_bounds__(kLinearThreads, (MT <= 4 ? 2 : 1)) fused_linea
 // Attention for one new token per sequence: RoPE on q and k, append k, v to the cache,
 // softmax(q k^T) v over one slice of the cache per CTA (flash-decoding split); the CTA that
 // finishes a (sequence, kv head) last combines the slices.  grid (n_kv_heads * S, batch),
-// 128 threads; a warp walks keys, a lane owns 4 dims.
+// 4 to 16 warps; a warp walks keys four at a time, a lane owns 4 dims.
 // ---------------------------------------------------------------------------------------
 template <int GMAX>
-__global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionParams p) {
+struct AttnCfg {
+    static constexpr int kWarps = GMAX <= 4 ? 16 : (GMAX <= 8 ? 8 : 4);   // bounded by registers
+    static constexpr int kThreads = kWarps * 32;
+};
+
+template <int GMAX>
+__global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kernel(const AttentionParams p) {
+    constexpr int NW = AttnCfg<GMAX>::kWarps, NT = AttnCfg<GMAX>::kThreads;
     extern __shared__ __align__(128) uint8_t smem[];
     const int D = p.D, G = p.H / p.Hkv;
     float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
     float* knew = q_s + G * D;                             // [D]
     float* vnew = knew + D;                                // [D]
-    float* red_m = vnew + D;                               // [4][GMAX]
-    float* red_l = red_m + 4 * GMAX;                       // [4][GMAX]
-    float* red_o = red_l + 4 * GMAX;                       // [4][G][D]
+    float* red_m = vnew + D;                               // [NW][GMAX]
+    float* red_l = red_m + NW * GMAX;                      // [NW][GMAX]
+    float* red_o = red_l + NW * GMAX;                      // [NW][G][D]
     __shared__ int is_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -416,7 +436,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
     // vectors: G query heads, then k, then v; pairs (2i, 2i+1) rotate together
-    for (int idx = tid; idx < (G + 2) * (D / 2); idx += 128) {
+    for (int idx = tid; idx < (G + 2) * (D / 2); idx += NT) {
         const int vec = idx / (D / 2), i = idx - vec * (D / 2);
         int col;
         if (vec < G) col = (kvh * G + vec) * D;
@@ -505,7 +525,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const int64_t key_stride = (int64_t)p.Hkv * D;
-    for (int j0 = lo + warp * U; j0 < hi; j0 += 4 * U) {
+    for (int j0 = lo + warp * U; j0 < hi; j0 += NW * U) {
         uint2 kr[U], vr[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -532,7 +552,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         visit(kf, vf, 1);
     }
     stamp(3);
-    // combine the four warps
+    // combine the warps
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
         if (h < G) {
@@ -544,12 +564,12 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < G * D; idx += 128) {
+    for (int idx = tid; idx < G * D; idx += NT) {
         const int h = idx / D, d = idx - h * D;
         float mx = -INFINITY;
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, red_m[w * GMAX + h]);
+        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, red_m[w * GMAX + h]);
         float l = 0.f, o = 0.f;
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float lw = red_l[w * GMAX + h];
             if (lw > 0.f) {
                 const float f = __expf(red_m[w * GMAX + h] - mx);
@@ -584,7 +604,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
     float* sl_m = red_o;                  // [G][S] max, then weight
     float* sl_l = red_o + G * p.S;        // [G][S] sum
     const int64_t head0 = (int64_t)b * p.H + kvh * G;
-    for (int idx = tid; idx < G * S; idx += 128) {
+    for (int idx = tid; idx < G * S; idx += NT) {
         const int h = idx / S, sidx = idx - h * S;
         sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
         sl_l[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2 + 1]);
@@ -603,7 +623,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttentionPa
         for (int sidx = 0; sidx < S; ++sidx) sl_m[tid * p.S + sidx] *= inv;
     }
     __syncthreads();
-    for (int idx = tid; idx < G * D; idx += 128) {
+    for (int idx = tid; idx < G * D; idx += NT) {
         const int h = idx / D, d = idx - h * D;
         const float* po = p.part_o + (head0 + h) * p.S * D + d;
         float num = 0.f;
@@ -800,16 +820,10 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
         if (e != cudaSuccess) return check_cuda(e);                                                 \
     }
-#define SET_SMEM_SRC(src)                                      \
-    SET_SMEM((fused_linear_kernel<src, 1>), max_linear_smem)   \
-    SET_SMEM((fused_linear_kernel<src, 2>), max_linear_smem)   \
-    SET_SMEM((fused_linear_kernel<src, 4>), max_linear_smem)   \
-    SET_SMEM((fused_linear_kernel<src, 8>), max_linear_smem)
-    SET_SMEM_SRC(kSrcVector)
-    SET_SMEM_SRC(kSrcEmbedding)
-    SET_SMEM_SRC(kSrcGlu)
-    SET_SMEM_SRC(kSrcQuantized)
-#undef SET_SMEM_SRC
+    SET_SMEM(fused_linear_kernel<kSrcVector>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcEmbedding>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcGlu>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel<kSrcQuantized>, max_linear_smem)
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
@@ -818,29 +832,22 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     return kOk;
 }
 
-template <int SRC>
-static cudaError_t launch_linear_src(const FusedLinearParams& p, size_t smem, cudaStream_t stream, bool pdl) {
-    if (p.M <= 1) return launch_k(fused_linear_kernel<SRC, 1>, p.grid, kLinearThreads, smem, stream, p, pdl);
-    if (p.M <= 2) return launch_k(fused_linear_kernel<SRC, 2>, p.grid, kLinearThreads, smem, stream, p, pdl);
-    if (p.M <= 4) return launch_k(fused_linear_kernel<SRC, 4>, p.grid, kLinearThreads, smem, stream, p, pdl);
-    return launch_k(fused_linear_kernel<SRC, 8>, p.grid, kLinearThreads, smem, stream, p, pdl);
-}
-
 int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pdl) {
     const size_t smem = fused_linear_smem(p);
     cudaError_t e;
     switch (p.src) {
-        case kSrcEmbedding: e = launch_linear_src<kSrcEmbedding>(p, smem, stream, pdl); break;
-        case kSrcGlu: e = launch_linear_src<kSrcGlu>(p, smem, stream, pdl); break;
-        case kSrcQuantized: e = launch_linear_src<kSrcQuantized>(p, smem, stream, pdl); break;
-        default: e = launch_linear_src<kSrcVector>(p, smem, stream, pdl); break;
+        case kSrcEmbedding: e = launch_k(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        case kSrcGlu: e = launch_k(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        case kSrcQuantized: e = launch_k(fused_linear_kernel<kSrcQuantized>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        default: e = launch_k(fused_linear_kernel<kSrcVector>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
     }
     return check_cuda(e);
 }
 
 size_t attention_smem(const AttentionParams& p) {
     const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
-    return sizeof(float) * ((size_t)(G + 2) * p.D + 8 * gmax + 4 * (size_t)G * p.D) + 64;
+    const int nw = gmax <= 4 ? 16 : (gmax <= 8 ? 8 : 4);
+    return sizeof(float) * ((size_t)(G + 2) * p.D + 2 * nw * gmax + (size_t)nw * G * p.D) + 64;
 }
 
 int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl) {
@@ -848,9 +855,9 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (G <= 4) e = launch_k(attention_decode_kernel<4>, grid, 128, smem, stream, p, pdl);
-    else if (G <= 8) e = launch_k(attention_decode_kernel<8>, grid, 128, smem, stream, p, pdl);
-    else e = launch_k(attention_decode_kernel<16>, grid, 128, smem, stream, p, pdl);
+    if (G <= 4) e = launch_k(attention_decode_kernel<4>, grid, AttnCfg<4>::kThreads, smem, stream, p, pdl);
+    else if (G <= 8) e = launch_k(attention_decode_kernel<8>, grid, AttnCfg<8>::kThreads, smem, stream, p, pdl);
+    else e = launch_k(attention_decode_kernel<16>, grid, AttnCfg<16>::kThreads, smem, stream, p, pdl);
     return check_cuda(e);
 }
 
