@@ -69,7 +69,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and the caller abandons the kernel) after about a second.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
@@ -88,10 +88,21 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads) : "memory"); }
 
 // bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
-__device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
+__device__ __noinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
 
 
-__device__ __forceinline__ void consumer_sync_fn() { consumer_sync(); }
+struct ConsumerSync {
+    __device__ __forceinline__ void operator()() const { consumer_sync(); }
+};
+// Out of line on purpose (code size): sum / max over the 256 consumer threads.
+__device__ __noinline__ float consumer_reduce(float v, bool is_max, float* scratch, int tid) {
+    return reduce_256(v, is_max, scratch, tid, ConsumerSync());
+}
+struct ConsumerReduce {   // reduction functor handed to the shared prologue
+    __device__ __forceinline__ float operator()(float v, bool is_max, float* scratch, int tid) const {
+        return consumer_reduce(v, is_max, scratch, tid);
+    }
+};
 
 // CTA that owns tile t under the even split (tiles_base + 1 tiles for the first tiles_rem CTAs).
 __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
@@ -100,9 +111,15 @@ __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Fused BitLinear
+// Fused BitLinear.  One kernel for all source kinds and token counts, with rolled loops:
+// the kernels of the chain run for a few microseconds each, so their code has to stay
+// resident in the instruction cache from launch to launch.
 // ---------------------------------------------------------------------------------------
-template <int SRC>
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
 __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const FusedLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
@@ -111,11 +128,12 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 8 floats
     int* ysum_s = reinterpret_cast<int*>(scratch + 8);                         // 8 ints
     float* a_s = reinterpret_cast<float*>(ysum_s + 8);                         // 8 floats
-    int* last_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (2 used)
-    int* sacc = last_s + 8;                                                    // [r_max][16][8]
-    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even]
-    const int k_stage = SRC == kSrcQuantized ? 0 : p.K_even;                    // no staging rows needed
-    __nv_bfloat16* gs = xv + k_stage;                                           // [K_even] RMSNorm weight
+    int* flag_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (1 used)
+    int* sacc = flag_s + 8;                                                    // [r_max][16][8]
+    const int k_stage = p.src == kSrcQuantized ? 0 : p.K_even;                 // staging rows
+    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even] source / normalised row
+    __nv_bfloat16* xb = xv + k_stage;                                           // [K_even] second GLU operand
+    __nv_bfloat16* gs = xb + k_stage;                                           // [K_even] RMSNorm weight
     const int k_pad = p.k_tiles * kTileCols;
     const int y_stride = k_pad + 16;
     int8_t* ys = reinterpret_cast<int8_t*>(gs + k_stage);                       // [M][y_stride]
@@ -136,10 +154,12 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     const int n_chunks = (n_tiles + kStageTiles - 1) / kStageTiles;
 
     if (tid == 0) {
+#pragma unroll 1
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kConsumerWarps);
         }
+        flag_s[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
@@ -149,6 +169,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         // ---- producer: streams the weight tiles; independent of the predecessor kernel ----
         if (lane == 0) {
             const uint8_t* src = p.w2t + (int64_t)t0 * kTileBytes;
+#pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 const int s = c % kStages;
                 if (c >= kStages && !mbar_wait(&empty_bar[s], ((c / kStages) - 1) & 1)) {
@@ -164,28 +185,33 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     }
 
     // ---- consumers ---------------------------------------------------------------------
+#pragma unroll 1
     for (int i = tid; i < p.r_max * 128; i += kConsumerThreads) sacc[i] = 0;
-    const __nv_bfloat16* gamma = nullptr;
-    if (SRC != kSrcQuantized && p.gamma) {   // the norm weight is a constant: stage it before the wait
-        const bool g_vec = aligned16(p.gamma, 8, 2);
-        for (int v = tid; v < p.K_even / 8; v += kConsumerThreads)
-            *reinterpret_cast<uint4*>(gs + v * 8) = pack_bf16x8(load_bf16x8(p.gamma, v * 8, p.K, g_vec));
-        gamma = gs;
+    const int n_vec = p.K_even / 8;
+    const bool use_gamma = p.src != kSrcQuantized && p.gamma != nullptr;
+    if (use_gamma) {   // the norm weight is a constant: stage it before the wait
+#pragma unroll 1
+        for (int v = tid; v < n_vec; v += kConsumerThreads) cp_async16(gs + v * 8, p.gamma + v * 8);
     }
 
     stamp(1);
     pdl_wait();   // the predecessor's results are visible from here on
     stamp(2);
 
-    // prologue: the int8 activations of every token, in shared memory
+    // prologue: the int8 activations of every token, in shared memory (plus one row of zeros)
+#pragma unroll 1
+    for (int v = tid; v < y_stride / 16; v += kConsumerThreads)
+        *reinterpret_cast<uint4*>(ys + (size_t)p.M * y_stride + v * 16) = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
     for (int m = 0; m < p.M; ++m) {
         int8_t* ym = ys + (size_t)m * y_stride;
         float a;
         int ysum;
-        if (SRC == kSrcQuantized) {
+        if (p.src == kSrcQuantized) {
             const int8_t* row = p.yq + (int64_t)m * p.ldy;
             const bool vec_ok = aligned16(p.yq, p.ldy, 1);
             float sy = 0.f;
+#pragma unroll 1
             for (int v = tid; v < k_pad / 16; v += kConsumerThreads) {
                 uint4 u = make_uint4(0, 0, 0, 0);
                 const int k = v * 16;
@@ -193,57 +219,53 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
                     u = *reinterpret_cast<const uint4*>(row + k);
                 } else {
                     uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll 1
                     for (int e = 0; e < 16; ++e)
                         if (k + e < p.K) w[e >> 2] |= (uint32_t)(uint8_t)row[k + e] << (8 * (e & 3));
                     u = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 *reinterpret_cast<uint4*>(ym + k) = u;
-                if (!p.ysum_q)
-                    sy += (float)(__dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) +
-                                  __dp4a((int)u.z, 0x01010101, 0) + __dp4a((int)u.w, 0x01010101, 0));
+                sy += (float)(__dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) +
+                              __dp4a((int)u.z, 0x01010101, 0) + __dp4a((int)u.w, 0x01010101, 0));
             }
-            if (!p.ysum_q) sy = reduce_256(sy, false, scratch, tid, consumer_sync_fn);
+            if (!p.ysum_q) sy = consumer_reduce(sy, false, scratch, tid);
             ysum = p.ysum_q ? p.ysum_q[m] : (int)sy;
             a = p.a_q ? p.a_q[m] : (p.a_q_bf16 ? __bfloat162float(p.a_q_bf16[m]) : 1.f);
-        } else if (SRC == kSrcEmbedding) {
-            const __nv_bfloat16* row = p.emb + p.tokens[m] * (int64_t)p.K;
-            const bool vec_ok = aligned16(p.emb, p.K, 2);
-            const int K = p.K;
-            norm_quant_token([&](int k) {
-                    const Vec8 x = load_bf16x8(row, k, K, vec_ok);
-                    if (cta == 0 && p.h_copy) {   // the residual stream starts as the embedding row
-                        for (int e = 0; e < 8; ++e)
-                            if (k + e < K) p.h_copy[(int64_t)m * K + k + e] = __float2bfloat16_rn(x.v[e]);
-                    }
-                    return x;
-                }, K, k_pad, gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
-        } else if (SRC == kSrcGlu) {
-            const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
-            const bool vec_ok = aligned16(p.x, p.ldx, 2) && (p.K % 8 == 0);
-            const int K = p.K;
-            norm_quant_token([&](int k) {
-                    const Vec8 x1 = load_bf16x8(row, k, K, vec_ok), x3 = load_bf16x8(row + K, k, K, vec_ok);
-                    Vec8 r;
+        } else {
+            // stage the source row(s) with asynchronous 16-byte copies, all in flight at once
+            const __nv_bfloat16* row = p.src == kSrcEmbedding ? p.emb + p.tokens[m] * (int64_t)p.K
+                                                              : p.x + (int64_t)m * p.ldx;
+#pragma unroll 1
+            for (int v = tid; v < n_vec; v += kConsumerThreads) {
+                cp_async16(xv + v * 8, row + v * 8);
+                if (p.src == kSrcGlu) cp_async16(xb + v * 8, row + p.K + v * 8);
+            }
+            cp_async_wait_all();
+            if (p.src == kSrcGlu) {          // relu(x1)^2 * x3 with bf16 rounding after each step
+#pragma unroll 1
+                for (int v = tid; v < n_vec; v += kConsumerThreads) {
+                    Vec8 x1 = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
+                    const Vec8 x3 = unpack_bf16x8(*reinterpret_cast<const uint4*>(xb + v * 8));
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const float t = fmaxf(x1.v[e], 0.f);
-                        r.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
+                        x1.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
                     }
-                    return r;
-                }, K, k_pad, gamma, p.eps, xv, ym, scratch, tid, consumer_sync_fn, a, ysum);
-        } else {
-            const __nv_bfloat16* row = p.x + (int64_t)m * p.ldx;
-            const bool vec_ok = aligned16(p.x, p.ldx, 2);
-            const int K = p.K;
-            norm_quant_token([&](int k) { return load_bf16x8(row, k, K, vec_ok); }, K, k_pad, gamma, p.eps, xv, ym,
-                             scratch, tid, consumer_sync_fn, a, ysum);
+                    *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x1);
+                }
+            } else if (p.src == kSrcEmbedding && p.h_copy && cta == 0) {
+                // the residual stream starts as the embedding row
+#pragma unroll 1
+                for (int v = tid; v < n_vec; v += kConsumerThreads)
+                    *reinterpret_cast<uint4*>(p.h_copy + (int64_t)m * p.K + v * 8) = *reinterpret_cast<const uint4*>(xv + v * 8);
+            }
+            norm_quant_row(xv, p.K, k_pad, use_gamma ? gs : nullptr, p.eps, ym, scratch, tid, ConsumerReduce(), a, ysum);
         }
         if (tid == 0) {
             ysum_s[m] = ysum;
             a_s[m] = a;
-            last_s[4] = 0;
         }
-        consumer_sync();   // xv is reused by the next token
+        consumer_sync();   // xv is reused by the next token; ys, ysum_s, a_s are complete
     }
 
     stamp(3);
@@ -251,97 +273,92 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     // Per tile a lane holds the A fragments of rows g, g+8 for four m16n8k32 MMAs: each of its
     // four words is split into its four 2-bit fields by AND masks alone (field j stays scaled
     // by 4^j and has its own accumulator).  Tokens are the MMA's 8 columns, so any M <= 8
-    // costs the same.  Measured on B200: 0.52 such MMAs per clock per SM, against 2 integer
+    // costs the same.  Measured on B200: 0.52 such MMAs per clock per SM against 2 integer
     // warp-instructions per clock, so the 16 ANDs per tile, not the MMAs, bound the loop.
     const int g = lane >> 2, q = lane & 3;
     const int rg_first = t0 / p.k_tiles;
-    constexpr int kTilesPerWarp = kStageTiles / kConsumerWarps;
-    // (row group, K tile) of this warp's next tile, advanced without divisions
-    int rg = (t0 + warp * kTilesPerWarp) / p.k_tiles;
-    int kt = (t0 + warp * kTilesPerWarp) - rg * p.k_tiles;
+    constexpr int kRoundTiles = kStages * kStageTiles;   // tiles resident in the ring at once
     int cur_rg = -1;
     int acc[4][4];
     auto flush = [&]() {
-        if (cur_rg < 0) return;
-        int* dst = sacc + (cur_rg - rg_first) * 128;
+        if (cur_rg >= 0) {
+            int* dst = sacc + (cur_rg - rg_first) * 128;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int tok = 2 * q + (i & 1);
-            if (tok < p.M) {
-                const int v = acc[0][i] + (acc[1][i] >> 2) + (acc[2][i] >> 4) + (acc[3][i] >> 6);
-                atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
+            for (int i = 0; i < 4; ++i) {
+                const int tok = 2 * q + (i & 1);
+                if (tok < p.M) {
+                    const int v = acc[0][i] + (acc[1][i] >> 2) + (acc[2][i] >> 4) + (acc[3][i] >> 6);
+                    atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
+                }
             }
         }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[j][e] = 0;
     };
-    const int8_t* y_lane = ys + (size_t)(g < p.M ? g : 0) * y_stride + 32 * q;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % kStages;
-        if (!mbar_wait(&full_bar[s], (c / kStages) & 1)) {   // gave up: flag it, leave together below
-            if (lane == 0) {
-                atomicExch(p.error_flag, 2);
-                last_s[4] = 1;
-            }
-            break;
-        }
-        if (c == 0) stamp(6);
-        if (c == n_chunks - 1) stamp(7);
-        const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
-        const int mine = max(0, min(kTilesPerWarp, tiles - warp * kTilesPerWarp));
-        const uint8_t* stage = ring + s * kStageBytes + (warp * kTilesPerWarp) * kTileBytes + lane * 16;
-        uint4 wv[kTilesPerWarp];
-#pragma unroll
-        for (int u = 0; u < kTilesPerWarp; ++u)
-            if (u < mine) wv[u] = *reinterpret_cast<const uint4*>(stage + u * kTileBytes);
-#pragma unroll
-        for (int u = 0; u < kTilesPerWarp; ++u) {
-            if (u < mine) {
-                if (rg != cur_rg) {
-                    flush();
-                    cur_rg = rg;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[j][e] = 0;
+    flush();
+    // MMA column g multiplies token g; columns beyond M read the zero row behind the last token
+    const int8_t* y_lane = ys + (size_t)(g < p.M ? g : p.M) * y_stride + 32 * q;
+    const int ysub0 = (2 * q < p.M) ? ysum_s[2 * q] : 0, ysub1 = (2 * q + 1 < p.M) ? ysum_s[2 * q + 1] : 0;
+    // The ring holds a round of up to 128 tiles; within a round each warp takes one
+    // contiguous run, so that it flushes rarely and its loop reaches a steady state.
+    const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
+#pragma unroll 1
+    for (int r = 0; r < n_rounds; ++r) {
+        const int nr = min(kRoundTiles, n_tiles - r * kRoundTiles);
+        const int lo = nr * warp / kConsumerWarps, hi = (p.debug & 1) ? lo : nr * (warp + 1) / kConsumerWarps;
+        if (hi > lo && !(p.debug & 2)) {
+            bool ok = true;
+#pragma unroll 1
+            for (int s = lo / kStageTiles; s <= (hi - 1) / kStageTiles; ++s) ok = ok && mbar_wait(&full_bar[s], r & 1);
+            if (!ok) {   // gave up: flag it, leave together below
+                if (lane == 0) {
+                    atomicExch(p.error_flag, 2);
+                    flag_s[0] = 1;
                 }
-                uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-                if (g < p.M) {
-                    const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
-                    v0 = yp[0];
-                    v1 = yp[1];
-                }
-                const uint32_t b[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                const uint32_t w[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t msk = 0x03030303u << (2 * j);
-                    mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
-                }
-                if (kt == 0) {   // fields hold weight + 1: take sum(y) off once per row
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int tok = 2 * q + (e & 1);
-                        if (tok < p.M) acc[0][e] -= ysum_s[tok];
-                    }
-                }
-                if (++kt == p.k_tiles) {
-                    kt = 0;
-                    ++rg;
-                }
+                break;
             }
         }
-        // on to this warp's first tile of the next chunk
-        kt += kStageTiles - mine;
-        while (kt >= p.k_tiles) {
-            kt -= p.k_tiles;
-            ++rg;
+        if (r == 0) stamp(6);
+        const int t_first = t0 + r * kRoundTiles + lo;
+        int rg = t_first / p.k_tiles, kt = t_first - rg * p.k_tiles;
+        const uint8_t* tile = ring + lo * kTileBytes + lane * 16;
+#pragma unroll 1
+        for (int i = lo; i < hi; ++i, tile += kTileBytes) {
+            if (rg != cur_rg) {
+                flush();
+                cur_rg = rg;
+            }
+            const uint4 wc = *reinterpret_cast<const uint4*>(tile);
+            const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
+            const uint4 y0 = yp[0], y1 = yp[1];
+            const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+            const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t msk = 0x03030303u << (2 * j);
+                mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
+            }
+            if (kt == 0) {   // fields hold weight + 1: take sum(y) off once per row
+                acc[0][0] -= ysub0; acc[0][1] -= ysub1; acc[0][2] -= ysub0; acc[0][3] -= ysub1;
+            }
+            if (++kt == p.k_tiles) {
+                kt = 0;
+                ++rg;
+            }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
+        if (lane == 0) {   // this warp is done with every stage of the round
+#pragma unroll 1
+            for (int s = 0; s < kStages; ++s) mbar_arrive(&empty_bar[s]);
+        }
     }
+    stamp(7);
     flush();
     consumer_sync();
     stamp(4);
-    if (last_s[4] || n_tiles == 0) return;
+    if (flag_s[0] || n_tiles == 0) return;
 
     // ---- epilogue --------------------------------------------------------------------------
     const int n_rg = (t0 + n_tiles - 1) / p.k_tiles - rg_first + 1;
@@ -349,21 +366,11 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     // only the first and the last row group of the range can be partial
     const bool part_first = t0 > rg_first * p.k_tiles || (t0 + n_tiles) < (rg_first + 1) * p.k_tiles;
     const bool part_last = n_rg > 1 && (t0 + n_tiles) < (rg_last + 1) * p.k_tiles;
-
-    auto finalize = [&](int m, int row, int v, float h_old) {
-        if (p.acc_out) p.acc_out[(int64_t)m * p.N + row] = v;
-        if (p.out) {
-            const int sg = segment_of(p.seg, row);
-            const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg]
-                                          : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : p.ws[sg]);
-            const float lin = lin_out(v, a_s[m], ws);
-            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(p.out_kind == kOutResidual ? h_old + lin : lin);
-        }
-    };
+#pragma unroll 1
     for (int idx = tid; idx < n_rg * 16 * p.M; idx += kConsumerThreads) {
         const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);      // consecutive threads -> consecutive rows
         const int li = rem >> 4, r = rem & 15;
-        const int rg = rg_first + li, row = rg * 16 + r;
+        const int rgi = rg_first + li, row = rgi * 16 + r;
         const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
         if (row >= p.N && !partial) continue;
         float h_old = 0.f;
@@ -374,9 +381,9 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             // slot in one atomic (sum in the low 40 bits, tickets above).  The contributor
             // whose atomic completes the ticket count sees the finished sum in the returned
             // value, finalises the element and clears the slot.  Nobody waits.
-            const int lo_t = rg * p.k_tiles, hi_t = lo_t + p.k_tiles - 1;
+            const int lo_t = rgi * p.k_tiles, hi_t = lo_t + p.k_tiles - 1;
             const long long expected = cta_of_tile(p, hi_t) - cta_of_tile(p, lo_t) + 1;
-            unsigned long long* slot = &p.acc_scratch[(int64_t)rg * 128 + r * 8 + m];
+            unsigned long long* slot = &p.acc_scratch[(int64_t)rgi * 128 + r * 8 + m];
             const unsigned long long add = (unsigned long long)((long long)v + (1LL << 40));
             const long long tot = (long long)(atomicAdd(slot, add) + add);
             const long long cnt = (tot + (1LL << 39)) >> 40;
@@ -384,7 +391,15 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             v = (int)(tot - (cnt << 40));
             *slot = 0ull;
         }
-        if (row < p.N) finalize(m, row, v, h_old);
+        if (row >= p.N) continue;
+        if (p.acc_out) p.acc_out[(int64_t)m * p.N + row] = v;
+        if (p.out) {
+            const int sg = segment_of(p.seg, row);
+            const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg]
+                                          : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : p.ws[sg]);
+            const float lin = lin_out(v, a_s[m], ws);
+            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(p.out_kind == kOutResidual ? h_old + lin : lin);
+        }
     }
     stamp(5);
 }
@@ -810,7 +825,7 @@ void plan_linear(FusedLinearParams& p, int n_sm) {
 size_t fused_linear_smem(const FusedLinearParams& p) {
     const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
     return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 4 + (size_t)p.r_max * 128 * 4 +
-           (p.src == kSrcQuantized ? 0 : (size_t)p.K_even * 4) + (size_t)p.M * y_stride + 128;
+           (p.src == kSrcQuantized ? 0 : (size_t)p.K_even * 6) + (size_t)(p.M + 1) * y_stride + 128;
 }
 
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {
@@ -820,10 +835,7 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(n));         \
         if (e != cudaSuccess) return check_cuda(e);                                                 \
     }
-    SET_SMEM(fused_linear_kernel<kSrcVector>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcEmbedding>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcGlu>, max_linear_smem)
-    SET_SMEM(fused_linear_kernel<kSrcQuantized>, max_linear_smem)
+    SET_SMEM(fused_linear_kernel, max_linear_smem)
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
@@ -836,10 +848,7 @@ int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pd
     const size_t smem = fused_linear_smem(p);
     cudaError_t e;
     switch (p.src) {
-        case kSrcEmbedding: e = launch_k(fused_linear_kernel<kSrcEmbedding>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        case kSrcGlu: e = launch_k(fused_linear_kernel<kSrcGlu>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        case kSrcQuantized: e = launch_k(fused_linear_kernel<kSrcQuantized>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-        default: e = launch_k(fused_linear_kernel<kSrcVector>, p.grid, kLinearThreads, smem, stream, p, pdl); break;
+        default: e = launch_k(fused_linear_kernel, p.grid, kLinearThreads, smem, stream, p, pdl); break;
     }
     return check_cuda(e);
 }

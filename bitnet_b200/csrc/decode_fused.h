@@ -47,6 +47,7 @@ struct FusedLinearParams {
     unsigned long long* acc_scratch; // [ceil16(N)/16][16][8] 64-bit slots (sum + tickets), zero between launches
     int* error_flag;
     unsigned long long* trace;       // optional: 8 phase timestamps written by CTA 0
+    int debug;                       // measurement aid: 1 = skip the math, 2 = skip the waits for weights
 };
 
 struct AttentionParams {

@@ -173,7 +173,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
                  o_qkv = take((size_t)B * Nqkv * 2), o_att = take((size_t)B * dim * 2),
                  o_13 = take((size_t)B * 2 * F * 2), o_po = take((size_t)B * H * d->kv_splits * D * 4),
                  o_pml = take((size_t)B * H * d->kv_splits * 2 * 4), o_pv = take((size_t)d->head_grid * 8 * 4),
-                 o_pi = take((size_t)d->head_grid * 8 * 4), o_tr = take((size_t)cfg->n_layers * 5 * 8 * 8);
+                 o_pi = take((size_t)d->head_grid * 8 * 4), o_tr = take((size_t)cfg->n_layers * 5 * 16 * 8);
     if (check_cuda(cudaMalloc(&d->scratch, off)) || check_cuda(cudaMemset(d->scratch, 0, off))) {
         delete d;
         return nullptr;
@@ -201,7 +201,9 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
     const int Nqkv = (H + 2 * Hkv) * D;
     int launch_no = 0;
     auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
-        p.trace = d->trace ? d->trace + 8 * launch_no : nullptr;
+        p.trace = d->trace ? d->trace + 16 * launch_no : nullptr;
+        static const int dbg = getenv("BITNET_DEBUG_SKIP") ? atoi(getenv("BITNET_DEBUG_SKIP")) : 0;
+        p.debug = dbg;
         ++launch_no;
         p.w2t = static_cast<const uint8_t*>(w);
         p.gamma = static_cast<const __nv_bfloat16*>(gamma);
@@ -229,7 +231,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
             ap.cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
             ap.out = d->attn_out; ap.part_o = d->part_o; ap.part_ml = d->part_ml; ap.counters = d->attn_counters;
             ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.L = c.max_seq_len; ap.S = d->kv_splits;
-            ap.trace = d->trace ? d->trace + 8 * (c.n_layers * 4 + l) : nullptr;
+            ap.trace = d->trace ? d->trace + 16 * (c.n_layers * 4 + l) : nullptr;
             if (launch_attention(ap, B, stream, true)) return bitnet_last_status();
         }
 
@@ -294,7 +296,7 @@ int bitnet_decoder_error_flag(void* dec) {
 int bitnet_decoder_read_trace(void* dec, unsigned long long* host_out, int n_values) {
     Decoder* d = static_cast<Decoder*>(dec);
     if (!d || !d->trace || !host_out) return set_status(kBadArgument), kBadArgument;
-    const int have = d->cfg.n_layers * 5 * 8;
+    const int have = d->cfg.n_layers * 5 * 16;
     return check_cuda(cudaMemcpy(host_out, d->trace, sizeof(unsigned long long) * (n_values < have ? n_values : have),
                                  cudaMemcpyDeviceToHost));
 }

@@ -3,7 +3,8 @@
 // (optional) RMSNorm -> round to bf16 -> absmax -> a = 127 / max(absmax, 1e-5)
 // -> y = clamp(rint(x * a), -128, 127), following gpu/model.py:68-71 behind the norms of
 // gpu/model.py:159-160, 195-196, 237-242.  Executed by exactly 256 threads per token;
-// thread t owns the 8-element groups t, t + 256, ... in all three passes.
+// thread t owns the 8-element groups t, t + 256, ... in every pass, so the result does not
+// depend on which kernel runs it.
 #pragma once
 #include "common.cuh"
 
@@ -64,42 +65,34 @@ __device__ __forceinline__ float reduce_256(float v, bool is_max, float* scratch
     return r;
 }
 
-// One token.  load8(k) returns the eight source values k..k+7 (already bf16-representable,
-// zero beyond K).  xv: staging row in shared memory, ceil8(K) bf16.  y: destination row of
-// k_pad bytes (shared or global), zero filled beyond K.  On return every thread holds the
-// token's activation scale and sum(y).
-template <class Load8, class Sync>
-__device__ __forceinline__ void norm_quant_token(Load8 load8, int K, int k_pad, const __nv_bfloat16* gamma, float eps,
-                                                 __nv_bfloat16* xv, int8_t* y, float* scratch, int tid, Sync sync,
-                                                 float& a_out, int& ysum_out) {
+// One token whose source values already sit in shared memory: xv holds ceil8(K) bf16
+// values (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero filled
+// beyond K.  On return every thread holds the token's activation scale and sum(y).  The
+// loops are deliberately not unrolled: these kernels run for microseconds, and code that
+// does not fit the instruction cache costs more than the loop overhead saves.
+// reduce(v, is_max, scratch, tid) must return the sum / max of v over the 256 threads, in
+// the order reduce_256 defines.
+template <class Reduce>
+__device__ __forceinline__ void norm_quant_row(__nv_bfloat16* xv, int K, int k_pad, const __nv_bfloat16* gamma,
+                                               float eps, int8_t* y, float* scratch, int tid, Reduce reduce,
+                                               float& a_out, int& ysum_out) {
     const int n_vec = (K + 7) / 8;
     const bool g_vec = gamma && aligned16(gamma, 8, 2);
     float ss = 0.f, mx = 0.f;
-    constexpr int U = 4;   // source loads in flight per thread
-    for (int base = 0; base < n_vec; base += kPrologueThreads * U) {
-        Vec8 x[U];
+#pragma unroll 1
+    for (int v = tid; v < n_vec; v += kPrologueThreads) {
+        const Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int v = base + u * kPrologueThreads + tid;
-            if (v < n_vec) x[u] = load8(v * 8);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int v = base + u * kPrologueThreads + tid;
-            if (v < n_vec) {
-                *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x[u]);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    ss += x[u].v[e] * x[u].v[e];
-                    mx = fmaxf(mx, fabsf(x[u].v[e]));
-                }
-            }
+        for (int e = 0; e < 8; ++e) {
+            ss += x.v[e] * x.v[e];
+            mx = fmaxf(mx, fabsf(x.v[e]));
         }
     }
     if (gamma) {
-        ss = reduce_256(ss, false, scratch, tid, sync);
+        ss = reduce(ss, false, scratch, tid);
         const float rinv = rsqrtf(ss / (float)K + eps);
         mx = 0.f;
+#pragma unroll 1
         for (int v = tid; v < n_vec; v += kPrologueThreads) {
             Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
             const Vec8 g = load_bf16x8(gamma, v * 8, K, g_vec);
@@ -111,9 +104,10 @@ __device__ __forceinline__ void norm_quant_token(Load8 load8, int K, int k_pad, 
             *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x);
         }
     }
-    mx = reduce_256(mx, true, scratch, tid, sync);
+    mx = reduce(mx, true, scratch, tid);
     const float a = 127.0f / fmaxf(mx, 1e-5f);
     float sy = 0.f;
+#pragma unroll 1
     for (int v = tid; v < k_pad / 8; v += kPrologueThreads) {
         uint32_t lo = 0, hi = 0;
         if (v < n_vec) {
@@ -130,7 +124,7 @@ __device__ __forceinline__ void norm_quant_token(Load8 load8, int K, int k_pad, 
         }
         *reinterpret_cast<uint2*>(y + v * 8) = make_uint2(lo, hi);
     }
-    sy = reduce_256(sy, false, scratch, tid, sync);   // exact: |sum| < 2^24
+    sy = reduce(sy, false, scratch, tid);   // exact: |sum| < 2^24
     a_out = a;
     ysum_out = (int)sy;
 }

@@ -20,8 +20,12 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
     const int K = p.K;
     float a;
     int ysum;
-    norm_quant_token([&](int k) { return load_bf16x8(row, k, K, vec_ok); }, K, (int)p.ldy, p.gamma, p.eps, xv,
-                     p.y + (int64_t)tok * p.ldy, scratch, tid, [] { __syncthreads(); }, a, ysum);
+#pragma unroll 1
+    for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads)
+        *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(load_bf16x8(row, v * 8, K, vec_ok));
+    norm_quant_row(xv, K, (int)p.ldy, p.gamma, p.eps, p.y + (int64_t)tok * p.ldy, scratch, tid,
+                   [](float v, bool is_max, float* sc, int t) { return reduce_256(v, is_max, sc, t, [] { __syncthreads(); }); },
+                   a, ysum);
     if (tid == 0) {
         if (p.a_f32) p.a_f32[tok] = a;
         if (p.a_bf16) p.a_bf16[tok] = __float2bfloat16_rn(a);

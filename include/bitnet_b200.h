@@ -135,7 +135,7 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
 /* Measurement aid: when the decoder was created with the environment variable BITNET_TRACE
  * set, CTA 0 of every fused BitLinear launch records six %globaltimer stamps (start, weights
  * requested, dependency resolved, activations quantised, matmul done, results stored);
- * this copies them out, eight 64-bit values per launch: first the 4 BitLinear launches of
+ * this copies them out, sixteen 64-bit values per launch: first the 4 BitLinear launches of
  * every layer, then one attention launch per layer. */
 int bitnet_decoder_read_trace(void* decoder, unsigned long long* host_out, int n_values);
 /* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
