@@ -308,6 +308,8 @@ def run_ours(a, args_model):
         tok_s, info, _ = cpu_i2s_tokens_per_s(args_model, B, steps=3, warmup=1, layers_sampled=min(args_model.n_layers, 4))
         cpu = dict(info, value=tok_s, unit="tok/s")
     n_lin = len(lins)
+    # every byte a decode step must read: packed BitLinear weights + the bf16 output projection
+    step_bytes = weight_bytes + 2 * args_model.vocab_size * args_model.dim
     line = {
         "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{B})", "value": world * B * K / (ms * 1e-3),
         "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
@@ -325,7 +327,9 @@ def run_ours(a, args_model):
                      "traffic": None, "peak_source": "measured" if peaks else "fallback",
                      "kernel": "fused_linear_kernel (prologue + W2A8 matmul, PDL chain)" if fused else "w2a8_gemv_kernel",
                      "launches_per_step": n_lin,
-                     "bytes_per_launch": weight_bytes / n_lin, "us_per_launch": 1e3 * ms_lin / n_lin},
+                     "bytes_per_launch": weight_bytes / n_lin, "us_per_launch": 1e3 * ms_lin / n_lin,
+                     "step_bytes": step_bytes, "step_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
+                     "step_frac": step_bytes / (ms / K * 1e-3) / 1e9 / peak},
         "cpu_baseline": cpu, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
