@@ -44,6 +44,16 @@ SIGNATURES = {
     "bitnet_pack_from_ref_int2": (_i, [_vp, _vp, _i, _i, _vp]),
     "bitnet_unpack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),
     "quantize_i2_s": (ctypes.c_size_t, [_vp, _vp, _i64, _i64, _vp]),
+    "ggml_bitnet_init": (None, []),
+    "ggml_bitnet_free": (None, []),
+    "ggml_bitnet_can_mul_mat": (ctypes.c_bool, [_vp, _vp, _vp]),
+    "ggml_bitnet_mul_mat_get_wsize": (ctypes.c_size_t, [_vp, _vp, _vp]),
+    "ggml_bitnet_mul_mat_task_init": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "ggml_bitnet_mul_mat_task_compute": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "ggml_bitnet_transform_tensor": (None, [_vp]),
+    "ggml_bitnet_mul_mat": (None, [_vp, _vp]),
+    "ggml_bitnet_get_type_bits": (_i, [_i]),
+    "ggml_bitnet_set_n_threads": (None, [_i]),
     "ggml_vec_dot_i2_i8_s": (None, [_i, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _i]),
 }
 
