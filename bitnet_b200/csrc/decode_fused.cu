@@ -881,3 +881,80 @@ int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl) {
 }
 
 }  // namespace bitnet
+
+// ---------------------------------------------------------------------------------------
+// BitLinear without any allocation: the scratch of the split-K epilogue lives in a fixed
+// device array inside the library image.
+// ---------------------------------------------------------------------------------------
+namespace bitnet {
+
+namespace {
+
+constexpr int kStaticRowGroups = 1024;                      // outputs of up to 16384 rows
+constexpr int kStaticSlots = kStaticRowGroups * 128;        // one 64-bit slot per (row, token)
+// 1 MB of slots plus one word for the kernel's error flag.  Every GPU that loads the library
+// holds this array until the process exits.
+static __device__ __align__(256) unsigned long long g_static_scratch[kStaticSlots + 32];
+
+struct StaticSetup {
+    bool ready = false;
+    unsigned long long* scratch = nullptr;   // device address of g_static_scratch on this device
+    int n_sm = 0;
+    int smem_optin = 0;
+};
+StaticSetup g_static_setup[64];
+
+}  // namespace
+
+}  // namespace bitnet
+
+extern "C" int bitlinear_int8xint2_noalloc(int8_t* input0, int8_t* input1, void* output0, void* s, void* ws, int M,
+                                           int N, int K, void* stream) {
+    using namespace bitnet;
+    set_status(kOk);
+    if (!input0 || !input1 || !output0 || !s || !ws || M < 1 || N < 1 || K < 1) return set_status(kBadArgument), kBadArgument;
+    if (N % 16 != 0 || K % 128 != 0) return set_status(kUnsupported), kUnsupported;
+    if (M > 8 || N / 16 > kStaticRowGroups) return set_status(kTooLarge), kTooLarge;   // beyond the fixed scratch
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev))) return kCudaError;
+    if (dev < 0 || dev >= 64) return set_status(kUnsupported), kUnsupported;
+    StaticSetup& st = g_static_setup[dev];
+    if (!st.ready) {
+        // Once per device, with that device current: the array's name is only a host-side
+        // handle, the kernel needs the address the runtime reports for it on this device.
+        void* ptr = nullptr;
+        if (check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch))) return kCudaError;
+        if (check_cuda(cudaDeviceGetAttribute(&st.n_sm, cudaDevAttrMultiProcessorCount, dev)) ||
+            check_cuda(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) ||
+            check_cuda(cudaFuncSetAttribute(fused_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            st.smem_optin)))
+            return kCudaError;
+        st.scratch = static_cast<unsigned long long*>(ptr);
+        st.ready = true;
+    }
+    FusedLinearParams p{};
+    p.w2t = reinterpret_cast<const uint8_t*>(input1);
+    p.N = N; p.K = K; p.M = M;
+    p.src = kSrcQuantized; p.out_kind = kOutBf16;
+    plan_linear(p, st.n_sm);
+    if (fused_linear_smem(p) > (size_t)st.smem_optin) return set_status(kTooLarge), kTooLarge;
+    p.yq = input0; p.ldy = K;
+    p.a_q_bf16 = static_cast<const __nv_bfloat16*>(s);
+    p.out = static_cast<__nv_bfloat16*>(output0); p.ldo = N;
+    p.ws_dev_bf16 = static_cast<const __nv_bfloat16*>(ws);
+    // row segments of the reference's shape ladder (gpu/bitnet_kernels/bitnet_kernels.cu:4-33)
+    int ws_num = 1;
+    if (N == 3840 && K == 2560) ws_num = 3;
+    else if ((N == 13824 && K == 2560) || (N == 20480 && K == 3200)) ws_num = 2;
+    else if (N == 4800 && K == 3200) ws_num = 6;
+    p.seg.n_seg = ws_num;
+    for (int i = 0; i < 8; ++i) p.seg.end[i] = i < ws_num ? (N / ws_num) * (i + 1) : N;
+    p.acc_scratch = st.scratch;
+    p.error_flag = reinterpret_cast<int*>(st.scratch + kStaticSlots);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the last call left; the slots this call uses must start at zero.
+    if (check_cuda(cudaMemsetAsync(st.scratch, 0, (size_t)(N / 16) * 128 * sizeof(unsigned long long), cs)))
+        return kCudaError;
+    return launch_fused_linear(p, cs, false);
+}
+

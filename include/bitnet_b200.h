@@ -56,6 +56,25 @@ int bitnet_init(void);
 void bitlinear_int8xint2(int8_t* input0, int8_t* input1, void* output0, void* s, void* ws,
                          int M, int N, int K, void* stream);
 
+/* ---- the same entry point for callers that must not allocate device memory ------------
+ * No counterpart in the reference.  Some hosts cannot call cudaMalloc at the point where
+ * they run a BitLinear: a plugin that executes inside another framework's captured CUDA
+ * graph or under its own memory-pool accounting, a real-time loop that forbids driver
+ * allocations after start-up, a process that runs with the device memory fully
+ * pre-assigned.  The other entry points for M <= 8 take their split-K scratch from a
+ * workspace that bitnet_init() (or their first call) allocates; this one takes it from a
+ * 1 MB array compiled into the library, which every GPU that loads the library holds until
+ * the process exits.  It calls no cudaMalloc, cudaFree or other allocating routine.
+ * Same arguments, arithmetic and row-segment rule as bitlinear_int8xint2, with these limits:
+ * 1 <= M <= 8, N % 16 == 0, N <= 16384, K % 128 == 0, and M, K small enough for the kernel's
+ * shared memory (status BITNET_STATUS_TOO_LARGE otherwise, nothing is launched).
+ * The first call on a device looks up the array's device address and configures the kernel;
+ * make that call before any stream capture.  All calls share the one array: calls that
+ * overlap on the GPU (different streams without ordering, or different host threads) race;
+ * keep them on one stream per device.  Returns 0 or a BITNET_STATUS_* code. */
+int bitlinear_int8xint2_noalloc(int8_t* input0, int8_t* input1, void* output0, void* s, void* ws,
+                                int M, int N, int K, void* stream);
+
 /* ---- the same operation with explicit arguments ---------------------------------------
  * Serves gpu/model.py:54-75 (BitLinearKernel.forward) with the row segments stated by the
  * caller instead of guessed from the shape (for the fused wqkv the segments are the q, k
