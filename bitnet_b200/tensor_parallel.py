@@ -1,0 +1,249 @@
+"""Tensor-parallel BitNet decoder: one process per GPU, `torch.distributed` for the exchange.
+
+The reference has no multi-GPU path (gpu/generate.py:324-326 fixes local_rank = 0); this is
+the partition its fused layout invites (gpu/model.py:103-118 names the per-rank head counts
+`n_local_heads` / `n_local_kv_heads`):
+
+* column-parallel `wqkv` (each rank owns n_heads/tp query heads and n_kv_heads/tp key/value
+  heads, with their slice of the KV cache) and `w13` (each rank owns ffn/tp gate rows and the
+  matching up rows): no exchange, the input is replicated;
+* row-parallel `wo` and `w2` (each rank owns a K slice of the weight).  The input of a
+  row-parallel BitLinear passes through an RMSNorm and an absmax over the *whole* vector
+  (gpu/model.py:159-160, 195-196), so the local slices are first **all-gathered** (a few KB
+  per token) and every rank quantises the whole vector, exactly as a single GPU would; it
+  then multiplies only its K slice and the exact int32 partial sums are **all-reduced**.
+  Integer sums do not depend on the order of addition, so the result is bit-identical to
+  the single-GPU result for every tp.
+* the output projection is split over the vocabulary; the greedy choice is an all-gather of
+  one (value, index) pair per rank.
+
+Per layer: 2 all-gathers + 2 all-reduces.  `backend="torch"` runs the same algebra with
+plain PyTorch BitLinear arithmetic (for CPU tests under gloo); `backend="kernel"` uses the
+library's kernels.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.nn import functional as F
+
+from .model import ModelArgs, RMSNorm, apply_rope, quant_weight_int8, rope_table, squared_relu
+
+
+def _seed(seed: int, layer: int, which: int, part: int) -> int:
+    """The seed build_synthetic uses for sub-matrix `part` of BitLinear `which` of `layer`."""
+    return seed * 1000003 + (100 + layer * 4 + which) * 8 + part
+
+
+def _ternary_rows(n: int, k: int, s: int, device, rows: slice, cols: slice = slice(None)):
+    """Rows/columns of the ternarised N(0,1) matrix with seed s.  The whole matrix is drawn and
+    ternarised first: its scale is the scale of the full tensor (gpu/convert_checkpoint.py:23-27)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(s)
+    q, scale = quant_weight_int8(torch.randn((n, k), generator=gen, device=device, dtype=torch.float32))
+    return q[rows, cols].contiguous(), scale
+
+
+class _Linear:
+    """One BitLinear shard.  `cols` = (k0, k1) for a row-parallel shard (it multiplies columns
+    k0..k1 of the quantised input), None for a column-parallel one."""
+
+    def __init__(self, parts, scales, in_features: int, backend: str, cols: Optional[Tuple[int, int]] = None):
+        self.backend, self.cols, self.in_features = backend, cols, in_features
+        self.segments = [p.shape[0] for p in parts]
+        self.n = sum(self.segments)
+        self.k_local = parts[0].shape[1]
+        ends, acc = [], 0
+        for s in self.segments:
+            acc += s
+            ends.append(acc)
+        self.seg_end = ends
+        dev = parts[0].device
+        self.scale = torch.stack([s.reshape(()).float() for s in scales]).to(dev)          # f32 [n_seg]
+        self.row_scale = torch.cat([s.float().reshape(1).expand(p.shape[0]) for p, s in zip(parts, scales)]).to(dev)
+        q = torch.cat(list(parts), dim=0)
+        if backend == "kernel":
+            from . import pack_weight
+            self.weight = pack_weight.convert_weight_int8_to_int2(q)
+        else:
+            self.ternary = q.float()
+
+    def quantize(self, x: torch.Tensor, norm: Optional[RMSNorm]):
+        """x bf16 [M, K] over the full K.  Returns the backend's quantised activations."""
+        if self.backend == "kernel":
+            from . import ops
+            return ops.quant_input(x, None if norm is None else norm.weight, 0.0 if norm is None else norm.eps)
+        xf = (norm(x) if norm is not None else x).float()
+        a = 127.0 / xf.abs().amax(dim=-1).clamp_(min=1e-5)
+        return (xf * a[:, None]).round().clamp(-128, 127), a, None
+
+    def accumulate(self, quantised) -> torch.Tensor:
+        """Exact sum_k y[m,k] * w[n,k] over this shard's columns: int32 (kernel) or f32 holding
+        exact integers (torch)."""
+        y, a, ysum = quantised
+        k0, k1 = self.cols if self.cols is not None else (0, self.in_features)
+        if self.backend == "kernel":
+            from . import ops
+            ys = y[:, k0:] if self.cols is not None else y
+            return ops.linear_w2a8(ys, None, ysum if self.cols is None else None, self.weight, None, [self.n], self.n,
+                                   k1 - k0, want_acc=True, want_out=False)
+        assert (k1 - k0) * 128 < (1 << 24)
+        return F.linear(y[:, k0:k1], self.ternary)
+
+    def rescale(self, acc: torch.Tensor, a: torch.Tensor) -> torch.Tensor:
+        """bf16(acc / a * ws), the order of gpu/bitnet_kernels/bitnet_kernels.h:82."""
+        return (acc.float() / a[:, None] * self.row_scale).to(torch.bfloat16)
+
+    def __call__(self, x: torch.Tensor, norm: Optional[RMSNorm]) -> torch.Tensor:
+        qz = self.quantize(x, norm)
+        return self.rescale(self.accumulate(qz), qz[1])
+
+
+class TPDecoder:
+    """The decoder of `model.Transformer`, sharded over `world` ranks.  With world == 1 it
+    computes exactly what `model.build_synthetic(args, seed)` computes."""
+
+    def __init__(self, args: ModelArgs, seed: int, rank: int, world: int, device, backend: str = "kernel",
+                 max_seq_len: int = 4096, group=None):
+        assert args.n_heads % world == 0 and args.n_kv_heads % world == 0, "heads must divide by the tp degree"
+        assert args.ffn_dim % world == 0 and args.vocab_size % world == 0
+        D = args.head_dim
+        self.args, self.rank, self.world, self.device, self.group, self.backend = args, rank, world, device, group, backend
+        self.Hl, self.Hkvl = args.n_heads // world, args.n_kv_heads // world
+        Fl = args.ffn_dim // world
+        if backend == "kernel":
+            assert (self.Hl * D) % 128 == 0 and Fl % 128 == 0, "K slices must be multiples of the 128-column tile"
+        gen = torch.Generator(device=device)
+
+        def bf16_randn(shape, s):
+            gen.manual_seed(s)
+            return torch.randn(shape, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+
+        self.emb = bf16_randn((args.vocab_size, args.dim), seed * 1000003 + 1)
+        out_w = self.emb if args.tie_embeddings else bf16_randn((args.vocab_size, args.dim), seed * 1000003 + 2)
+        Vl = args.vocab_size // world
+        self.out_w = out_w[rank * Vl:(rank + 1) * Vl].contiguous()
+        self.vocab_lo = rank * Vl
+        self.final_norm = RMSNorm(args.dim, args.norm_eps).to(device)
+        self.layers = []
+        r = rank
+        for i in range(args.n_layers):
+            qs, ks = slice(r * self.Hl * D, (r + 1) * self.Hl * D), slice(r * self.Hkvl * D, (r + 1) * self.Hkvl * D)
+            q_p, s_q = _ternary_rows(args.n_heads * D, args.dim, _seed(seed, i, 0, 0), device, qs)
+            k_p, s_k = _ternary_rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 1), device, ks)
+            v_p, s_v = _ternary_rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 2), device, ks)
+            wo_p, s_o = _ternary_rows(args.dim, args.n_heads * D, _seed(seed, i, 1, 0), device, slice(None), qs)
+            fs = slice(r * Fl, (r + 1) * Fl)
+            g_p, s_1 = _ternary_rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 0), device, fs)
+            u_p, s_3 = _ternary_rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 1), device, fs)
+            w2_p, s_2 = _ternary_rows(args.dim, args.ffn_dim, _seed(seed, i, 3, 0), device, slice(None), fs)
+            norms = {}
+            for name, nd in (("attention_norm", args.dim), ("ffn_norm", args.dim), ("attn_sub_norm", args.dim),
+                             ("ffn_sub_norm", args.ffn_dim)):
+                gen.manual_seed(seed * 1000003 + 7 + i)
+                nrm = RMSNorm(nd, args.norm_eps).to(device)
+                nrm.weight.data = (1.0 + 0.1 * torch.randn(nd, generator=gen, device=device)).to(torch.bfloat16)
+                norms[name] = nrm
+            self.layers.append(dict(
+                wqkv=_Linear([q_p, k_p, v_p], [s_q, s_k, s_v], args.dim, backend),
+                wo=_Linear([wo_p], [s_o], args.n_heads * D, backend, cols=(qs.start, qs.stop)),
+                w13=_Linear([g_p, u_p], [s_1, s_3], args.dim, backend),
+                w2=_Linear([w2_p], [s_2], args.ffn_dim, backend, cols=(fs.start, fs.stop)), **norms))
+        self.rope = rope_table(D, max_seq_len, args.rope_theta, device)
+        self.max_seq_len = max_seq_len
+
+    # ---- collectives --------------------------------------------------------------------
+    def _all_gather_cols(self, x: torch.Tensor) -> torch.Tensor:
+        """[M, n_local] per rank -> [M, world * n_local], rank-major columns."""
+        if self.world == 1:
+            return x
+        out = torch.empty((self.world * x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return out.view(self.world, x.shape[0], x.shape[1]).permute(1, 0, 2).reshape(x.shape[0], -1)
+
+    def _all_reduce(self, acc: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.group)
+        return acc
+
+    # ---- model ----------------------------------------------------------------------------
+    def make_cache(self, batch: int, length: int):
+        shape = (batch, length, self.Hkvl, self.args.head_dim)
+        return [(torch.zeros(shape, device=self.device, dtype=torch.bfloat16),
+                 torch.zeros(shape, device=self.device, dtype=torch.bfloat16)) for _ in self.layers]
+
+    def _attention(self, xqkv, cache, pos, T, B, kv_len):
+        Hl, Hkvl, D = self.Hl, self.Hkvl, self.args.head_dim
+        if T == 1 and kv_len is None and self.backend == "kernel":
+            from . import ops
+            return ops.attention_decode(xqkv, pos, self.rope, cache[0], cache[1], Hl, Hkvl, D)
+        xq = xqkv[:, : Hl * D].view(B, T, Hl, D)
+        xk = xqkv[:, Hl * D: (Hl + Hkvl) * D].view(B, T, Hkvl, D)
+        xv = xqkv[:, (Hl + Hkvl) * D:].view(B, T, Hkvl, D)
+        p = pos[:, None] + torch.arange(T, device=xqkv.device)[None, :]
+        cs = self.rope[p]
+        xq, xk = apply_rope(xq, cs), apply_rope(xk, cs)
+        bidx = torch.arange(B, device=xqkv.device)[:, None].expand(B, T)
+        cache[0].index_put_((bidx, p), xk)
+        cache[1].index_put_((bidx, p), xv)
+        L = cache[0].shape[1] if kv_len is None else kv_len
+        mask = torch.arange(L, device=xqkv.device)[None, None, None, :] <= p[:, None, :, None]
+        keys, vals = cache[0][:, :L].transpose(1, 2), cache[1][:, :L].transpose(1, 2)
+        if xq.device.type == "cpu":     # CPU SDPA has no bf16 GQA path everywhere: do it in f32
+            rep = Hl // Hkvl
+            out = F.scaled_dot_product_attention(xq.transpose(1, 2).float(), keys.float().repeat_interleave(rep, 1),
+                                                 vals.float().repeat_interleave(rep, 1), attn_mask=mask)
+            out = out.to(torch.bfloat16)
+        else:
+            out = F.scaled_dot_product_attention(xq.transpose(1, 2), keys, vals, attn_mask=mask, enable_gqa=True)
+        return out.transpose(1, 2).reshape(B * T, Hl * D)
+
+    @torch.no_grad()
+    def hidden(self, tokens: torch.Tensor, pos: torch.Tensor, cache, kv_len: Optional[int] = None) -> torch.Tensor:
+        """tokens int64 [B, T] -> final hidden state bf16 [B*T, dim] (identical on every rank)."""
+        B, T = tokens.shape
+        h = self.emb[tokens.reshape(-1)]
+        for L, c in zip(self.layers, cache):
+            xqkv = L["wqkv"](h, L["attention_norm"])
+            att = self._all_gather_cols(self._attention(xqkv, c, pos, T, B, kv_len))
+            qz = L["wo"].quantize(att, L["attn_sub_norm"])
+            h = h + L["wo"].rescale(self._all_reduce(L["wo"].accumulate(qz)), qz[1])
+            x13 = L["w13"](h, L["ffn_norm"])
+            x1, x3 = x13.chunk(2, -1)
+            inner = self._all_gather_cols(squared_relu(x1) * x3)
+            qz = L["w2"].quantize(inner, L["ffn_sub_norm"])
+            h = h + L["w2"].rescale(self._all_reduce(L["w2"].accumulate(qz)), qz[1])
+        return h
+
+    @torch.no_grad()
+    def logits_local(self, h: torch.Tensor) -> torch.Tensor:
+        x = self.final_norm(h)
+        if x.device.type == "cpu":
+            return F.linear(x.float(), self.out_w.float()).to(torch.bfloat16).float()
+        return F.linear(x, self.out_w).float()
+
+    @torch.no_grad()
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        """Full-vocabulary logits f32 [M, vocab] (gathers the shards; for tests)."""
+        return self._all_gather_cols(self.logits_local(h))
+
+    @torch.no_grad()
+    def greedy(self, h: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row: one (value, index) pair per rank is exchanged."""
+        lg = self.logits_local(h)
+        val, idx = lg.max(dim=-1)
+        if self.world == 1:
+            return idx + self.vocab_lo
+        pair = torch.stack([val, (idx + self.vocab_lo).float()], dim=-1)                # [M, 2]; indices < 2^24
+        allp = torch.empty((self.world * pair.shape[0], 2), dtype=pair.dtype, device=pair.device)
+        dist.all_gather_into_tensor(allp, pair.contiguous(), group=self.group)
+        allp = allp.view(self.world, pair.shape[0], 2)
+        best = allp[..., 0].argmax(dim=0)                                               # first maximum: lowest rank
+        return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].long()
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor, pos: torch.Tensor, cache) -> torch.Tensor:
+        """tokens int64 [B, 1] -> next tokens int64 [B]."""
+        return self.greedy(self.hidden(tokens, pos, cache))
