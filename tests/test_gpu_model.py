@@ -93,8 +93,14 @@ def test_prefill_equals_token_by_token(models):
     pos = torch.zeros(B, dtype=torch.int64, device="cuda")
     full = kern(toks, pos, make_cache(args, B, 128, "cuda"), kv_len=T)
     cache = make_cache(args, B, 128, "cuda")
-    for t in range(T):
-        step = kern(toks[:, t:t + 1], pos + t, cache)
+    for layer in kern.layers:                      # same attention arithmetic on both sides
+        layer.attention.kernel_attention = False
+    try:
+        for t in range(T):
+            step = kern(toks[:, t:t + 1], pos + t, cache)
+    finally:
+        for layer in kern.layers:
+            layer.attention.kernel_attention = True
     assert torch.allclose(step[:, -1], full[:, -1], rtol=0, atol=1e-2 * float(full.abs().max()))
     assert torch.equal(step[:, -1].argmax(-1), full[:, -1].argmax(-1))
 
