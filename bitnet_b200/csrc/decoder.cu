@@ -61,6 +61,11 @@ Workspace* workspace() {
     return &w;
 }
 
+int* workspace_error_flag() {
+    Workspace* w = workspace();
+    return w ? w->error_flag : nullptr;
+}
+
 // BitLinear on caller-quantised activations through the fused kernel (M <= 8).
 int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream) {
     Workspace* w = workspace();

@@ -1,0 +1,342 @@
+// W2A8 BitLinear for M >= 16 tokens (batched decode, prefill) on the 5th-generation tensor
+// cores: tcgen05.mma kind::i8 with the accumulators in tensor memory.  The reference has no
+// counterpart (its GPU kernel takes M == 1 only, gpu/bitnet_kernels/bitnet_kernels.cu:4-36,
+// and its prefill runs in bf16, gpu/generate.py:56-57).
+//
+// D[128 weight rows, TN tokens] += A[128 x 32, u8, K-major] * B[TN x 32, s8, K-major].
+// One CTA owns a 128-row block of the weight matrix and a block of TN tokens and walks K in
+// tiles of 128 columns.  Roles (10 warps):
+//   warp 8   - producer: packed 2-bit weight tiles, global -> shared ring (cp.async.bulk)
+//   warps 0-7 - unpack: warp w turns row group w (16 rows) of the current K tile into int8
+//               operands in the canonical no-swizzle K-major layout, and all of them stage the
+//               int8 activations of the K tile in the same layout
+//   warp 9   - issues the MMAs (one elected lane) and commits them to mbarriers
+//   warps 0-7 - epilogue: tcgen05.ld, fold, rescale, store
+// The 2-bit fields are separated by AND masks only, as in the decode kernel: field j of every
+// byte stays scaled by 4^j and gets its own accumulator (TMEM columns j*TN..), which the
+// epilogue folds with exact shifts.  In the W2T layout field j of lane chunk q covers columns
+// 32q+8j..32q+8j+7 of a K tile, so operand slab j holds those 4 x 8 = 32 columns of A, and
+// the activations are staged with the same column selection.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bitnet {
+
+namespace {
+
+constexpr int kRows = 128;                       // weight rows per CTA (UMMA M)
+constexpr int kWorkerWarps = 8;
+constexpr int kThreadsTc = (kWorkerWarps + 2) * 32;
+constexpr int kPackStages = 3;                   // packed-weight ring
+constexpr int kPackTiles = 4;                    // K tiles per packed stage
+constexpr int kPackStageBytes = 8 * kPackTiles * kTileBytes;   // 16 KB
+constexpr int kOpStages = 3;                     // unpacked operand buffers (one K tile each)
+constexpr int kSlabA = 4096;                     // 128 rows x 32 int8, canonical K-major
+constexpr long long kWaitCyclesTc = 2000000000LL;
+
+struct TcParams {
+    const uint8_t* w2t;
+    const int8_t* y;
+    int64_t ldy;
+    const int32_t* ysum;         // [M] or null (then computed from y on the fly is not offered: required)
+    int32_t* acc_out;            // [M, N] or null
+    __nv_bfloat16* out;          // [M, ldo] or null
+    int64_t ldo;
+    const float* a_f32;
+    const __nv_bfloat16* a_bf16;
+    const float* ws_f32;
+    const __nv_bfloat16* ws_bf16;
+    ScaleSegments seg;
+    int M, N, K, k_tiles, n_rowgroups;
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after about a second; `abort_flag` (shared) makes everybody else give up too.
+__device__ __noinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (bar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!bar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCyclesTc) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+// Shared memory operand descriptor: K-major, no swizzle.  Core matrices (8 rows x 16 bytes)
+// are 128 contiguous bytes; the two core matrices along K are `lbo` bytes apart, 8-row
+// groups `sbo` bytes apart.  Bits: [0,14) address >> 4, [16,30) lbo >> 4, [32,46) sbo >> 4,
+// [46,48) descriptor version 1 (sm_100), [61,64) swizzle mode 0.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+// Instruction descriptor for kind::i8: D s32 (bits 4-5 = 2), A u8 (bits 7-9 = 0), B s8
+// (bits 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(int m, int n) {
+    return (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+template <int TN>
+struct TcSmem {
+    static constexpr int kSlabB = TN * 32;                              // TN tokens x 32 int8
+    static constexpr int kOpBytes = 4 * kSlabA + 4 * kSlabB;            // one operand buffer (4 fields)
+    static constexpr int kPackOff = 0;
+    static constexpr int kOpOff = kPackStages * kPackStageBytes;
+    static constexpr int kBarOff = kOpOff + kOpStages * kOpBytes;
+    static constexpr int kBytes = kBarOff + 256;
+};
+
+template <int TN>
+__global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcParams p) {
+    using S = TcSmem<TN>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* pack = smem + S::kPackOff;
+    uint8_t* ops = smem + S::kOpOff;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
+    uint64_t* wfull = bars;                       // [kPackStages] packed stage filled (tx bytes)
+    uint64_t* wempty = bars + kPackStages;        // [kPackStages] packed stage consumed (8 warps)
+    uint64_t* ofull = bars + 2 * kPackStages;     // [kOpStages] operands written (8 warps)
+    uint64_t* oempty = ofull + kOpStages;         // [kOpStages] operands consumed (tcgen05.commit)
+    uint64_t* accfull = oempty + kOpStages;       // accumulators complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rb = blockIdx.x;                    // 128-row block
+    const int tok0 = blockIdx.y * TN;
+    const int k_tiles = p.k_tiles;
+    const int rg0 = rb * 8;                       // first row group of the block
+    const int n_rg = min(8, p.n_rowgroups - rg0); // row groups that exist
+
+    if (tid == 0) {
+        for (int s = 0; s < kPackStages; ++s) {
+            bar_init(&wfull[s], 1);
+            bar_init(&wempty[s], kWorkerWarps);
+        }
+        for (int s = 0; s < kOpStages; ++s) {
+            bar_init(&ofull[s], kWorkerWarps);
+            bar_init(&oempty[s], 1);
+        }
+        bar_init(accfull, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 9) {   // the MMA warp owns the tensor memory: 4 fields x TN columns
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)),
+                     "r"(4 * TN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_pack = (k_tiles + kPackTiles - 1) / kPackTiles;
+
+    if (warp == 8) {
+        // ---- producer ---------------------------------------------------------------------
+        if (lane == 0) {
+            for (int c = 0; c < n_pack; ++c) {
+                const int s = c % kPackStages;
+                if (c >= kPackStages && !bar_wait(&wempty[s], ((c / kPackStages) - 1) & 1, abort_flag)) break;
+                const int kt0 = c * kPackTiles, nt = min(kPackTiles, k_tiles - kt0);
+                bar_expect_tx(&wfull[s], (uint32_t)(n_rg * nt * kTileBytes));
+                for (int r = 0; r < n_rg; ++r)
+                    bulk_load(pack + s * kPackStageBytes + r * kPackTiles * kTileBytes,
+                              p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt0) * kTileBytes, (uint32_t)(nt * kTileBytes),
+                              &wfull[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issue ----------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(kRows, TN);
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int b = kt % kOpStages;
+                if (!bar_wait(&ofull[b], (kt / kOpStages) & 1, abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t base = smem_addr(ops + b * S::kOpBytes);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint64_t da = umma_desc(base + j * kSlabA, 128, 256);
+                    const uint64_t db = umma_desc(base + 4 * kSlabA + j * S::kSlabB, 128, 256);
+                    umma_i8(tmem_base + j * TN, da, db, idesc, kt > 0);
+                }
+                umma_commit(&oempty[b]);           // frees the operand buffer when these MMAs retire
+            }
+            umma_commit(accfull);
+        }
+    } else {
+        // ---- unpack + activation staging ------------------------------------------------------
+        const int g = lane >> 2, q = lane & 3;
+        const int wtid = tid;                      // 0..255 among the workers
+        for (int kt = 0; kt < k_tiles; ++kt) {
+            const int c = kt / kPackTiles, s = c % kPackStages, ktl = kt - c * kPackTiles;
+            const int b = kt % kOpStages;
+            if (ktl == 0 && !bar_wait(&wfull[s], (c / kPackStages) & 1, abort_flag)) break;
+            if (kt >= kOpStages && !bar_wait(&oempty[b], ((kt / kOpStages) - 1) & 1, abort_flag)) break;
+            uint8_t* opb = ops + b * S::kOpBytes;
+            if (warp < n_rg) {
+                const uint4 wv = *reinterpret_cast<const uint4*>(pack + s * kPackStageBytes +
+                                                                 (warp * kPackTiles + ktl) * kTileBytes + lane * 16);
+                const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t msk = 0x03030303u << (2 * j);
+#pragma unroll
+                    for (int rs = 0; rs < 2; ++rs) {
+                        // row 16*warp + g + 8*rs, field-j columns 8q + 4h + b: words rs (h=0), rs+2 (h=1)
+                        const uint2 v = make_uint2(w[rs] & msk, w[rs + 2] & msk);
+                        *reinterpret_cast<uint2*>(opb + j * kSlabA + (2 * warp + rs) * 256 + (q >> 1) * 128 + g * 16 +
+                                                  (q & 1) * 8) = v;
+                    }
+                }
+            }
+            // activations: TN tokens x 128 bytes of this K tile, 16 bytes per piece
+#pragma unroll
+            for (int i = 0; i < (TN * 8) / 256; ++i) {
+                const int piece = wtid + i * 256;
+                const int t = piece >> 3, c16 = piece & 7;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (tok0 + t < p.M) v = *reinterpret_cast<const uint4*>(p.y + (int64_t)(tok0 + t) * p.ldy + kt * kTileCols + c16 * 16);
+                const int qq = c16 >> 1, j0 = (c16 & 1) * 2;   // bytes 0-7: field j0, bytes 8-15: field j0+1
+                uint8_t* dst = opb + 4 * kSlabA + (t >> 3) * 256 + (qq >> 1) * 128 + (t & 7) * 16 + (qq & 1) * 8;
+                *reinterpret_cast<uint2*>(dst + j0 * S::kSlabB) = make_uint2(v.x, v.y);
+                *reinterpret_cast<uint2*>(dst + (j0 + 1) * S::kSlabB) = make_uint2(v.z, v.w);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> tensor core reads
+            __syncwarp();
+            if (lane == 0) {
+                bar_arrive(&ofull[b]);
+                if (ktl == kPackTiles - 1 || kt == k_tiles - 1) bar_arrive(&wempty[s]);
+            }
+        }
+
+        // ---- epilogue: warp w reads TMEM lanes 32*(w%4).., token half w/4 ----------------------
+        if (bar_wait(accfull, 0, abort_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int lane_blk = warp & 3, half = warp >> 2;
+            const int row = rb * kRows + lane_blk * 32 + lane;
+            const int sg = segment_of(p.seg, row < p.N ? row : 0);
+            const float ws = p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
+            for (int cb = half * (TN / 2); cb < (half + 1) * (TN / 2); cb += 16) {
+                int c0[16], c1[16], c2[16], c3[16];
+                const uint32_t ta = tmem_base + ((uint32_t)(lane_blk * 32) << 16) + cb;
+                tmem_ld16(ta, c0);
+                tmem_ld16(ta + TN, c1);
+                tmem_ld16(ta + 2 * TN, c2);
+                tmem_ld16(ta + 3 * TN, c3);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int tok = tok0 + cb + e;
+                    if (tok < p.M && row < p.N) {
+                        const int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6) - p.ysum[tok];
+                        if (p.acc_out) p.acc_out[(int64_t)tok * p.N + row] = v;
+                        if (p.out) {
+                            const float a = p.a_f32 ? p.a_f32[tok] : __bfloat162float(p.a_bf16[tok]);
+                            p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / a * ws);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(4 * TN) : "memory");
+    }
+    if (tid == 0 && *abort_flag) atomicExch(p.error_flag, 3);
+}
+
+template <int TN>
+cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(w2a8_gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TcSmem<TN>::kBytes + 1024);
+    if (e != cudaSuccess) return e;
+    const dim3 grid((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN));
+    w2a8_gemm_tc_kernel<TN><<<grid, kThreadsTc, TcSmem<TN>::kBytes + 1024, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// y must be 16-byte aligned with ldy % 16 == 0 and readable up to ceil128(K) columns (zero
+// filled beyond K); ysum is required.
+int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, cudaStream_t stream) {
+    TcParams p{};
+    p.w2t = static_cast<const uint8_t*>(a.w2t);
+    p.y = a.y; p.ldy = a.ldy; p.ysum = a.ysum;
+    p.acc_out = a.acc_out; p.out = a.out; p.ldo = a.ldo;
+    p.a_f32 = a.a_f32; p.a_bf16 = a.a_bf16; p.ws_f32 = a.ws_f32; p.ws_bf16 = a.ws_bf16;
+    p.seg = a.seg;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.k_tiles = (a.K + kTileCols - 1) / kTileCols;
+    p.n_rowgroups = (a.N + 15) / 16;
+    p.error_flag = error_flag;
+    cudaError_t e;
+    if (a.M <= 32) e = launch_tc<32>(p, stream);
+    else if (a.M <= 64) e = launch_tc<64>(p, stream);
+    else e = launch_tc<128>(p, stream);
+    return check_cuda(e);
+}
+
+}  // namespace bitnet

@@ -183,6 +183,15 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
     // the direct-load kernel below (for comparisons).
     static const bool direct = getenv("BITNET_GEMV_DIRECT") != nullptr;
     if (a.M <= 8 && !direct && a.K % 8 == 0) return fused_linear_quantized(a, stream);
+    // Larger batches go to the tcgen05 kernel when the activations are laid out for it.
+    static const bool no_tc = getenv("BITNET_NO_TCGEN05") != nullptr;
+    const int64_t k_pad = (a.K + kTileCols - 1) / kTileCols * kTileCols;
+    if (a.M >= 16 && !no_tc && a.ysum && a.ldy % 16 == 0 && a.ldy >= k_pad &&
+        (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+        int* flag = workspace_error_flag();
+        if (!flag) return kCudaError;
+        return w2a8_gemm_tc(a, flag, stream);
+    }
     GemvParams p;
     p.w = reinterpret_cast<const uint4*>(a.w2t);
     p.y = a.y; p.ldy = a.ldy; p.ysum = a.ysum;

@@ -26,6 +26,10 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream);
 // The same for M <= 8 through the fused decode kernel (bulk-copy weight staging, even
 // tile split); uses the per-device workspace.
 int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream);
+// M >= 16 on tcgen05 (gemm_tc.cu).  Needs ysum, 16-byte aligned y rows padded with zeros to a
+// multiple of 128 columns; error_flag is a device word set when a bounded wait gave up.
+int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, cudaStream_t stream);
+int* workspace_error_flag();
 
 // Packers (all buffers on the device).
 int pack_ternary_to_w2t(const int8_t* q, void* w2t, int N, int K, cudaStream_t stream);

@@ -257,3 +257,22 @@ def test_rmsnorm_quant_close_to_oracle(bn):
     assert d.max() <= 1 and (d != 0).mean() < 0.01   # rsqrt rounding may move a value across a .5 boundary
     assert np.allclose(ga.cpu().numpy(), a, rtol=1e-2)
     assert np.array_equal(gs.cpu().numpy(), gy.cpu().numpy().astype(np.int32).sum(-1))
+
+
+# ---------------------------------------------------------------------------- tcgen05 path (M >= 16)
+
+
+@pytest.mark.parametrize("n,k,m", [(2560, 2560, 16), (3840, 2560, 33), (48, 384, 64), (2560, 6912, 100),
+                                    (13824, 2560, 128), (272, 200, 130), (2560, 2560, 300)])
+def test_tensor_core_path_int32_exact_and_bf16(bn, port_lib, n, k, m):
+    """Batches of 16 and more tokens with padded activations and their sums go to the tcgen05
+    kernel; its int32 sums are exact and its bf16 outputs equal the oracle's."""
+    q, ws, x, y, a, ysum, acc = _oracle_case(n, k, m, seed=11 * n + m, port_lib=port_lib)
+    w2t = bn.pack.convert_weight_int8_to_int2(_dev(q))
+    gy, ga, gs = bn.ops.quant_input(_dev(x).bfloat16())            # padded to 128 columns, with sums
+    assert np.array_equal(gy.cpu().numpy()[:, :k], y)
+    wsd = _dev(np.array([ws], dtype=np.float32))
+    out, got = bn.ops.linear_w2a8(gy, ga, gs, w2t, wsd, [n], n, k, want_acc=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), acc)
+    assert np.array_equal(out.float().cpu().numpy(), O.to_bf16(O.rescale(acc, a, [ws])))
