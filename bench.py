@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--workload", default="2b", help="architecture preset (2b, 3b, 8b, 100b)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
     return ap.parse_args()
 
 
@@ -175,6 +176,91 @@ def run_reference(a, args_model):
         "gpu_launches": 0, "wall_s": time.time() - t0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------
+# extra measurements reported beside the headline (rank 0, one GPU)
+# ----------------------------------------------------------------------------------------
+def kernel_sweep(dev, peak_gbs):
+    """The isolated BitLinear call over the 2B shapes and M in {1..2048}: quantised
+    activations in, bf16 out, through bitnet_linear_w2a8; distinct weight buffers (> 2 x L2)
+    cycled inside a CUDA graph, time per launch from CUDA events."""
+    import ctypes
+
+    import torch
+
+    from bitnet_b200 import _lib
+
+    L = _lib.lib
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(1)
+    stream = torch.cuda.Stream(device=dev)
+    for n, k in [(3840, 2560), (2560, 2560), (13824, 2560), (2560, 6912)]:
+        nbytes = n * k // 4
+        copies = max(2, int(300e6 // nbytes))
+        ws = [torch.randint(-128, 127, (n, k // 4), dtype=torch.int8, device=dev, generator=g) for _ in range(copies)]
+        for m in (1, 8, 32, 128, 512, 2048):
+            y = torch.randint(-127, 127, (m, k), dtype=torch.int8, device=dev, generator=g)
+            a = torch.ones(m, device=dev)
+            ysum = y.int().sum(-1).int()
+            wsc = torch.ones(1, device=dev)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            seg = (ctypes.c_int * 1)(n)
+            reps = copies if m <= 128 else max(2, copies // 8)
+
+            def run():
+                st = _lib.stream_ptr()
+                for w in ws[:reps]:
+                    L.bitnet_linear_w2a8(_lib.ptr(y), k, _lib.ptr(w), _lib.ptr(out), n, None, _lib.ptr(a), _lib.ptr(ysum),
+                                         _lib.ptr(wsc), seg, 1, m, n, k, st)
+
+            with torch.cuda.stream(stream):
+                run()
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    run()
+                for _ in range(3):
+                    graph.replay()
+                stream.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(3):
+                    graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
+            rows.append({"N": n, "K": k, "M": m, "us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1),
+                         "hbm_frac": round(nbytes / us / 1e3 / peak_gbs, 4), "tops": round(2.0 * m * n * k / us / 1e6, 1)})
+        del ws
+    return rows
+
+
+def decode_batch(model, args_model, dev, batch, steps, warmup):
+    """Decode tokens/s at a larger batch through the op-by-op path (tcgen05 BitLinear kernel,
+    library attention), captured in a CUDA graph; device-resident."""
+    import torch
+
+    from bitnet_b200.generate import Generator
+
+    max_seq = (PROMPT_LEN + steps + warmup + 64 + 127) // 128 * 128
+    gen = Generator(model, batch, max_seq)
+    g = torch.Generator(device=dev).manual_seed(SEED + 5)
+    prompt = torch.randint(0, args_model.vocab_size, (batch, PROMPT_LEN), generator=g, device=dev)
+    gen.prefill(prompt)
+    gen.capture()
+    with torch.cuda.stream(gen.stream):
+        for _ in range(warmup):
+            gen.decode_step()
+        gen.stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(gen.stream)
+        for _ in range(steps):
+            gen.decode_step()
+        e1.record(gen.stream)
+        gen.stream.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"batch": batch, "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "steps": steps}
 
 
 # ----------------------------------------------------------------------------------------
@@ -307,6 +393,13 @@ def run_ours(a, args_model):
     if world == 1 and not a.no_cpu_baseline:
         tok_s, info, _ = cpu_i2s_tokens_per_s(args_model, B, steps=3, warmup=1, layers_sampled=min(args_model.n_layers, 4))
         cpu = dict(info, value=tok_s, unit="tok/s")
+    extras = {}
+    if world == 1 and not a.no_extras:
+        try:
+            extras["decode_bs64"] = decode_batch(model, args_model, dev, 64, steps=min(K, 16), warmup=3)
+            extras["kernel_sweep"] = kernel_sweep(dev, peak)
+        except Exception as exc:   # the headline stands on its own
+            extras["extras_error"] = repr(exc)[:300]
     n_lin = len(lins)
     # every byte a decode step must read: packed BitLinear weights + the bf16 output projection
     step_bytes = weight_bytes + 2 * args_model.vocab_size * args_model.dim
@@ -330,7 +423,7 @@ def run_ours(a, args_model):
                      "bytes_per_launch": weight_bytes / n_lin, "us_per_launch": 1e3 * ms_lin / n_lin,
                      "step_bytes": step_bytes, "step_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
                      "step_frac": step_bytes / (ms / K * 1e-3) / 1e9 / peak},
-        "cpu_baseline": cpu, "clocks": clocks,
+        "cpu_baseline": cpu, "clocks": clocks, **extras,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:

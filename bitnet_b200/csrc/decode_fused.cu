@@ -94,16 +94,6 @@ __device__ __noinline__ float lin_out(int acc, float a, float ws) { return bf16_
 struct ConsumerSync {
     __device__ __forceinline__ void operator()() const { consumer_sync(); }
 };
-// Out of line on purpose (code size): sum / max over the 256 consumer threads.
-__device__ __noinline__ float consumer_reduce(float v, bool is_max, float* scratch, int tid) {
-    return reduce_256(v, is_max, scratch, tid, ConsumerSync());
-}
-struct ConsumerReduce {   // reduction functor handed to the shared prologue
-    __device__ __forceinline__ float operator()(float v, bool is_max, float* scratch, int tid) const {
-        return consumer_reduce(v, is_max, scratch, tid);
-    }
-};
-
 // CTA that owns tile t under the even split (tiles_base + 1 tiles for the first tiles_rem CTAs).
 __device__ __forceinline__ int cta_of_tile(const FusedLinearParams& p, int t) {
     const int big = p.tiles_rem * (p.tiles_base + 1);
@@ -125,8 +115,9 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* empty_bar = full_bar + kStages;
-    float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 8 floats
-    int* ysum_s = reinterpret_cast<int*>(scratch + 8);                         // 8 ints
+    float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 16 floats
+    float* sy_part = scratch + 16;                                             // [8 tokens][8 warps]
+    int* ysum_s = reinterpret_cast<int*>(sy_part + 64);                        // 8 ints
     float* a_s = reinterpret_cast<float*>(ysum_s + 8);                         // 8 floats
     int* flag_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (1 used)
     int* sacc = flag_s + 8;                                                    // [r_max][16][8]
@@ -205,8 +196,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
 #pragma unroll 1
     for (int m = 0; m < p.M; ++m) {
         int8_t* ym = ys + (size_t)m * y_stride;
-        float a;
-        int ysum;
+        float a, sy_warp;
         if (p.src == kSrcQuantized) {
             const int8_t* row = p.yq + (int64_t)m * p.ldy;
             const bool vec_ok = aligned16(p.yq, p.ldy, 1);
@@ -228,8 +218,9 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
                 sy += (float)(__dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) +
                               __dp4a((int)u.z, 0x01010101, 0) + __dp4a((int)u.w, 0x01010101, 0));
             }
-            if (!p.ysum_q) sy = consumer_reduce(sy, false, scratch, tid);
-            ysum = p.ysum_q ? p.ysum_q[m] : (int)sy;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
+            sy_warp = p.ysum_q ? (warp == 0 ? (float)p.ysum_q[m] : 0.f) : sy;
             a = p.a_q ? p.a_q[m] : (p.a_q_bf16 ? __bfloat162float(p.a_q_bf16[m]) : 1.f);
         } else {
             // stage the source row(s) with asynchronous 16-byte copies, all in flight at once
@@ -259,14 +250,19 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
                 for (int v = tid; v < n_vec; v += kConsumerThreads)
                     *reinterpret_cast<uint4*>(p.h_copy + (int64_t)m * p.K + v * 8) = *reinterpret_cast<const uint4*>(xv + v * 8);
             }
-            norm_quant_row(xv, p.K, k_pad, use_gamma ? gs : nullptr, p.eps, ym, scratch, tid, ConsumerReduce(), a, ysum);
+            norm_quant_row(xv, p.K, k_pad, use_gamma ? gs : nullptr, p.eps, ym, scratch, tid, ConsumerSync(), a, sy_warp);
         }
-        if (tid == 0) {
-            ysum_s[m] = ysum;
-            a_s[m] = a;
-        }
-        consumer_sync();   // xv is reused by the next token; ys, ysum_s, a_s are complete
+        if (lane == 0) sy_part[m * 8 + warp] = sy_warp;
+        if (tid == 0) a_s[m] = a;
+        consumer_sync();   // xv is reused by the next token; ys, sy_part, a_s are complete
     }
+    if (tid < p.M) {       // sum(y) per token: the eight warp sums are exact integers
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) t += sy_part[tid * 8 + w];
+        ysum_s[tid] = (int)t;
+    }
+    consumer_sync();
 
     stamp(3);
     // ---- matmul over the staged tiles ----------------------------------------------------
@@ -684,7 +680,7 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const Head
         for (int i = 0; i < kHeadThreads / 32; ++i) tot += scratch[i];
         const float rinv = rsqrtf(tot / (float)p.K + p.eps);
         for (int k = tid; k < p.K; k += kHeadThreads)
-            xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * rinv * __bfloat162float(p.gamma[k]));
+            xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * __bfloat162float(p.gamma[k]) * rinv);
     }
     __syncthreads();
 
@@ -824,7 +820,7 @@ void plan_linear(FusedLinearParams& p, int n_sm) {
 
 size_t fused_linear_smem(const FusedLinearParams& p) {
     const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
-    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + 8 * 4 * 4 + (size_t)p.r_max * 128 * 4 +
+    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + (16 + 64 + 8 * 3) * 4 + (size_t)p.r_max * 128 * 4 +
            (p.src == kSrcQuantized ? 0 : (size_t)p.K_even * 6) + (size_t)(p.M + 1) * y_stride + 128;
 }
 

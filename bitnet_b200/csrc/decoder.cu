@@ -32,6 +32,8 @@ struct Workspace {
     float* attn_part = nullptr;                   // attention split partials, grown on demand
     size_t attn_part_bytes = 0;
     int* attn_counters = nullptr;                 // [4096]
+    int32_t* tc_acc = nullptr;                    // split-K sums of the tcgen05 kernel, zero between launches
+    size_t tc_acc_ints = 0;
 };
 
 static Workspace g_ws[kMaxDevices];
@@ -51,19 +53,24 @@ Workspace* workspace() {
     w.smem_optin = prop.sharedMemPerBlockOptin;
     const size_t acc_bytes = (size_t)kWsRowGroups * 128 * 8, ctr_bytes = 0;
     uint8_t* base = nullptr;
-    const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256;
+    const size_t tc_ints = (size_t)4 << 20;    // 16 MB: up to 128 tokens x 32768 rows
+    const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256 + tc_ints * 4;
     if (check_cuda(cudaMalloc(&base, total)) || check_cuda(cudaMemset(base, 0, total))) return nullptr;
     w.acc_scratch = reinterpret_cast<unsigned long long*>(base);
     w.attn_counters = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes);
     w.error_flag = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes + 4096 * 4);
+    w.tc_acc = reinterpret_cast<int32_t*>(base + acc_bytes + ctr_bytes + 4096 * 4 + 256);
+    w.tc_acc_ints = tc_ints;
     if (prepare_fused_kernels(w.smem_optin, 96 * 1024, w.smem_optin)) return nullptr;
     w.ready = true;
     return &w;
 }
 
-int* workspace_error_flag() {
+bool workspace_view(WorkspaceView* out) {
     Workspace* w = workspace();
-    return w ? w->error_flag : nullptr;
+    if (!w) return false;
+    *out = WorkspaceView{w->error_flag, w->tc_acc, w->tc_acc_ints, w->n_sm};
+    return true;
 }
 
 // BitLinear on caller-quantised activations through the fused kernel (M <= 8).

@@ -50,6 +50,8 @@ struct TcParams {
     const __nv_bfloat16* ws_bf16;
     ScaleSegments seg;
     int M, N, K, k_tiles, n_rowgroups;
+    int k_splits;                // grid.z: CTAs that share an output tile and add into acc_ws
+    int32_t* acc_ws;             // [M, N] zero-initialised int32 work space (k_splits > 1)
     int* error_flag;
 };
 
@@ -159,6 +161,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     const int k_tiles = p.k_tiles;
     const int rg0 = rb * 8;                       // first row group of the block
     const int n_rg = min(8, p.n_rowgroups - rg0); // row groups that exist
+    // this CTA's share of K: tiles [kt_lo, kt_lo + nk)
+    const int kt_lo = (int)((int64_t)p.k_tiles * blockIdx.z / p.k_splits);
+    const int nk = (int)((int64_t)p.k_tiles * (blockIdx.z + 1) / p.k_splits) - kt_lo;
 
     if (tid == 0) {
         for (int s = 0; s < kPackStages; ++s) {
@@ -185,7 +190,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    const int n_pack = (k_tiles + kPackTiles - 1) / kPackTiles;
+    const int n_pack = (nk + kPackTiles - 1) / kPackTiles;
 
     if (warp == 8) {
         // ---- producer ---------------------------------------------------------------------
@@ -193,19 +198,19 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             for (int c = 0; c < n_pack; ++c) {
                 const int s = c % kPackStages;
                 if (c >= kPackStages && !bar_wait(&wempty[s], ((c / kPackStages) - 1) & 1, abort_flag)) break;
-                const int kt0 = c * kPackTiles, nt = min(kPackTiles, k_tiles - kt0);
+                const int i0 = c * kPackTiles, nt = min(kPackTiles, nk - i0);
                 bar_expect_tx(&wfull[s], (uint32_t)(n_rg * nt * kTileBytes));
                 for (int r = 0; r < n_rg; ++r)
                     bulk_load(pack + s * kPackStageBytes + r * kPackTiles * kTileBytes,
-                              p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt0) * kTileBytes, (uint32_t)(nt * kTileBytes),
-                              &wfull[s]);
+                              p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt_lo + i0) * kTileBytes,
+                              (uint32_t)(nt * kTileBytes), &wfull[s]);
             }
         }
     } else if (warp == 9) {
         // ---- MMA issue ----------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(kRows, TN);
-            for (int kt = 0; kt < k_tiles; ++kt) {
+            for (int kt = 0; kt < nk; ++kt) {
                 const int b = kt % kOpStages;
                 if (!bar_wait(&ofull[b], (kt / kOpStages) & 1, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -224,9 +229,28 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
         // ---- unpack + activation staging ------------------------------------------------------
         const int g = lane >> 2, q = lane & 3;
         const int wtid = tid;                      // 0..255 among the workers
-        for (int kt = 0; kt < k_tiles; ++kt) {
+        // activations of a K tile: TN tokens x 128 bytes in 16-byte pieces, loaded one tile ahead
+        constexpr int kPieces = (TN * 8) / 256;
+        uint4 ynext[kPieces];
+        auto load_y = [&](int kt) {
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) {
+                const int piece = wtid + i * 256;
+                const int t = piece >> 3, c16 = piece & 7;
+                ynext[i] = make_uint4(0, 0, 0, 0);
+                if (tok0 + t < p.M && kt < nk)
+                    ynext[i] = *reinterpret_cast<const uint4*>(p.y + (int64_t)(tok0 + t) * p.ldy +
+                                                               (int64_t)(kt_lo + kt) * kTileCols + c16 * 16);
+            }
+        };
+        load_y(0);
+        for (int kt = 0; kt < nk; ++kt) {
             const int c = kt / kPackTiles, s = c % kPackStages, ktl = kt - c * kPackTiles;
             const int b = kt % kOpStages;
+            uint4 ycur[kPieces];
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) ycur[i] = ynext[i];
+            load_y(kt + 1);
             if (ktl == 0 && !bar_wait(&wfull[s], (c / kPackStages) & 1, abort_flag)) break;
             if (kt >= kOpStages && !bar_wait(&oempty[b], ((kt / kOpStages) - 1) & 1, abort_flag)) break;
             uint8_t* opb = ops + b * S::kOpBytes;
@@ -246,13 +270,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                     }
                 }
             }
-            // activations: TN tokens x 128 bytes of this K tile, 16 bytes per piece
 #pragma unroll
-            for (int i = 0; i < (TN * 8) / 256; ++i) {
+            for (int i = 0; i < kPieces; ++i) {
                 const int piece = wtid + i * 256;
                 const int t = piece >> 3, c16 = piece & 7;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (tok0 + t < p.M) v = *reinterpret_cast<const uint4*>(p.y + (int64_t)(tok0 + t) * p.ldy + kt * kTileCols + c16 * 16);
+                const uint4 v = ycur[i];
                 const int qq = c16 >> 1, j0 = (c16 & 1) * 2;   // bytes 0-7: field j0, bytes 8-15: field j0+1
                 uint8_t* dst = opb + 4 * kSlabA + (t >> 3) * 256 + (qq >> 1) * 128 + (t & 7) * 16 + (qq & 1) * 8;
                 *reinterpret_cast<uint2*>(dst + j0 * S::kSlabB) = make_uint2(v.x, v.y);
@@ -262,7 +284,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             __syncwarp();
             if (lane == 0) {
                 bar_arrive(&ofull[b]);
-                if (ktl == kPackTiles - 1 || kt == k_tiles - 1) bar_arrive(&wempty[s]);
+                if (ktl == kPackTiles - 1 || kt == nk - 1) bar_arrive(&wempty[s]);
             }
         }
 
@@ -285,7 +307,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                 for (int e = 0; e < 16; ++e) {
                     const int tok = tok0 + cb + e;
                     if (tok < p.M && row < p.N) {
-                        const int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6) - p.ysum[tok];
+                        int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6);
+                        if (p.k_splits > 1) {      // partial sum over this CTA's K share
+                            atomicAdd(&p.acc_ws[(int64_t)tok * p.N + row], v);
+                            continue;
+                        }
+                        v -= p.ysum[tok];
                         if (p.acc_out) p.acc_out[(int64_t)tok * p.N + row] = v;
                         if (p.out) {
                             const float a = p.a_f32 ? p.a_f32[tok] : __bfloat162float(p.a_bf16[tok]);
@@ -307,13 +334,35 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     if (tid == 0 && *abort_flag) atomicExch(p.error_flag, 3);
 }
 
+// Second pass of a split-K launch: subtract sum(y), rescale, store, and clear the work space.
+__global__ void __launch_bounds__(256) tc_finalize_kernel(const TcParams p) {
+    const int64_t n = (int64_t)p.M * p.N;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+        const int tok = (int)(i / p.N), row = (int)(i - (int64_t)tok * p.N);
+        const int v = p.acc_ws[i] - p.ysum[tok];
+        p.acc_ws[i] = 0;
+        if (p.acc_out) p.acc_out[i] = v;
+        if (p.out) {
+            const int sg = segment_of(p.seg, row);
+            const float ws = p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
+            const float a = p.a_f32 ? p.a_f32[tok] : __bfloat162float(p.a_bf16[tok]);
+            p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / a * ws);
+        }
+    }
+}
+
 template <int TN>
 cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(w2a8_gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          TcSmem<TN>::kBytes + 1024);
     if (e != cudaSuccess) return e;
-    const dim3 grid((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN));
+    const dim3 grid((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN), (unsigned)p.k_splits);
     w2a8_gemm_tc_kernel<TN><<<grid, kThreadsTc, TcSmem<TN>::kBytes + 1024, stream>>>(p);
+    if (p.k_splits > 1) {
+        const int64_t n = (int64_t)p.M * p.N;
+        const int blocks = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+        tc_finalize_kernel<<<blocks, 256, 0, stream>>>(p);
+    }
     return cudaGetLastError();
 }
 
@@ -321,7 +370,8 @@ cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
 
 // y must be 16-byte aligned with ldy % 16 == 0 and readable up to ceil128(K) columns (zero
 // filled beyond K); ysum is required.
-int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, cudaStream_t stream) {
+int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t acc_ws_ints, int n_sm,
+                 cudaStream_t stream) {
     TcParams p{};
     p.w2t = static_cast<const uint8_t*>(a.w2t);
     p.y = a.y; p.ldy = a.ldy; p.ysum = a.ysum;
@@ -332,6 +382,14 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, cudaStream_t stream) {
     p.k_tiles = (a.K + kTileCols - 1) / kTileCols;
     p.n_rowgroups = (a.N + 15) / 16;
     p.error_flag = error_flag;
+    // Few output tiles (decode-sized M): split K over enough CTAs to occupy the SMs.
+    const int tn = a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128);
+    const int tiles = ((a.N + kRows - 1) / kRows) * ((a.M + tn - 1) / tn);
+    int ks = n_sm / (tiles > 0 ? tiles : 1);
+    if (ks > p.k_tiles / 2) ks = p.k_tiles / 2;          // at least two K tiles per CTA
+    if (ks < 1 || !acc_ws || (size_t)a.M * a.N > acc_ws_ints) ks = 1;
+    p.k_splits = ks;
+    p.acc_ws = acc_ws;
     cudaError_t e;
     if (a.M <= 32) e = launch_tc<32>(p, stream);
     else if (a.M <= 64) e = launch_tc<64>(p, stream);

@@ -188,9 +188,9 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
     const int64_t k_pad = (a.K + kTileCols - 1) / kTileCols * kTileCols;
     if (a.M >= 16 && !no_tc && a.ysum && a.ldy % 16 == 0 && a.ldy >= k_pad &&
         (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
-        int* flag = workspace_error_flag();
-        if (!flag) return kCudaError;
-        return w2a8_gemm_tc(a, flag, stream);
+        WorkspaceView ws;
+        if (!workspace_view(&ws)) return kCudaError;
+        return w2a8_gemm_tc(a, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, stream);
     }
     GemvParams p;
     p.w = reinterpret_cast<const uint4*>(a.w2t);

@@ -28,8 +28,16 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream);
 int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream);
 // M >= 16 on tcgen05 (gemm_tc.cu).  Needs ysum, 16-byte aligned y rows padded with zeros to a
 // multiple of 128 columns; error_flag is a device word set when a bounded wait gave up.
-int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, cudaStream_t stream);
-int* workspace_error_flag();
+int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t acc_ws_ints, int n_sm,
+                 cudaStream_t stream);
+// The per-device work space of the stand-alone entry points (allocated on first use).
+struct WorkspaceView {
+    int* error_flag;
+    int32_t* tc_acc;          // zero between launches
+    size_t tc_acc_ints;
+    int n_sm;
+};
+bool workspace_view(WorkspaceView* out);
 
 // Packers (all buffers on the device).
 int pack_ternary_to_w2t(const int8_t* q, void* w2t, int N, int K, cudaStream_t stream);

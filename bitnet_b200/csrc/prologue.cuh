@@ -65,56 +65,74 @@ __device__ __forceinline__ float reduce_256(float v, bool is_max, float* scratch
     return r;
 }
 
-// One token whose source values already sit in shared memory: xv holds ceil8(K) bf16
-// values (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero filled
-// beyond K.  On return every thread holds the token's activation scale and sum(y).  The
-// loops are deliberately not unrolled: these kernels run for microseconds, and code that
-// does not fit the instruction cache costs more than the loop overhead saves.
-// reduce(v, is_max, scratch, tid) must return the sum / max of v over the 256 threads, in
-// the order reduce_256 defines.
-template <class Reduce>
-__device__ __forceinline__ void norm_quant_row(__nv_bfloat16* xv, int K, int k_pad, const __nv_bfloat16* gamma,
-                                               float eps, int8_t* y, float* scratch, int tid, Reduce reduce,
-                                               float& a_out, int& ysum_out) {
+// Sum of `ss` and max of `mx` over the 256 threads in one round (two barriers).  `scratch`
+// holds 16 floats.
+template <class Sync>
+__device__ __forceinline__ void reduce2_256(float& ss, float& mx, float* scratch, int tid, Sync sync) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    sync();
+    if ((tid & 31) == 0) {
+        scratch[tid >> 5] = ss;
+        scratch[8 + (tid >> 5)] = mx;
+    }
+    sync();
+    ss = scratch[0];
+    mx = scratch[8];
+#pragma unroll
+    for (int i = 1; i < kPrologueThreads / 32; ++i) {
+        ss += scratch[i];
+        mx = fmaxf(mx, scratch[8 + i]);
+    }
+}
+
+// One token whose source values already sit in shared memory: xv holds ceil8(K) bf16 values
+// (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero filled beyond
+// K.  Arithmetic, in f32: t = x * g; r = rsqrt(mean(x^2) + eps); xn = bf16(t * r);
+// a = 127 / max(max|xn|, 1e-5); y = clamp(rint(xn * a), -128, 127).  Because rounding and
+// multiplication by r > 0 are monotone, max|xn| = bf16(max|t| * r), so one reduction round
+// (sum of squares and max|t| together) and two passes suffice.  On return every thread holds
+// the activation scale; `sy_warp` is the sum of y over the calling warp's elements (exact in
+// f32), which the caller adds up over the eight warps.  The loops are deliberately not
+// unrolled: these kernels run for microseconds, and code that does not fit the instruction
+// cache costs more than the loop overhead saves.
+template <class Sync>
+__device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, int k_pad, const __nv_bfloat16* gamma,
+                                               float eps, int8_t* y, float* scratch, int tid, Sync sync, float& a_out,
+                                               float& sy_warp) {
     const int n_vec = (K + 7) / 8;
     const bool g_vec = gamma && aligned16(gamma, 8, 2);
-    float ss = 0.f, mx = 0.f;
+    float ss = 0.f, mt = 0.f;
 #pragma unroll 1
     for (int v = tid; v < n_vec; v += kPrologueThreads) {
         const Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
+        Vec8 g;
+        if (gamma) g = load_bf16x8(gamma, v * 8, K, g_vec);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             ss += x.v[e] * x.v[e];
-            mx = fmaxf(mx, fabsf(x.v[e]));
+            mt = fmaxf(mt, fabsf(gamma ? x.v[e] * g.v[e] : x.v[e]));
         }
     }
-    if (gamma) {
-        ss = reduce(ss, false, scratch, tid);
-        const float rinv = rsqrtf(ss / (float)K + eps);
-        mx = 0.f;
-#pragma unroll 1
-        for (int v = tid; v < n_vec; v += kPrologueThreads) {
-            Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
-            const Vec8 g = load_bf16x8(gamma, v * 8, K, g_vec);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                x.v[e] = bf16_round(x.v[e] * rinv * g.v[e]);
-                mx = fmaxf(mx, fabsf(x.v[e]));
-            }
-            *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x);
-        }
-    }
-    mx = reduce(mx, true, scratch, tid);
-    const float a = 127.0f / fmaxf(mx, 1e-5f);
+    reduce2_256(ss, mt, scratch, tid, sync);
+    const float rinv = gamma ? rsqrtf(ss / (float)K + eps) : 1.f;
+    const float amax = gamma ? bf16_round(mt * rinv) : mt;
+    const float a = 127.0f / fmaxf(amax, 1e-5f);
     float sy = 0.f;
 #pragma unroll 1
     for (int v = tid; v < k_pad / 8; v += kPrologueThreads) {
         uint32_t lo = 0, hi = 0;
         if (v < n_vec) {
             const Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
+            Vec8 g;
+            if (gamma) g = load_bf16x8(gamma, v * 8, K, g_vec);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float f = rintf(x.v[e] * a);
+                const float xn = gamma ? bf16_round(x.v[e] * g.v[e] * rinv) : x.v[e];
+                float f = rintf(xn * a);
                 f = fminf(fmaxf(f, -128.f), 127.f);
                 sy += f;
                 const uint32_t b = (uint32_t)(uint8_t)(int8_t)(int)f;
@@ -124,9 +142,10 @@ __device__ __forceinline__ void norm_quant_row(__nv_bfloat16* xv, int K, int k_p
         }
         *reinterpret_cast<uint2*>(y + v * 8) = make_uint2(lo, hi);
     }
-    sy = reduce(sy, false, scratch, tid);   // exact: |sum| < 2^24
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
     a_out = a;
-    ysum_out = (int)sy;
+    sy_warp = sy;
 }
 
 }  // namespace bitnet

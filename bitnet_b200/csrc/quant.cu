@@ -12,20 +12,24 @@ namespace {
 
 __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const QuantArgs p) {
     extern __shared__ __align__(16) uint8_t smem_q[];
-    __shared__ float scratch[kPrologueThreads / 32];
+    __shared__ float scratch[16];
+    __shared__ float sy_part[kPrologueThreads / 32];
     __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(smem_q);
     const int tok = blockIdx.x, tid = threadIdx.x;
     const __nv_bfloat16* row = p.x_bf16 + (int64_t)tok * p.ldx;
     const bool vec_ok = aligned16(p.x_bf16, p.ldx, 2);
     const int K = p.K;
-    float a;
-    int ysum;
+    float a, sy_warp;
 #pragma unroll 1
     for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads)
         *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(load_bf16x8(row, v * 8, K, vec_ok));
     norm_quant_row(xv, K, (int)p.ldy, p.gamma, p.eps, p.y + (int64_t)tok * p.ldy, scratch, tid,
-                   [](float v, bool is_max, float* sc, int t) { return reduce_256(v, is_max, sc, t, [] { __syncthreads(); }); },
-                   a, ysum);
+                   [] { __syncthreads(); }, a, sy_warp);
+    if ((tid & 31) == 0) sy_part[tid >> 5] = sy_warp;
+    __syncthreads();
+    float sy = 0.f;
+    for (int i = 0; i < kPrologueThreads / 32; ++i) sy += sy_part[i];
+    const int ysum = (int)sy;
     if (tid == 0) {
         if (p.a_f32) p.a_f32[tok] = a;
         if (p.a_bf16) p.a_bf16[tok] = __float2bfloat16_rn(a);

@@ -131,7 +131,7 @@ class Generator:
         B, T = prompt.shape
         assert B == self.batch and T < self.max_seq_len
         self.pos.zero_()
-        logits = self.model(prompt, self.pos, self.cache, kv_len=T)
+        logits = self.model(prompt, self.pos, self.cache, kv_len=T, last_only=True)
         nxt = logits[:, -1].argmax(-1)
         self.out.copy_(nxt)
         self.tokens.copy_(nxt[:, None])

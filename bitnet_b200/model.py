@@ -70,7 +70,8 @@ LayerCache = Tuple[torch.Tensor, torch.Tensor]
 
 
 class RMSNorm(nn.Module):
-    """x * rsqrt(mean(x^2) + eps) * weight, computed in f32, returned in x's dtype."""
+    """(x * weight) * rsqrt(mean(x^2) + eps), computed in f32, returned in x's dtype (the
+    operation order of the library's fused prologue)."""
 
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
@@ -80,7 +81,7 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         xf = x.float()
         r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (xf * r * self.weight.float()).to(x.dtype)
+        return (xf * self.weight.float() * r).to(x.dtype)
 
 
 def quant_weight_int8(weight: torch.Tensor):
@@ -273,13 +274,16 @@ class Transformer(nn.Module):
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, cache: List[LayerCache],
-                kv_len: Optional[int] = None) -> torch.Tensor:
-        """tokens int64 [B, T]; pos int64 [B] (tokens already cached); returns f32 logits [B, T, vocab]."""
+                kv_len: Optional[int] = None, last_only: bool = False) -> torch.Tensor:
+        """tokens int64 [B, T]; pos int64 [B] (tokens already cached); returns f32 logits
+        [B, T, vocab], or [B, 1, vocab] for the last position only."""
         if self.rope is None or self.rope.device != tokens.device:
             self.rope = rope_table(self.args.head_dim, self.max_seq_len, self.args.rope_theta, tokens.device)
         h = self.tok_embeddings(tokens)
         for layer, c in zip(self.layers, cache):
             h = layer(h, c, pos, self.rope, kv_len)
+        if last_only:
+            h = h[:, -1:]
         return self.output(self.norm(h)).float()
 
 

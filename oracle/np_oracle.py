@@ -48,10 +48,10 @@ def act_quant(x: np.ndarray):
 
 def rmsnorm(x: np.ndarray, g: np.ndarray, eps: float = 1e-5):
     """RMSNorm as the reference's decode model applies it before each BitLinear
-    (gpu/model.py:159-160,195-196,237-242): x * rsqrt(mean(x^2) + eps) * g, in f32."""
+    (gpu/model.py:159-160,195-196,237-242): (x * g) * rsqrt(mean(x^2) + eps), in f32."""
     x = np.asarray(x, dtype=np.float32)
     ms = (x.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
-    return (x * (1.0 / np.sqrt(ms + eps)).astype(np.float32) * g.astype(np.float32)).astype(np.float32)
+    return (x * g.astype(np.float32) * (1.0 / np.sqrt(ms + eps)).astype(np.float32)).astype(np.float32)
 
 
 def to_bf16(x: np.ndarray) -> np.ndarray:
