@@ -49,6 +49,11 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
+    ap.add_argument("--tp", action="store_true",
+                    help="shard one model tensor-parallel over the ranks (strong scaling) instead of replicas; "
+                         "needs head counts divisible by the rank count (8b, 100b presets)")
+    ap.add_argument("--layers", type=int, default=0, help="use only the first LAYERS layers (0 = all; with --tp)")
+    ap.add_argument("--context", type=int, default=PROMPT_LEN, help="tokens in the KV cache when decode starts (with --tp)")
     return ap.parse_args()
 
 
@@ -417,7 +422,9 @@ def run_ours(a, args_model):
                 "d2h_bytes_per_step": 8 * B},
         "gpu_launches": (gen.fused.kernels_per_step if fused else 2 * n_lin) * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                     # dram__bytes_read + write per launch from one ncu capture of the four 2B shapes
+                     # (profiles/fused_linear_kernel_2b_m1.md), averaged as the launches are mixed
+                     "traffic": 4.505e6 if (fused and a.workload == "2b" and B == 1) else None, "peak_source": "measured" if peaks else "fallback",
                      "kernel": "fused_linear_kernel (prologue + W2A8 matmul, PDL chain)" if fused else "w2a8_gemv_kernel",
                      "launches_per_step": n_lin,
                      "bytes_per_launch": weight_bytes / n_lin, "us_per_launch": 1e3 * ms_lin / n_lin,
@@ -430,11 +437,86 @@ def run_ours(a, args_model):
         dist.destroy_process_group()
 
 
+def run_tp(a, args_model):
+    """One model sharded over the ranks (bitnet_b200.tensor_parallel): column-parallel wqkv/w13,
+    row-parallel wo/w2 with an all-gather and an exact int32 all-reduce each; decode steps are
+    issued op by op (no CUDA graph), timed with CUDA events, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from bitnet_b200.tensor_parallel import TPDecoder
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, K, W = a.batch, a.steps, a.warmup
+    max_seq = (a.context + K + W + 8 + 127) // 128 * 128
+    dec = TPDecoder(args_model, SEED, rank, world, dev, backend="kernel", max_seq_len=max_seq)
+    cache = dec.make_cache(B, max_seq)
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    for ck, cv in cache:     # a context of random keys and values stands in for a prefill
+        ck[:, : a.context].copy_(torch.randn(ck[:, : a.context].shape, generator=g, device=dev).to(torch.bfloat16))
+        cv[:, : a.context].copy_(torch.randn(cv[:, : a.context].shape, generator=g, device=dev).to(torch.bfloat16))
+    tok = torch.randint(0, args_model.vocab_size, (B, 1), generator=g, device=dev)
+    pos = torch.full((B,), a.context, dtype=torch.int64, device=dev)
+    for _ in range(W):
+        tok = dec.decode_step(tok, pos, cache).view(B, 1)
+        pos += 1
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        tok = dec.decode_step(tok, pos, cache).view(B, 1)
+        pos += 1
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        D = args_model.head_dim
+        per_layer = ((args_model.n_heads + 2 * args_model.n_kv_heads) * D * args_model.dim + args_model.dim * args_model.dim
+                     + 3 * args_model.ffn_dim * args_model.dim) // 4
+        step_bytes = per_layer * args_model.n_layers + 2 * args_model.vocab_size * args_model.dim
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        gbs = step_bytes / (ms / K * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{B}, tp{world})", "value": B * K / (ms * 1e-3),
+            "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x 2-bit ternary -> int32 (bf16 elsewhere)",
+            "data": "synthetic",
+            "config": {"workload": f"{a.workload} architecture ({args_model.n_layers} layers) random-init, batch {B}, "
+                                   f"context {a.context}, tensor parallel x{world}", "batch": B},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
+                         "frac": gbs / (peak * world), "traffic": None,
+                         "note": "whole step: packed weights + bf16 output projection over aggregate HBM bandwidth"},
+            "gpu_launches": None}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     a = parse_args()
     from bitnet_b200.model import preset
 
     args_model = preset(a.workload)
+    if a.tp:
+        if a.layers:
+            args_model = preset(a.workload, n_layers=a.layers)
+        return run_tp(a, args_model)
     if a.impl == "reference":
         run_reference(a, args_model)
     else:

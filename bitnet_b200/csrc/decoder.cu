@@ -149,10 +149,13 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->head_grid = d->n_sm;
 
     const int dim = cfg->dim, F = cfg->ffn_dim, Nqkv = (H + 2 * Hkv) * D;
+    // CTAs per SM for the BitLinear kernels (measurement knob; 1 leaves room for the successor's
+    // CTAs to become resident early and prefetch their weights)
+    const int ctas_per_sm = getenv("BITNET_CTAS_PER_SM") ? atoi(getenv("BITNET_CTAS_PER_SM")) : 1;
     auto plan = [&](FusedLinearParams& p, int N, int K, int src, int out_kind) {
         p = FusedLinearParams{};
         p.N = N; p.K = K; p.src = src; p.out_kind = out_kind; p.M = B; p.eps = cfg->norm_eps;
-        plan_linear(p, d->n_sm);
+        plan_linear(p, d->n_sm * (ctas_per_sm > 0 ? ctas_per_sm : 1));
     };
     plan(d->plan_qkv, Nqkv, dim, kSrcVector, kOutBf16);
     plan(d->plan_o, dim, dim, kSrcVector, kOutResidual);

@@ -1,0 +1,60 @@
+"""Tensor parallel on real GPUs: two ranks over NCCL must reproduce the single-GPU logits bit
+for bit (needs two B200s; skipped otherwise)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["BITNET_ROOT"])
+from bitnet_b200.model import preset
+from bitnet_b200.tensor_parallel import TPDecoder
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+args = preset("8b", n_layers=2, vocab_size=4096)
+def run(dec):
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, args.vocab_size, (2, 9), generator=g).cuda()
+    cache = dec.make_cache(2, 64)
+    pos = torch.zeros(2, dtype=torch.int64, device="cuda")
+    h = dec.hidden(prompt, pos, cache, kv_len=9)
+    outs = [dec.logits(h)]
+    tok = dec.greedy(h).view(2, 9)[:, -1:]
+    for s in range(5):
+        h = dec.hidden(tok, pos + 9 + s, cache)
+        outs.append(dec.logits(h))
+        tok = dec.greedy(h).view(2, 1)
+    return torch.cat([o.reshape(-1) for o in outs]), tok
+tp = run(TPDecoder(args, 7, rank, world, "cuda", backend="kernel", max_seq_len=64))
+if rank == 0:
+    one = run(TPDecoder(args, 7, 0, 1, "cuda", backend="kernel", max_seq_len=64))
+    assert torch.equal(tp[0], one[0]), float((tp[0] - one[0]).abs().max())
+    assert torch.equal(tp[1], one[1])
+    print("TP_OK")
+dist.barrier()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_nccl_equals_single_gpu(tmp_path):
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, BITNET_ROOT=ROOT)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
