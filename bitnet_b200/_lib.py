@@ -36,6 +36,7 @@ SIGNATURES = {
     "bitnet_decoder_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_bench_linears": (_i, [_vp, _vp, _vp]),
     "bitnet_decoder_read_trace": (_i, [_vp, _vp, _i]),
+    "bitnet_debug_read_workspace_words": (_i, [_vp, _i]),
     "bitnet_decoder_error_flag": (_i, [_vp]),
     "bitnet_decoder_kernels_per_step": (_i, [_vp]),
     "bitnet_decoder_destroy": (None, [_vp]),

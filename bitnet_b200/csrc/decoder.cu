@@ -316,6 +316,13 @@ int bitnet_decoder_read_trace(void* dec, unsigned long long* host_out, int n_val
                                  cudaMemcpyDeviceToHost));
 }
 
+int bitnet_debug_read_workspace_words(unsigned long long* host_out, int n_words) {
+    Workspace* w = workspace();
+    if (!w || !host_out || n_words < 1 || n_words > 24) return set_status(kBadArgument), kBadArgument;
+    return check_cuda(cudaMemcpy(host_out, reinterpret_cast<unsigned long long*>(w->error_flag + 16),
+                                 sizeof(unsigned long long) * n_words, cudaMemcpyDeviceToHost));
+}
+
 int bitnet_decoder_kernels_per_step(void* dec) {
     Decoder* d = static_cast<Decoder*>(dec);
     return d ? 5 * d->cfg.n_layers + 2 : 0;

@@ -5,19 +5,20 @@
 //
 // D[128 weight rows, TN tokens] += A[128 x 32, u8, K-major] * B[TN x 32, s8, K-major].
 // One CTA owns a 128-row block of the weight matrix and a block of TN tokens and walks K in
-// tiles of 128 columns.  Roles (10 warps):
-//   warp 8   - producer: packed 2-bit weight tiles, global -> shared ring (cp.async.bulk)
-//   warps 0-7 - unpack: warp w turns row group w (16 rows) of the current K tile into int8
-//               operands in the canonical no-swizzle K-major layout, and all of them stage the
-//               int8 activations of the K tile in the same layout
-//   warp 9   - issues the MMAs (one elected lane) and commits them to mbarriers
-//   warps 0-7 - epilogue: tcgen05.ld, fold, rescale, store
+// tiles of 128 columns, two per pipeline step.  Roles (18 warps):
+//   warp 16    - producer: packed 2-bit weight tiles, global -> shared ring (cp.async.bulk)
+//   warps 0-15 - unpack: warp w turns row group w & 7 (16 rows) of K tile w >> 3 of the step
+//                into int8 operands in the canonical no-swizzle K-major layout, and all of
+//                them stage the int8 activations of the step in the same layout
+//   warp 17    - issues the MMAs (one elected lane) and commits them to mbarriers
+//   warps 0-7  - epilogue: tcgen05.ld, fold, rescale, store
 // The 2-bit fields are separated by AND masks only, as in the decode kernel: field j of every
 // byte stays scaled by 4^j and gets its own accumulator (TMEM columns j*TN..), which the
 // epilogue folds with exact shifts.  In the W2T layout field j of lane chunk q covers columns
 // 32q+8j..32q+8j+7 of a K tile, so operand slab j holds those 4 x 8 = 32 columns of A, and
 // the activations are staged with the same column selection.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -27,12 +28,15 @@ namespace bitnet {
 namespace {
 
 constexpr int kRows = 128;                       // weight rows per CTA (UMMA M)
-constexpr int kWorkerWarps = 8;
+constexpr int kWorkerWarps = 16;                 // warp w: row group w & 7 of K tile w >> 3 of the stage
+constexpr int kWorkerThreads = kWorkerWarps * 32;
+constexpr int kProducerWarp = kWorkerWarps, kMmaWarp = kWorkerWarps + 1;
 constexpr int kThreadsTc = (kWorkerWarps + 2) * 32;
 constexpr int kPackStages = 3;                   // packed-weight ring
 constexpr int kPackTiles = 4;                    // K tiles per packed stage
 constexpr int kPackStageBytes = 8 * kPackTiles * kTileBytes;   // 16 KB
-constexpr int kOpStages = 3;                     // unpacked operand buffers (one K tile each)
+constexpr int kOpStages = 2;                     // unpacked operand buffers
+constexpr int kOpTiles = 2;                      // K tiles per operand buffer
 constexpr int kSlabA = 4096;                     // 128 rows x 32 int8, canonical K-major
 constexpr long long kWaitCyclesTc = 2000000000LL;
 
@@ -53,6 +57,7 @@ struct TcParams {
     int k_splits;                // grid.z: CTAs that share an output tile and add into acc_ws
     int32_t* acc_ws;             // [M, N] zero-initialised int32 work space (k_splits > 1)
     int* error_flag;
+    unsigned long long* trace;   // optional cycle counters (measurement aid)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -130,13 +135,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
         : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
+}
+
 template <int TN>
 struct TcSmem {
     static constexpr int kSlabB = TN * 32;                              // TN tokens x 32 int8
-    static constexpr int kOpBytes = 4 * kSlabA + 4 * kSlabB;            // one operand buffer (4 fields)
+    static constexpr int kOpBytes = 4 * kSlabA + 4 * kSlabB;            // operands of one K tile (4 fields)
     static constexpr int kPackOff = 0;
     static constexpr int kOpOff = kPackStages * kPackStageBytes;
-    static constexpr int kBarOff = kOpOff + kOpStages * kOpBytes;
+    static constexpr int kBarOff = kOpOff + kOpStages * kOpTiles * kOpBytes;
     static constexpr int kBytes = kBarOff + 256;
 };
 
@@ -178,7 +189,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 9) {   // the MMA warp owns the tensor memory: 4 fields x TN columns
+    if (warp == kMmaWarp) {   // the MMA warp owns the tensor memory: 4 fields x TN columns
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)),
                      "r"(4 * TN)
@@ -191,8 +202,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_pack = (nk + kPackTiles - 1) / kPackTiles;
+    const int n_os = (nk + kOpTiles - 1) / kOpTiles;      // pipeline steps
 
-    if (warp == 8) {
+    if (warp == kProducerWarp) {
         // ---- producer ---------------------------------------------------------------------
         if (lane == 0) {
             for (int c = 0; c < n_pack; ++c) {
@@ -206,20 +218,23 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                               (uint32_t)(nt * kTileBytes), &wfull[s]);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
         // ---- MMA issue ----------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(kRows, TN);
-            for (int kt = 0; kt < nk; ++kt) {
-                const int b = kt % kOpStages;
-                if (!bar_wait(&ofull[b], (kt / kOpStages) & 1, abort_flag)) break;
+            for (int os = 0; os < n_os; ++os) {
+                const int b = os % kOpStages;
+                if (!bar_wait(&ofull[b], (os / kOpStages) & 1, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t base = smem_addr(ops + b * S::kOpBytes);
+                const int tiles = min(kOpTiles, nk - os * kOpTiles);
+                for (int kw = 0; kw < tiles; ++kw) {
+                    const uint32_t base = smem_addr(ops + (b * kOpTiles + kw) * S::kOpBytes);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint64_t da = umma_desc(base + j * kSlabA, 128, 256);
-                    const uint64_t db = umma_desc(base + 4 * kSlabA + j * S::kSlabB, 128, 256);
-                    umma_i8(tmem_base + j * TN, da, db, idesc, kt > 0);
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = umma_desc(base + j * kSlabA, 128, 256);
+                        const uint64_t db = umma_desc(base + 4 * kSlabA + j * S::kSlabB, 128, 256);
+                        umma_i8(tmem_base + j * TN, da, db, idesc, os > 0 || kw > 0);
+                    }
                 }
                 umma_commit(&oempty[b]);           // frees the operand buffer when these MMAs retire
             }
@@ -228,15 +243,18 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     } else {
         // ---- unpack + activation staging ------------------------------------------------------
         const int g = lane >> 2, q = lane & 3;
-        const int wtid = tid;                      // 0..255 among the workers
-        // activations of a K tile: TN tokens x 128 bytes in 16-byte pieces, loaded one tile ahead
-        constexpr int kPieces = (TN * 8) / 256;
+        const int wtid = tid;                      // 0..511 among the workers
+        const int rgw = warp & 7, kw_mine = warp >> 3;
+        // activations of a step: 2 K tiles x TN tokens x 128 bytes in 16-byte pieces, one step ahead
+        constexpr int kPieces = (TN * 8 * kOpTiles) / kWorkerThreads;
         uint4 ynext[kPieces];
-        auto load_y = [&](int kt) {
+        auto load_y = [&](int os) {
 #pragma unroll
             for (int i = 0; i < kPieces; ++i) {
-                const int piece = wtid + i * 256;
-                const int t = piece >> 3, c16 = piece & 7;
+                const int piece = wtid + i * kWorkerThreads;
+                const int kw = piece / (TN * 8), rest = piece - kw * (TN * 8);
+                const int t = rest >> 3, c16 = rest & 7;
+                const int kt = os * kOpTiles + kw;
                 ynext[i] = make_uint4(0, 0, 0, 0);
                 if (tok0 + t < p.M && kt < nk)
                     ynext[i] = *reinterpret_cast<const uint4*>(p.y + (int64_t)(tok0 + t) * p.ldy +
@@ -244,67 +262,107 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             }
         };
         load_y(0);
-        for (int kt = 0; kt < nk; ++kt) {
-            const int c = kt / kPackTiles, s = c % kPackStages, ktl = kt - c * kPackTiles;
-            const int b = kt % kOpStages;
+        // optional cycle counters of warp 0 of CTA (0,0,0): a measurement aid behind error_flag
+        const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+        long long c_wfull = 0, c_oempty = 0, c_unpack = 0, c_stage = 0, c_fence = 0, c_t = clock64();
+        auto lap = [&](long long& acc) {
+            if (tracing) {
+                const long long t = clock64();
+                acc += t - c_t;
+                c_t = t;
+            }
+        };
+        for (int os = 0; os < n_os; ++os) {
+            const int kt = os * kOpTiles + kw_mine;                // this warp's K tile of the step
+            const int c = (os * kOpTiles) / kPackTiles, s = c % kPackStages;
+            const int ktl = kt - c * kPackTiles;
+            const int b = os % kOpStages;
             uint4 ycur[kPieces];
 #pragma unroll
             for (int i = 0; i < kPieces; ++i) ycur[i] = ynext[i];
-            load_y(kt + 1);
-            if (ktl == 0 && !bar_wait(&wfull[s], (c / kPackStages) & 1, abort_flag)) break;
-            if (kt >= kOpStages && !bar_wait(&oempty[b], ((kt / kOpStages) - 1) & 1, abort_flag)) break;
-            uint8_t* opb = ops + b * S::kOpBytes;
-            if (warp < n_rg) {
+            load_y(os + 1);
+            lap(c_stage);
+            if ((os * kOpTiles) % kPackTiles == 0 && !bar_wait(&wfull[s], (c / kPackStages) & 1, abort_flag)) break;
+            lap(c_wfull);
+            if (os >= kOpStages && !bar_wait(&oempty[b], ((os / kOpStages) - 1) & 1, abort_flag)) break;
+            lap(c_oempty);
+            if (rgw < n_rg && kt < nk) {
+                uint8_t* opb = ops + (b * kOpTiles + kw_mine) * S::kOpBytes;
                 const uint4 wv = *reinterpret_cast<const uint4*>(pack + s * kPackStageBytes +
-                                                                 (warp * kPackTiles + ktl) * kTileBytes + lane * 16);
+                                                                 (rgw * kPackTiles + ktl) * kTileBytes + lane * 16);
                 const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t msk = 0x03030303u << (2 * j);
 #pragma unroll
                     for (int rs = 0; rs < 2; ++rs) {
-                        // row 16*warp + g + 8*rs, field-j columns 8q + 4h + b: words rs (h=0), rs+2 (h=1)
+                        // row 16*rgw + g + 8*rs, field-j columns 8q + 4h + b: words rs (h=0), rs+2 (h=1)
                         const uint2 v = make_uint2(w[rs] & msk, w[rs + 2] & msk);
-                        *reinterpret_cast<uint2*>(opb + j * kSlabA + (2 * warp + rs) * 256 + (q >> 1) * 128 + g * 16 +
+                        *reinterpret_cast<uint2*>(opb + j * kSlabA + (2 * rgw + rs) * 256 + (q >> 1) * 128 + g * 16 +
                                                   (q & 1) * 8) = v;
                     }
                 }
             }
+            lap(c_unpack);
 #pragma unroll
             for (int i = 0; i < kPieces; ++i) {
-                const int piece = wtid + i * 256;
-                const int t = piece >> 3, c16 = piece & 7;
+                const int piece = wtid + i * kWorkerThreads;
+                const int kw = piece / (TN * 8), rest = piece - kw * (TN * 8);
+                const int t = rest >> 3, c16 = rest & 7;
                 const uint4 v = ycur[i];
                 const int qq = c16 >> 1, j0 = (c16 & 1) * 2;   // bytes 0-7: field j0, bytes 8-15: field j0+1
-                uint8_t* dst = opb + 4 * kSlabA + (t >> 3) * 256 + (qq >> 1) * 128 + (t & 7) * 16 + (qq & 1) * 8;
+                uint8_t* dst = ops + (b * kOpTiles + kw) * S::kOpBytes + 4 * kSlabA + (t >> 3) * 256 + (qq >> 1) * 128 +
+                               (t & 7) * 16 + (qq & 1) * 8;
                 *reinterpret_cast<uint2*>(dst + j0 * S::kSlabB) = make_uint2(v.x, v.y);
                 *reinterpret_cast<uint2*>(dst + (j0 + 1) * S::kSlabB) = make_uint2(v.z, v.w);
             }
+            lap(c_stage);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // generic writes -> tensor core reads
             __syncwarp();
+            lap(c_fence);
             if (lane == 0) {
                 bar_arrive(&ofull[b]);
-                if (ktl == kPackTiles - 1 || kt == nk - 1) bar_arrive(&wempty[s]);
+                // last step that reads this packed stage
+                if (((os + 1) * kOpTiles) % kPackTiles == 0 || os == n_os - 1) bar_arrive(&wempty[s]);
             }
         }
 
-        // ---- epilogue: warp w reads TMEM lanes 32*(w%4).., token half w/4 ----------------------
+        if (tracing) {
+            p.trace[0] = c_wfull; p.trace[1] = c_oempty; p.trace[2] = c_unpack; p.trace[3] = c_stage; p.trace[4] = c_fence;
+            p.trace[5] = n_os;
+        }
+        const long long c_ep0 = clock64();
+        // ---- epilogue: all 16 warps; warp w reads TMEM lanes 32*(w%4).., token quarter w/4 ------
         if (bar_wait(accfull, 0, abort_flag)) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int lane_blk = warp & 3, half = warp >> 2;
+            const int lane_blk = warp & 3, quarter = warp >> 2;
             const int row = rb * kRows + lane_blk * 32 + lane;
             const int sg = segment_of(p.seg, row < p.N ? row : 0);
             const float ws = p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
-            for (int cb = half * (TN / 2); cb < (half + 1) * (TN / 2); cb += 16) {
+            constexpr int kCols = TN / 4;                 // tokens per warp: 8, 16 or 32
+            constexpr int kChunk = kCols < 16 ? 8 : 16;
+#pragma unroll 1
+            for (int cb = quarter * kCols; cb < (quarter + 1) * kCols; cb += kChunk) {
                 int c0[16], c1[16], c2[16], c3[16];
                 const uint32_t ta = tmem_base + ((uint32_t)(lane_blk * 32) << 16) + cb;
-                tmem_ld16(ta, c0);
-                tmem_ld16(ta + TN, c1);
-                tmem_ld16(ta + 2 * TN, c2);
-                tmem_ld16(ta + 3 * TN, c3);
+                if (kChunk == 16) {
+                    tmem_ld16(ta, c0); tmem_ld16(ta + TN, c1); tmem_ld16(ta + 2 * TN, c2); tmem_ld16(ta + 3 * TN, c3);
+                } else {
+                    tmem_ld8(ta, c0); tmem_ld8(ta + TN, c1); tmem_ld8(ta + 2 * TN, c2); tmem_ld8(ta + 3 * TN, c3);
+                }
+                // per-token sum(y) and scale of this chunk (the same for every lane)
+                int ys[16];
+                float as[16];
+#pragma unroll
+                for (int e = 0; e < kChunk; ++e) {
+                    const int tok = tok0 + cb + e;
+                    const bool ok = tok < p.M;
+                    ys[e] = ok ? p.ysum[tok] : 0;
+                    as[e] = ok ? (p.a_f32 ? p.a_f32[tok] : (p.a_bf16 ? __bfloat162float(p.a_bf16[tok]) : 1.f)) : 1.f;
+                }
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
+                for (int e = 0; e < kChunk; ++e) {
                     const int tok = tok0 + cb + e;
                     if (tok < p.M && row < p.N) {
                         int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6);
@@ -312,21 +370,19 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                             atomicAdd(&p.acc_ws[(int64_t)tok * p.N + row], v);
                             continue;
                         }
-                        v -= p.ysum[tok];
+                        v -= ys[e];
                         if (p.acc_out) p.acc_out[(int64_t)tok * p.N + row] = v;
-                        if (p.out) {
-                            const float a = p.a_f32 ? p.a_f32[tok] : __bfloat162float(p.a_bf16[tok]);
-                            p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / a * ws);
-                        }
+                        if (p.out) p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / as[e] * ws);
                     }
                 }
             }
         }
+        if (tracing) p.trace[6] = clock64() - c_ep0;
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(4 * TN) : "memory");
@@ -382,6 +438,8 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t a
     p.k_tiles = (a.K + kTileCols - 1) / kTileCols;
     p.n_rowgroups = (a.N + 15) / 16;
     p.error_flag = error_flag;
+    static const bool trace_on = getenv("BITNET_TC_TRACE") != nullptr;
+    p.trace = trace_on ? reinterpret_cast<unsigned long long*>(error_flag + 16) : nullptr;   // spare words behind the flag
     // Few output tiles (decode-sized M): split K over enough CTAs to occupy the SMs.
     const int tn = a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128);
     const int tiles = ((a.N + kRows - 1) / kRows) * ((a.M + tn - 1) / tn);

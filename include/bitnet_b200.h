@@ -157,6 +157,10 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
  * this copies them out, sixteen 64-bit values per launch: first the 4 BitLinear launches of
  * every layer, then one attention launch per layer. */
 int bitnet_decoder_read_trace(void* decoder, unsigned long long* host_out, int n_values);
+/* Measurement aid: copies out the spare words behind the workspace's error flag, where the
+ * tcgen05 kernel leaves cycle counters of one warp when BITNET_TC_TRACE is set (waits for
+ * weights, waits for operand buffers, unpack, activation staging, proxy fence, steps, epilogue). */
+int bitnet_debug_read_workspace_words(unsigned long long* host_out, int n_words);
 /* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
 int bitnet_decoder_error_flag(void* decoder);
 /* Number of kernels one step launches. */
