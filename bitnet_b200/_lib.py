@@ -39,6 +39,7 @@ SIGNATURES = {
     "bitnet_debug_read_workspace_words": (_i, [_vp, _i]),
     "bitnet_decoder_error_flag": (_i, [_vp]),
     "bitnet_decoder_kernels_per_step": (_i, [_vp]),
+    "bitnet_decoder_use_persistent": (_i, [_vp, _i]),
     "bitnet_decoder_destroy": (None, [_vp]),
     "bitnet_w2t_bytes": (ctypes.c_size_t, [_i, _i]),
     "bitnet_pack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),

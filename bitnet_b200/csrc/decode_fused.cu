@@ -30,6 +30,7 @@
 #include "common.cuh"
 #include "decode_fused.h"
 #include "prologue.cuh"
+#include "decode_device.cuh"
 
 namespace bitnet {
 
@@ -41,55 +42,8 @@ constexpr int kStageBytes = kStageTiles * kTileBytes;     // 16 KB
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kLinearThreads = kConsumerThreads + 32;     // + one producer warp
-constexpr long long kWaitCycles = 2000000000LL;           // about one second: then give up
 
-// ---------------------------------------------------------------------------------------
-// PTX helpers
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: returns false (and the caller abandons the kernel) after about a second.
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitCycles) return false;
-    }
-    return true;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads) : "memory"); }
-
-// bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
-__device__ __noinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
-
 
 struct ConsumerSync {
     __device__ __forceinline__ void operator()() const { consumer_sync(); }
@@ -407,241 +361,13 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
 // 4 to 16 warps; a warp walks keys four at a time, a lane owns 4 dims.
 // ---------------------------------------------------------------------------------------
 template <int GMAX>
-struct AttnCfg {
-    static constexpr int kWarps = GMAX <= 4 ? 16 : (GMAX <= 8 ? 8 : 4);   // bounded by registers
-    static constexpr int kThreads = kWarps * 32;
-};
-
-template <int GMAX>
 __global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kernel(const AttentionParams p) {
-    constexpr int NW = AttnCfg<GMAX>::kWarps, NT = AttnCfg<GMAX>::kThreads;
     extern __shared__ __align__(128) uint8_t smem[];
-    const int D = p.D, G = p.H / p.Hkv;
-    float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
-    float* knew = q_s + G * D;                             // [D]
-    float* vnew = knew + D;                                // [D]
-    float* red_m = vnew + D;                               // [NW][GMAX]
-    float* red_l = red_m + NW * GMAX;                      // [NW][GMAX]
-    float* red_o = red_l + NW * GMAX;                      // [NW][G][D]
     __shared__ int is_last;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.y, kvh = blockIdx.x / p.S, split = blockIdx.x % p.S;
-    auto stamp = [&](int i) {   // optional phase timestamps of CTA (0, 0) (a measurement aid)
-        if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[i] = t;
-        }
-    };
-    stamp(0);
     pdl_launch_dependents();
     pdl_wait();
-    stamp(1);
-
-    const int P = (int)p.pos[b];                           // keys already in the cache
-    // Short contexts use fewer slices (at least 64 keys each); the surplus CTAs leave at once.
-    const int S = min(p.S, max(1, (P + 64) / 64));
-    if (split >= S) return;
-    const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
-    const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
-    const float qscale = rsqrtf((float)D);
-    // vectors: G query heads, then k, then v; pairs (2i, 2i+1) rotate together
-    for (int idx = tid; idx < (G + 2) * (D / 2); idx += NT) {
-        const int vec = idx / (D / 2), i = idx - vec * (D / 2);
-        int col;
-        if (vec < G) col = (kvh * G + vec) * D;
-        else if (vec == G) col = p.H * D + kvh * D;
-        else col = (p.H + p.Hkv) * D + kvh * D;
-        float x0 = __bfloat162float(x[col + 2 * i]), x1 = __bfloat162float(x[col + 2 * i + 1]);
-        if (vec <= G) {
-            const float cs = rope[2 * i], sn = rope[2 * i + 1];
-            const float r0 = bf16_round(__fmul_rn(x0, cs) - __fmul_rn(x1, sn));
-            const float r1 = bf16_round(__fmul_rn(x0, sn) + __fmul_rn(x1, cs));
-            x0 = r0; x1 = r1;
-        }
-        if (vec < G) { q_s[vec * D + 2 * i] = x0 * qscale; q_s[vec * D + 2 * i + 1] = x1 * qscale; }
-        else {
-            float* dst = vec == G ? knew : vnew;
-            dst[2 * i] = x0; dst[2 * i + 1] = x1;
-            if (split == 0) {
-                __nv_bfloat16* c = (vec == G ? p.cache_k : p.cache_v) + (((int64_t)b * p.L + P) * p.Hkv + kvh) * D;
-                c[2 * i] = __float2bfloat16_rn(x0);
-                c[2 * i + 1] = __float2bfloat16_rn(x1);
-            }
-        }
-    }
-    __syncthreads();
-    stamp(2);
-
-    const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
-    const int d0 = 4 * lane;
-    const bool live = d0 < D;
-    // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
-    float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
-#pragma unroll
-    for (int h = 0; h < GMAX; ++h) {
-        m_h[h] = -INFINITY; l_h[h] = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            o_h[h][e] = 0.f;
-            q_r[h][e] = (h < G && live) ? q_s[h * D + d0 + e] : 0.f;
-        }
-    }
-    constexpr int U = 4;   // keys per step: their scores are reduced together, then one softmax update
-    auto visit = [&](const float (&kf)[U][4], const float (&vf)[U][4], int n) {
-        float sc[GMAX][U];
-#pragma unroll
-        for (int h = 0; h < GMAX; ++h)
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-                sc[h][u] = q_r[h][0] * kf[u][0] + q_r[h][1] * kf[u][1] + q_r[h][2] * kf[u][2] + q_r[h][3] * kf[u][3];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int h = 0; h < GMAX; ++h)
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (h < G) sc[h][u] += __shfl_xor_sync(0xffffffffu, sc[h][u], o);
-#pragma unroll
-        for (int h = 0; h < GMAX; ++h) {
-            if (h < G) {
-                float mn = m_h[h];
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (u < n) mn = fmaxf(mn, sc[h][u]);
-                const float corr = __expf(m_h[h] - mn);
-                float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (u < n) {
-                        const float pr = __expf(sc[h][u] - mn);
-                        ps += pr;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) ov[e] += pr * vf[u][e];
-                    }
-                }
-                l_h[h] = l_h[h] * corr + ps;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
-                m_h[h] = mn;
-            }
-        }
-    };
-    auto unpack4 = [](const uint2& r, float (&f)[4]) {
-        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
-        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
-        f[0] = __low2float(lo2); f[1] = __high2float(lo2); f[2] = __low2float(hi2); f[3] = __high2float(hi2);
-    };
-    const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
-    const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
-    const int64_t key_stride = (int64_t)p.Hkv * D;
-    for (int j0 = lo + warp * U; j0 < hi; j0 += NW * U) {
-        uint2 kr[U], vr[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            kr[u] = make_uint2(0, 0); vr[u] = make_uint2(0, 0);
-            if (j0 + u < hi && live) {
-                kr[u] = *reinterpret_cast<const uint2*>(ck + (j0 + u) * key_stride);
-                vr[u] = *reinterpret_cast<const uint2*>(cv + (j0 + u) * key_stride);
-            }
-        }
-        float kf[U][4], vf[U][4];
-#pragma unroll
-        for (int u = 0; u < U; ++u) { unpack4(kr[u], kf[u]); unpack4(vr[u], vf[u]); }
-        visit(kf, vf, min(U, hi - j0));
-    }
-    if (split == S - 1 && warp == 0) {   // the new token attends to itself
-        float kf[U][4], vf[U][4];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                kf[u][e] = (u == 0 && live) ? knew[d0 + e] : 0.f;
-                vf[u][e] = (u == 0 && live) ? vnew[d0 + e] : 0.f;
-            }
-        visit(kf, vf, 1);
-    }
-    stamp(3);
-    // combine the warps
-#pragma unroll
-    for (int h = 0; h < GMAX; ++h) {
-        if (h < G) {
-            if (lane == 0) { red_m[warp * GMAX + h] = m_h[h]; red_l[warp * GMAX + h] = l_h[h]; }
-            if (live) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) red_o[(warp * G + h) * D + d0 + e] = o_h[h][e];
-            }
-        }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < G * D; idx += NT) {
-        const int h = idx / D, d = idx - h * D;
-        float mx = -INFINITY;
-        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, red_m[w * GMAX + h]);
-        float l = 0.f, o = 0.f;
-        for (int w = 0; w < NW; ++w) {
-            const float lw = red_l[w * GMAX + h];
-            if (lw > 0.f) {
-                const float f = __expf(red_m[w * GMAX + h] - mx);
-                l += lw * f;
-                o += red_o[(w * G + h) * D + d] * f;
-            }
-        }
-        const float on = l > 0.f ? o / l : 0.f;
-        if (S == 1) {                       // a single slice: this is the result
-            p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(on);
-            continue;
-        }
-        const int64_t slot = ((int64_t)b * p.H + kvh * G + h) * p.S + split;
-        p.part_o[slot * D + d] = on;
-        if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
-    }
-    stamp(4);
-    if (S == 1) return;
-    // the last slice of this (sequence, kv head) to finish combines all of them
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        int* ctr = &p.counters[b * p.Hkv + kvh];
-        const int ticket = atomicAdd(ctr, 1);
-        is_last = ticket == S - 1;
-        if (is_last) *ctr = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // weights of the slices per head, then one pass over the partial outputs
-    float* sl_m = red_o;                  // [G][S] max, then weight
-    float* sl_l = red_o + G * p.S;        // [G][S] sum
-    const int64_t head0 = (int64_t)b * p.H + kvh * G;
-    for (int idx = tid; idx < G * S; idx += NT) {
-        const int h = idx / S, sidx = idx - h * S;
-        sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
-        sl_l[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2 + 1]);
-    }
-    __syncthreads();
-    if (tid < G) {
-        float mx = -INFINITY, den = 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, sl_m[tid * p.S + sidx]);
-        for (int sidx = 0; sidx < S; ++sidx) {
-            const float l = sl_l[tid * p.S + sidx];
-            const float w = l > 0.f ? __expf(sl_m[tid * p.S + sidx] - mx) * l : 0.f;
-            sl_m[tid * p.S + sidx] = w;
-            den += w;
-        }
-        const float inv = den > 0.f ? 1.f / den : 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) sl_m[tid * p.S + sidx] *= inv;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < G * D; idx += NT) {
-        const int h = idx / D, d = idx - h * D;
-        const float* po = p.part_o + (head0 + h) * p.S * D + d;
-        float num = 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) num += sl_m[h * p.S + sidx] * __ldcg(po + (int64_t)sidx * D);
-        p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(num);
-    }
-    stamp(5);
+    attention_body<GMAX, AttnCfg<GMAX>::kWarps>(p, smem, &is_last, blockIdx.y, blockIdx.x / p.S, blockIdx.x % p.S,
+                                                 threadIdx.x, [] { __syncthreads(); });
 }
 
 // ---------------------------------------------------------------------------------------
@@ -649,104 +375,11 @@ __global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kern
 // (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281) and the
 // slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
 // ---------------------------------------------------------------------------------------
-constexpr int kHeadThreads = 512;
-constexpr int kHeadMaxLoads = 10;   // 16-byte loads per lane per pass over a row
-
 __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const HeadParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    float* xs = reinterpret_cast<float*>(smem);                 // [M][K]
-    float* scratch = xs + (size_t)p.M * p.K;                    // [16]
-    float* best_v = scratch + 16;                               // [16 warps][8]
-    int* best_i = reinterpret_cast<int*>(best_v + 16 * 8);      // [16 warps][8]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cta = blockIdx.x, n_cta = gridDim.x;
-
     pdl_launch_dependents();
     pdl_wait();
-
-    for (int m = 0; m < p.M; ++m) {
-        float ss = 0.f;
-        for (int k = tid; k < p.K; k += kHeadThreads) {
-            const float v = __bfloat162float(p.h[(int64_t)m * p.K + k]);
-            xs[(size_t)m * p.K + k] = v;
-            ss += v * v;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        __syncthreads();
-        if (lane == 0) scratch[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int i = 0; i < kHeadThreads / 32; ++i) tot += scratch[i];
-        const float rinv = rsqrtf(tot / (float)p.K + p.eps);
-        for (int k = tid; k < p.K; k += kHeadThreads)
-            xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * __bfloat162float(p.gamma[k]) * rinv);
-    }
-    __syncthreads();
-
-    const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
-    float bv[8];
-    int bi[8];
-#pragma unroll
-    for (int m = 0; m < 8; ++m) { bv[m] = -INFINITY; bi[m] = 0x7fffffff; }
-    const int vec_per_row = p.K / 8;     // 16-byte pieces
-    for (int row = r0 + warp; row < r1; row += kHeadThreads / 32) {
-        const uint4* wr = reinterpret_cast<const uint4*>(p.w + (int64_t)row * p.K);
-        float dot[8];
-#pragma unroll
-        for (int m = 0; m < 8; ++m) dot[m] = 0.f;
-        for (int base = 0; base < vec_per_row; base += 32 * kHeadMaxLoads) {
-            uint4 wv[kHeadMaxLoads];
-#pragma unroll
-            for (int u = 0; u < kHeadMaxLoads; ++u) {
-                const int v = base + u * 32 + lane;
-                if (v < vec_per_row) wv[u] = ldg_stream(wr + v);
-            }
-#pragma unroll
-            for (int u = 0; u < kHeadMaxLoads; ++u) {
-                const int v = base + u * 32 + lane;
-                if (v < vec_per_row) {
-                    const Vec8 wf = unpack_bf16x8(wv[u]);
-#pragma unroll
-                    for (int m = 0; m < 8; ++m) {
-                        if (m < p.M) {
-                            const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8);
-                            const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8 + 4);
-                            dot[m] += wf.v[0] * x0.x + wf.v[1] * x0.y + wf.v[2] * x0.z + wf.v[3] * x0.w +
-                                      wf.v[4] * x1.x + wf.v[5] * x1.y + wf.v[6] * x1.z + wf.v[7] * x1.w;
-                        }
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            if (m < p.M) {
-                float d = dot[m];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                d = bf16_round(d);
-                if (lane == 0 && p.logits) p.logits[(int64_t)m * p.V + row] = d;
-                if (d > bv[m]) { bv[m] = d; bi[m] = row; }     // rows ascend: first maximum wins
-            }
-        }
-    }
-    if (lane == 0) {
-#pragma unroll
-        for (int m = 0; m < 8; ++m) { best_v[warp * 8 + m] = bv[m]; best_i[warp * 8 + m] = bi[m]; }
-    }
-    __syncthreads();
-    if (tid < p.M) {
-        float v = -INFINITY;
-        int i = 0x7fffffff;
-        for (int w = 0; w < kHeadThreads / 32; ++w) {
-            const float wv = best_v[w * 8 + tid];
-            const int wi = best_i[w * 8 + tid];
-            if (wv > v || (wv == v && wi < i)) { v = wv; i = wi; }
-        }
-        p.part_val[cta * 8 + tid] = v;
-        p.part_idx[cta * 8 + tid] = i;
-    }
+    head_body(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
 }
 
 // Greedy choice over the per-CTA maxima; writes the chosen ids, feeds them back as the next

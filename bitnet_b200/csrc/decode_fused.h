@@ -95,4 +95,14 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl);
 int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl);
 
+// The whole decode step as one persistent kernel (decode_mega.cu).  mega_create builds the
+// device tables from fully filled parameter blocks - lin: [n_layers][4] in the order wqkv, wo,
+// w13, w2, planned for `grid` CTAs; att: [n_layers] - and returns null with the status set when
+// the step does not fit that kernel.
+void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, const HeadParams& hp, int n_layers, int M,
+                  int grid, size_t smem_optin);
+void mega_destroy(void* plan);
+int mega_launch(void* plan, const HeadParams& hp, int64_t* tokens, int64_t* pos, int64_t* out, int* error_flag,
+                cudaStream_t stream);
+
 }  // namespace bitnet

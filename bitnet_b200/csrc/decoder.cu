@@ -107,6 +107,8 @@ struct Decoder {
     float *part_o = nullptr, *part_ml = nullptr, *part_val = nullptr;
     unsigned long long* trace = nullptr;          // [n_layers * 4][8] phase timestamps (measurement aid)
     FusedLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
+    void* mega = nullptr;                         // tables of the persistent kernel, when it fits this model
+    bool use_mega = false;
 };
 
 static size_t align_up(size_t x) { return (x + 255) / 256 * 256; }
@@ -121,6 +123,10 @@ int bitnet_init(void) {
     set_status(kOk);
     return workspace() ? kOk : bitnet_last_status();
 }
+
+static void layer_params(const Decoder* d, int l, const int64_t* tokens, const int64_t* pos, FusedLinearParams lin[4],
+                         AttentionParams* ap);
+static HeadParams head_params(const Decoder* d, float* logits);
 
 void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
                             const void* tok_embeddings, const void* norm, const void* output, const float* rope) {
@@ -206,84 +212,123 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->part_val = reinterpret_cast<float*>(base + o_pv);
     d->part_idx = reinterpret_cast<int*>(base + o_pi);
     if (getenv("BITNET_TRACE")) d->trace = reinterpret_cast<unsigned long long*>(base + o_tr);
+
+    // The persistent single-kernel step, when the model fits it and the chain's plans use one
+    // CTA per SM.  Off unless BITNET_PERSISTENT=1 or bitnet_decoder_use_persistent turns it on.
+    if (ctas_per_sm <= 1 && !getenv("BITNET_NO_PERSISTENT")) {
+        std::vector<FusedLinearParams> lin((size_t)cfg->n_layers * 4);
+        std::vector<AttentionParams> att(cfg->n_layers);
+        for (int l = 0; l < cfg->n_layers; ++l) layer_params(d, l, nullptr, nullptr, &lin[(size_t)l * 4], &att[l]);
+        d->mega = mega_create(lin.data(), att.data(), head_params(d, nullptr), cfg->n_layers, B, d->n_sm,
+                              prop.sharedMemPerBlockOptin);
+        set_status(kOk);   // not fitting the persistent kernel is not an error: the chain remains
+        d->use_mega = d->mega && getenv("BITNET_PERSISTENT") && atoi(getenv("BITNET_PERSISTENT")) != 0;
+    }
     return d;
+}
+
+// Parameter blocks of layer l: lin[0..3] = wqkv, wo, w13, w2 and the attention between the
+// first two.  `tokens` and `pos` may be null when the caller supplies them at launch.
+static void layer_params(const Decoder* d, int l, const int64_t* tokens, const int64_t* pos, FusedLinearParams lin[4],
+                         AttentionParams* ap) {
+    const bitnet_decoder_config& c = d->cfg;
+    const int D = c.head_dim, H = c.n_heads, Hkv = c.n_kv_heads, dim = c.dim, F = c.ffn_dim;
+    const int Nqkv = (H + 2 * Hkv) * D;
+    const bitnet_decoder_layer& L = d->layers[l];
+    auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
+        p.w2t = static_cast<const uint8_t*>(w);
+        p.gamma = static_cast<const __nv_bfloat16*>(gamma);
+        p.acc_scratch = d->acc_scratch; p.error_flag = d->error_flag;
+    };
+    // wqkv: (embedding ->) h -> attention_norm -> wqkv -> xqkv
+    FusedLinearParams& q = lin[0];
+    q = d->plan_qkv;
+    common(q, L.wqkv, L.attention_norm);
+    if (l == 0) {
+        q.src = kSrcEmbedding;
+        q.tokens = tokens; q.emb = d->emb; q.h_copy = d->h;
+    } else {
+        q.x = d->h; q.ldx = dim;
+    }
+    q.out = d->xqkv; q.ldo = Nqkv;
+    q.seg.n_seg = 3; q.seg.end[0] = H * D; q.seg.end[1] = (H + Hkv) * D; q.seg.end[2] = Nqkv;
+    q.ws[0] = L.s_q; q.ws[1] = L.s_k; q.ws[2] = L.s_v;
+
+    *ap = AttentionParams{};
+    ap->xqkv = d->xqkv; ap->ld_qkv = Nqkv; ap->pos = pos; ap->rope = d->rope;
+    ap->cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap->cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
+    ap->out = d->attn_out; ap->part_o = d->part_o; ap->part_ml = d->part_ml; ap->counters = d->attn_counters;
+    ap->H = H; ap->Hkv = Hkv; ap->D = D; ap->L = c.max_seq_len; ap->S = d->kv_splits;
+
+    // wo: attention output -> attn_sub_norm -> wo -> h += ...
+    FusedLinearParams& o = lin[1];
+    o = d->plan_o;
+    common(o, L.wo, L.attn_sub_norm);
+    o.x = d->attn_out; o.ldx = dim;
+    o.out = d->h; o.ldo = dim;
+    o.seg.n_seg = 1; o.seg.end[0] = dim; o.ws[0] = L.s_o;
+
+    // w13: h -> ffn_norm -> w13 -> x13
+    FusedLinearParams& u = lin[2];
+    u = d->plan_13;
+    common(u, L.w13, L.ffn_norm);
+    u.x = d->h; u.ldx = dim;
+    u.out = d->x13; u.ldo = 2 * F;
+    u.seg.n_seg = 2; u.seg.end[0] = F; u.seg.end[1] = 2 * F; u.ws[0] = L.s_1; u.ws[1] = L.s_3;
+
+    // w2: relu(x1)^2 * x3 -> ffn_sub_norm -> w2 -> h += ...
+    FusedLinearParams& w = lin[3];
+    w = d->plan_2;
+    common(w, L.w2, L.ffn_sub_norm);
+    w.x = d->x13; w.ldx = 2 * F;
+    w.out = d->h; w.ldo = dim;
+    w.seg.n_seg = 1; w.seg.end[0] = dim; w.ws[0] = L.s_2;
+}
+
+static HeadParams head_params(const Decoder* d, float* logits) {
+    HeadParams hp{};
+    hp.w = d->output; hp.gamma = d->final_norm; hp.eps = d->cfg.norm_eps;
+    hp.h = d->h; hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
+    hp.M = d->cfg.batch; hp.K = d->cfg.dim; hp.V = d->cfg.vocab_size;
+    return hp;
 }
 
 static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, cudaStream_t stream,
                         bool linears_only) {
     const bitnet_decoder_config& c = d->cfg;
-    const int B = c.batch, D = c.head_dim, H = c.n_heads, Hkv = c.n_kv_heads, dim = c.dim, F = c.ffn_dim;
-    const int Nqkv = (H + 2 * Hkv) * D;
-    int launch_no = 0;
-    auto common = [&](FusedLinearParams& p, const void* w, const void* gamma) {
-        p.trace = d->trace ? d->trace + 16 * launch_no : nullptr;
-        static const int dbg = getenv("BITNET_DEBUG_SKIP") ? atoi(getenv("BITNET_DEBUG_SKIP")) : 0;
-        p.debug = dbg;
-        ++launch_no;
-        p.w2t = static_cast<const uint8_t*>(w);
-        p.gamma = static_cast<const __nv_bfloat16*>(gamma);
-        p.acc_scratch = d->acc_scratch; p.error_flag = d->error_flag;
-    };
+    if (d->mega && d->use_mega && !linears_only)
+        return mega_launch(d->mega, head_params(d, logits), tokens, pos, out, d->error_flag, stream);
+    static const int dbg = getenv("BITNET_DEBUG_SKIP") ? atoi(getenv("BITNET_DEBUG_SKIP")) : 0;
     for (int l = 0; l < c.n_layers; ++l) {
-        const bitnet_decoder_layer& L = d->layers[l];
-        // wqkv: (embedding ->) h -> attention_norm -> wqkv -> xqkv
-        FusedLinearParams p = d->plan_qkv;
-        common(p, L.wqkv, L.attention_norm);
-        if (l == 0) {
-            p.src = kSrcEmbedding;
-            p.tokens = tokens; p.emb = d->emb; p.h_copy = d->h;
-        } else {
-            p.x = d->h; p.ldx = dim;
+        FusedLinearParams lin[4];
+        AttentionParams ap;
+        layer_params(d, l, tokens, pos, lin, &ap);
+        for (int j = 0; j < 4; ++j) {
+            lin[j].trace = d->trace ? d->trace + 16 * (4 * l + j) : nullptr;
+            lin[j].debug = dbg;
         }
-        p.out = d->xqkv; p.ldo = Nqkv;
-        p.seg.n_seg = 3; p.seg.end[0] = H * D; p.seg.end[1] = (H + Hkv) * D; p.seg.end[2] = Nqkv;
-        p.ws[0] = L.s_q; p.ws[1] = L.s_k; p.ws[2] = L.s_v;
-        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
-
-        if (!linears_only) {
-            AttentionParams ap{};
-            ap.xqkv = d->xqkv; ap.ld_qkv = Nqkv; ap.pos = pos; ap.rope = d->rope;
-            ap.cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap.cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
-            ap.out = d->attn_out; ap.part_o = d->part_o; ap.part_ml = d->part_ml; ap.counters = d->attn_counters;
-            ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.L = c.max_seq_len; ap.S = d->kv_splits;
-            ap.trace = d->trace ? d->trace + 16 * (c.n_layers * 4 + l) : nullptr;
-            if (launch_attention(ap, B, stream, true)) return bitnet_last_status();
-        }
-
-        // wo: attention output -> attn_sub_norm -> wo -> h += ...
-        p = d->plan_o;
-        common(p, L.wo, L.attn_sub_norm);
-        p.x = d->attn_out; p.ldx = dim;
-        p.out = d->h; p.ldo = dim;
-        p.seg.n_seg = 1; p.seg.end[0] = dim; p.ws[0] = L.s_o;
-        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
-
-        // w13: h -> ffn_norm -> w13 -> x13
-        p = d->plan_13;
-        common(p, L.w13, L.ffn_norm);
-        p.x = d->h; p.ldx = dim;
-        p.out = d->x13; p.ldo = 2 * F;
-        p.seg.n_seg = 2; p.seg.end[0] = F; p.seg.end[1] = 2 * F; p.ws[0] = L.s_1; p.ws[1] = L.s_3;
-        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
-
-        // w2: relu(x1)^2 * x3 -> ffn_sub_norm -> w2 -> h += ...
-        p = d->plan_2;
-        common(p, L.w2, L.ffn_sub_norm);
-        p.x = d->x13; p.ldx = 2 * F;
-        p.out = d->h; p.ldo = dim;
-        p.seg.n_seg = 1; p.seg.end[0] = dim; p.ws[0] = L.s_2;
-        if (launch_fused_linear(p, stream, true)) return bitnet_last_status();
+        ap.trace = d->trace ? d->trace + 16 * (c.n_layers * 4 + l) : nullptr;
+        if (launch_fused_linear(lin[0], stream, true)) return bitnet_last_status();
+        if (!linears_only && launch_attention(ap, c.batch, stream, true)) return bitnet_last_status();
+        for (int j = 1; j < 4; ++j)
+            if (launch_fused_linear(lin[j], stream, true)) return bitnet_last_status();
     }
     if (linears_only) return kOk;
-    HeadParams hp{};
-    hp.w = d->output; hp.gamma = d->final_norm; hp.eps = c.norm_eps;
-    hp.h = d->h; hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
-    hp.M = B; hp.K = dim; hp.V = c.vocab_size;
-    if (launch_head(hp, d->head_grid, stream, true)) return bitnet_last_status();
+    if (launch_head(head_params(d, logits), d->head_grid, stream, true)) return bitnet_last_status();
     ArgmaxParams am{};
-    am.part_val = d->part_val; am.part_idx = d->part_idx; am.n_part = d->head_grid; am.M = B;
+    am.part_val = d->part_val; am.part_idx = d->part_idx; am.n_part = d->head_grid; am.M = c.batch;
     am.out = out; am.tokens = tokens; am.pos = pos;
     return launch_argmax(am, stream, true);
+}
+
+// Chooses between the single persistent kernel (on = 1) and the chain of kernels (on = 0) for
+// bitnet_decoder_step.  Returns the mode now in effect: 0 when the persistent kernel is not
+// available for this model (see mega_create).
+int bitnet_decoder_use_persistent(void* dec, int on) {
+    Decoder* d = static_cast<Decoder*>(dec);
+    if (!d) return 0;
+    d->use_mega = on != 0 && d->mega != nullptr;
+    return d->use_mega ? 1 : 0;
 }
 
 int bitnet_decoder_step(void* dec, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream) {
@@ -325,13 +370,15 @@ int bitnet_debug_read_workspace_words(unsigned long long* host_out, int n_words)
 
 int bitnet_decoder_kernels_per_step(void* dec) {
     Decoder* d = static_cast<Decoder*>(dec);
-    return d ? 5 * d->cfg.n_layers + 2 : 0;
+    if (!d) return 0;
+    return d->use_mega ? 1 : 5 * d->cfg.n_layers + 2;
 }
 
 void bitnet_decoder_destroy(void* dec) {
     Decoder* d = static_cast<Decoder*>(dec);
     if (!d) return;
     if (d->scratch) cudaFree(d->scratch);
+    mega_destroy(d->mega);
     delete d;
 }
 

@@ -30,7 +30,8 @@ class _DecoderLayer(ctypes.Structure):
 
 class FusedDecoder:
     """One decode step for a batch of at most 8 through `bitnet_decoder_step`: the whole
-    step is a chain of fused kernels inside the library (see include/bitnet_b200.h)."""
+    step runs inside the library (see include/bitnet_b200.h), either as a chain of fused
+    kernels or, with `use_persistent(True)`, as one persistent kernel; both give the same bits."""
 
     MAX_BATCH = 8
 
@@ -69,6 +70,13 @@ class FusedDecoder:
             raise _lib.BitnetError("bitnet_decoder_create failed")
         self.kernels_per_step = _lib.lib.bitnet_decoder_kernels_per_step(self.handle)
 
+    def use_persistent(self, on: bool) -> bool:
+        """Switches between the single persistent kernel and the kernel chain; returns whether
+        the persistent kernel is now in use (False when it does not fit the model)."""
+        got = bool(_lib.lib.bitnet_decoder_use_persistent(self.handle, 1 if on else 0))
+        self.kernels_per_step = _lib.lib.bitnet_decoder_kernels_per_step(self.handle)
+        return got
+
     def step(self, tokens: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, logits: Optional[torch.Tensor] = None):
         """tokens int64 [B] (or [B,1]), pos int64 [B], out int64 [B] on the device; enqueued on the current stream."""
         _lib.check(_lib.lib.bitnet_decoder_step(self.handle, _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(out),
@@ -89,8 +97,10 @@ class FusedDecoder:
 
 class Generator:
     def __init__(self, model: Transformer, batch: int, max_seq_len: int, use_cuda_graph: bool = True,
-                 fused: Optional[bool] = None):
-        """fused=None picks the fused kernel chain whenever it applies (kernel model, batch <= 8)."""
+                 fused: Optional[bool] = None, persistent: Optional[bool] = None):
+        """fused=None picks the in-library decode step whenever it applies (kernel model, batch
+        <= 8).  persistent=True/False chooses the single persistent kernel or the kernel chain
+        for it; None leaves the library's default."""
         self.model, self.batch, self.max_seq_len = model, batch, max_seq_len
         dev = model.tok_embeddings.weight.device
         self.device = dev
@@ -107,12 +117,15 @@ class Generator:
         if fused and not can_fuse:
             raise ValueError("the fused decode chain needs the kernel model and batch <= 8")
         self.fused: Optional[FusedDecoder] = None
+        self.persistent = False
         if can_fuse and fused is not False:
             if model.rope is None or model.rope.shape[0] < max_seq_len:
                 from .model import rope_table
                 model.rope = rope_table(model.args.head_dim, max(max_seq_len, model.max_seq_len),
                                         model.args.rope_theta, dev)
             self.fused = FusedDecoder(model, self.cache, batch, max_seq_len)
+            if persistent is not None:
+                self.persistent = self.fused.use_persistent(persistent)
 
     def _step(self):
         if self.fused is not None:

@@ -165,6 +165,13 @@ int bitnet_debug_read_workspace_words(unsigned long long* host_out, int n_words)
 int bitnet_decoder_error_flag(void* decoder);
 /* Number of kernels one step launches. */
 int bitnet_decoder_kernels_per_step(void* decoder);
+/* Chooses how bitnet_decoder_step runs: on = 1, the whole step as one persistent kernel (one
+ * CTA per SM, launched cooperatively, grid-wide barriers between the phases of a layer);
+ * on = 0, a chain of five kernels per layer.  Both give the same bits.  Returns the mode in
+ * effect afterwards: 0 when the persistent kernel does not fit the model (grouped-query ratio
+ * above 4, or shared memory).  Environment: BITNET_PERSISTENT=1 turns it on at creation,
+ * BITNET_NO_PERSISTENT=1 removes it.  No counterpart in the reference. */
+int bitnet_decoder_use_persistent(void* decoder, int on);
 void bitnet_decoder_destroy(void* decoder);
 
 /* ---- weight layout conversion ----------------------------------------------------------
