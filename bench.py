@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="2b", help="architecture preset (2b, 3b, 8b, 100b)")
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--engine", choices=["persistent", "chain"], default="persistent",
+                    help="decode step as one persistent kernel (falls back to the chain when it does not fit) or as "
+                         "the chain of kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
     ap.add_argument("--tp", action="store_true",
@@ -294,7 +297,8 @@ def run_ours(a, args_model):
     B, K, W = a.batch, a.steps, a.warmup
     max_seq = (PROMPT_LEN + 2 * (K + W) + 3 * W + 64 + 127) // 128 * 128
     model = build_synthetic(args_model, seed=SEED + rank, device=dev, max_seq_len=max_seq)
-    gen = Generator(model, B, max_seq)
+    gen = Generator(model, B, max_seq, persistent=(a.engine == "persistent") if B <= 8 else None)
+    persistent = gen.persistent
     g = torch.Generator(device=dev)
     g.manual_seed(SEED + 17 * rank)
     prompt = torch.randint(0, args_model.vocab_size, (B, PROMPT_LEN), generator=g, device=dev)

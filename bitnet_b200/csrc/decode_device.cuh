@@ -66,24 +66,68 @@ struct AttnCfg {
     static constexpr int kThreads = kWarps * 32;
 };
 
-// Attention of one (sequence b, kv head kvh, KV slice `split`) by NW warps.  `smem` needs
+// Number of KV slices for a context of P cached keys when at most s_max are available.  The
+// split costs a second pass (partials through memory, a ticket, a combine), which only pays
+// off once a single CTA would walk the keys for longer than that.
+__device__ __forceinline__ int attention_slices(int s_max, int P) { return P <= 384 ? 1 : min(s_max, (P + 64) / 64); }
+
+// Which part of the attention CTA number x of a sequence takes, x in [0, Hkv * s_max).  With a
+// single slice every query head gets its own CTA (the scores of one head need a quarter of the
+// shuffles); with several slices a CTA takes all query heads of a kv head for one slice.
+struct AttnItem {
+    int kvh, h0, G, split, S;   // G = 0: nothing to do
+};
+__device__ __forceinline__ AttnItem attention_item(const AttentionParams& p, int x, int P) {
+    const int Gfull = p.H / p.Hkv;
+    const int S = attention_slices(p.S, P);
+    AttnItem it{0, 0, 0, 0, S};
+    if (S == 1 && p.S >= Gfull) {
+        if (x < p.H) { it.kvh = x / Gfull; it.h0 = x - it.kvh * Gfull; it.G = 1; }
+    } else {
+        it.kvh = x / p.S; it.split = x - it.kvh * p.S;
+        if (it.split < S) it.G = Gfull;
+    }
+    return it;
+}
+
+// Attention of query heads h0 .. h0+G-1 of kv head kvh of sequence b over KV slice `split` of S,
+// by NW warps, with P keys already in the cache (the caller reads p.pos[b]; the body does not).
+// A subset of the heads (G < H / Hkv) is only allowed with S = 1.  `smem` needs
 // attention_smem() bytes; `sync` is a barrier over the NW * 32 participating threads.
-template <int GMAX, int NW, class Sync>
+// The first keys of the slice are requested before `wait()`, which returns once the new token's
+// q, k, v (xqkv) are visible: the cache rows and the positions must not change meanwhile.
+template <int GMAX, int NW, class Sync, class Wait>
 __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t* smem, int* is_last_s, int b, int kvh,
-                                               int split, int tid, Sync sync) {
+                                               int h0, int G, int split, int S, int P, int tid, Sync sync, Wait wait) {
     constexpr int NT = NW * 32;
     const int warp = tid >> 5, lane = tid & 31;
-    const int D = p.D, G = p.H / p.Hkv;
+    const int D = p.D, Gfull = p.H / p.Hkv;
     float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
     float* knew = q_s + G * D;                             // [D]
     float* vnew = knew + D;                                // [D]
     float* red_m = vnew + D;                               // [NW][GMAX]
     float* red_l = red_m + NW * GMAX;                      // [NW][GMAX]
     float* red_o = red_l + NW * GMAX;                      // [NW][G][D]
-    const int P = (int)p.pos[b];                           // keys already in the cache
-    // Short contexts use fewer slices (at least 64 keys each); the surplus CTAs leave at once.
-    const int S = min(p.S, max(1, (P + 64) / 64));
-    if (split >= S) return;
+    constexpr int U = 4;   // keys per step: their scores are reduced together, then one softmax update
+    const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
+    const int d0 = 4 * lane;
+    const bool live = d0 < D;
+    const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
+    const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
+    const int64_t key_stride = (int64_t)p.Hkv * D;
+    uint2 kr[U], vr[U];
+    auto request = [&](int j0) {   // raw rows of keys j0 .. j0+U-1 (zero beyond the slice)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            kr[u] = make_uint2(0, 0); vr[u] = make_uint2(0, 0);
+            if (j0 + u < hi && live) {
+                kr[u] = *reinterpret_cast<const uint2*>(ck + (j0 + u) * key_stride);
+                vr[u] = *reinterpret_cast<const uint2*>(cv + (j0 + u) * key_stride);
+            }
+        }
+    };
+    request(lo + warp * U);
+    wait();
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
@@ -91,7 +135,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     for (int idx = tid; idx < (G + 2) * (D / 2); idx += NT) {
         const int vec = idx / (D / 2), i = idx - vec * (D / 2);
         int col;
-        if (vec < G) col = (kvh * G + vec) * D;
+        if (vec < G) col = (kvh * Gfull + h0 + vec) * D;
         else if (vec == G) col = p.H * D + kvh * D;
         else col = (p.H + p.Hkv) * D + kvh * D;
         const unsigned int xx = __ldcg(reinterpret_cast<const unsigned int*>(x + col + 2 * i));   // L2: written by other SMs
@@ -106,7 +150,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         else {
             float* dst = vec == G ? knew : vnew;
             dst[2 * i] = x0; dst[2 * i + 1] = x1;
-            if (split == 0) {
+            if (split == 0 && h0 == 0) {
                 __nv_bfloat16* c = (vec == G ? p.cache_k : p.cache_v) + (((int64_t)b * p.L + P) * p.Hkv + kvh) * D;
                 c[2 * i] = __float2bfloat16_rn(x0);
                 c[2 * i + 1] = __float2bfloat16_rn(x1);
@@ -115,9 +159,6 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     }
     sync();
 
-    const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
-    const int d0 = 4 * lane;
-    const bool live = d0 < D;
     // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
     float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
 #pragma unroll
@@ -129,7 +170,6 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
             q_r[h][e] = (h < G && live) ? q_s[h * D + d0 + e] : 0.f;
         }
     }
-    constexpr int U = 4;   // keys per step: their scores are reduced together, then one softmax update
     auto visit = [&](const float (&kf)[U][4], const float (&vf)[U][4], int n) {
         float sc[GMAX][U];
 #pragma unroll
@@ -174,22 +214,11 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
         f[0] = __low2float(lo2); f[1] = __high2float(lo2); f[2] = __low2float(hi2); f[3] = __high2float(hi2);
     };
-    const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
-    const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
-    const int64_t key_stride = (int64_t)p.Hkv * D;
     for (int j0 = lo + warp * U; j0 < hi; j0 += NW * U) {
-        uint2 kr[U], vr[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            kr[u] = make_uint2(0, 0); vr[u] = make_uint2(0, 0);
-            if (j0 + u < hi && live) {
-                kr[u] = *reinterpret_cast<const uint2*>(ck + (j0 + u) * key_stride);
-                vr[u] = *reinterpret_cast<const uint2*>(cv + (j0 + u) * key_stride);
-            }
-        }
         float kf[U][4], vf[U][4];
 #pragma unroll
         for (int u = 0; u < U; ++u) { unpack4(kr[u], kf[u]); unpack4(vr[u], vf[u]); }
+        if (j0 + NW * U < hi) request(j0 + NW * U);   // in flight during this visit
         visit(kf, vf, min(U, hi - j0));
     }
     if (split == S - 1 && warp == 0) {   // the new token attends to itself
@@ -230,10 +259,10 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         }
         const float on = l > 0.f ? o / l : 0.f;
         if (S == 1) {                       // a single slice: this is the result
-            p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(on);
+            p.out[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(on);
             continue;
         }
-        const int64_t slot = ((int64_t)b * p.H + kvh * G + h) * p.S + split;
+        const int64_t slot = ((int64_t)b * p.H + kvh * Gfull + h0 + h) * p.S + split;
         p.part_o[slot * D + d] = on;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
@@ -253,7 +282,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     // weights of the slices per head, then one pass over the partial outputs
     float* sl_m = red_o;                  // [G][S] max, then weight
     float* sl_l = red_o + G * p.S;        // [G][S] sum
-    const int64_t head0 = (int64_t)b * p.H + kvh * G;
+    const int64_t head0 = (int64_t)b * p.H + kvh * Gfull + h0;
     for (int idx = tid; idx < G * S; idx += NT) {
         const int h = idx / S, sidx = idx - h * S;
         sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
@@ -278,7 +307,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         const float* po = p.part_o + (head0 + h) * p.S * D + d;
         float num = 0.f;
         for (int sidx = 0; sidx < S; ++sidx) num += sl_m[h * p.S + sidx] * __ldcg(po + (int64_t)sidx * D);
-        p.out[(int64_t)b * p.H * D + (kvh * G + h) * D + d] = __float2bfloat16_rn(num);
+        p.out[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(num);
     }
 }
 

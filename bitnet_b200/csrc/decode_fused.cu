@@ -366,8 +366,16 @@ __global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kern
     __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
-    attention_body<GMAX, AttnCfg<GMAX>::kWarps>(p, smem, &is_last, blockIdx.y, blockIdx.x / p.S, blockIdx.x % p.S,
-                                                 threadIdx.x, [] { __syncthreads(); });
+    const int P = (int)p.pos[blockIdx.y];
+    const AttnItem it = attention_item(p, blockIdx.x, P);
+    if (it.G == 0) return;
+    constexpr int NW = AttnCfg<GMAX>::kWarps;
+    if (it.G == 1)
+        attention_body<1, NW>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, 1, it.split, it.S, P, threadIdx.x,
+                              [] { __syncthreads(); }, [] {});
+    else
+        attention_body<GMAX, NW>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
+                                 [] { __syncthreads(); }, [] {});
 }
 
 // ---------------------------------------------------------------------------------------

@@ -103,6 +103,6 @@ void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, cons
                   int grid, size_t smem_optin);
 void mega_destroy(void* plan);
 int mega_launch(void* plan, const HeadParams& hp, int64_t* tokens, int64_t* pos, int64_t* out, int* error_flag,
-                cudaStream_t stream);
+                unsigned long long* trace, cudaStream_t stream);
 
 }  // namespace bitnet

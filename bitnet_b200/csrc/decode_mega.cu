@@ -29,7 +29,11 @@ constexpr int kMaxHalfStages = 4;                         // a round: up to 4 st
 constexpr int kMegaWarps = 16;                            // consumer warps
 constexpr int kMegaConsumers = kMegaWarps * 32;           // 512
 constexpr int kMegaThreads = kMegaConsumers;
+constexpr int kIssueTid = 256;                            // lane 0 of warp 8 issues the weight copies: idle during prologues
 constexpr int kMiscBytes = 1024;                          // barriers and small arrays behind the ring
+constexpr int kLinBlockBytes = (sizeof(FusedLinearParams) + 127) / 128 * 128;
+constexpr int kAttBlockBytes = (sizeof(AttentionParams) + 127) / 128 * 128;
+constexpr int kMaxLinears = 1024;                         // BitLinears per step the issue table holds
 
 __device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kMegaConsumers) : "memory"); }
 __device__ __forceinline__ void psync() { asm volatile("bar.sync 2, %0;\n" ::"n"(kPrologueThreads) : "memory"); }
@@ -50,18 +54,6 @@ __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
     return v;
 }
 
-struct Range {
-    int t0, n_tiles;
-};
-__device__ __forceinline__ Range cta_range(const FusedLinearParams* d, int cta) {
-    if (cta >= d->grid) return Range{0, 0};
-    return Range{cta * d->tiles_base + min(cta, d->tiles_rem), d->tiles_base + (cta < d->tiles_rem ? 1 : 0)};
-}
-__device__ __forceinline__ int cta_of_tile(const FusedLinearParams* d, int t) {
-    const int big = d->tiles_rem * (d->tiles_base + 1);
-    return t < big ? t / (d->tiles_base + 1) : d->tiles_rem + (t - big) / d->tiles_base;
-}
-
 struct MegaParams {
     const FusedLinearParams* lin;    // [n_layers][4]: wqkv, wo, w13, w2 (device memory)
     const AttentionParams* att;      // [n_layers]
@@ -72,7 +64,35 @@ struct MegaParams {
     int64_t* out;                    // [M]
     unsigned int* bar;               // [0] barrier arrivals, [1] exit tickets; zero between steps
     int* error_flag;
+    unsigned long long* trace;       // optional: [n_layers * 5][16] timestamps of CTA 0 (a measurement aid)
 };
+
+__device__ __forceinline__ void stamp(const MegaParams& P, int cta, int tid, int phase, int i) {
+    if (P.trace && cta == 0 && tid == 0) {
+        P.trace[phase * 16 + i] = (unsigned long long)clock64();   // SM cycles: CTA 0 stays on one SM
+    }
+}
+
+__device__ __forceinline__ void cstamp(const MegaParams& P, int cta, int tid, int phase, int i) {
+    if (P.trace && cta == 0 && tid == 0) P.trace[phase * 16 + i] = (unsigned long long)clock64();
+}
+
+// What the copy stream needs to know of a BitLinear: this CTA's tiles.
+struct LinIssue {
+    const uint8_t* src;
+    int n_tiles, pad;
+};
+
+// Whole row groups per CTA: row group rg belongs to CTA floor(rg * n_cta / row_groups)'s range,
+// so every output row is summed inside one CTA and nothing is exchanged between CTAs.
+struct Range {
+    int rg0, n_rg;
+};
+__device__ __forceinline__ Range cta_range(int row_groups, int cta, int n_cta) {   // row_groups * n_cta < 2^32
+    const unsigned int rg0 = (unsigned int)row_groups * (unsigned int)cta / (unsigned int)n_cta,
+                       rg1 = (unsigned int)row_groups * (unsigned int)(cta + 1) / (unsigned int)n_cta;
+    return Range{(int)rg0, (int)(rg1 - rg0)};
+}
 
 struct Shared {          // views into the dynamic shared memory
     uint8_t* ring;
@@ -83,30 +103,34 @@ struct Shared {          // views into the dynamic shared memory
     int* ysum_s;         // [8]
     float* a_s;          // [8]
     int* flag_s;         // [0] abort, [1] attention is_last, [2] exit ticket is last
+    int64_t* pos_s;      // [8] positions at the start of the step
+    LinIssue* issue;     // [n_layers * 4]
+    FusedLinearParams* lin_s;   // [2] parameter blocks of the current and the next BitLinear
+    AttentionParams* att_s;     // [2] same for the attention
     uint8_t* u;          // phase-private region
 };
 
 // Position of the copy stream: the next round to issue is round `r` of BitLinear `ph`; `gr`
-// rounds have been issued so far.  Only thread 0 uses it.
+// rounds have been issued so far; `pending` consumed rounds still wait for their successor to
+// be issued.  Only thread kIssueTid uses it.
 struct Cursor {
     int ph, r;
     unsigned int gr;
+    int pending;
 };
 // Issues the bulk copies of the next round of the step, if there is one.
-__device__ __noinline__ void issue_round(const MegaParams& P, const Shared& sh, int cta, Cursor& c) {
+__device__ __noinline__ void issue_round(const MegaParams& P, const Shared& sh, Cursor& c) {
     const int hs = P.half_stages, round_tiles = hs * kStageTiles, n_lin = P.n_layers * 4;
     while (c.ph < n_lin) {
-        const FusedLinearParams* d = P.lin + c.ph;
-        const Range rng = cta_range(d, cta);
-        const int n_rounds = (rng.n_tiles + round_tiles - 1) / round_tiles;
-        if (c.r >= n_rounds) {
+        const LinIssue li = sh.issue[c.ph];
+        if (c.r * round_tiles >= li.n_tiles) {
             ++c.ph;
             c.r = 0;
             continue;
         }
         const int half = c.gr & 1;
-        const int nr = min(round_tiles, rng.n_tiles - c.r * round_tiles);
-        const uint8_t* src = d->w2t + ((int64_t)rng.t0 + (int64_t)c.r * round_tiles) * kTileBytes;
+        const int nr = min(round_tiles, li.n_tiles - c.r * round_tiles);
+        const uint8_t* src = li.src + (int64_t)c.r * round_tiles * kTileBytes;
 #pragma unroll 1
         for (int s = 0; s < hs; ++s) {
             uint64_t* bar = &sh.full_bar[half * hs + s];
@@ -134,16 +158,22 @@ __device__ __noinline__ void drain_rounds(const Shared& sh, int hs, const Cursor
     }
 }
 
-// Arrival at grid barrier number `k` of the step (counted from 0): everything this CTA wrote
-// is visible to whoever later sees the count.
+// Copies a parameter block from global to shared memory with `n_threads` threads starting at
+// thread `first`; visible to the CTA after its next barrier.
+template <class T>
+__device__ __forceinline__ void fetch_block(T* dst, const T* src, int tid, int first) {
+    static_assert(sizeof(T) % 8 == 0, "parameter blocks are copied in 8-byte words");
+    const int i = tid - first;
+    if (i >= 0 && i < (int)(sizeof(T) / 8))
+        reinterpret_cast<unsigned long long*>(dst)[i] = __ldg(reinterpret_cast<const unsigned long long*>(src) + i);
+}
+
+// Arrival at a grid barrier: everything this CTA wrote is visible to whoever later sees the count.
 __device__ __forceinline__ void grid_arrive(unsigned int* ctr, int tid) {
     csync();
-    if (tid == 0) {
-        __threadfence();
-        atomicAdd(ctr, 1u);
-    }
+    if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(ctr) : "memory");
 }
-// Wait until all n_cta CTAs have arrived at barrier k.  False when the wait gave up.
+// Wait until the arrivals reach `target`.  False when the wait gave up.
 __device__ __forceinline__ bool grid_wait(unsigned int* ctr, unsigned int target, int tid, const Shared& sh, int* error_flag) {
     if (tid == 0) {
         const long long t0 = clock64();
@@ -166,25 +196,28 @@ struct LinLayout {
     int8_t* ys;
     int k_pad, y_stride;
 };
-__device__ __forceinline__ LinLayout lin_layout(const FusedLinearParams* d, uint8_t* u, int M) {
+__device__ __host__ __forceinline__ int rg_cap(int N, int n_cta) { return ((N + 15) / 16 + n_cta - 1) / n_cta; }
+__device__ __forceinline__ LinLayout lin_layout(const FusedLinearParams* d, uint8_t* u, int n_cta) {
     LinLayout l;
     l.sacc = reinterpret_cast<int*>(u);
-    l.xv = reinterpret_cast<__nv_bfloat16*>(l.sacc + d->r_max * 128);
+    l.xv = reinterpret_cast<__nv_bfloat16*>(l.sacc + rg_cap(d->N, n_cta) * 128);
     l.xb = l.xv + d->K_even;
     l.gs = l.xb + d->K_even;
     l.ys = reinterpret_cast<int8_t*>(l.gs + d->K_even);
     l.k_pad = d->k_tiles * kTileCols;
     l.y_stride = l.k_pad + 16;
-    (void)M;
     return l;
 }
 
 // Work of a BitLinear phase that does not depend on other CTAs: clear the row sums, stage the
-// norm weight, write the row of zeros that the unused MMA columns read.
-__device__ __forceinline__ void linear_pre(const FusedLinearParams* d, const Shared& sh, int M, int tid) {
-    const LinLayout l = lin_layout(d, sh.u, M);
+// norm weight, write the row of zeros that the unused MMA columns read, and read the old
+// residual value of the output element this thread will finalise (the residual stream was
+// completed two phases ago).  `d` is the block in shared memory.
+__device__ __forceinline__ float linear_pre(const FusedLinearParams* d, const Shared& sh, int M, int cta, int n_cta, int tid) {
+    const LinLayout l = lin_layout(d, sh.u, n_cta);
+    const int cap = rg_cap(d->N, n_cta) * 128;
 #pragma unroll 1
-    for (int i = tid; i < d->r_max * 128; i += kMegaConsumers) l.sacc[i] = 0;
+    for (int i = tid; i < cap; i += kMegaConsumers) l.sacc[i] = 0;
     if (d->gamma && tid < kPrologueThreads) {   // each prologue thread stages the pieces it will read itself
 #pragma unroll 1
         for (int v = tid; v < d->K_even / 8; v += kPrologueThreads) cp_async16(l.gs + v * 8, d->gamma + v * 8);
@@ -192,22 +225,39 @@ __device__ __forceinline__ void linear_pre(const FusedLinearParams* d, const Sha
 #pragma unroll 1
     for (int v = tid; v < l.y_stride / 16; v += kMegaConsumers)
         *reinterpret_cast<uint4*>(l.ys + (size_t)M * l.y_stride + v * 16) = make_uint4(0, 0, 0, 0);
+    float h_old = 0.f;
+    if (d->out_kind == kOutResidual) {
+        const Range rng = cta_range((d->N + 15) / 16, cta, n_cta);
+        if (tid < rng.n_rg * 16 * M) {
+            const int m = tid / (rng.n_rg * 16), row = rng.rg0 * 16 + (tid - m * (rng.n_rg * 16));
+            if (row < d->N)
+                h_old = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(d->out + (int64_t)m * d->ldo + row)) << 16);
+        }
+    }
+    return h_old;
 }
 
-// The BitLinear itself.  `gr` counts this CTA's ring rounds over the whole step.
+// The BitLinear itself.  `gr` counts this CTA's ring rounds over the whole step; `h_pre` is the
+// value linear_pre returned.
 __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLinearParams* d, const Shared& sh, int cta,
-                                             int tid, unsigned int& gr, Cursor& cur) {
+                                             int n_cta, int tid, unsigned int& gr, Cursor& cur, int phase_no, float h_pre) {
     const int64_t* tokens = P.tokens;
     const int M = P.M, hs = P.half_stages;
     int* error_flag = P.error_flag;
     const int warp = tid >> 5, lane = tid & 31;
-    const LinLayout l = lin_layout(d, sh.u, M);
+    const LinLayout l = lin_layout(d, sh.u, n_cta);
     const int K = d->K, k_tiles = d->k_tiles, src = d->src;
     const int n_vec = d->K_even / 8;
-    const Range rng = cta_range(d, cta);
-    const int t0 = rng.t0, n_tiles = rng.n_tiles;
+    const Range rng = cta_range((d->N + 15) / 16, cta, n_cta);
+    const int n_tiles = rng.n_rg * k_tiles;
 
-    // ---- prologue: int8 activations of every token, by warps 0-7 -------------------------
+    // ---- prologue: int8 activations of every token, by warps 0-7; meanwhile the copies that
+    // refill the ring half the previous BitLinear left are issued -----------------------------
+    cstamp(P, cta, tid, phase_no, 6);
+    if (tid == kIssueTid) {
+#pragma unroll 1
+        for (; cur.pending > 0; --cur.pending) issue_round(P, sh, cur);
+    }
     if (warp < 8) {
 #pragma unroll 1
         for (int m = 0; m < M; ++m) {
@@ -218,6 +268,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
                 if (src == kSrcGlu) cp_async16(l.xb + v * 8, row + K + v * 8);
             }
             cp_async_wait_all();   // also covers the norm weight staged before the barrier
+            cstamp(P, cta, tid, phase_no, 7);
             if (src == kSrcGlu) {
 #pragma unroll 1
                 for (int v = tid; v < n_vec; v += kPrologueThreads) {
@@ -238,6 +289,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
             float a, sy_warp;
             norm_quant_row(l.xv, K, l.k_pad, d->gamma ? l.gs : nullptr, d->eps, l.ys + (size_t)m * l.y_stride, sh.scratch,
                            tid, PSync(), a, sy_warp);
+            cstamp(P, cta, tid, phase_no, 8);
             if (lane == 0) sh.sy_part[m * 8 + warp] = sy_warp;
             if (tid == 0) sh.a_s[m] = a;
             psync();
@@ -249,17 +301,18 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
             sh.ysum_s[tid] = (int)t;
         }
     }
+    cstamp(P, cta, tid, phase_no, 9);
     csync();
+    cstamp(P, cta, tid, phase_no, 10);
 
     // ---- matmul over the staged tiles (see fused_linear_kernel for the scheme) ------------
     const int g = lane >> 2, q = lane & 3;
-    const int rg_first = t0 / k_tiles;
     const int round_tiles = hs * kStageTiles;
     int cur_rg = -1;
     int acc[4][4];
     auto flush = [&]() {
         if (cur_rg >= 0) {
-            int* dst = l.sacc + (cur_rg - rg_first) * 128;
+            int* dst = l.sacc + cur_rg * 128;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int tok = 2 * q + (i & 1);
@@ -279,6 +332,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
     const int ysub0 = (2 * q < M) ? sh.ysum_s[2 * q] : 0, ysub1 = (2 * q + 1 < M) ? sh.ysum_s[2 * q + 1] : 0;
     const int n_rounds = (n_tiles + round_tiles - 1) / round_tiles;
     bool ok = true;
+    cstamp(P, cta, tid, phase_no, 2);
 #pragma unroll 1
     for (int r = 0; r < n_rounds; ++r, ++gr) {
         const int half = gr & 1;
@@ -297,7 +351,8 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
                 break;
             }
         }
-        const int t_first = t0 + r * round_tiles + lo;
+        cstamp(P, cta, tid, phase_no, 11);
+        const int t_first = r * round_tiles + lo;          // tile index within this CTA's range
         int rg = t_first / k_tiles, kt = t_first - rg * k_tiles;
         const uint8_t* tile = sh.ring + (size_t)half * hs * kStageBytes + lo * kTileBytes + lane * 16;
 #pragma unroll 1
@@ -324,12 +379,13 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
                 ++rg;
             }
         }
+        cstamp(P, cta, tid, phase_no, 12);
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.empty_bar[half]);
-        if (tid == 0 && r + 1 < n_rounds) {
+        if (tid == kIssueTid && r + 1 < n_rounds) {
             // more rounds of this BitLinear follow: refill this half as soon as all warps left it
             if (mbar_wait(&sh.empty_bar[half], parity)) {
-                issue_round(P, sh, cta, cur);
+                issue_round(P, sh, cur);
             } else {
                 atomicExch(error_flag, 1);
                 sh.flag_s[0] = 1;
@@ -337,54 +393,39 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
         }
     }
     flush();
+    cstamp(P, cta, tid, phase_no, 13);
     csync();
+    cstamp(P, cta, tid, phase_no, 14);
     if (sh.flag_s[0]) return false;
     if (n_tiles == 0) return true;
-    if (tid == 0) issue_round(P, sh, cta, cur);   // every warp has left the last round's half
+    ++cur.pending;   // every warp has left the last round's half: refilled during the next prologue
+    cstamp(P, cta, tid, phase_no, 15);
 
-    // ---- epilogue: rows whose sums are complete here are finalised here; row groups shared
-    // with other CTAs go through the 64-bit ticket slots, the last contributor finalises ----
-    const int n_rg = (t0 + n_tiles - 1) / k_tiles - rg_first + 1;
-    const int rg_last = rg_first + n_rg - 1;
-    const bool part_first = t0 > rg_first * k_tiles || (t0 + n_tiles) < (rg_first + 1) * k_tiles;
-    const bool part_last = n_rg > 1 && (t0 + n_tiles) < (rg_last + 1) * k_tiles;
+    // ---- epilogue: every row of this CTA's row groups is complete --------------------------
     __nv_bfloat16* out = d->out;
     const int64_t ldo = d->ldo;
     const int N = d->N;
     const bool residual = d->out_kind == kOutResidual;
+    const int per_m = rng.n_rg * 16;
 #pragma unroll 1
-    for (int idx = tid; idx < n_rg * 16 * M; idx += kMegaConsumers) {
-        const int m = idx / (n_rg * 16), rem = idx - m * (n_rg * 16);
-        const int li = rem >> 4, r = rem & 15;
-        const int rgi = rg_first + li, row = rgi * 16 + r;
-        const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
-        if (row >= N && !partial) continue;
-        float h_old = 0.f;
-        if (residual && row < N)   // written by another SM in an earlier phase: read it from L2
-            h_old = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(out + (int64_t)m * ldo + row)) << 16);
-        int v = l.sacc[rem * 8 + m];
-        if (partial) {
-            const int lo_t = rgi * k_tiles, hi_t = lo_t + k_tiles - 1;
-            const long long expected = cta_of_tile(d, hi_t) - cta_of_tile(d, lo_t) + 1;
-            unsigned long long* slot = &d->acc_scratch[(int64_t)rgi * 128 + r * 8 + m];
-            const unsigned long long add = (unsigned long long)((long long)v + (1LL << 40));
-            const long long tot = (long long)(atomicAdd(slot, add) + add);
-            const long long cnt = (tot + (1LL << 39)) >> 40;
-            if (cnt != expected) continue;
-            v = (int)(tot - (cnt << 40));
-            *slot = 0ull;
-        }
+    for (int idx = tid; idx < per_m * M; idx += kMegaConsumers) {
+        const int m = idx / per_m, rem = idx - m * per_m;      // consecutive threads -> consecutive rows
+        const int row = rng.rg0 * 16 + rem;
         if (row >= N) continue;
-        const float lin = lin_out(v, sh.a_s[m], d->ws[segment_of(d->seg, row)]);
+        float h_old = h_pre;
+        if (residual && idx >= kMegaConsumers)   // beyond the element read ahead; written by another SM: read from L2
+            h_old = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(out + (int64_t)m * ldo + row)) << 16);
+        const float lin = lin_out(l.sacc[rem * 8 + m], sh.a_s[m], d->ws[segment_of(d->seg, row)]);
         out[(int64_t)m * ldo + row] = __float2bfloat16_rn(residual ? h_old + lin : lin);
     }
+    stamp(P, cta, tid, phase_no, 4);
     return true;
 }
-
 
 __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const MegaParams P) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int hs = P.half_stages;
+    const int n_lin = P.n_layers * 4;
     Shared sh;
     sh.ring = smem;
     uint8_t* misc = smem + (size_t)2 * hs * kStageBytes;
@@ -395,7 +436,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
     sh.ysum_s = reinterpret_cast<int*>(sh.sy_part + 64);
     sh.a_s = reinterpret_cast<float*>(sh.ysum_s + 8);
     sh.flag_s = reinterpret_cast<int*>(sh.a_s + 8);
-    sh.u = misc + kMiscBytes;
+    sh.pos_s = reinterpret_cast<int64_t*>(sh.flag_s + 8);
+    sh.lin_s = reinterpret_cast<FusedLinearParams*>(misc + kMiscBytes);
+    sh.att_s = reinterpret_cast<AttentionParams*>(misc + kMiscBytes + 2 * kLinBlockBytes);
+    sh.issue = reinterpret_cast<LinIssue*>(misc + kMiscBytes + 2 * kLinBlockBytes + 2 * kAttBlockBytes);
+    sh.u = reinterpret_cast<uint8_t*>(sh.issue) + (size_t)(n_lin * sizeof(LinIssue) + 127) / 128 * 128;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, n_cta = gridDim.x;
@@ -410,58 +455,94 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
         sh.flag_s[2] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
+    // the step's constants: what the copy stream needs of every BitLinear, the first two
+    // parameter blocks, the positions
+#pragma unroll 1
+    for (int i = tid; i < n_lin; i += kMegaThreads) {
+        const FusedLinearParams* d = P.lin + i;
+        const Range rng = cta_range((d->N + 15) / 16, cta, n_cta);
+        sh.issue[i] = LinIssue{d->w2t + (int64_t)rng.rg0 * d->k_tiles * kTileBytes, rng.n_rg * d->k_tiles, 0};
+    }
+    fetch_block(&sh.lin_s[0], P.lin, tid, 0);
+    if (n_lin > 1) fetch_block(&sh.lin_s[1], P.lin + 1, tid, 64);
+    fetch_block(&sh.att_s[0], P.att, tid, 128);
+    if (tid >= 256 && tid < 256 + M) sh.pos_s[tid - 256] = P.pos[tid - 256];
     __syncthreads();
 
-    Cursor cur{0, 0, 0u};
-    if (tid == 0) {   // the first two rounds of the step
-        issue_round(P, sh, cta, cur);
-        issue_round(P, sh, cta, cur);
+    Cursor cur{0, 0, 0u, 0};
+    if (tid == kIssueTid) {   // the first two rounds of the step
+        issue_round(P, sh, cur);
+        issue_round(P, sh, cur);
     }
 
     unsigned int gr = 0, barrier_no = 0;
     auto wait_prev = [&]() -> bool {   // all CTAs have finished the previous phase
         const bool ok = grid_wait(&P.bar[0], (unsigned int)n_cta * barrier_no, tid, sh, P.error_flag);
-        if (!ok && tid == 0) drain_rounds(sh, hs, cur);
+        if (!ok && tid == kIssueTid) drain_rounds(sh, hs, cur);
         return ok;
     };
-    auto linear = [&](const FusedLinearParams* d) -> bool {
-        const bool ok = linear_phase(P, d, sh, cta, tid, gr, cur);
-        if (!ok && tid == 0) drain_rounds(sh, hs, cur);
-        return ok;
+    // BitLinear number li of the step; its block is in lin_s[li & 1], the next one's is fetched
+    // into the other slot (free since the barrier that ended BitLinear li - 1).
+    auto linear = [&](int li, int phase_no) -> bool {
+        const FusedLinearParams* d = &sh.lin_s[li & 1];
+        stamp(P, cta, tid, phase_no, 0);
+        if (li >= 1 && li + 1 < n_lin) fetch_block(&sh.lin_s[(li + 1) & 1], P.lin + li + 1, tid, 448);
+        const float h_pre = linear_pre(d, sh, M, cta, n_cta, tid);
+        if (barrier_no > 0) {
+            if (!wait_prev()) return false;
+        } else {
+            csync();
+        }
+        stamp(P, cta, tid, phase_no, 1);
+        const bool ok = linear_phase(P, d, sh, cta, n_cta, tid, gr, cur, phase_no, h_pre);
+        if (!ok) {
+            if (tid == kIssueTid) drain_rounds(sh, hs, cur);
+            return false;
+        }
+        grid_arrive(&P.bar[0], tid);
+        stamp(P, cta, tid, phase_no, 5);
+        ++barrier_no;
+        return true;
     };
 #pragma unroll 1
     for (int layer = 0; layer < P.n_layers; ++layer) {
-        const FusedLinearParams* lin = P.lin + layer * 4;
-        // wqkv
-        linear_pre(lin, sh, M, tid);
-        if (barrier_no > 0 && !wait_prev()) return;
-        if (!linear(lin)) return;
-        grid_arrive(&P.bar[0], tid);
-        ++barrier_no;
-        // attention: one (sequence, kv head, slice) per CTA and turn
-        if (!wait_prev()) return;
+        if (!linear(layer * 4, layer * 5)) return;   // wqkv
+        // attention: one (sequence, kv head, slice) per CTA and turn; the slice's first keys are
+        // requested before the barrier
         {
-            AttentionParams ap = P.att[layer];
-            ap.pos = P.pos;
-            const int items = M * ap.Hkv * ap.S;
+            const AttentionParams& ap = sh.att_s[layer & 1];
+            const int per_seq = ap.Hkv * ap.S, items = M * per_seq;
+            bool waited = false, ok = true;
+            auto wait_once = [&]() {
+                if (!waited) ok = wait_prev();
+                waited = true;
+            };
+            stamp(P, cta, tid, layer * 5 + 1, 0);
 #pragma unroll 1
-            for (int item = cta; item < items; item += n_cta) {
-                const int b = item / (ap.Hkv * ap.S), rem = item - b * (ap.Hkv * ap.S);
-                attention_body<4, kMegaWarps>(ap, sh.u, &sh.flag_s[1], b, rem / ap.S, rem % ap.S, tid, CSync());
+            for (int item = cta; item < items && ok; item += n_cta) {
+                const int b = item / per_seq;
+                const int pos_b = (int)sh.pos_s[b];
+                const AttnItem it = attention_item(ap, item - b * per_seq, pos_b);
+                if (it.G == 0) continue;
+                if (it.G == 1)
+                    attention_body<1, kMegaWarps>(ap, sh.u, &sh.flag_s[1], b, it.kvh, it.h0, 1, it.split, it.S, pos_b, tid,
+                                                  CSync(), wait_once);
+                else
+                    attention_body<4, kMegaWarps>(ap, sh.u, &sh.flag_s[1], b, it.kvh, it.h0, it.G, it.split, it.S, pos_b,
+                                                  tid, CSync(), wait_once);
                 csync();
             }
+            wait_once();
+            if (!ok) return;
+            if (layer + 1 < P.n_layers) fetch_block(&sh.att_s[(layer + 1) & 1], P.att + layer + 1, tid, 448);
         }
+        stamp(P, cta, tid, layer * 5 + 1, 4);
         grid_arrive(&P.bar[0], tid);
+        stamp(P, cta, tid, layer * 5 + 1, 5);
         ++barrier_no;
-        // wo, w13, w2
 #pragma unroll 1
-        for (int j = 1; j < 4; ++j) {
-            linear_pre(lin + j, sh, M, tid);
-            if (!wait_prev()) return;
-            if (!linear(lin + j)) return;
-            grid_arrive(&P.bar[0], tid);
-            ++barrier_no;
-        }
+        for (int j = 1; j < 4; ++j)   // wo, w13, w2
+            if (!linear(layer * 4 + j, layer * 5 + 1 + j)) return;
     }
     if (!wait_prev()) return;
 
@@ -525,15 +606,16 @@ struct MegaPlan {
 
 // Shared memory the phase-private region needs for these phases.
 static size_t mega_union_bytes(const FusedLinearParams* lin, int n_lin, const AttentionParams& ap, const HeadParams& hp,
-                               int M) {
+                               int M, int grid) {
     size_t u = attention_smem(ap) > head_smem(hp) ? attention_smem(ap) : head_smem(hp);
     for (int i = 0; i < n_lin; ++i) {
         const FusedLinearParams& p = lin[i];
         const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
-        const size_t b = (size_t)p.r_max * 128 * 4 + (size_t)p.K_even * 6 + (size_t)(M + 1) * y_stride;
+        const size_t b = (size_t)rg_cap(p.N, grid) * 128 * 4 + (size_t)p.K_even * 6 + (size_t)(M + 1) * y_stride;
         u = b > u ? b : u;
     }
-    return u + 128;
+    // plus what sits between the ring and the phase-private region
+    return u + 128 + kMiscBytes + 2 * kLinBlockBytes + 2 * kAttBlockBytes + ((size_t)n_lin * sizeof(LinIssue) + 127) / 128 * 128;
 }
 
 // Builds the device-side tables of a step.  lin: [n_layers * 4] fully filled parameter blocks
@@ -543,15 +625,15 @@ static size_t mega_union_bytes(const FusedLinearParams* lin, int n_lin, const At
 void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, const HeadParams& hp, int n_layers, int M,
                   int grid, size_t smem_optin) {
     const int G = att[0].H / att[0].Hkv;
-    if (G > 4 || M < 1 || M > 8) return set_status(kUnsupported), nullptr;
-    const size_t u = mega_union_bytes(lin, n_layers * 4, att[0], hp, M);
+    if (G > 4 || M < 1 || M > 8 || n_layers * 4 > kMaxLinears) return set_status(kUnsupported), nullptr;
+    const size_t u = mega_union_bytes(lin, n_layers * 4, att[0], hp, M, grid);
     int hs = kMaxHalfStages;
-    while (hs >= 1 && (size_t)2 * hs * kStageBytes + kMiscBytes + u > smem_optin) --hs;
+    while (hs >= 1 && (size_t)2 * hs * kStageBytes + u > smem_optin) --hs;
     if (hs < 1) return set_status(kTooLarge), nullptr;
     MegaPlan* mp = new (std::nothrow) MegaPlan();
     if (!mp) return set_status(kBadArgument), nullptr;
     mp->n_layers = n_layers; mp->M = M; mp->half_stages = hs; mp->grid = grid;
-    mp->smem = (size_t)2 * hs * kStageBytes + kMiscBytes + u;
+    mp->smem = (size_t)2 * hs * kStageBytes + u;
     const size_t lin_bytes = sizeof(FusedLinearParams) * n_layers * 4, att_bytes = sizeof(AttentionParams) * n_layers;
     uint8_t* base = nullptr;
     int occ = 0;
@@ -586,12 +668,12 @@ void mega_destroy(void* plan) {
 }
 
 int mega_launch(void* plan, const HeadParams& hp, int64_t* tokens, int64_t* pos, int64_t* out, int* error_flag,
-                cudaStream_t stream) {
+                unsigned long long* trace, cudaStream_t stream) {
     MegaPlan* mp = static_cast<MegaPlan*>(plan);
     MegaParams P{};
     P.lin = mp->lin_dev; P.att = mp->att_dev; P.head = hp;
     P.n_layers = mp->n_layers; P.M = mp->M; P.half_stages = mp->half_stages;
-    P.tokens = tokens; P.pos = pos; P.out = out; P.bar = mp->bar; P.error_flag = error_flag;
+    P.tokens = tokens; P.pos = pos; P.out = out; P.bar = mp->bar; P.error_flag = error_flag; P.trace = trace;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(mp->grid);
     cfg.blockDim = dim3(kMegaThreads);

@@ -297,7 +297,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
                         bool linears_only) {
     const bitnet_decoder_config& c = d->cfg;
     if (d->mega && d->use_mega && !linears_only)
-        return mega_launch(d->mega, head_params(d, logits), tokens, pos, out, d->error_flag, stream);
+        return mega_launch(d->mega, head_params(d, logits), tokens, pos, out, d->error_flag, d->trace, stream);
     static const int dbg = getenv("BITNET_DEBUG_SKIP") ? atoi(getenv("BITNET_DEBUG_SKIP")) : 0;
     for (int l = 0; l < c.n_layers; ++l) {
         FusedLinearParams lin[4];
