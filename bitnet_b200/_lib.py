@@ -34,6 +34,7 @@ SIGNATURES = {
     "bitnet_quant_input": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
     "bitnet_decoder_create": (_vp, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "bitnet_decoder_step_sync": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_bench_linears": (_i, [_vp, _vp, _vp]),
     "bitnet_decoder_read_trace": (_i, [_vp, _vp, _i]),
     "bitnet_debug_read_workspace_words": (_i, [_vp, _i]),

@@ -33,14 +33,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: returns false (and the caller abandons the kernel) after about a second.
-__device__ __noinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity) {
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > kWaitCycles) return false;
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    return mbar_test_wait(bar, parity) || mbar_wait_slow(bar, parity);   // usually complete already
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
@@ -108,7 +121,8 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     float* red_m = vnew + D;                               // [NW][GMAX]
     float* red_l = red_m + NW * GMAX;                      // [NW][GMAX]
     float* red_o = red_l + NW * GMAX;                      // [NW][G][D]
-    constexpr int U = 4;   // keys per step: their scores are reduced together, then one softmax update
+    // keys per step: their scores are reduced together, then one softmax update
+    constexpr int U = 4;
     const int lo = (int)((int64_t)P * split / S), hi = (int)((int64_t)P * (split + 1) / S);
     const int d0 = 4 * lane;
     const bool live = d0 < D;

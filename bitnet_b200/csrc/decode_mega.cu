@@ -64,17 +64,18 @@ struct MegaParams {
     int64_t* out;                    // [M]
     unsigned int* bar;               // [0] barrier arrivals, [1] exit tickets; zero between steps
     int* error_flag;
-    unsigned long long* trace;       // optional: [n_layers * 5][16] timestamps of CTA 0 (a measurement aid)
+    unsigned long long* trace;       // optional: [n_layers * 5][16] cycle stamps of one CTA (a measurement aid)
+    int trace_cta;                   // which CTA writes them (BITNET_TRACE_CTA, default 0)
 };
 
 __device__ __forceinline__ void stamp(const MegaParams& P, int cta, int tid, int phase, int i) {
-    if (P.trace && cta == 0 && tid == 0) {
-        P.trace[phase * 16 + i] = (unsigned long long)clock64();   // SM cycles: CTA 0 stays on one SM
+    if (P.trace && cta == P.trace_cta && tid == 0) {
+        P.trace[phase * 16 + i] = (unsigned long long)clock64();   // SM cycles: a CTA stays on one SM
     }
 }
 
 __device__ __forceinline__ void cstamp(const MegaParams& P, int cta, int tid, int phase, int i) {
-    if (P.trace && cta == 0 && tid == 0) P.trace[phase * 16 + i] = (unsigned long long)clock64();
+    if (P.trace && cta == P.trace_cta && tid == 0) P.trace[phase * 16 + i] = (unsigned long long)clock64();
 }
 
 // What the copy stream needs to know of a BitLinear: this CTA's tiles.
@@ -674,6 +675,7 @@ int mega_launch(void* plan, const HeadParams& hp, int64_t* tokens, int64_t* pos,
     P.lin = mp->lin_dev; P.att = mp->att_dev; P.head = hp;
     P.n_layers = mp->n_layers; P.M = mp->M; P.half_stages = mp->half_stages;
     P.tokens = tokens; P.pos = pos; P.out = out; P.bar = mp->bar; P.error_flag = error_flag; P.trace = trace;
+    P.trace_cta = getenv("BITNET_TRACE_CTA") ? atoi(getenv("BITNET_TRACE_CTA")) : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(mp->grid);
     cfg.blockDim = dim3(kMegaThreads);

@@ -3,6 +3,7 @@
 // which owns its scratch and enqueues one step - five kernels per layer, then the output
 // head and the greedy choice - on the caller's stream.
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 #include <new>
@@ -109,6 +110,7 @@ struct Decoder {
     FusedLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
     void* mega = nullptr;                         // tables of the persistent kernel, when it fits this model
     bool use_mega = false;
+    bool trace_chain = false;                     // BITNET_TRACE=chain: time-stamp the chain (which then is the default)
 };
 
 static size_t align_up(size_t x) { return (x + 255) / 256 * 256; }
@@ -211,10 +213,14 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->part_ml = reinterpret_cast<float*>(base + o_pml);
     d->part_val = reinterpret_cast<float*>(base + o_pv);
     d->part_idx = reinterpret_cast<int*>(base + o_pi);
-    if (getenv("BITNET_TRACE")) d->trace = reinterpret_cast<unsigned long long*>(base + o_tr);
+    if (getenv("BITNET_TRACE")) {
+        d->trace = reinterpret_cast<unsigned long long*>(base + o_tr);
+        d->trace_chain = strcmp(getenv("BITNET_TRACE"), "chain") == 0;
+    }
 
     // The persistent single-kernel step, when the model fits it and the chain's plans use one
-    // CTA per SM.  Off unless BITNET_PERSISTENT=1 or bitnet_decoder_use_persistent turns it on.
+    // CTA per SM.  It is the default; BITNET_PERSISTENT=0 or bitnet_decoder_use_persistent(d, 0)
+    // selects the chain of kernels.
     if (ctas_per_sm <= 1 && !getenv("BITNET_NO_PERSISTENT")) {
         std::vector<FusedLinearParams> lin((size_t)cfg->n_layers * 4);
         std::vector<AttentionParams> att(cfg->n_layers);
@@ -222,7 +228,8 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         d->mega = mega_create(lin.data(), att.data(), head_params(d, nullptr), cfg->n_layers, B, d->n_sm,
                               prop.sharedMemPerBlockOptin);
         set_status(kOk);   // not fitting the persistent kernel is not an error: the chain remains
-        d->use_mega = d->mega && getenv("BITNET_PERSISTENT") && atoi(getenv("BITNET_PERSISTENT")) != 0;
+        const char* env = getenv("BITNET_PERSISTENT");
+        d->use_mega = d->mega && !(env && atoi(env) == 0) && !d->trace_chain;
     }
     return d;
 }
@@ -296,8 +303,15 @@ static HeadParams head_params(const Decoder* d, float* logits) {
 static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, cudaStream_t stream,
                         bool linears_only) {
     const bitnet_decoder_config& c = d->cfg;
-    if (d->mega && d->use_mega && !linears_only)
-        return mega_launch(d->mega, head_params(d, logits), tokens, pos, out, d->error_flag, d->trace, stream);
+    if (d->mega && d->use_mega && !linears_only) {
+        const int rc = mega_launch(d->mega, head_params(d, logits), tokens, pos, out, d->error_flag, d->trace, stream);
+        if (rc == kOk) return rc;
+        // The cooperative launch was refused (e.g. the device cannot hold all CTAs at once right
+        // now): nothing ran; take the chain of kernels from here on.
+        cudaGetLastError();
+        set_status(kOk);
+        d->use_mega = false;
+    }
     static const int dbg = getenv("BITNET_DEBUG_SKIP") ? atoi(getenv("BITNET_DEBUG_SKIP")) : 0;
     for (int l = 0; l < c.n_layers; ++l) {
         FusedLinearParams lin[4];
@@ -336,6 +350,12 @@ int bitnet_decoder_step(void* dec, int64_t* tokens, int64_t* pos, int64_t* out, 
     Decoder* d = static_cast<Decoder*>(dec);
     if (!d || !tokens || !pos || !out) return set_status(kBadArgument), kBadArgument;
     return enqueue_step(d, tokens, pos, out, logits, static_cast<cudaStream_t>(stream), false);
+}
+
+int bitnet_decoder_step_sync(void* dec, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream) {
+    const int rc = bitnet_decoder_step(dec, tokens, pos, out, logits, stream);
+    if (rc != kOk) return rc;
+    return check_cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
 }
 
 int bitnet_decoder_bench_linears(void* dec, int64_t* tokens, void* stream) {

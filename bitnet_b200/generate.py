@@ -82,6 +82,12 @@ class FusedDecoder:
         _lib.check(_lib.lib.bitnet_decoder_step(self.handle, _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(out),
                                                 _lib.ptr(logits), _lib.stream_ptr()))
 
+    def step_sync(self, tokens: torch.Tensor, pos: torch.Tensor, out: torch.Tensor):
+        """`step` and a wait for the current stream in one library call; tokens and out may be
+        pinned host tensors (the kernels read and write them in place)."""
+        _lib.check(_lib.lib.bitnet_decoder_step_sync(self.handle, _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(out), None,
+                                                     _lib.stream_ptr()))
+
     def bench_linears(self, tokens: torch.Tensor):
         """Enqueues only the fused BitLinear kernels of every layer (a measurement aid)."""
         _lib.check(_lib.lib.bitnet_decoder_bench_linears(self.handle, _lib.ptr(tokens), _lib.stream_ptr()))
@@ -112,6 +118,8 @@ class Generator:
         self.host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
         self.use_cuda_graph = use_cuda_graph
         self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.graph_host: Optional[torch.cuda.CUDAGraph] = None
+        self._host_state = False
         self.stream = torch.cuda.Stream(device=dev)
         can_fuse = model.args.use_kernel and batch <= FusedDecoder.MAX_BATCH
         if fused and not can_fuse:
@@ -165,6 +173,18 @@ class Generator:
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self.stream):
                 self._step()
+            # The same step for callers that hand over and read back ids in host memory.  The
+            # in-library step reads the ids from, and writes the chosen ids to, the pinned host
+            # buffers directly (they are addressable from the device), so no copy engine sits
+            # between the host and the kernel; otherwise the two copies are part of the graph.
+            self.graph_host = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph_host, stream=self.stream):
+                if self.fused is not None:
+                    self.fused.step(self.host_in, self.pos, self.host_out)
+                else:
+                    self.tokens.copy_(self.host_in, non_blocking=True)
+                    self._step()
+                    self.host_out.copy_(self.out, non_blocking=True)
         torch.cuda.synchronize()
         self.tokens.copy_(saved[0]); self.pos.copy_(saved[1]); self.out.copy_(saved[2])
         torch.cuda.synchronize()
@@ -172,6 +192,10 @@ class Generator:
     @torch.no_grad()
     def decode_step(self):
         """One token for every sequence, device resident (input = previous output)."""
+        if self._host_state:   # the last steps ran on the host buffers: take their state over
+            self.tokens.copy_(self.host_in)
+            self.out.copy_(self.host_out)
+            self._host_state = False
         if self.graph is not None:
             self.graph.replay()
         else:
@@ -179,14 +203,26 @@ class Generator:
 
     @torch.no_grad()
     def decode_step_host(self, tokens_host: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """One token with host buffers on both sides: copies the input ids from pinned host
-        memory, runs the step, copies the chosen ids back and waits for them."""
+        """One token with host buffers on both sides: takes the input ids from pinned host
+        memory (tokens_host, or the ids the previous step chose), runs the step, and returns
+        the chosen ids in pinned host memory once they have arrived."""
         with torch.cuda.stream(self.stream):
             if tokens_host is not None:
                 self.host_in.copy_(tokens_host)
-            self.tokens.copy_(self.host_in, non_blocking=True)
-            self.decode_step()
-            self.host_out.copy_(self.out, non_blocking=True)
+            elif not self._host_state:
+                self.host_in.copy_(self.tokens)
+            if self.fused is not None and self.fused.kernels_per_step == 1:
+                # one kernel: launching it directly costs less than replaying a graph
+                self.fused.step_sync(self.host_in, self.pos, self.host_out)
+                self._host_state = True
+                return self.host_out
+            if self.graph_host is not None:
+                self.graph_host.replay()
+                self._host_state = self.fused is not None   # next input and result live in host_in / host_out
+            else:
+                self.tokens.copy_(self.host_in, non_blocking=True)
+                self.decode_step()
+                self.host_out.copy_(self.out, non_blocking=True)
             self.stream.synchronize()
         return self.host_out
 

@@ -136,6 +136,11 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
  * call continues the sequence); pos int64 [batch]: tokens already in the cache (incremented);
  * out int64 [batch]: chosen ids; logits f32 [batch, vocab] or NULL. */
 int bitnet_decoder_step(void* decoder, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream);
+/* bitnet_decoder_step followed by a wait for the stream: returns when `out` (and `logits`)
+ * hold the step's result.  With `tokens` and `out` in pinned host memory (which the device can
+ * address) this is the whole host-in, host-out step in one call, without copy nodes.  Not for
+ * use under stream capture.  No counterpart in the reference. */
+int bitnet_decoder_step_sync(void* decoder, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream);
 /* Measurement aid: enqueues only the four fused BitLinear kernels of every layer (no
  * attention, no output head), so that the BitLinear kernel can be timed alone on the
  * model's real weights.  The activations it leaves behind are meaningless. */
@@ -169,8 +174,10 @@ int bitnet_decoder_kernels_per_step(void* decoder);
  * CTA per SM, launched cooperatively, grid-wide barriers between the phases of a layer);
  * on = 0, a chain of five kernels per layer.  Both give the same bits.  Returns the mode in
  * effect afterwards: 0 when the persistent kernel does not fit the model (grouped-query ratio
- * above 4, or shared memory).  Environment: BITNET_PERSISTENT=1 turns it on at creation,
- * BITNET_NO_PERSISTENT=1 removes it.  No counterpart in the reference. */
+ * above 4, or shared memory).  The persistent kernel is the default where it fits; a refused
+ * cooperative launch switches the decoder to the chain for good.  Environment:
+ * BITNET_PERSISTENT=0 starts with the chain, BITNET_NO_PERSISTENT=1 removes the persistent
+ * kernel.  No counterpart in the reference. */
 int bitnet_decoder_use_persistent(void* decoder, int on);
 void bitnet_decoder_destroy(void* decoder);
 

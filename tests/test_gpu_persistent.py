@@ -81,3 +81,30 @@ def test_persistent_in_cuda_graph():
     assert pers.graph is not None
     assert torch.equal(a, b)
     assert pers.fused.error_flag() == 0
+
+
+@pytest.mark.parametrize("persistent", [False, True])
+def test_host_buffer_steps_equal_device_steps(persistent):
+    """decode_step_host (ids read from and written to pinned host memory by the kernels
+    themselves) gives the same tokens as device-resident steps, also when the two are mixed."""
+    from bitnet_b200.generate import Generator
+    from bitnet_b200.model import build_synthetic, preset
+
+    args = preset("2b", n_layers=2, vocab_size=4096)
+    model = build_synthetic(args, seed=35, device="cuda", max_seq_len=128)
+    prompt = torch.randint(0, args.vocab_size, (2, 8), device="cuda", generator=torch.Generator("cuda").manual_seed(9))
+    a = Generator(model, 2, 128, fused=True, persistent=persistent)
+    b = Generator(model, 2, 128, fused=True, persistent=persistent)
+    ref = a.generate(prompt, 40)
+    first = b.prefill(prompt)
+    b.capture()
+    got = [first.clone().cpu()]
+    for i in range(39):
+        if i % 10 < 6:
+            got.append(b.decode_step_host().clone())
+        else:
+            with torch.cuda.stream(b.stream):
+                b.decode_step()
+                b.stream.synchronize()
+            got.append(b.out.clone().cpu())
+    assert torch.equal(torch.stack(got, dim=1), ref.cpu())
