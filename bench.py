@@ -36,7 +36,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # dram__bytes_read + dram__bytes_write of one decode_mega_kernel launch (ncu, profiles/decode_mega_kernel_2b_m1.md)
-PERSISTENT_TRAFFIC = {}
+PERSISTENT_TRAFFIC = {("2b", 1): 1.1989e9}
 PROMPT_LEN = 128
 SEED = 20240611
 
