@@ -114,6 +114,10 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
                                                int h0, int G, int split, int S, int P, int tid, Sync sync, Wait wait) {
     constexpr int NT = NW * 32;
     const int warp = tid >> 5, lane = tid & 31;
+    auto mark = [&](int i) {   // optional cycle stamps of thread 0 (a measurement aid)
+        if (p.trace && tid == 0) p.trace[i] = (unsigned long long)clock64();
+    };
+    mark(6);
     const int D = p.D, Gfull = p.H / p.Hkv;
     float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
     float* knew = q_s + G * D;                             // [D]
@@ -142,6 +146,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     };
     request(lo + warp * U);
     wait();
+    mark(7);
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
@@ -172,6 +177,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         }
     }
     sync();
+    mark(8);
 
     // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
     float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
@@ -246,6 +252,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
             }
         visit(kf, vf, 1);
     }
+    mark(9);
     // combine the warps
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
@@ -280,6 +287,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         p.part_o[slot * D + d] = on;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
+    mark(10);
     if (S == 1) return;
     // the last slice of this (sequence, kv head) to finish combines all of them
     __threadfence();

@@ -100,7 +100,7 @@ struct Shared {          // views into the dynamic shared memory
     uint64_t* full_bar;  // [2 * hs]
     uint64_t* empty_bar; // [2]
     float* scratch;      // [16]
-    float* sy_part;      // [8][8]
+    float* sy_part;      // [8 tokens][8 warps]
     int* ysum_s;         // [8]
     float* a_s;          // [8]
     int* flag_s;         // [0] abort, [1] attention is_last, [2] exit ticket is last
@@ -198,7 +198,7 @@ struct LinLayout {
     int k_pad, y_stride;
 };
 __device__ __host__ __forceinline__ int rg_cap(int N, int n_cta) { return ((N + 15) / 16 + n_cta - 1) / n_cta; }
-__device__ __forceinline__ LinLayout lin_layout(const FusedLinearParams* d, uint8_t* u, int n_cta) {
+__device__ __forceinline__ LinLayout lin_layout(const FusedLinearParams* d, uint8_t* u, int n_cta, int M) {
     LinLayout l;
     l.sacc = reinterpret_cast<int*>(u);
     l.xv = reinterpret_cast<__nv_bfloat16*>(l.sacc + rg_cap(d->N, n_cta) * 128);
@@ -215,7 +215,7 @@ __device__ __forceinline__ LinLayout lin_layout(const FusedLinearParams* d, uint
 // residual value of the output element this thread will finalise (the residual stream was
 // completed two phases ago).  `d` is the block in shared memory.
 __device__ __forceinline__ float linear_pre(const FusedLinearParams* d, const Shared& sh, int M, int cta, int n_cta, int tid) {
-    const LinLayout l = lin_layout(d, sh.u, n_cta);
+    const LinLayout l = lin_layout(d, sh.u, n_cta, M);
     const int cap = rg_cap(d->N, n_cta) * 128;
 #pragma unroll 1
     for (int i = tid; i < cap; i += kMegaConsumers) l.sacc[i] = 0;
@@ -246,7 +246,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
     const int M = P.M, hs = P.half_stages;
     int* error_flag = P.error_flag;
     const int warp = tid >> 5, lane = tid & 31;
-    const LinLayout l = lin_layout(d, sh.u, n_cta);
+    const LinLayout l = lin_layout(d, sh.u, n_cta, M);
     const int K = d->K, k_tiles = d->k_tiles, src = d->src;
     const int n_vec = d->K_even / 8;
     const Range rng = cta_range((d->N + 15) / 16, cta, n_cta);
@@ -255,10 +255,6 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
     // ---- prologue: int8 activations of every token, by warps 0-7; meanwhile the copies that
     // refill the ring half the previous BitLinear left are issued -----------------------------
     cstamp(P, cta, tid, phase_no, 6);
-    if (tid == kIssueTid) {
-#pragma unroll 1
-        for (; cur.pending > 0; --cur.pending) issue_round(P, sh, cur);
-    }
     if (warp < 8) {
 #pragma unroll 1
         for (int m = 0; m < M; ++m) {
@@ -270,7 +266,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
             }
             cp_async_wait_all();   // also covers the norm weight staged before the barrier
             cstamp(P, cta, tid, phase_no, 7);
-            if (src == kSrcGlu) {
+            if (src == kSrcGlu) {          // relu(x1)^2 * x3 with bf16 rounding after each step
 #pragma unroll 1
                 for (int v = tid; v < n_vec; v += kPrologueThreads) {
                     Vec8 x1 = unpack_bf16x8(*reinterpret_cast<const uint4*>(l.xv + v * 8));
@@ -282,18 +278,18 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
                     }
                     *reinterpret_cast<uint4*>(l.xv + v * 8) = pack_bf16x8(x1);
                 }
-            } else if (src == kSrcEmbedding && d->h_copy && cta == 0) {
+            } else if (src == kSrcEmbedding && d->h_copy && cta == 0) {   // the residual stream starts as the embedding row
 #pragma unroll 1
                 for (int v = tid; v < n_vec; v += kPrologueThreads)
                     *reinterpret_cast<uint4*>(d->h_copy + (int64_t)m * K + v * 8) = *reinterpret_cast<const uint4*>(l.xv + v * 8);
             }
             float a, sy_warp;
-            norm_quant_row(l.xv, K, l.k_pad, d->gamma ? l.gs : nullptr, d->eps, l.ys + (size_t)m * l.y_stride, sh.scratch,
-                           tid, PSync(), a, sy_warp);
+            norm_quant_row<true>(l.xv, K, l.k_pad, d->gamma ? l.gs : nullptr, d->eps, l.ys + (size_t)m * l.y_stride,
+                                 sh.scratch, tid, PSync(), a, sy_warp);
             cstamp(P, cta, tid, phase_no, 8);
             if (lane == 0) sh.sy_part[m * 8 + warp] = sy_warp;
             if (tid == 0) sh.a_s[m] = a;
-            psync();
+            psync();   // xv is reused by the next token
         }
         if (tid < M) {
             float t = 0.f;
@@ -399,7 +395,7 @@ __device__ __forceinline__ bool linear_phase(const MegaParams& P, const FusedLin
     cstamp(P, cta, tid, phase_no, 14);
     if (sh.flag_s[0]) return false;
     if (n_tiles == 0) return true;
-    ++cur.pending;   // every warp has left the last round's half: refilled during the next prologue
+    ++cur.pending;   // every warp has left the last round's half: refilled during the next barrier wait
     cstamp(P, cta, tid, phase_no, 15);
 
     // ---- epilogue: every row of this CTA's row groups is complete --------------------------
@@ -478,6 +474,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
 
     unsigned int gr = 0, barrier_no = 0;
     auto wait_prev = [&]() -> bool {   // all CTAs have finished the previous phase
+        if (tid == kIssueTid) {        // meanwhile: the copies that refill the ring half the last BitLinear left
+#pragma unroll 1
+            for (; cur.pending > 0; --cur.pending) issue_round(P, sh, cur);
+        }
         const bool ok = grid_wait(&P.bar[0], (unsigned int)n_cta * barrier_no, tid, sh, P.error_flag);
         if (!ok && tid == kIssueTid) drain_rounds(sh, hs, cur);
         return ok;
@@ -525,6 +525,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_mega_kernel(const Mega
                 const int pos_b = (int)sh.pos_s[b];
                 const AttnItem it = attention_item(ap, item - b * per_seq, pos_b);
                 if (it.G == 0) continue;
+                if (P.trace && tid == 0)   // cycle stamps of the traced CTA's attention go behind its phase stamps
+                    sh.att_s[layer & 1].trace = cta == P.trace_cta ? P.trace + (layer * 5 + 1) * 16 : nullptr;
+                csync();
                 if (it.G == 1)
                     attention_body<1, kMegaWarps>(ap, sh.u, &sh.flag_s[1], b, it.kvh, it.h0, 1, it.split, it.S, pos_b, tid,
                                                   CSync(), wait_once);

@@ -35,6 +35,18 @@ __device__ __forceinline__ uint4 pack_bf16x8(const Vec8& x) {
     return u;
 }
 
+// clamp(rint(f), -128, 127) as one conversion: round to nearest even, saturate to int8
+// (the low byte of the result is the quantised value; NaN gives 0).
+__device__ __forceinline__ int quant_s8(float f) {
+    int q;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(f));
+    return q;
+}
+// The low bytes of four integers as one word (a in the lowest byte).
+__device__ __forceinline__ uint32_t pack_bytes(int a, int b, int c, int d) {
+    return __byte_perm(__byte_perm((uint32_t)a, (uint32_t)b, 0x0040), __byte_perm((uint32_t)c, (uint32_t)d, 0x0040), 0x5410);
+}
+
 // Eight consecutive bf16 values starting at element k of a row of length K (zero beyond K).
 __device__ __forceinline__ Vec8 load_bf16x8(const __nv_bfloat16* row, int k, int K, bool vec_ok) {
     if (vec_ok && k + 8 <= K) return unpack_bf16x8(*reinterpret_cast<const uint4*>(row + k));
@@ -89,63 +101,88 @@ __device__ __forceinline__ void reduce2_256(float& ss, float& mx, float* scratch
     }
 }
 
-// One token whose source values already sit in shared memory: xv holds ceil8(K) bf16 values
-// (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero filled beyond
-// K.  Arithmetic, in f32: t = x * g; r = rsqrt(mean(x^2) + eps); xn = bf16(t * r);
-// a = 127 / max(max|xn|, 1e-5); y = clamp(rint(xn * a), -128, 127).  Because rounding and
-// multiplication by r > 0 are monotone, max|xn| = bf16(max|t| * r), so one reduction round
-// (sum of squares and max|t| together) and two passes suffice.  On return every thread holds
-// the activation scale; `sy_warp` is the sum of y over the calling warp's elements (exact in
-// f32), which the caller adds up over the eight warps.  The loops are deliberately not
-// unrolled: these kernels run for microseconds, and code that does not fit the instruction
-// cache costs more than the loop overhead saves.
-template <class Sync>
+// ---- the arithmetic of one token, shared by every kernel that quantises activations ----------
+// In f32: t = x * g; r = rsqrt(mean(x^2) + eps); xn = bf16(t * r); a = 127 / max(max|xn|, 1e-5);
+// y = clamp(rint(xn * a), -128, 127).  Because rounding and multiplication by r > 0 are
+// monotone, max|xn| = bf16(max|t| * r), so one reduction round (sum of squares and max|t|
+// together) and two passes over the values suffice.
+//
+// The sum of squares has a fixed association, independent of how many threads work on it:
+// p(v) = x0^2 + ... + x7^2 of group v (fused multiply-adds from zero, in order); "lane" L of 256
+// adds p(L), p(L + 256), ... in order; 32 consecutive lanes combine by a butterfly of shuffles;
+// the 8 results are added in order.
+
+// Sum of squares of a group, and max |x * g| (max |x| without norm weight).
+__device__ __forceinline__ void group_stats(const Vec8& x, const Vec8& g, bool use_g, float& p, float& m) {
+    p = 0.f;
+    m = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        p = fmaf(x.v[e], x.v[e], p);
+        m = fmaxf(m, fabsf(use_g ? x.v[e] * g.v[e] : x.v[e]));
+    }
+}
+// From the reduced statistics to the normalisation factor and the activation scale.
+__device__ __forceinline__ void finish_stats(float ss, float mt, int K, float eps, bool use_g, float& rinv, float& a) {
+    rinv = use_g ? rsqrtf(ss / (float)K + eps) : 1.f;
+    const float amax = use_g ? bf16_round(mt * rinv) : mt;
+    a = 127.0f / fmaxf(amax, 1e-5f);
+}
+// The eight int8 values of a group (two words) and their sum added to sy.
+__device__ __forceinline__ uint2 quant_group(const Vec8& x, const Vec8& g, bool use_g, float rinv, float a, int& sy) {
+    int q[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float xn = use_g ? bf16_round(x.v[e] * g.v[e] * rinv) : x.v[e];
+        q[e] = quant_s8(xn * a);
+    }
+    const uint32_t lo = pack_bytes(q[0], q[1], q[2], q[3]), hi = pack_bytes(q[4], q[5], q[6], q[7]);
+    sy = __dp4a((int)lo, 0x01010101, sy);
+    sy = __dp4a((int)hi, 0x01010101, sy);
+    return make_uint2(lo, hi);
+}
+
+// One token whose source values already sit in shared memory, by 256 threads: xv holds ceil8(K)
+// bf16 values (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero
+// filled beyond K.  On return every thread holds the activation scale; `sy_warp` is the sum of
+// y over the calling warp's elements (exact in f32), which the caller adds up over the eight
+// warps.  The loops are deliberately not unrolled: these kernels run for microseconds, and code
+// that does not fit the instruction cache costs more than the loop overhead saves.
+// GVEC: gamma is 16-byte aligned and padded to whole groups of 8 (e.g. staged in shared memory),
+// so the element-wise fallback is left out of the code.
+template <bool GVEC = false, class Sync>
 __device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, int k_pad, const __nv_bfloat16* gamma,
                                                float eps, int8_t* y, float* scratch, int tid, Sync sync, float& a_out,
                                                float& sy_warp) {
     const int n_vec = (K + 7) / 8;
-    const bool g_vec = gamma && aligned16(gamma, 8, 2);
+    const bool use_g = gamma != nullptr;
+    const bool g_vec = GVEC || (use_g && aligned16(gamma, 8, 2));
+    auto load_g = [&](int v) -> Vec8 {
+        if (!use_g) return Vec8{};
+        return GVEC ? unpack_bf16x8(*reinterpret_cast<const uint4*>(gamma + v * 8)) : load_bf16x8(gamma, v * 8, K, g_vec);
+    };
     float ss = 0.f, mt = 0.f;
 #pragma unroll 1
     for (int v = tid; v < n_vec; v += kPrologueThreads) {
-        const Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
-        Vec8 g;
-        if (gamma) g = load_bf16x8(gamma, v * 8, K, g_vec);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            ss += x.v[e] * x.v[e];
-            mt = fmaxf(mt, fabsf(gamma ? x.v[e] * g.v[e] : x.v[e]));
-        }
+        float p, m;
+        group_stats(unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8)), load_g(v), use_g, p, m);
+        ss += p;
+        mt = fmaxf(mt, m);
     }
     reduce2_256(ss, mt, scratch, tid, sync);
-    const float rinv = gamma ? rsqrtf(ss / (float)K + eps) : 1.f;
-    const float amax = gamma ? bf16_round(mt * rinv) : mt;
-    const float a = 127.0f / fmaxf(amax, 1e-5f);
-    float sy = 0.f;
+    float rinv, a;
+    finish_stats(ss, mt, K, eps, use_g, rinv, a);
+    int sy_i = 0;
 #pragma unroll 1
     for (int v = tid; v < k_pad / 8; v += kPrologueThreads) {
-        uint32_t lo = 0, hi = 0;
-        if (v < n_vec) {
-            const Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
-            Vec8 g;
-            if (gamma) g = load_bf16x8(gamma, v * 8, K, g_vec);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float xn = gamma ? bf16_round(x.v[e] * g.v[e] * rinv) : x.v[e];
-                float f = rintf(xn * a);
-                f = fminf(fmaxf(f, -128.f), 127.f);
-                sy += f;
-                const uint32_t b = (uint32_t)(uint8_t)(int8_t)(int)f;
-                if (e < 4) lo |= b << (8 * e);
-                else hi |= b << (8 * (e - 4));
-            }
-        }
-        *reinterpret_cast<uint2*>(y + v * 8) = make_uint2(lo, hi);
+        uint2 w = make_uint2(0, 0);
+        if (v < n_vec) w = quant_group(unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8)), load_g(v), use_g, rinv, a, sy_i);
+        *reinterpret_cast<uint2*>(y + v * 8) = w;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
+    for (int o = 16; o > 0; o >>= 1) sy_i += __shfl_xor_sync(0xffffffffu, sy_i, o);
     a_out = a;
-    sy_warp = sy;
+    sy_warp = (float)sy_i;   // |sum| <= 128 * 8 * groups per warp: exact
 }
 
 }  // namespace bitnet
