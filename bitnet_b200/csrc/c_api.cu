@@ -126,6 +126,20 @@ int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, 
     return act_quant(q, static_cast<cudaStream_t>(stream));
 }
 
+int bitnet_quant_input_glu(const void* x13_bf16, int64_t ldx, const void* gamma_bf16, float eps, int8_t* y, int64_t ldy,
+                           float* act_scale, void* s_bf16, int32_t* ysum, int M, int K, void* stream) {
+    g_status = kOk;
+    if (!x13_bf16 || !y || M < 1 || K < 1 || ldx < 2 * (int64_t)K || ldy < K) return fail(kBadArgument);
+    if (ldy % 8 != 0 || (reinterpret_cast<uintptr_t>(y) & 7) != 0) return fail(kBadArgument);
+    QuantArgs q;
+    q.x_bf16 = static_cast<const __nv_bfloat16*>(x13_bf16); q.ldx = ldx;
+    q.gamma = static_cast<const __nv_bfloat16*>(gamma_bf16); q.eps = eps;
+    q.y = y; q.ldy = ldy;
+    q.a_f32 = act_scale; q.a_bf16 = static_cast<__nv_bfloat16*>(s_bf16); q.ysum = ysum;
+    q.M = M; q.K = K; q.glu = true;
+    return act_quant(q, static_cast<cudaStream_t>(stream));
+}
+
 size_t bitnet_w2t_bytes(int N, int K) {
     if (N < 1 || K < 1) return 0;
     return (size_t)(round_up(N, 16) * round_up(K, 128) / 4);

@@ -1,11 +1,13 @@
 // One decode step (batch <= 8) as a single persistent kernel: one CTA per SM walks the
 // layers' phases - wqkv, attention, wo, w13, w2 - and the output head, with a grid-wide
 // barrier between phases instead of a kernel boundary.  The packed weight tiles of all
-// BitLinears stream, in order, through a shared-memory ring of two rounds; as soon as a
-// round has been consumed, thread 0 issues the bulk copies of the round after next - weights
-// are constants, so the copies run ahead of the barriers and the next phase's weights are
-// already on the SM when its activations become visible.  Arithmetic and reduction orders are those of the
-// chained kernels (decode_fused.cu), so both produce the same bits.
+// BitLinears stream, in order, through a shared-memory ring of two rounds; once a round has
+// been consumed, one thread issues the bulk copies of the round after next while the CTA waits
+// at the next grid barrier - weights are constants, so the copies run ahead of the barriers and
+// the next phase's weights are already on the SM when its activations become visible.  Every
+// CTA owns whole 16-row groups of each BitLinear, so no partial sums cross CTAs.  Arithmetic
+// and reduction orders are those of the chained kernels (decode_fused.cu), so both produce the
+// same bits.
 //
 // All CTAs must be resident at once: the kernel is launched cooperatively with at most one
 // CTA per SM.  Every wait is bounded; a wait that gives up sets the error flag and the CTA
@@ -29,7 +31,7 @@ constexpr int kMaxHalfStages = 4;                         // a round: up to 4 st
 constexpr int kMegaWarps = 16;                            // consumer warps
 constexpr int kMegaConsumers = kMegaWarps * 32;           // 512
 constexpr int kMegaThreads = kMegaConsumers;
-constexpr int kIssueTid = 256;                            // lane 0 of warp 8 issues the weight copies: idle during prologues
+constexpr int kIssueTid = 256;                            // lane 0 of warp 8 issues the weight copies (thread 0 polls the barrier)
 constexpr int kMiscBytes = 1024;                          // barriers and small arrays behind the ring
 constexpr int kLinBlockBytes = (sizeof(FusedLinearParams) + 127) / 128 * 128;
 constexpr int kAttBlockBytes = (sizeof(AttentionParams) + 127) / 128 * 128;
@@ -605,6 +607,7 @@ struct MegaPlan {
     AttentionParams* att_dev = nullptr;
     unsigned int* bar = nullptr;
     int n_layers = 0, M = 0, half_stages = 0, grid = 0;
+    bool single_round = false;   // every BitLinear's tiles of a CTA fit one ring round
     size_t smem = 0;
 };
 
@@ -637,6 +640,9 @@ void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, cons
     MegaPlan* mp = new (std::nothrow) MegaPlan();
     if (!mp) return set_status(kBadArgument), nullptr;
     mp->n_layers = n_layers; mp->M = M; mp->half_stages = hs; mp->grid = grid;
+    mp->single_round = true;
+    for (int i = 0; i < n_layers * 4; ++i)
+        mp->single_round = mp->single_round && rg_cap(lin[i].N, grid) * lin[i].k_tiles <= hs * kStageTiles;
     mp->smem = (size_t)2 * hs * kStageBytes + u;
     const size_t lin_bytes = sizeof(FusedLinearParams) * n_layers * 4, att_bytes = sizeof(AttentionParams) * n_layers;
     uint8_t* base = nullptr;
@@ -663,6 +669,11 @@ void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, cons
     mp->bar = reinterpret_cast<unsigned int*>(base + lin_al + att_al);
     return mp;
 }
+
+// True when the persistent kernel is expected to beat the chain of kernels: every BitLinear's
+// share of a CTA fits one round of the ring, so that all its weights are on the SM before the
+// phase starts.  (Measured on B200: 2B architecture at batch 1 and 8 faster, 3B and 8B slower.)
+bool mega_recommended(const void* plan) { return plan && static_cast<const MegaPlan*>(plan)->single_round; }
 
 void mega_destroy(void* plan) {
     MegaPlan* mp = static_cast<MegaPlan*>(plan);

@@ -219,8 +219,8 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     }
 
     // The persistent single-kernel step, when the model fits it and the chain's plans use one
-    // CTA per SM.  It is the default; BITNET_PERSISTENT=0 or bitnet_decoder_use_persistent(d, 0)
-    // selects the chain of kernels.
+    // CTA per SM.  It is the default where it is expected to be the faster one (mega_recommended);
+    // BITNET_PERSISTENT=0/1 or bitnet_decoder_use_persistent choose explicitly.
     if (ctas_per_sm <= 1 && !getenv("BITNET_NO_PERSISTENT")) {
         std::vector<FusedLinearParams> lin((size_t)cfg->n_layers * 4);
         std::vector<AttentionParams> att(cfg->n_layers);
@@ -229,7 +229,7 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
                               prop.sharedMemPerBlockOptin);
         set_status(kOk);   // not fitting the persistent kernel is not an error: the chain remains
         const char* env = getenv("BITNET_PERSISTENT");
-        d->use_mega = d->mega && !(env && atoi(env) == 0) && !d->trace_chain;
+        d->use_mega = d->mega && (env ? atoi(env) != 0 : mega_recommended(d->mega)) && !d->trace_chain;
     }
     return d;
 }

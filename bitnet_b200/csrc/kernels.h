@@ -58,6 +58,7 @@ struct QuantArgs {
     __nv_bfloat16* a_bf16 = nullptr;         // optional [M]
     int32_t* ysum = nullptr;                 // optional [M]
     int M = 0, K = 0;
+    bool glu = false;                        // rows hold 2K values: quantise relu(x[k])^2 * x[K + k] (gpu/model.py:193-195)
 };
 int act_quant(const QuantArgs& a, cudaStream_t stream);
 

@@ -1,5 +1,5 @@
-// Stand-alone activation prologue of a BitLinear: optional RMSNorm, then per-token absmax
-// int8 quantisation (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242).
+// Stand-alone activation prologue of a BitLinear: optional gating (squared ReLU times the
+// second half of the row), optional RMSNorm, then per-token absmax int8 quantisation (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242).
 // One CTA of 256 threads per token; the arithmetic lives in prologue.cuh, shared with the
 // fused decode kernels.
 #include "common.cuh"
@@ -21,8 +21,18 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
     const int K = p.K;
     float a, sy_warp;
 #pragma unroll 1
-    for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads)
-        *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(load_bf16x8(row, v * 8, K, vec_ok));
+    for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads) {
+        Vec8 x = load_bf16x8(row, v * 8, K, vec_ok);
+        if (p.glu) {   // relu(x1)^2 * x3 with bf16 rounding after each step, as the bf16 tensor ops round
+            const Vec8 x3 = load_bf16x8(row + K, v * 8, K, vec_ok && K % 8 == 0);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float t = fmaxf(x.v[e], 0.f);
+                x.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
+            }
+        }
+        *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x);
+    }
     norm_quant_row(xv, K, (int)p.ldy, p.gamma, p.eps, p.y + (int64_t)tok * p.ldy, scratch, tid,
                    [] { __syncthreads(); }, a, sy_warp);
     if ((tid & 31) == 0) sy_part[tid >> 5] = sy_warp;

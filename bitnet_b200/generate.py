@@ -131,9 +131,18 @@ class Generator:
                 from .model import rope_table
                 model.rope = rope_table(model.args.head_dim, max(max_seq_len, model.max_seq_len),
                                         model.args.rope_theta, dev)
-            self.fused = FusedDecoder(model, self.cache, batch, max_seq_len)
-            if persistent is not None:
-                self.persistent = self.fused.use_persistent(persistent)
+            try:
+                self.fused = FusedDecoder(model, self.cache, batch, max_seq_len)
+            except _lib.BitnetError:
+                # e.g. batch x hidden size beyond the fused kernels' shared memory: the
+                # op-by-op path (same kernels, one launch per operation) takes over
+                if fused:
+                    raise
+            if self.fused is not None:
+                if persistent is not None:
+                    self.persistent = self.fused.use_persistent(persistent)
+                else:   # the library's choice
+                    self.persistent = self.fused.kernels_per_step == 1
 
     def _step(self):
         if self.fused is not None:

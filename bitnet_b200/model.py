@@ -130,6 +130,14 @@ class BitLinearKernel(nn.Module):
                               self.in_features)
         return out.view(*x.shape[:-1], self.out_features)
 
+    def forward_glu(self, x13: torch.Tensor, norm: Optional[RMSNorm] = None) -> torch.Tensor:
+        """forward(squared_relu(x1) * x3, norm) for x13 = [x1 | x3], the gate fused into the
+        quantisation kernel."""
+        y, a, ysum = ops.quant_input_glu(x13, None if norm is None else norm.weight, 0.0 if norm is None else norm.eps)
+        out = ops.linear_w2a8(y, a, ysum, self.weight, self.scale_f32, self.seg_end, self.out_features,
+                              self.in_features)
+        return out.view(*x13.shape[:-1], self.out_features)
+
 
 class BitLinear(nn.Linear):
     """The BitLinear arithmetic in plain PyTorch: per-token absmax int8 quantisation
@@ -235,6 +243,8 @@ class FeedForward(nn.Module):
 
     def forward(self, x: torch.Tensor, norm: RMSNorm) -> torch.Tensor:
         x13 = self.w13(x, norm)
+        if isinstance(self.w2, BitLinearKernel):
+            return self.w2.forward_glu(x13, self.ffn_sub_norm)
         x1, x3 = x13.chunk(2, -1)
         return self.w2(squared_relu(x1) * x3, self.ffn_sub_norm)
 

@@ -48,6 +48,24 @@ def quant_input(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: floa
     return y, a, ysum
 
 
+def quant_input_glu(x13: torch.Tensor, gamma: Optional[torch.Tensor] = None, eps: float = 1e-5, pad_to: int = 128):
+    """quant_input of squared_relu(x1) * x3 for bf16 x13 = [x1 | x3] of shape [.., 2K]
+    (gpu/model.py:193-196) without materialising the product."""
+    assert x13.dtype == torch.bfloat16 and x13.is_cuda and x13.shape[-1] % 2 == 0
+    k = x13.shape[-1] // 2
+    x2 = x13.reshape(-1, 2 * k)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    m = x2.shape[0]
+    k_pad = (k + pad_to - 1) // pad_to * pad_to
+    y = torch.empty((m, k_pad), dtype=torch.int8, device=x13.device)
+    a = torch.empty((m,), dtype=torch.float32, device=x13.device)
+    ysum = torch.empty((m,), dtype=torch.int32, device=x13.device)
+    _lib.check(_lib.lib.bitnet_quant_input_glu(_lib.ptr(x2), x2.stride(0), _lib.ptr(gamma), eps, _lib.ptr(y), k_pad,
+                                               _lib.ptr(a), None, _lib.ptr(ysum), m, k, _lib.stream_ptr()))
+    return y, a, ysum
+
+
 def linear_w2a8(y: torch.Tensor, act_scale: torch.Tensor, ysum: Optional[torch.Tensor], weight: torch.Tensor,
                 w_scale: torch.Tensor, seg_end: Sequence[int], n: int, k: int,
                 want_acc: bool = False, want_out: bool = True):

@@ -102,6 +102,13 @@ int bitnet_linear_w2a8(const int8_t* y, int64_t ldy, const void* w2t, void* out_
 int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, float eps,
                        int8_t* y, int64_t ldy, float* act_scale, void* s_bf16, int32_t* ysum,
                        int M, int K, void* stream);
+/* The same behind the gate of the feed-forward block (gpu/model.py:193-196): rows of x13_bf16
+ * hold 2K values [x1 | x3] (ldx >= 2K); the value that is normalised and quantised is
+ * bf16(bf16(relu(x1)^2) * x3), rounded after each step as the reference's bf16 tensor
+ * operations round. */
+int bitnet_quant_input_glu(const void* x13_bf16, int64_t ldx, const void* gamma_bf16, float eps,
+                           int8_t* y, int64_t ldy, float* act_scale, void* s_bf16, int32_t* ysum,
+                           int M, int K, void* stream);
 
 /* ---- one decode step of the whole decoder (batch <= 8) --------------------------------
  * Counterpart of the decode model that the reference captures in a CUDA graph
@@ -174,10 +181,11 @@ int bitnet_decoder_kernels_per_step(void* decoder);
  * CTA per SM, launched cooperatively, grid-wide barriers between the phases of a layer);
  * on = 0, a chain of five kernels per layer.  Both give the same bits.  Returns the mode in
  * effect afterwards: 0 when the persistent kernel does not fit the model (grouped-query ratio
- * above 4, or shared memory).  The persistent kernel is the default where it fits; a refused
- * cooperative launch switches the decoder to the chain for good.  Environment:
- * BITNET_PERSISTENT=0 starts with the chain, BITNET_NO_PERSISTENT=1 removes the persistent
- * kernel.  No counterpart in the reference. */
+ * above 4, or shared memory).  The persistent kernel is the default where it fits and every
+ * BitLinear's share of an SM fits the kernel's weight ring at once (the 2B architecture); a
+ * refused cooperative launch switches the decoder to the chain for good.  Environment:
+ * BITNET_PERSISTENT=0 / 1 starts with the chain / the persistent kernel, BITNET_NO_PERSISTENT=1
+ * removes the persistent kernel.  No counterpart in the reference. */
 int bitnet_decoder_use_persistent(void* decoder, int on);
 void bitnet_decoder_destroy(void* decoder);
 

@@ -259,6 +259,22 @@ def test_rmsnorm_quant_close_to_oracle(bn):
     assert np.array_equal(gs.cpu().numpy(), gy.cpu().numpy().astype(np.int32).sum(-1))
 
 
+@pytest.mark.parametrize("m,k", [(1, 6912), (5, 8640), (64, 6912), (3, 200)])
+def test_quant_input_glu_equals_gate_then_quant(bn, m, k):
+    """The gate of the feed-forward block fused into the quantisation kernel gives the bytes that
+    the bf16 tensor operations followed by the plain kernel give."""
+    g = torch.Generator("cuda").manual_seed(100 * m + k)
+    x13 = (torch.randn((m, 2 * k), generator=g, device="cuda") * 2).bfloat16()
+    gamma = (torch.rand((k,), generator=g, device="cuda") + 0.5).bfloat16()
+    x1, x3 = x13.chunk(2, -1)
+    gated = torch.relu(x1) ** 2 * x3
+    for gm in (None, gamma):
+        want = bn.ops.quant_input(gated, gm, 1e-5)
+        got = bn.ops.quant_input_glu(x13, gm, 1e-5)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+
+
 # ---------------------------------------------------------------------------- tcgen05 path (M >= 16)
 
 
