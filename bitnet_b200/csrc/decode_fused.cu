@@ -358,10 +358,12 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
 // Attention for one new token per sequence: RoPE on q and k, append k, v to the cache,
 // softmax(q k^T) v over one slice of the cache per CTA (flash-decoding split); the CTA that
 // finishes a (sequence, kv head) last combines the slices.  grid (n_kv_heads * S, batch),
-// 4 to 16 warps; a warp walks keys four at a time, a lane owns 4 dims.
+// 4 to 16 warps; a warp walks keys four at a time, a lane owns 4 dims.  With many sequences
+// (at least two CTAs per SM without any split) the 4-warp form runs: several CTAs share an SM
+// and hide each other's latencies, where one wide CTA per SM would run wave after wave.
 // ---------------------------------------------------------------------------------------
-template <int GMAX>
-__global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kernel(const AttentionParams p) {
+template <int GMAX, int NW = AttnCfg<GMAX>::kWarps>
+__global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const AttentionParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
     pdl_launch_dependents();
@@ -369,7 +371,6 @@ __global__ void __launch_bounds__(AttnCfg<GMAX>::kThreads) attention_decode_kern
     const int P = (int)p.pos[blockIdx.y];
     const AttnItem it = attention_item(p, blockIdx.x, P);
     if (it.G == 0) return;
-    constexpr int NW = AttnCfg<GMAX>::kWarps;
     if (it.G == 1)
         attention_body<1, NW>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, 1, it.split, it.S, P, threadIdx.x,
                               [] { __syncthreads(); }, [] {});
@@ -490,18 +491,25 @@ int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pd
     return check_cuda(e);
 }
 
-size_t attention_smem(const AttentionParams& p) {
+static size_t attention_smem_nw(const AttentionParams& p, int nw) {
     const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
-    const int nw = gmax <= 4 ? 16 : (gmax <= 8 ? 8 : 4);
     return sizeof(float) * ((size_t)(G + 2) * p.D + 2 * nw * gmax + (size_t)nw * G * p.D) + 64;
 }
+size_t attention_smem(const AttentionParams& p) {
+    const int G = p.H / p.Hkv;
+    return attention_smem_nw(p, G <= 4 ? 16 : (G <= 8 ? 8 : 4));
+}
 
-int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl) {
+int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl, bool many_sequences) {
     const int G = p.H / p.Hkv;
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (G <= 4) e = launch_k(attention_decode_kernel<4>, grid, AttnCfg<4>::kThreads, smem, stream, p, pdl);
+    if (many_sequences && G <= 4)
+        e = launch_k(attention_decode_kernel<4, 4>, grid, 4 * 32, attention_smem_nw(p, 4), stream, p, pdl);
+    else if (many_sequences && G <= 8)
+        e = launch_k(attention_decode_kernel<8, 4>, grid, 4 * 32, attention_smem_nw(p, 4), stream, p, pdl);
+    else if (G <= 4) e = launch_k(attention_decode_kernel<4>, grid, AttnCfg<4>::kThreads, smem, stream, p, pdl);
     else if (G <= 8) e = launch_k(attention_decode_kernel<8>, grid, AttnCfg<8>::kThreads, smem, stream, p, pdl);
     else e = launch_k(attention_decode_kernel<16>, grid, AttnCfg<16>::kThreads, smem, stream, p, pdl);
     return check_cuda(e);

@@ -91,7 +91,8 @@ size_t attention_smem(const AttentionParams& p);
 size_t head_smem(const HeadParams& p);
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem);
 int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pdl);
-int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl);
+// many_sequences: the 4-warp form of the kernel (see decode_fused.cu)
+int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl, bool many_sequences = false);
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl);
 int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl);
 

@@ -433,7 +433,8 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
     ap.counters = w->attn_counters;
     ap.H = n_heads; ap.Hkv = n_kv_heads; ap.D = head_dim; ap.L = max_seq_len; ap.S = s;
     if (attention_smem(ap) > 96 * 1024) return set_status(kTooLarge), kTooLarge;
-    return launch_attention(ap, batch, static_cast<cudaStream_t>(stream), false);
+    return launch_attention(ap, batch, static_cast<cudaStream_t>(stream), false,
+                            s == 1 && batch * n_kv_heads >= 2 * w->n_sm);
 }
 
 }  // extern "C"

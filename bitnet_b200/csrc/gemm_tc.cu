@@ -391,19 +391,45 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
 }
 
 // Second pass of a split-K launch: subtract sum(y), rescale, store, and clear the work space.
+// blockIdx.y = token; a thread takes four consecutive rows (one 16-byte load of sums, one
+// 8-byte store of results) when the row count and the pointers allow it.
 __global__ void __launch_bounds__(256) tc_finalize_kernel(const TcParams p) {
-    const int64_t n = (int64_t)p.M * p.N;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
-        const int tok = (int)(i / p.N), row = (int)(i - (int64_t)tok * p.N);
-        const int v = p.acc_ws[i] - p.ysum[tok];
-        p.acc_ws[i] = 0;
-        if (p.acc_out) p.acc_out[i] = v;
-        if (p.out) {
-            const int sg = segment_of(p.seg, row);
-            const float ws = p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
-            const float a = p.a_f32 ? p.a_f32[tok] : __bfloat162float(p.a_bf16[tok]);
-            p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / a * ws);
+    const int tok = blockIdx.y;
+    const int ysum = p.ysum[tok];
+    // (the scales may be absent when only the integer sums are wanted)
+    const float a = !p.out ? 1.f : (p.a_f32 ? p.a_f32[tok] : (p.a_bf16 ? __bfloat162float(p.a_bf16[tok]) : 1.f));
+    int32_t* acc = p.acc_ws + (int64_t)tok * p.N;
+    auto scale_of = [&](int row) -> float {
+        const int sg = segment_of(p.seg, row);
+        return p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
+    };
+    const bool vec = p.N % 4 == 0 && (!p.out || (p.ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0)) &&
+                     (reinterpret_cast<uintptr_t>(p.acc_ws) & 15) == 0 &&
+                     (!p.acc_out || (reinterpret_cast<uintptr_t>(p.acc_out) & 15) == 0);
+    if (vec) {
+        for (int row = (blockIdx.x * 256 + threadIdx.x) * 4; row < p.N; row += gridDim.x * 256 * 4) {
+            int4 v = *reinterpret_cast<const int4*>(acc + row);
+            *reinterpret_cast<int4*>(acc + row) = make_int4(0, 0, 0, 0);
+            v.x -= ysum; v.y -= ysum; v.z -= ysum; v.w -= ysum;
+            if (p.acc_out) *reinterpret_cast<int4*>(p.acc_out + (int64_t)tok * p.N + row) = v;
+            if (p.out) {
+                const float w0 = scale_of(row), w3 = scale_of(row + 3);
+                const float w1 = w0 == w3 ? w0 : scale_of(row + 1), w2 = w0 == w3 ? w0 : scale_of(row + 2);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn((float)v.x / a * w0, (float)v.y / a * w1);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn((float)v.z / a * w2, (float)v.w / a * w3);
+                uint2 o;
+                o.x = *reinterpret_cast<const unsigned int*>(&lo);
+                o.y = *reinterpret_cast<const unsigned int*>(&hi);
+                *reinterpret_cast<uint2*>(p.out + (int64_t)tok * p.ldo + row) = o;
+            }
         }
+        return;
+    }
+    for (int row = blockIdx.x * 256 + threadIdx.x; row < p.N; row += gridDim.x * 256) {
+        const int v = acc[row] - ysum;
+        acc[row] = 0;
+        if (p.acc_out) p.acc_out[(int64_t)tok * p.N + row] = v;
+        if (p.out) p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / a * scale_of(row));
     }
 }
 
@@ -415,9 +441,8 @@ cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
     const dim3 grid((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN), (unsigned)p.k_splits);
     w2a8_gemm_tc_kernel<TN><<<grid, kThreadsTc, TcSmem<TN>::kBytes + 1024, stream>>>(p);
     if (p.k_splits > 1) {
-        const int64_t n = (int64_t)p.M * p.N;
-        const int blocks = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
-        tc_finalize_kernel<<<blocks, 256, 0, stream>>>(p);
+        const int bx = (p.N + 1023) / 1024;   // four rows per thread
+        tc_finalize_kernel<<<dim3((unsigned)(bx < 64 ? bx : 64), (unsigned)p.M), 256, 0, stream>>>(p);
     }
     return cudaGetLastError();
 }

@@ -45,7 +45,8 @@ def test_attention_kernel_matches_pytorch_attention(models):
     from bitnet_b200.model import apply_rope, rope_table
 
     for B, H, Hkv, D, L, P in [(1, 20, 5, 128, 256, 200), (3, 8, 2, 64, 64, 5), (2, 32, 32, 100, 96, 37),
-                               (2, 80, 8, 128, 128, 0), (64, 8, 8, 128, 64, 33)]:
+                               (2, 80, 8, 128, 128, 0), (64, 8, 8, 128, 64, 33), (64, 20, 5, 128, 256, 140),
+                               (70, 32, 8, 128, 640, 600)]:
         g = torch.Generator("cuda").manual_seed(B * 100 + H)
         xqkv = torch.randn((B, (H + 2 * Hkv) * D), device="cuda", generator=g).bfloat16()
         ck = torch.randn((B, L, Hkv, D), device="cuda", generator=g).bfloat16()
