@@ -54,6 +54,8 @@ def parse_args():
                          "the library picks for the model (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
+    ap.add_argument("--sweep-only", default="", metavar="N,K,M",
+                    help="run only the isolated BitLinear call for one shape and token count (for profilers) and exit")
     ap.add_argument("--tp", action="store_true",
                     help="shard one model tensor-parallel over the ranks (strong scaling) instead of replicas; "
                          "needs head counts divisible by the rank count (8b, 100b presets)")
@@ -191,7 +193,7 @@ def run_reference(a, args_model):
 # ----------------------------------------------------------------------------------------
 # extra measurements reported beside the headline (rank 0, one GPU)
 # ----------------------------------------------------------------------------------------
-def kernel_sweep(dev, peak_gbs):
+def kernel_sweep(dev, peak_gbs, shapes=None, ms=None):
     """The isolated BitLinear call over the 2B shapes and M in {1..2048}: quantised
     activations in, bf16 out, through bitnet_linear_w2a8; distinct weight buffers (> 2 x L2)
     cycled inside a CUDA graph, time per launch from CUDA events."""
@@ -205,11 +207,11 @@ def kernel_sweep(dev, peak_gbs):
     rows = []
     g = torch.Generator(device=dev).manual_seed(1)
     stream = torch.cuda.Stream(device=dev)
-    for n, k in [(3840, 2560), (2560, 2560), (13824, 2560), (2560, 6912)]:
+    for n, k in (shapes or [(3840, 2560), (2560, 2560), (13824, 2560), (2560, 6912)]):
         nbytes = n * k // 4
         copies = max(2, int(300e6 // nbytes))
         ws = [torch.randint(-128, 127, (n, k // 4), dtype=torch.int8, device=dev, generator=g) for _ in range(copies)]
-        for m in (1, 8, 32, 128, 512, 2048):
+        for m in (ms or (1, 8, 32, 128, 512, 2048)):
             y = torch.randint(-127, 127, (m, k), dtype=torch.int8, device=dev, generator=g)
             a = torch.ones(m, device=dev)
             ysum = y.int().sum(-1).int()
@@ -532,6 +534,18 @@ def main():
     from bitnet_b200.model import preset
 
     args_model = preset(a.workload)
+    if a.sweep_only:
+        import torch
+
+        n, k, m = (int(v) for v in a.sweep_only.split(","))
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs", 6650.0))
+        except (OSError, ValueError):
+            peak = 6650.0
+        print(json.dumps({"kernel_sweep": kernel_sweep(dev, peak, shapes=[(n, k)], ms=[m])}), flush=True)
+        return
     if a.tp:
         if a.layers:
             args_model = preset(a.workload, n_layers=a.layers)

@@ -35,6 +35,8 @@ struct Workspace {
     int* attn_counters = nullptr;                 // [4096]
     int32_t* tc_acc = nullptr;                    // split-K sums of the tcgen05 kernel, zero between launches
     size_t tc_acc_ints = 0;
+    uint8_t* tc_y = nullptr;                      // activations in operand layout (tcgen05 kernel), grown on demand
+    size_t tc_y_bytes = 0;
 };
 
 static Workspace g_ws[kMaxDevices];
@@ -72,6 +74,29 @@ bool workspace_view(WorkspaceView* out) {
     if (!w) return false;
     *out = WorkspaceView{w->error_flag, w->tc_acc, w->tc_acc_ints, w->n_sm};
     return true;
+}
+
+uint8_t* workspace_tc_activations(size_t bytes, cudaStream_t stream) {
+    Workspace* w = workspace();
+    if (!w) return nullptr;
+    if (bytes <= w->tc_y_bytes) return w->tc_y;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return nullptr;                           // no allocation while a graph is being captured
+    }
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if (bytes > w->tc_y_bytes) {
+        uint8_t* nb = nullptr;
+        const size_t want = bytes + bytes / 4;
+        if (cudaMalloc(&nb, want) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        w->tc_y = nb;                             // the old buffer may still be in use by enqueued work: it is kept
+        w->tc_y_bytes = want;
+    }
+    return w->tc_y;
 }
 
 // BitLinear on caller-quantised activations through the fused kernel (M <= 8).

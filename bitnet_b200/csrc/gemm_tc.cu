@@ -58,6 +58,12 @@ struct TcParams {
     int32_t* acc_ws;             // [M, N] zero-initialised int32 work space (k_splits > 1)
     int* error_flag;
     unsigned long long* trace;   // optional cycle counters (measurement aid)
+    // Optional: the activations already in the tensor core's operand layout (restage_kernel):
+    // for K tile kt and field j, m_groups blocks of 8 tokens x 32 selected int8 (256 bytes each,
+    // two 8 x 16-byte core matrices), so that the slab of TN tokens is one contiguous piece
+    // that a bulk copy drops into the operand buffer.  Null: worker warps stage them from y.
+    const uint8_t* ycanon;
+    int m_groups;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -163,7 +169,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     uint64_t* ofull = bars + 2 * kPackStages;     // [kOpStages] operands written (8 warps)
     uint64_t* oempty = ofull + kOpStages;         // [kOpStages] operands consumed (tcgen05.commit)
     uint64_t* accfull = oempty + kOpStages;       // accumulators complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
+    uint64_t* bfull = accfull + 1;                // [kOpStages] activation slabs landed (tx bytes; ycanon only)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bfull + kOpStages);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,6 +191,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
         for (int s = 0; s < kOpStages; ++s) {
             bar_init(&ofull[s], kWorkerWarps);
             bar_init(&oempty[s], 1);
+            bar_init(&bfull[s], 1);
         }
         bar_init(accfull, 1);
         *abort_flag = 0;
@@ -200,6 +208,11 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Launched as a programmatic dependent: the set-up above and the producer's weight stream
+    // (weights are constants) overlap the tail of the preceding kernel; everything that reads
+    // or writes activations, sums or outputs waits for that kernel to finish.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    if (warp != kProducerWarp) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     const int n_pack = (nk + kPackTiles - 1) / kPackTiles;
     const int n_os = (nk + kOpTiles - 1) / kOpTiles;      // pipeline steps
@@ -217,6 +230,20 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                               p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt_lo + i0) * kTileBytes,
                               (uint32_t)(nt * kTileBytes), &wfull[s]);
             }
+        } else if (lane == 1 && p.ycanon) {
+            // the activation slabs of every pipeline step, straight into the operand buffers
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");   // written by the preceding kernel
+            for (int os = 0; os < n_os; ++os) {
+                const int b = os % kOpStages;
+                if (os >= kOpStages && !bar_wait(&oempty[b], ((os / kOpStages) - 1) & 1, abort_flag)) break;
+                const int tiles = min(kOpTiles, nk - os * kOpTiles);
+                bar_expect_tx(&bfull[b], (uint32_t)(tiles * 4 * S::kSlabB));
+                for (int kw = 0; kw < tiles; ++kw)
+                    for (int j = 0; j < 4; ++j)
+                        bulk_load(ops + (b * kOpTiles + kw) * S::kOpBytes + 4 * kSlabA + j * S::kSlabB,
+                                  p.ycanon + (((int64_t)(kt_lo + os * kOpTiles + kw) * 4 + j) * p.m_groups + (tok0 >> 3)) * 256,
+                                  (uint32_t)S::kSlabB, &bfull[b]);
+            }
         }
     } else if (warp == kMmaWarp) {
         // ---- MMA issue ----------------------------------------------------------------------
@@ -225,6 +252,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             for (int os = 0; os < n_os; ++os) {
                 const int b = os % kOpStages;
                 if (!bar_wait(&ofull[b], (os / kOpStages) & 1, abort_flag)) break;
+                if (p.ycanon && !bar_wait(&bfull[b], (os / kOpStages) & 1, abort_flag)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const int tiles = min(kOpTiles, nk - os * kOpTiles);
                 for (int kw = 0; kw < tiles; ++kw) {
@@ -261,7 +289,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                                                                (int64_t)(kt_lo + kt) * kTileCols + c16 * 16);
             }
         };
-        load_y(0);
+        const bool stage_y = p.ycanon == nullptr;
+        if (stage_y) load_y(0);
         // optional cycle counters of warp 0 of CTA (0,0,0): a measurement aid behind error_flag
         const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
         long long c_wfull = 0, c_oempty = 0, c_unpack = 0, c_stage = 0, c_fence = 0, c_t = clock64();
@@ -280,7 +309,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             uint4 ycur[kPieces];
 #pragma unroll
             for (int i = 0; i < kPieces; ++i) ycur[i] = ynext[i];
-            load_y(os + 1);
+            if (stage_y) load_y(os + 1);
             lap(c_stage);
             if ((os * kOpTiles) % kPackTiles == 0 && !bar_wait(&wfull[s], (c / kPackStages) & 1, abort_flag)) break;
             lap(c_wfull);
@@ -305,7 +334,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             }
             lap(c_unpack);
 #pragma unroll
-            for (int i = 0; i < kPieces; ++i) {
+            for (int i = 0; i < kPieces && stage_y; ++i) {
                 const int piece = wtid + i * kWorkerThreads;
                 const int kw = piece / (TN * 8), rest = piece - kw * (TN * 8);
                 const int t = rest >> 3, c16 = rest & 7;
@@ -394,6 +423,8 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
 // blockIdx.y = token; a thread takes four consecutive rows (one 16-byte load of sums, one
 // 8-byte store of results) when the row count and the pointers allow it.
 __global__ void __launch_bounds__(256) tc_finalize_kernel(const TcParams p) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");   // the partial sums of the preceding kernel
     const int tok = blockIdx.y;
     const int ysum = p.ysum[tok];
     // (the scales may be absent when only the integer sums are wanted)
@@ -433,16 +464,59 @@ __global__ void __launch_bounds__(256) tc_finalize_kernel(const TcParams p) {
     }
 }
 
+// Activations [M, ldy] (rows zero filled up to a multiple of 128 columns) into the operand
+// layout described at TcParams::ycanon.  One thread per 16-byte piece of a row.
+__global__ void __launch_bounds__(256) restage_kernel(const int8_t* __restrict__ y, int64_t ldy, uint8_t* __restrict__ out,
+                                                      int M, int k_tiles, int m_groups) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int64_t n = (int64_t)M * k_tiles * 8;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+        const int c16 = (int)(i & 7);
+        const int64_t r = i >> 3;
+        const int kt = (int)(r % k_tiles), t = (int)(r / k_tiles);
+        const uint4 v = *reinterpret_cast<const uint4*>(y + (int64_t)t * ldy + (int64_t)kt * kTileCols + c16 * 16);
+        const int qq = c16 >> 1, j0 = (c16 & 1) * 2;   // bytes 0-7: field j0, bytes 8-15: field j0 + 1
+        uint8_t* dst = out + (((int64_t)kt * 4 + j0) * m_groups + (t >> 3)) * 256 + (qq >> 1) * 128 + (t & 7) * 16 + (qq & 1) * 8;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(v.x, v.y);
+        *reinterpret_cast<uint2*>(dst + (int64_t)m_groups * 256) = make_uint2(v.z, v.w);
+    }
+}
+
 template <int TN>
 cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(w2a8_gemm_tc_kernel<TN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          TcSmem<TN>::kBytes + 1024);
     if (e != cudaSuccess) return e;
-    const dim3 grid((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN), (unsigned)p.k_splits);
-    w2a8_gemm_tc_kernel<TN><<<grid, kThreadsTc, TcSmem<TN>::kBytes + 1024, stream>>>(p);
+    if (p.ycanon) {
+        const int64_t pieces = (int64_t)p.M * p.k_tiles * 8;
+        const int blocks = (int)((pieces + 255) / 256 < 4736 ? (pieces + 255) / 256 : 4736);
+        restage_kernel<<<blocks, 256, 0, stream>>>(p.y, p.ldy, const_cast<uint8_t*>(p.ycanon), p.M, p.k_tiles, p.m_groups);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    // Both kernels are launched as programmatic dependents of whatever precedes them in the
+    // stream (BITNET_NO_PDL=1: ordinary stream order).
+    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((p.N + kRows - 1) / kRows), (unsigned)((p.M + TN - 1) / TN), (unsigned)p.k_splits);
+    cfg.blockDim = dim3(kThreadsTc);
+    cfg.dynamicSmemBytes = TcSmem<TN>::kBytes + 1024;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    e = cudaLaunchKernelEx(&cfg, w2a8_gemm_tc_kernel<TN>, p);
+    if (e != cudaSuccess) return e;
     if (p.k_splits > 1) {
         const int bx = (p.N + 1023) / 1024;   // four rows per thread
-        tc_finalize_kernel<<<dim3((unsigned)(bx < 64 ? bx : 64), (unsigned)p.M), 256, 0, stream>>>(p);
+        cfg.gridDim = dim3((unsigned)(bx < 64 ? bx : 64), (unsigned)p.M);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        e = cudaLaunchKernelEx(&cfg, tc_finalize_kernel, p);
+        if (e != cudaSuccess) return e;
     }
     return cudaGetLastError();
 }
@@ -473,6 +547,12 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t a
     if (ks < 1 || !acc_ws || (size_t)a.M * a.N > acc_ws_ints) ks = 1;
     p.k_splits = ks;
     p.acc_ws = acc_ws;
+    // Many tokens: lay the activations out for the tensor core once, instead of in every CTA.
+    static const bool no_prestage = getenv("BITNET_TC_NO_PRESTAGE") != nullptr;
+    if (a.M >= 128 && !no_prestage) {
+        p.m_groups = (a.M + 127) / 128 * 16;
+        p.ycanon = workspace_tc_activations((size_t)p.m_groups * 8 * p.k_tiles * kTileCols, stream);
+    }
     cudaError_t e;
     if (a.M <= 32) e = launch_tc<32>(p, stream);
     else if (a.M <= 64) e = launch_tc<64>(p, stream);

@@ -38,6 +38,10 @@ struct WorkspaceView {
     int n_sm;
 };
 bool workspace_view(WorkspaceView* out);
+// Device buffer of at least `bytes` bytes for the re-laid-out activations of the tcgen05 kernel,
+// owned by the per-device workspace.  Grows by allocation, so only outside stream capture; null
+// when it cannot be had (the kernel then stages the activations itself).
+uint8_t* workspace_tc_activations(size_t bytes, cudaStream_t stream);
 
 // Packers (all buffers on the device).
 int pack_ternary_to_w2t(const int8_t* q, void* w2t, int N, int K, cudaStream_t stream);

@@ -2,6 +2,8 @@
 // second half of the row), optional RMSNorm, then per-token absmax int8 quantisation (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242).
 // One CTA of 256 threads per token; the arithmetic lives in prologue.cuh, shared with the
 // fused decode kernels.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "prologue.cuh"
@@ -16,6 +18,10 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
     __shared__ float sy_part[kPrologueThreads / 32];
     __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(smem_q);
     const int tok = blockIdx.x, tid = threadIdx.x;
+    // launched as a programmatic dependent: the launch overlaps the tail of the kernel that
+    // produces x
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const __nv_bfloat16* row = p.x_bf16 + (int64_t)tok * p.ldx;
     const bool vec_ok = aligned16(p.x_bf16, p.ldx, 2);
     const int K = p.K;
@@ -59,8 +65,18 @@ int act_quant(const QuantArgs& a, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return check_cuda(e);
     }
-    act_quant_kernel<<<a.M, kPrologueThreads, smem, stream>>>(a);
-    return check_cuda(cudaGetLastError());
+    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.M);
+    cfg.blockDim = dim3(kPrologueThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = no_pdl ? 0 : 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, act_quant_kernel, a));
 }
 
 }  // namespace bitnet
