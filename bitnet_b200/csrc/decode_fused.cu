@@ -36,7 +36,8 @@ namespace bitnet {
 
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kStages = 6;                                // ring: 96 KB
+constexpr int kRoundStages = 2;                           // stages a round of the consumers spans
 constexpr int kStageTiles = 32;
 constexpr int kStageBytes = kStageTiles * kTileBytes;     // 16 KB
 constexpr int kConsumerWarps = 8;
@@ -227,7 +228,9 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     // warp-instructions per clock, so the 16 ANDs per tile, not the MMAs, bound the loop.
     const int g = lane >> 2, q = lane & 3;
     const int rg_first = t0 / p.k_tiles;
-    constexpr int kRoundTiles = kStages * kStageTiles;   // tiles resident in the ring at once
+    // A round spans two of the ring's six stages: while the warps work on one round, the copies
+    // of the next two rounds are in flight (64 KB per SM, what the HBM latency asks for).
+    constexpr int kRoundTiles = kRoundStages * kStageTiles;
     int cur_rg = -1;
     int acc[4][4];
     auto flush = [&]() {
@@ -251,8 +254,8 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     // MMA column g multiplies token g; columns beyond M read the zero row behind the last token
     const int8_t* y_lane = ys + (size_t)(g < p.M ? g : p.M) * y_stride + 32 * q;
     const int ysub0 = (2 * q < p.M) ? ysum_s[2 * q] : 0, ysub1 = (2 * q + 1 < p.M) ? ysum_s[2 * q + 1] : 0;
-    // The ring holds a round of up to 128 tiles; within a round each warp takes one
-    // contiguous run, so that it flushes rarely and its loop reaches a steady state.
+    // Within a round (up to 64 tiles) each warp takes one contiguous run, so that it flushes
+    // rarely and its loop reaches a steady state.
     const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
 #pragma unroll 1
     for (int r = 0; r < n_rounds; ++r) {
@@ -261,7 +264,10 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         if (hi > lo && !(p.debug & 2)) {
             bool ok = true;
 #pragma unroll 1
-            for (int s = lo / kStageTiles; s <= (hi - 1) / kStageTiles; ++s) ok = ok && mbar_wait(&full_bar[s], r & 1);
+            for (int ls = lo / kStageTiles; ls <= (hi - 1) / kStageTiles; ++ls) {
+                const int c = r * kRoundStages + ls;     // chunk number of the CTA's tile range
+                ok = ok && mbar_wait(&full_bar[c % kStages], (c / kStages) & 1);
+            }
             if (!ok) {   // gave up: flag it, leave together below
                 if (lane == 0) {
                     atomicExch(p.error_flag, 2);
@@ -273,7 +279,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         if (r == 0) stamp(6);
         const int t_first = t0 + r * kRoundTiles + lo;
         int rg = t_first / p.k_tiles, kt = t_first - rg * p.k_tiles;
-        const uint8_t* tile = ring + lo * kTileBytes + lane * 16;
+        const uint8_t* tile = ring + ((r * kRoundStages) % kStages) * kStageBytes + lo * kTileBytes + lane * 16;
 #pragma unroll 1
         for (int i = lo; i < hi; ++i, tile += kTileBytes) {
             if (rg != cur_rg) {
@@ -301,7 +307,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         __syncwarp();
         if (lane == 0) {   // this warp is done with every stage of the round
 #pragma unroll 1
-            for (int s = 0; s < kStages; ++s) mbar_arrive(&empty_bar[s]);
+            for (int ls = 0; ls < kRoundStages; ++ls) mbar_arrive(&empty_bar[(r * kRoundStages + ls) % kStages]);
         }
     }
     stamp(7);

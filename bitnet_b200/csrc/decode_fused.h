@@ -102,7 +102,7 @@ int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl);
 // the step does not fit that kernel.
 void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, const HeadParams& hp, int n_layers, int M,
                   int grid, size_t smem_optin);
-bool mega_recommended(const void* plan);
+bool mega_single_round(const void* plan);
 void mega_destroy(void* plan);
 int mega_launch(void* plan, const HeadParams& hp, int64_t* tokens, int64_t* pos, int64_t* out, int* error_flag,
                 unsigned long long* trace, cudaStream_t stream);

@@ -670,10 +670,11 @@ void* mega_create(const FusedLinearParams* lin, const AttentionParams* att, cons
     return mp;
 }
 
-// True when the persistent kernel is expected to beat the chain of kernels: every BitLinear's
-// share of a CTA fits one round of the ring, so that all its weights are on the SM before the
-// phase starts.  (Measured on B200: 2B architecture at batch 1 and 8 faster, 3B and 8B slower.)
-bool mega_recommended(const void* plan) { return plan && static_cast<const MegaPlan*>(plan)->single_round; }
+// True when every BitLinear's share of a CTA fits one round of the ring, so that all its weights
+// are on the SM before the phase starts: the condition under which the persistent kernel comes
+// within a few per cent of the chain of kernels (2B architecture; 3B and 8B need several rounds
+// per phase and lose more).
+bool mega_single_round(const void* plan) { return plan && static_cast<const MegaPlan*>(plan)->single_round; }
 
 void mega_destroy(void* plan) {
     MegaPlan* mp = static_cast<MegaPlan*>(plan);

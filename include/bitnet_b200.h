@@ -181,11 +181,10 @@ int bitnet_decoder_kernels_per_step(void* decoder);
  * CTA per SM, launched cooperatively, grid-wide barriers between the phases of a layer);
  * on = 0, a chain of five kernels per layer.  Both give the same bits.  Returns the mode in
  * effect afterwards: 0 when the persistent kernel does not fit the model (grouped-query ratio
- * above 4, or shared memory).  The persistent kernel is the default where it fits and every
- * BitLinear's share of an SM fits the kernel's weight ring at once (the 2B architecture); a
- * refused cooperative launch switches the decoder to the chain for good.  Environment:
- * BITNET_PERSISTENT=0 / 1 starts with the chain / the persistent kernel, BITNET_NO_PERSISTENT=1
- * removes the persistent kernel.  No counterpart in the reference. */
+ * above 4, or shared memory).  The chain is the default (measured faster on B200); a refused
+ * cooperative launch also switches the decoder back to the chain for good.  Environment:
+ * BITNET_PERSISTENT=1 starts with the persistent kernel, BITNET_NO_PERSISTENT=1 removes it.
+ * No counterpart in the reference. */
 int bitnet_decoder_use_persistent(void* decoder, int on);
 void bitnet_decoder_destroy(void* decoder);
 
