@@ -59,7 +59,7 @@ def parse_args():
     ap.add_argument("--tp", action="store_true",
                     help="shard one model tensor-parallel over the ranks (strong scaling) instead of replicas; "
                          "needs head counts divisible by the rank count (8b, 100b presets)")
-    ap.add_argument("--layers", type=int, default=0, help="use only the first LAYERS layers (0 = all; with --tp)")
+    ap.add_argument("--layers", type=int, default=0, help="use only the first LAYERS layers (0 = all): a small case for profilers, or with --tp")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="tokens in the KV cache when decode starts (with --tp)")
     return ap.parse_args()
 
@@ -425,7 +425,7 @@ def run_ours(a, args_model):
                      "us_per_launch": 1e3 * ms_lin / n_lin, "achieved": achieved, "frac": achieved / peak,
                      # dram__bytes_read + write per launch from one ncu capture of the four 2B shapes
                      # (profiles/fused_linear_kernel_2b_m1.md), averaged as the launches are mixed
-                     "traffic": 4.505e6 if (fused and a.workload == "2b" and B == 1) else None}
+                     "traffic": 4.50e6 if (fused and a.workload == "2b" and B == 1) else None}
     if persistent:
         # One kernel per step: its algorithmic bytes are everything the step must read.
         roofline = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
@@ -533,7 +533,7 @@ def main():
     a = parse_args()
     from bitnet_b200.model import preset
 
-    args_model = preset(a.workload)
+    args_model = preset(a.workload, n_layers=a.layers) if a.layers else preset(a.workload)
     if a.sweep_only:
         import torch
 
@@ -547,8 +547,6 @@ def main():
         print(json.dumps({"kernel_sweep": kernel_sweep(dev, peak, shapes=[(n, k)], ms=[m])}), flush=True)
         return
     if a.tp:
-        if a.layers:
-            args_model = preset(a.workload, n_layers=a.layers)
         return run_tp(a, args_model)
     if a.impl == "reference":
         run_reference(a, args_model)
