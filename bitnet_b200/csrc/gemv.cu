@@ -179,10 +179,20 @@ cudaError_t launch(const GemvParams& p, cudaStream_t stream) {
 }  // namespace
 
 int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
-    // Decode-sized batches go through the fused kernel; BITNET_GEMV_DIRECT=1 keeps them on
-    // the direct-load kernel below (for comparisons).
+    // Decode-sized batches of already quantised activations: measured on B200, the direct-load
+    // kernel below is the faster one for almost every shape (13824 x 2560: 5.2 vs 8.4 us at M = 1,
+    // 5.4 vs 13.7 us at M = 8; 65536 x 10240: 43 vs 68 us, 61 % of the measured copy bandwidth) -
+    // the fused kernel earns its keep inside the decode chain, where it also does the prologue and
+    // overlaps its predecessor.  It stays ahead for one or two tokens on short, wide matrices
+    // (2560 x 6912: 6.7 vs 8.2 us), where the direct kernel has too few row groups to fill the SMs.
+    // BITNET_GEMV_DIRECT=1 / BITNET_GEMV_FUSED=1 force one or the other (for comparisons).
     static const bool direct = getenv("BITNET_GEMV_DIRECT") != nullptr;
-    if (a.M <= 8 && !direct && a.K % 8 == 0) return fused_linear_quantized(a, stream);
+    static const bool fused = getenv("BITNET_GEMV_FUSED") != nullptr;
+    if (a.M <= 8 && !direct && a.K % 8 == 0 && (fused || (a.M <= 2 && a.K >= 2 * a.N && a.N <= 4096))) {
+        const int rc = fused_linear_quantized(a, stream);
+        if (rc != kTooLarge) return rc;
+        set_status(kOk);   // does not fit the fused kernel's shared memory: the direct kernel takes it
+    }
     // Larger batches go to the tcgen05 kernel when the activations are laid out for it.
     static const bool no_tc = getenv("BITNET_NO_TCGEN05") != nullptr;
     const int64_t k_pad = (a.K + kTileCols - 1) / kTileCols * kTileCols;
