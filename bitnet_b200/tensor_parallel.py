@@ -247,3 +247,38 @@ class TPDecoder:
     def decode_step(self, tokens: torch.Tensor, pos: torch.Tensor, cache) -> torch.Tensor:
         """tokens int64 [B, 1] -> next tokens int64 [B]."""
         return self.greedy(self.hidden(tokens, pos, cache))
+
+
+class GraphedStep:
+    """One greedy decode step of a TPDecoder captured in a CUDA graph (collectives included:
+    NCCL work enqueued on the capturing stream becomes graph nodes).  The step feeds itself:
+    `tokens` [B, 1] is overwritten with the chosen ids and `pos` [B] advances by one, so a
+    decode loop is a sequence of `replay()` calls.  Every rank must build and replay it
+    in step with the others."""
+
+    def __init__(self, dec: "TPDecoder", tokens: torch.Tensor, pos: torch.Tensor, cache, warmup: int = 2):
+        assert tokens.is_cuda and tokens.dim() == 2 and tokens.shape[1] == 1
+        self.dec, self.tokens, self.pos, self.cache = dec, tokens, pos, cache
+        self.out = torch.zeros((tokens.shape[0],), dtype=torch.int64, device=tokens.device)
+        self.stream = torch.cuda.Stream(device=tokens.device)
+        saved = tokens.clone()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):      # allocations, lazy initialisation, NCCL connections
+                self._body()
+                self.tokens.copy_(saved)
+                self.pos.sub_(1)
+            self.stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream, capture_error_mode="thread_local"):
+                self._body()
+        torch.cuda.synchronize()
+
+    def _body(self):
+        nxt = self.dec.decode_step(self.tokens, self.pos, self.cache)
+        self.out.copy_(nxt)
+        self.tokens.copy_(nxt.view(-1, 1))
+        self.pos.add_(1)
+
+    def replay(self):
+        self.graph.replay()

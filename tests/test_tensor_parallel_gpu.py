@@ -35,7 +35,29 @@ def run(dec):
         outs.append(dec.logits(h))
         tok = dec.greedy(h).view(2, 1)
     return torch.cat([o.reshape(-1) for o in outs]), tok
-tp = run(TPDecoder(args, 7, rank, world, "cuda", backend="kernel", max_seq_len=64))
+dec_tp = TPDecoder(args, 7, rank, world, "cuda", backend="kernel", max_seq_len=64)
+tp = run(dec_tp)
+# the same decode steps replayed from a CUDA graph (collectives captured) give the same tokens
+from bitnet_b200.tensor_parallel import GraphedStep
+def greedy_loop(graph):
+    g = torch.Generator().manual_seed(6)
+    tok = torch.randint(0, args.vocab_size, (2, 1), generator=g).cuda()
+    pos = torch.full((2,), 3, dtype=torch.int64, device="cuda")
+    cache = dec_tp.make_cache(2, 64)
+    outs = []
+    step = GraphedStep(dec_tp, tok, pos, cache) if graph else None
+    for s in range(6):
+        if graph:
+            step.replay()
+            torch.cuda.synchronize()
+            outs.append(step.out.clone())
+        else:
+            nxt = dec_tp.decode_step(tok, pos, cache)
+            tok = nxt.view(2, 1)
+            pos += 1
+            outs.append(nxt.clone())
+    return torch.stack(outs)
+assert torch.equal(greedy_loop(True), greedy_loop(False))
 if rank == 0:
     one = run(TPDecoder(args, 7, 0, 1, "cuda", backend="kernel", max_seq_len=64))
     assert torch.equal(tp[0], one[0]), float((tp[0] - one[0]).abs().max())
