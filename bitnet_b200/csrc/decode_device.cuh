@@ -204,28 +204,67 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
 #pragma unroll
                 for (int u = 0; u < U; ++u)
                     if (h < G) sc[h][u] += __shfl_xor_sync(0xffffffffu, sc[h][u], o);
+        if constexpr (GMAX * U + GMAX <= 32) {
+            // Every lane holds all scores.  The exponentials are shared out: lane h*U+u computes the
+            // weight of key u for head h, lane GMAX*U+h the correction of head h's running sums (one
+            // special-function instruction per warp instead of GMAX*U+GMAX), and shuffles hand them
+            // round.  A key beyond n gets exp(-inf) = 0.
+            float mn[GMAX];
+            float arg = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < GMAX; ++h) {
-            if (h < G) {
-                float mn = m_h[h];
+            for (int h = 0; h < GMAX; ++h) {
+                mn[h] = m_h[h];
 #pragma unroll
                 for (int u = 0; u < U; ++u)
-                    if (u < n) mn = fmaxf(mn, sc[h][u]);
-                const float corr = __expf(m_h[h] - mn);
-                float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (u < n) mn[h] = fmaxf(mn[h], sc[h][u]);
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (u < n) {
-                        const float pr = __expf(sc[h][u] - mn);
+                for (int u = 0; u < U; ++u)
+                    if (lane == h * U + u && h < G && u < n) arg = sc[h][u] - mn[h];
+                if (lane == GMAX * U + h && h < G) arg = m_h[h] - mn[h];
+            }
+            const float ex = __expf(arg);
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) {
+                if (h < G) {
+                    const float corr = __shfl_sync(0xffffffffu, ex, GMAX * U + h);
+                    float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const float pr = __shfl_sync(0xffffffffu, ex, h * U + u);
                         ps += pr;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) ov[e] += pr * vf[u][e];
                     }
-                }
-                l_h[h] = l_h[h] * corr + ps;
+                    l_h[h] = l_h[h] * corr + ps;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
-                m_h[h] = mn;
+                    for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
+                    m_h[h] = mn[h];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) {
+                if (h < G) {
+                    float mn = m_h[h];
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        if (u < n) mn = fmaxf(mn, sc[h][u]);
+                    const float corr = __expf(m_h[h] - mn);
+                    float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (u < n) {
+                            const float pr = __expf(sc[h][u] - mn);
+                            ps += pr;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ov[e] += pr * vf[u][e];
+                        }
+                    }
+                    l_h[h] = l_h[h] * corr + ps;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
+                    m_h[h] = mn;
+                }
             }
         }
     };
