@@ -197,6 +197,56 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
 #pragma unroll
             for (int u = 0; u < U; ++u)
                 sc[h][u] = q_r[h][0] * kf[u][0] + q_r[h][1] * kf[u][1] + q_r[h][2] * kf[u][2] + q_r[h][3] * kf[u][3];
+        if constexpr (GMAX == 4 && U == 4) {
+            // Sixteen partial scores per lane, to be summed over the 32 lanes.  Instead of a
+            // butterfly on all of them (80 shuffles) the lanes halve their set in every round
+            // (8 + 4 + 2 + 1 + 1 shuffles; the same additions in the same order for each value):
+            // lanes 2i and 2i+1 end up with the total of value i = 4 h + u, take the head's
+            // maximum with the three other keys' lanes, compute the one weight they own and the
+            // head's correction, and shuffles hand the results to everybody.
+            const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+            float a8[8], a4[4], a2[2];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float lo_v = sc[i >> 2][i & 3], hi_v = sc[(i + 8) >> 2][i & 3];
+                a8[i] = (b4 ? hi_v : lo_v) + __shfl_xor_sync(0xffffffffu, b4 ? lo_v : hi_v, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a4[i] = (b3 ? a8[i + 4] : a8[i]) + __shfl_xor_sync(0xffffffffu, b3 ? a8[i] : a8[i + 4], 8);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) a2[i] = (b2 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, b2 ? a4[i] : a4[i + 2], 4);
+            float s_mine = (b1 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, b1 ? a2[0] : a2[1], 2);
+            s_mine += __shfl_xor_sync(0xffffffffu, s_mine, 1);
+            const int h_mine = (lane >> 3) & 3, u_mine = (lane >> 1) & 3;
+            const bool valid = h_mine < G && u_mine < n;
+            float mx = valid ? s_mine : -INFINITY;
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            const float m_old = h_mine == 0 ? m_h[0] : (h_mine == 1 ? m_h[1] : (h_mine == 2 ? m_h[2] : m_h[3]));
+            const float mn_mine = fmaxf(m_old, mx);
+            const float p_mine = valid ? __expf(s_mine - mn_mine) : 0.f;
+            const float corr_mine = __expf(m_old - mn_mine);
+#pragma unroll
+            for (int h = 0; h < GMAX; ++h) {
+                if (h < G) {
+                    const float mn = __shfl_sync(0xffffffffu, mn_mine, h * 8);
+                    const float corr = __shfl_sync(0xffffffffu, corr_mine, h * 8);
+                    float ps = 0.f, ov[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const float pr = __shfl_sync(0xffffffffu, p_mine, h * 8 + u * 2);
+                        ps += pr;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ov[e] += pr * vf[u][e];
+                    }
+                    l_h[h] = l_h[h] * corr + ps;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o_h[h][e] = o_h[h][e] * corr + ov[e];
+                    m_h[h] = mn;
+                }
+            }
+            return;
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
