@@ -49,9 +49,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="2b", help="architecture preset (2b, 3b, 8b, 100b)")
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--engine", choices=["auto", "persistent", "chain"], default="auto",
+    ap.add_argument("--engine", choices=["auto", "persistent", "chain", "ops"], default="auto",
                     help="decode step (batch <= 8) as one persistent kernel, as the chain of kernels, or whichever "
-                         "the library picks for the model (auto)")
+                         "the library picks for the model (auto); ops = one launch per operation (the path of batches above 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
     ap.add_argument("--sweep-only", default="", metavar="N,K,M",
@@ -305,7 +305,12 @@ def run_ours(a, args_model):
     B, K, W = a.batch, a.steps, a.warmup
     max_seq = (PROMPT_LEN + 2 * (K + W) + 3 * W + 64 + 127) // 128 * 128
     model = build_synthetic(args_model, seed=SEED + rank, device=dev, max_seq_len=max_seq)
-    gen = Generator(model, B, max_seq, persistent=None if (a.engine == "auto" or B > 8) else a.engine == "persistent")
+    if a.engine == "ops":
+        gen = Generator(model, B, max_seq, fused=False)
+    else:
+        explicit = a.engine in ("persistent", "chain") and B <= 8
+        gen = Generator(model, B, max_seq, fused=True if explicit else None,
+                        persistent=(a.engine == "persistent") if explicit else None)
     persistent = gen.persistent
     g = torch.Generator(device=dev)
     g.manual_seed(SEED + 17 * rank)
