@@ -142,7 +142,8 @@ def cpu_i2s_tokens_per_s(args_model, batch: int, steps: int, warmup: int, layers
         lib, kind = O.RefLib(ref_path), "reference"
     else:
         lib, kind = O.PortLib(build_oracle.build_port()), "port"
-    threads = lib.max_threads()
+    # every core this process may run on, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     rng = np.random.default_rng(SEED)
     # bytes whose four 2-bit fields are all in {0,1,2}: valid I2_S codes, ternary weights
     valid = np.array([a << 6 | b << 4 | c << 2 | d for a in range(3) for b in range(3) for c in range(3)
@@ -567,7 +568,7 @@ def run_tp(a, args_model):
 
 def main():
     a = parse_args()
-    from bitnet_b200.model import preset
+    from bitnet_b200.config import preset   # no torch, no CUDA library: the reference arm loads neither
 
     args_model = preset(a.workload, n_layers=a.layers) if a.layers else preset(a.workload)
     if a.sweep_only:

@@ -23,6 +23,7 @@ namespace bitnet {
 // ---------------------------------------------------------------------------------------
 constexpr int kMaxDevices = 64;
 constexpr int kWsRowGroups = 1 << 15;             // BitLinear outputs up to 524288 rows
+constexpr size_t kWsYsumInts = 1 << 16;           // row sums for up to 65536 tokens
 
 struct Workspace {
     bool ready = false;
@@ -35,6 +36,7 @@ struct Workspace {
     int* attn_counters = nullptr;                 // [4096]
     int32_t* tc_acc = nullptr;                    // split-K sums of the tcgen05 kernel, zero between launches
     size_t tc_acc_ints = 0;
+    int32_t* ysum = nullptr;                      // row sums computed for callers that pass none
     uint8_t* tc_y = nullptr;                      // activations in operand layout (tcgen05 kernel), grown on demand
     size_t tc_y_bytes = 0;
 };
@@ -57,13 +59,14 @@ Workspace* workspace() {
     const size_t acc_bytes = (size_t)kWsRowGroups * 128 * 8, ctr_bytes = 0;
     uint8_t* base = nullptr;
     const size_t tc_ints = (size_t)4 << 20;    // 16 MB: up to 128 tokens x 32768 rows
-    const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256 + tc_ints * 4;
+    const size_t total = acc_bytes + ctr_bytes + 4096 * 4 + 256 + tc_ints * 4 + kWsYsumInts * 4;
     if (check_cuda(cudaMalloc(&base, total)) || check_cuda(cudaMemset(base, 0, total))) return nullptr;
     w.acc_scratch = reinterpret_cast<unsigned long long*>(base);
     w.attn_counters = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes);
     w.error_flag = reinterpret_cast<int*>(base + acc_bytes + ctr_bytes + 4096 * 4);
     w.tc_acc = reinterpret_cast<int32_t*>(base + acc_bytes + ctr_bytes + 4096 * 4 + 256);
     w.tc_acc_ints = tc_ints;
+    w.ysum = w.tc_acc + tc_ints;
     if (prepare_fused_kernels(w.smem_optin, 96 * 1024, w.smem_optin)) return nullptr;
     w.ready = true;
     return &w;
@@ -72,7 +75,7 @@ Workspace* workspace() {
 bool workspace_view(WorkspaceView* out) {
     Workspace* w = workspace();
     if (!w) return false;
-    *out = WorkspaceView{w->error_flag, w->tc_acc, w->tc_acc_ints, w->n_sm};
+    *out = WorkspaceView{w->error_flag, w->tc_acc, w->tc_acc_ints, w->ysum, kWsYsumInts, w->n_sm};
     return true;
 }
 

@@ -71,6 +71,11 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
     const int g = lane >> 2, q = lane & 3;
     const int row_group = blockIdx.x;
     const int tok0 = blockIdx.y * (8 * MB);
+    // Launched as a programmatic dependent: the activations may be the predecessor's output.
+    // (The weights are constants, but this kernel loads them straight into registers, where
+    // only a few fit, so nothing is fetched ahead of the wait.)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     int acc[NC][MB][4];
 #pragma unroll
@@ -168,12 +173,54 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
     }
 }
 
+// Both kernels of this file are launched as programmatic dependents of whatever precedes them
+// in the stream: the launch and the set-up overlap the predecessor's tail.
+template <class Kernel, class Params>
+cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t stream, const Params& p) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <int MB, bool FOUR>
 cudaError_t launch(const GemvParams& p, cudaStream_t stream) {
     const dim3 grid((unsigned)((p.N + 15) / 16), (unsigned)((p.M + 8 * MB - 1) / (8 * MB)));
-    if (p.ysum) w2a8_gemv_kernel<MB, FOUR, false><<<grid, kThreads, 0, stream>>>(p);
-    else w2a8_gemv_kernel<MB, FOUR, true><<<grid, kThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+    if (p.ysum) return launch_pdl(w2a8_gemv_kernel<MB, FOUR, false>, grid, dim3(kThreads), stream, p);
+    return launch_pdl(w2a8_gemv_kernel<MB, FOUR, true>, grid, dim3(kThreads), stream, p);
+}
+
+// sum_k y[m, k] per token, one warp per token: for callers of the tensor-core kernel that hand
+// over plain int8 rows without their sums (the reference's bitlinear_int8xint2 arguments).
+struct RowSumParams {
+    const int8_t* y;
+    int64_t ldy;
+    int32_t* ysum;
+    int M, K;
+};
+__global__ void __launch_bounds__(256) row_sum_kernel(const RowSumParams p) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= p.M) return;
+    const uint4* row = reinterpret_cast<const uint4*>(p.y + (int64_t)tok * p.ldy);   // 16-byte aligned, K % 16 == 0
+    int s = 0;
+    for (int v = lane; v < p.K / 16; v += 32) {
+        const uint4 u = row[v];
+        s = __dp4a((int)u.x, 0x01010101, s);
+        s = __dp4a((int)u.y, 0x01010101, s);
+        s = __dp4a((int)u.z, 0x01010101, s);
+        s = __dp4a((int)u.w, 0x01010101, s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) p.ysum[tok] = s;
 }
 
 }  // namespace
@@ -196,11 +243,20 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
     // Larger batches go to the tcgen05 kernel when the activations are laid out for it.
     static const bool no_tc = getenv("BITNET_NO_TCGEN05") != nullptr;
     const int64_t k_pad = (a.K + kTileCols - 1) / kTileCols * kTileCols;
-    if (a.M >= 16 && !no_tc && a.ysum && a.ldy % 16 == 0 && a.ldy >= k_pad &&
-        (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+    if (a.M >= 16 && !no_tc && a.ldy % 16 == 0 && a.ldy >= k_pad && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
         WorkspaceView ws;
         if (!workspace_view(&ws)) return kCudaError;
-        return w2a8_gemm_tc(a, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, stream);
+        if (a.ysum) return w2a8_gemm_tc(a, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, stream);
+        if ((size_t)a.M <= ws.ysum_ints) {
+            // plain int8 rows without their sums (the arguments of the reference's symbol): one
+            // small kernel adds them up into the workspace, then the same tensor-core path
+            const RowSumParams rp{a.y, a.ldy, ws.ysum, a.M, (int)k_pad};
+            if (check_cuda(launch_pdl(row_sum_kernel, dim3((unsigned)((a.M + 7) / 8)), dim3(256), stream, rp)))
+                return kCudaError;
+            LinearArgs b = a;
+            b.ysum = ws.ysum;
+            return w2a8_gemm_tc(b, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, stream);
+        }
     }
     GemvParams p;
     p.w = reinterpret_cast<const uint4*>(a.w2t);

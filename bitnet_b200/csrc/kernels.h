@@ -35,6 +35,8 @@ struct WorkspaceView {
     int* error_flag;
     int32_t* tc_acc;          // zero between launches
     size_t tc_acc_ints;
+    int32_t* ysum;            // room for the row sums of callers that pass none
+    size_t ysum_ints;
     int n_sm;
 };
 bool workspace_view(WorkspaceView* out);

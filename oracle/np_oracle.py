@@ -63,8 +63,10 @@ def to_bf16(x: np.ndarray) -> np.ndarray:
 
 
 def matmul_i32(y: np.ndarray, w: np.ndarray) -> np.ndarray:
-    """Exact int32 y[M,K] @ w[N,K]^T (what gpu/test.py:46-50 computes with NumPy)."""
-    return y.astype(np.int32) @ w.astype(np.int32).T
+    """Exact int32 y[M,K] @ w[N,K]^T (what gpu/test.py:46-50 computes with NumPy).  Evaluated
+    in f64 through BLAS: every partial sum is an integer far below 2^53, so the result is
+    exact, and large cases finish in seconds."""
+    return (y.astype(np.float64) @ w.astype(np.float64).T).astype(np.int64).astype(np.int32)
 
 
 def rescale(acc: np.ndarray, a: np.ndarray, w_scale, seg_end=None) -> np.ndarray:

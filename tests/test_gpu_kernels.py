@@ -136,6 +136,76 @@ def test_gemv_sweep_int32_exact_and_bf16(bn, port_lib, ref_lib, n, k, m):
         assert rel.max() <= 1e-2                                             # the stated tolerance
 
 
+@pytest.mark.parametrize("n,k", S2B)
+@pytest.mark.parametrize("m", [128, 512, 2048])
+def test_kernel_sweep_grid_large_m(bn, port_lib, n, k, m):
+    """The remaining cells of the isolated-kernel sweep (the four 2B shapes x M in {1, 8, 32,
+    128, 512, 2048}; the small M are covered above): padded int8 activations with their sums, as
+    the model hands them over, int32 sums bit-exact against the C port of the reference kernel
+    and bf16 outputs equal to the oracle's rescale."""
+    q, ws, x, y, a, ysum, acc = _oracle_case(n, k, m, seed=3 * n + k + m, port_lib=port_lib)
+    w2t = bn.pack.convert_weight_int8_to_int2(_dev(q))
+    gy, ga, gs = bn.ops.quant_input(_dev(x).bfloat16())
+    assert np.array_equal(gy.cpu().numpy()[:, :k], y) and np.array_equal(gs.cpu().numpy(), ysum)
+    wsd = _dev(np.array([ws], dtype=np.float32))
+    out, got = bn.ops.linear_w2a8(gy, ga, gs, w2t, wsd, [n], n, k, want_acc=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), acc)                           # bit-exact int32
+    want = O.to_bf16(O.rescale(acc, a, [ws]))
+    got_f = out.float().cpu().numpy()
+    assert (np.abs(got_f - want) <= 1e-2 * np.maximum(np.abs(want), 1e-6)).all()   # the stated tolerance
+    assert np.array_equal(got_f, want)                                       # same f32 operations -> same bf16
+
+
+@pytest.mark.parametrize("n,k,m", [(2560, 2560, 128), (3840, 2560, 16), (13824, 2560, 512), (2560, 6912, 130)])
+def test_reference_entry_point_many_tokens(bn, port_lib, n, k, m):
+    """bitlinear_int8xint2 with M >= 16 (the reference's symbol takes plain [M, K] int8 rows and
+    no row sums, gpu/model.py:21-37): same bf16 results as the oracle, per-token scales."""
+    q, ws, x, y, a, ysum, acc = _oracle_case(n, k, m, seed=n + 7 * m, port_lib=port_lib)
+    s_bf = O.to_bf16(a)
+    ws_bf = O.to_bf16(np.array([0.5, 1.25, 0.875, 2.0], dtype=np.float32))
+    seg = O.ref_gpu_scale_segments(n, k)
+    weight = bn.pack.convert_weight_int8_to_int2(_dev(q))
+    out = bn.ops.bitnet_int8xint2_linear(_dev(y), weight, _dev(s_bf).bfloat16(), _dev(ws_bf).bfloat16())
+    torch.cuda.synchronize()
+    want = O.to_bf16(O.rescale(acc, s_bf, ws_bf[: len(seg)], seg))
+    assert np.array_equal(out.float().cpu().numpy(), want)
+
+
+def test_reference_gpu_kernel_agrees(bn):
+    """The reference's own GPU kernel (gpu/bitnet_kernels/bitnet_kernels.cu, built with its own
+    command line, loaded from PTX) on its own packing against this library's symbol on the W2T
+    packing of the same weights: identical bf16 outputs for the four 2B shapes at M = 1."""
+    from oracle import build_oracle
+
+    path = build_oracle.build_ref_gpu()
+    if not path:
+        pytest.skip("the reference's GPU kernel library is not available")
+    try:
+        ref = ctypes.CDLL(path)
+    except OSError as exc:
+        pytest.skip(f"the reference's GPU kernel library does not load here: {exc}")
+    ref.bitlinear_int8xint2.restype = None
+    ref.bitlinear_int8xint2.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p]
+    for n, k in S2B:
+        q, _ = O.synth_weights(n, k, seed=n + k)
+        y, a, ysum = O.act_quant(O.synth_acts(1, k, seed=k + 1))
+        s_bf = _dev(O.to_bf16(a)).bfloat16()
+        ws_bf = _dev(O.to_bf16(np.array([0.5, 1.25, 0.875, 2.0], dtype=np.float32))).bfloat16()
+        yd = _dev(y)
+        ref_w = _dev(O.ref_gpu_pack(q))
+        ref_out = torch.zeros((1, n), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        ref.bitlinear_int8xint2(bn._lib.ptr(yd), bn._lib.ptr(ref_w), bn._lib.ptr(ref_out), bn._lib.ptr(s_bf),
+                                bn._lib.ptr(ws_bf), 1, n, k, bn._lib.stream_ptr())
+        torch.cuda.synchronize()
+        ours = bn.ops.bitnet_int8xint2_linear(yd, bn.pack.convert_ref_int2_to_w2t(ref_w), s_bf, ws_bf)
+        torch.cuda.synchronize()
+        if not ref_out.any():
+            pytest.skip("the reference kernel's PTX produced no output on this GPU")
+        assert torch.equal(ours, ref_out), (n, k)
+
+
 @pytest.mark.parametrize("n,k,m", [(2560, 2560, 128), (3840, 2560, 65), (2560, 6912, 130), (13824, 2560, 512)])
 def test_large_m_int32_exact(bn, port_lib, n, k, m):
     q, ws, x, y, a, ysum, acc = _oracle_case(n, k, m, seed=5 * n + m, port_lib=port_lib)
