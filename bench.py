@@ -35,8 +35,6 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read + dram__bytes_write of one decode_mega_kernel launch (ncu, profiles/decode_mega_kernel_2b_m1.md)
-PERSISTENT_TRAFFIC = {("2b", 1): 1.1989e9}
 PROMPT_LEN = 128
 SEED = 20240611
 
@@ -49,9 +47,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="2b", help="architecture preset (2b, 3b, 8b, 100b)")
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--engine", choices=["auto", "persistent", "chain", "ops"], default="auto",
-                    help="decode step (batch <= 8) as one persistent kernel, as the chain of kernels, or whichever "
-                         "the library picks for the model (auto); ops = one launch per operation (the path of batches above 8)")
+    ap.add_argument("--engine", choices=["auto", "chain", "ops"], default="auto",
+                    help="decode step (batch <= 8) as the in-library chain of fused kernels, or whichever path the "
+                         "generator picks for the batch (auto); ops = one launch per operation (the path of batches above 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel sweep and the batch-64 decode")
     ap.add_argument("--sweep-only", default="", metavar="N,K,M",
@@ -309,10 +307,7 @@ def run_ours(a, args_model):
     if a.engine == "ops":
         gen = Generator(model, B, max_seq, fused=False)
     else:
-        explicit = a.engine in ("persistent", "chain") and B <= 8
-        gen = Generator(model, B, max_seq, fused=True if explicit else None,
-                        persistent=(a.engine == "persistent") if explicit else None)
-    persistent = gen.persistent
+        gen = Generator(model, B, max_seq, fused=True if (a.engine == "chain" and B <= 8) else None)
     g = torch.Generator(device=dev)
     g.manual_seed(SEED + 17 * rank)
     prompt = torch.randint(0, args_model.vocab_size, (B, PROMPT_LEN), generator=g, device=dev)
@@ -430,22 +425,14 @@ def run_ours(a, args_model):
     step_bytes = weight_bytes + 2 * args_model.vocab_size * args_model.dim
     step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
     # the BitLinear kernels of the chain on their own (prologue + matmul, no attention, no head)
-    chain_linears = {"kernel": "fused_linear_kernel (prologue + W2A8 matmul, PDL chain)" if fused else "w2a8_gemv_kernel",
+    chain_linears = {"kernel": "chain_linear_kernel (prologue + W2A8 matmul + epilogue, PDL chain)" if fused else "w2a8_gemv_kernel",
                      "launches_per_step": n_lin, "bytes_per_launch": weight_bytes / n_lin,
                      "us_per_launch": 1e3 * ms_lin / n_lin, "achieved": achieved, "frac": achieved / peak,
                      # dram__bytes_read + write per launch from one ncu capture of the four 2B shapes
                      # (profiles/fused_linear_kernel_2b_m1.md), averaged as the launches are mixed
                      "traffic": 4.50e6 if (fused and a.workload == "2b" and B == 1) else None}
-    if persistent:
-        # One kernel per step: its algorithmic bytes are everything the step must read.
-        roofline = {"bound": "hbm", "achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
-                    "traffic": PERSISTENT_TRAFFIC.get((a.workload, B)), "peak_source": "measured" if peaks else "fallback",
-                    "kernel": "decode_mega_kernel (whole decode step: %d BitLinears, attention, output head)" % n_lin,
-                    "launches_per_step": 1, "bytes_per_launch": step_bytes, "us_per_launch": 1e3 * ms / K,
-                    "bitlinear_bytes": weight_bytes, "chain_bitlinear": chain_linears}
-    else:
-        roofline = dict(chain_linears, bound="hbm", peak=peak, unit="GB/s", peak_source="measured" if peaks else "fallback",
-                        step_bytes=step_bytes, step_gbs=step_gbs, step_frac=step_gbs / peak)
+    roofline = dict(chain_linears, bound="hbm", peak=peak, unit="GB/s", peak_source="measured" if peaks else "fallback",
+                    step_bytes=step_bytes, step_gbs=step_gbs, step_frac=step_gbs / peak)
     line = {
         "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{B})", "value": world * B * K / (ms * 1e-3),
         "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
@@ -454,7 +441,7 @@ def run_ours(a, args_model):
         "config": {"workload": f"{a.workload} architecture random-init (seed {SEED}), batch {B}, {PROMPT_LEN} random "
                                f"prompt tokens then greedy decode; replicas x{world}",
                    "batch": B, "prompt_len": PROMPT_LEN,
-                   "engine": "persistent kernel" if persistent else ("kernel chain" if fused else "op by op"),
+                   "engine": "kernel chain" if fused else "op by op",
                    "l2": "weights read per step (%.0f MB packed + bf16 output projection) exceed the 126 MB L2"
                          % (weight_bytes / 1e6)},
         "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,

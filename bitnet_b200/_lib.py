@@ -21,7 +21,7 @@ lib = ctypes.CDLL(LIB_PATH)
 
 _vp, _i, _i64, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
-# every symbol include/bitnet_b200.h declares: name -> (restype, argtypes)
+# every symbol the headers under include/ declare: name -> (restype, argtypes)
 SIGNATURES = {
     "bitnet_last_status": (_i, []),
     "bitnet_status_string": (ctypes.c_char_p, [_i]),
@@ -30,6 +30,7 @@ SIGNATURES = {
     "bitnet_attention_decode": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "bitlinear_int8xint2": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bitlinear_int8xint2_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "bitlinear_int8xint2_noalloc_error": (_i, [_i]),
     "bitnet_linear_w2a8": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _vp]),
     "bitnet_quant_input": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
     "bitnet_quant_input_glu": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
@@ -38,10 +39,11 @@ SIGNATURES = {
     "bitnet_decoder_step_sync": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "bitnet_decoder_bench_linears": (_i, [_vp, _vp, _vp]),
     "bitnet_decoder_read_trace": (_i, [_vp, _vp, _i]),
-    "bitnet_debug_read_workspace_words": (_i, [_vp, _i]),
+    "bitnet_decoder_set_attention_tap": (_i, [_vp, _vp]),
     "bitnet_decoder_error_flag": (_i, [_vp]),
+    "bitnet_decoder_clear_error": (_i, [_vp]),
     "bitnet_decoder_kernels_per_step": (_i, [_vp]),
-    "bitnet_decoder_use_persistent": (_i, [_vp, _i]),
+    "bitnet_workspace_error": (_i, [_i]),
     "bitnet_decoder_destroy": (None, [_vp]),
     "bitnet_w2t_bytes": (ctypes.c_size_t, [_i, _i]),
     "bitnet_pack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),
@@ -59,6 +61,8 @@ SIGNATURES = {
     "ggml_bitnet_mul_mat": (None, [_vp, _vp]),
     "ggml_bitnet_get_type_bits": (_i, [_i]),
     "ggml_bitnet_set_n_threads": (None, [_i]),
+    "ggml_preprocessor": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "ggml_qgemm_lut": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ggml_vec_dot_i2_i8_s": (None, [_i, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _vp, ctypes.c_size_t, _i]),
 }
 

@@ -1,5 +1,5 @@
-// Device code shared by the PDL-chained decode kernels (decode_fused.cu) and the persistent
-// decode kernel (decode_mega.cu): PTX helpers, the attention body and the output-head body.
+// Device code shared by the decode kernels (decode_fused.cu, decode_chain.cu): PTX helpers,
+// the split-KV attention body and the output-head body.
 #pragma once
 #include "common.cuh"
 #include "decode_fused.h"
@@ -109,15 +109,13 @@ __device__ __forceinline__ AttnItem attention_item(const AttentionParams& p, int
 // attention_smem() bytes; `sync` is a barrier over the NW * 32 participating threads.
 // The first keys of the slice are requested before `wait()`, which returns once the new token's
 // q, k, v (xqkv) are visible: the cache rows and the positions must not change meanwhile.
+// Returns true when this CTA wrote p.out for its heads (always with S == 1; with several slices
+// only the CTA that combined them).
 template <int GMAX, int NW, class Sync, class Wait>
-__device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t* smem, int* is_last_s, int b, int kvh,
+__device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t* smem, int* is_last_s, int b, int kvh,
                                                int h0, int G, int split, int S, int P, int tid, Sync sync, Wait wait) {
     constexpr int NT = NW * 32;
     const int warp = tid >> 5, lane = tid & 31;
-    auto mark = [&](int i) {   // optional cycle stamps of thread 0 (a measurement aid)
-        if (p.trace && tid == 0) p.trace[i] = (unsigned long long)clock64();
-    };
-    mark(6);
     const int D = p.D, Gfull = p.H / p.Hkv;
     float* q_s = reinterpret_cast<float*>(smem);          // [G][D]
     float* knew = q_s + G * D;                             // [D]
@@ -146,7 +144,6 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
     };
     request(lo + warp * U);
     wait();
-    mark(7);
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
@@ -177,7 +174,6 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         }
     }
     sync();
-    mark(8);
 
     // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
     float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
@@ -341,7 +337,6 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
             }
         visit(kf, vf, 1);
     }
-    mark(9);
     // combine the warps
 #pragma unroll
     for (int h = 0; h < GMAX; ++h) {
@@ -370,14 +365,14 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         const float on = l > 0.f ? o / l : 0.f;
         if (S == 1) {                       // a single slice: this is the result
             p.out[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(on);
+            if (p.tap) p.tap[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(on);
             continue;
         }
         const int64_t slot = ((int64_t)b * p.H + kvh * Gfull + h0 + h) * p.S + split;
         p.part_o[slot * D + d] = on;
         if (d == 0) { p.part_ml[slot * 2] = mx; p.part_ml[slot * 2 + 1] = l; }
     }
-    mark(10);
-    if (S == 1) return;
+    if (S == 1) return true;
     // the last slice of this (sequence, kv head) to finish combines all of them
     __threadfence();
     sync();
@@ -388,7 +383,7 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         if (*is_last_s) *ctr = 0;
     }
     sync();
-    if (!*is_last_s) return;
+    if (!*is_last_s) return false;
     __threadfence();
     // weights of the slices per head, then one pass over the partial outputs
     float* sl_m = red_o;                  // [G][S] max, then weight
@@ -419,7 +414,9 @@ __device__ __forceinline__ void attention_body(const AttentionParams& p, uint8_t
         float num = 0.f;
         for (int sidx = 0; sidx < S; ++sidx) num += sl_m[h * p.S + sidx] * __ldcg(po + (int64_t)sidx * D);
         p.out[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(num);
+        if (p.tap) p.tap[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(num);
     }
+    return true;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -436,31 +433,35 @@ constexpr int kHeadMaxLoads = 10;   // 16-byte loads per lane per pass over a ro
 template <class Sync>
 __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, int cta, int n_cta, int tid, Sync sync) {
     float* xs = reinterpret_cast<float*>(smem);                 // [M][K]
-    float* scratch = xs + (size_t)p.M * p.K;                    // [16]
-    float* best_v = scratch + 16;                               // [16 warps][8]
+    double* red_d = reinterpret_cast<double*>(xs + (size_t)p.M * p.K);   // [16] (M * K is even)
+    float* best_v = reinterpret_cast<float*>(red_d + 16);       // [16 warps][8]
     int* best_i = reinterpret_cast<int*>(best_v + 16 * 8);      // [16 warps][8]
     const int warp = tid >> 5, lane = tid & 31;
 
+    // final RMSNorm (gpu/model.py:280) of every token into shared memory, as f32 values of the
+    // bf16 result; the sum of squares in double precision (see prologue.cuh), taken from the
+    // producer's partial statistics when it published them
     for (int m = 0; m < p.M; ++m) {
-        float ss = 0.f;
+        double ss = 0.0;
+        if (p.stats_in) {
+            for (int i = tid; i < p.n_stats_in; i += kHeadThreads) ss += __ldcg(&p.stats_in[(size_t)m * p.n_stats_in + i].ss);
+        }
         for (int k = tid; k < p.K; k += kHeadThreads) {
             const float v = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(p.h + (int64_t)m * p.K + k)) << 16);   // L2: written by other SMs
             xs[(size_t)m * p.K + k] = v;
-            ss += v * v;
+            if (!p.stats_in) ss = fma((double)v, (double)v, ss);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         sync();
-        if (lane == 0) scratch[warp] = ss;
+        if (lane == 0) red_d[warp] = ss;
         sync();
-        float tot = 0.f;
-        for (int i = 0; i < kHeadThreads / 32; ++i) tot += scratch[i];
-        const float rinv = rsqrtf(tot / (float)p.K + p.eps);
+        double tot = 0.0;
+        for (int i = 0; i < kHeadThreads / 32; ++i) tot += red_d[i];
+        const float rinv = (float)(1.0 / sqrt(tot / (double)p.K + (double)p.eps));
         for (int k = tid; k < p.K; k += kHeadThreads)
             xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * __bfloat162float(p.gamma[k]) * rinv);
     }
-    sync();
-
     const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
     float bv[8];
     int bi[8];
@@ -504,7 +505,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
                 for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
                 d = bf16_round(d);
                 if (lane == 0 && p.logits) p.logits[(int64_t)m * p.V + row] = d;
-                if (d > bv[m]) { bv[m] = d; bi[m] = row; }     // rows ascend: first maximum wins
+                if (d > bv[m]) { bv[m] = d; bi[m] = row + p.row_offset; }     // rows ascend: first maximum wins
             }
         }
     }

@@ -1,32 +1,20 @@
-// Fused decode kernels for batches of at most 8 tokens, and the chain that makes one
-// decode step of the BitNet decoder out of them:
+// The stand-alone fused BitLinear for batches of at most 8 tokens on caller-quantised
+// activations, the decode attention of the op-by-op path, the output head and the greedy
+// choice.  (The BitLinear and attention kernels of the decode chain live in decode_chain.cu.)
 //
-//   per layer:  wqkv -> attention -> wo -> w13 -> w2          then:  output head -> argmax
-//
-// A BitLinear at batch 1 moves 1.6-8.8 MB of packed weights: about a microsecond of HBM
-// time, less than a kernel boundary costs.  The chain therefore hides the boundaries
-// instead of paying them: with programmatic dependent launch every kernel lets its
-// successor start at once (griddepcontrol.launch_dependents as its first instruction); the
-// successor's CTAs bring their share of the weight matrix into shared memory with bulk
-// asynchronous copies - the weights do not depend on the predecessor - and only then wait
-// for the predecessor (griddepcontrol.wait) to read the activations.
-//
-// fused_linear_kernel = prologue + W2A8 matmul + epilogue:
-//  * prologue (every CTA, redundantly; the vector is a few KB): source vector -> RMSNorm ->
-//    bf16 -> absmax -> int8 (prologue.cuh), following gpu/model.py:68-71, 159-160, 192-197,
-//    237-243;
-//  * matmul: the matrix is a flat sequence of 16x128 tiles (row-group major); CTA c of G
-//    takes a contiguous range of total/G tiles, so the load is even for every shape.  A
-//    producer warp streams the range through a ring of 16 KB stages with cp.async.bulk; eight
-//    consumer warps unpack with masks only and multiply with mma.sync m16n8k32 (u8 x s8);
-//  * epilogue: ranges cut through row groups, so a CTA that holds only part of a row
-//    group's K range adds its int32 sums to a scratch buffer (red.global.add; integer
-//    addition is order independent) and takes a ticket from the row group's counter; the
-//    CTA that draws the last ticket rescales the finished sums to bf16 (and adds the
-//    residual), then clears scratch and counter for the next launch.  Nobody waits.
+// fused_linear_kernel: the matrix is a flat sequence of 16x128 tiles (row-group major); CTA c
+// of G takes a contiguous range of total/G tiles, so the load is even for every shape.  A
+// producer warp streams the range through a ring of 16 KB stages with cp.async.bulk; eight
+// consumer warps unpack with masks only and multiply with mma.sync m16n8k32 (u8 x s8).
+// Ranges cut through row groups, so a CTA that holds only part of a row group's K range adds
+// its int32 sums and a ticket to a 64-bit scratch slot in one atomic; the contributor that
+// completes the count rescales the finished sums to bf16, then clears the slot.  Nobody waits.
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <mutex>
+
+#include "../../include/bitnet_b200.h"
 #include "common.cuh"
 #include "decode_fused.h"
 #include "prologue.cuh"
@@ -74,30 +62,17 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     uint8_t* ring = smem;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* empty_bar = full_bar + kStages;
-    float* scratch = reinterpret_cast<float*>(empty_bar + kStages);            // 16 floats
-    float* sy_part = scratch + 16;                                             // [8 tokens][8 warps]
-    int* ysum_s = reinterpret_cast<int*>(sy_part + 64);                        // 8 ints
+    int* sy_part = reinterpret_cast<int*>(empty_bar + kStages);                // [8 tokens][8 warps]
+    int* ysum_s = sy_part + 64;                                                // 8 ints
     float* a_s = reinterpret_cast<float*>(ysum_s + 8);                         // 8 floats
     int* flag_s = reinterpret_cast<int*>(a_s + 8);                             // 8 ints (1 used)
     int* sacc = flag_s + 8;                                                    // [r_max][16][8]
-    const int k_stage = p.src == kSrcQuantized ? 0 : p.K_even;                 // staging rows
-    __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(sacc + p.r_max * 128); // [K_even] source / normalised row
-    __nv_bfloat16* xb = xv + k_stage;                                           // [K_even] second GLU operand
-    __nv_bfloat16* gs = xb + k_stage;                                           // [K_even] RMSNorm weight
     const int k_pad = p.k_tiles * kTileCols;
     const int y_stride = k_pad + 16;
-    int8_t* ys = reinterpret_cast<int8_t*>(gs + k_stage);                       // [M][y_stride]
+    int8_t* ys = reinterpret_cast<int8_t*>(sacc + p.r_max * 128);              // [M + 1][y_stride]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
-    auto stamp = [&](int i) {   // optional phase timestamps of CTA 0 (a measurement aid)
-        if (p.trace && cta == 0 && tid == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[i] = t;
-        }
-    };
-    stamp(0);
 
     const int t0 = cta * p.tiles_base + min(cta, p.tiles_rem);
     const int n_tiles = p.tiles_base + (cta < p.tiles_rem ? 1 : 0);
@@ -123,7 +98,7 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             for (int c = 0; c < n_chunks; ++c) {
                 const int s = c % kStages;
                 if (c >= kStages && !mbar_wait(&empty_bar[s], ((c / kStages) - 1) & 1)) {
-                    atomicExch(p.error_flag, 1);
+                    atomicExch(p.error_flag, kErrProducerWait);
                     break;
                 }
                 const int tiles = min(kStageTiles, n_tiles - c * kStageTiles);
@@ -137,93 +112,50 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
     // ---- consumers ---------------------------------------------------------------------
 #pragma unroll 1
     for (int i = tid; i < p.r_max * 128; i += kConsumerThreads) sacc[i] = 0;
-    const int n_vec = p.K_even / 8;
-    const bool use_gamma = p.src != kSrcQuantized && p.gamma != nullptr;
-    if (use_gamma) {   // the norm weight is a constant: stage it before the wait
-#pragma unroll 1
-        for (int v = tid; v < n_vec; v += kConsumerThreads) cp_async16(gs + v * 8, p.gamma + v * 8);
-    }
-
-    stamp(1);
     pdl_wait();   // the predecessor's results are visible from here on
-    stamp(2);
 
-    // prologue: the int8 activations of every token, in shared memory (plus one row of zeros)
+    // the int8 activations of every token, in shared memory (plus one row of zeros)
 #pragma unroll 1
     for (int v = tid; v < y_stride / 16; v += kConsumerThreads)
         *reinterpret_cast<uint4*>(ys + (size_t)p.M * y_stride + v * 16) = make_uint4(0, 0, 0, 0);
 #pragma unroll 1
     for (int m = 0; m < p.M; ++m) {
         int8_t* ym = ys + (size_t)m * y_stride;
-        float a, sy_warp;
-        if (p.src == kSrcQuantized) {
-            const int8_t* row = p.yq + (int64_t)m * p.ldy;
-            const bool vec_ok = aligned16(p.yq, p.ldy, 1);
-            float sy = 0.f;
+        const int8_t* row = p.yq + (int64_t)m * p.ldy;
+        const bool vec_ok = aligned16(p.yq, p.ldy, 1);
+        int sy = 0;
 #pragma unroll 1
-            for (int v = tid; v < k_pad / 16; v += kConsumerThreads) {
-                uint4 u = make_uint4(0, 0, 0, 0);
-                const int k = v * 16;
-                if (vec_ok && k + 16 <= p.K) {
-                    u = *reinterpret_cast<const uint4*>(row + k);
-                } else {
-                    uint32_t w[4] = {0, 0, 0, 0};
+        for (int v = tid; v < k_pad / 16; v += kConsumerThreads) {
+            uint4 u = make_uint4(0, 0, 0, 0);
+            const int k = v * 16;
+            if (vec_ok && k + 16 <= p.K) {
+                u = *reinterpret_cast<const uint4*>(row + k);
+            } else {
+                uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll 1
-                    for (int e = 0; e < 16; ++e)
-                        if (k + e < p.K) w[e >> 2] |= (uint32_t)(uint8_t)row[k + e] << (8 * (e & 3));
-                    u = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                *reinterpret_cast<uint4*>(ym + k) = u;
-                sy += (float)(__dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) +
-                              __dp4a((int)u.z, 0x01010101, 0) + __dp4a((int)u.w, 0x01010101, 0));
+                for (int e = 0; e < 16; ++e)
+                    if (k + e < p.K) w[e >> 2] |= (uint32_t)(uint8_t)row[k + e] << (8 * (e & 3));
+                u = make_uint4(w[0], w[1], w[2], w[3]);
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
-            sy_warp = p.ysum_q ? (warp == 0 ? (float)p.ysum_q[m] : 0.f) : sy;
-            a = p.a_q ? p.a_q[m] : (p.a_q_bf16 ? __bfloat162float(p.a_q_bf16[m]) : 1.f);
-        } else {
-            // stage the source row(s) with asynchronous 16-byte copies, all in flight at once
-            const __nv_bfloat16* row = p.src == kSrcEmbedding ? p.emb + p.tokens[m] * (int64_t)p.K
-                                                              : p.x + (int64_t)m * p.ldx;
-#pragma unroll 1
-            for (int v = tid; v < n_vec; v += kConsumerThreads) {
-                cp_async16(xv + v * 8, row + v * 8);
-                if (p.src == kSrcGlu) cp_async16(xb + v * 8, row + p.K + v * 8);
-            }
-            cp_async_wait_all();
-            if (p.src == kSrcGlu) {          // relu(x1)^2 * x3 with bf16 rounding after each step
-#pragma unroll 1
-                for (int v = tid; v < n_vec; v += kConsumerThreads) {
-                    Vec8 x1 = unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8));
-                    const Vec8 x3 = unpack_bf16x8(*reinterpret_cast<const uint4*>(xb + v * 8));
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float t = fmaxf(x1.v[e], 0.f);
-                        x1.v[e] = bf16_round(bf16_round(t * t) * x3.v[e]);
-                    }
-                    *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x1);
-                }
-            } else if (p.src == kSrcEmbedding && p.h_copy && cta == 0) {
-                // the residual stream starts as the embedding row
-#pragma unroll 1
-                for (int v = tid; v < n_vec; v += kConsumerThreads)
-                    *reinterpret_cast<uint4*>(p.h_copy + (int64_t)m * p.K + v * 8) = *reinterpret_cast<const uint4*>(xv + v * 8);
-            }
-            norm_quant_row(xv, p.K, k_pad, use_gamma ? gs : nullptr, p.eps, ym, scratch, tid, ConsumerSync(), a, sy_warp);
+            *reinterpret_cast<uint4*>(ym + k) = u;
+            sy += __dp4a((int)u.x, 0x01010101, 0) + __dp4a((int)u.y, 0x01010101, 0) + __dp4a((int)u.z, 0x01010101, 0) +
+                  __dp4a((int)u.w, 0x01010101, 0);
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
+        const int sy_warp = p.ysum_q ? (warp == 0 ? p.ysum_q[m] : 0) : sy;
+        const float a = p.a_q ? p.a_q[m] : (p.a_q_bf16 ? __bfloat162float(p.a_q_bf16[m]) : 1.f);
         if (lane == 0) sy_part[m * 8 + warp] = sy_warp;
         if (tid == 0) a_s[m] = a;
         consumer_sync();   // xv is reused by the next token; ys, sy_part, a_s are complete
     }
-    if (tid < p.M) {       // sum(y) per token: the eight warp sums are exact integers
-        float t = 0.f;
+    if (tid < p.M) {       // sum(y) per token
+        int t = 0;
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) t += sy_part[tid * 8 + w];
-        ysum_s[tid] = (int)t;
+        ysum_s[tid] = t;
     }
     consumer_sync();
-
-    stamp(3);
     // ---- matmul over the staged tiles ----------------------------------------------------
     // Per tile a lane holds the A fragments of rows g, g+8 for four m16n8k32 MMAs: each of its
     // four words is split into its four 2-bit fields by AND masks alone (field j stays scaled
@@ -264,8 +196,8 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
 #pragma unroll 1
     for (int r = 0; r < n_rounds; ++r) {
         const int nr = min(kRoundTiles, n_tiles - r * kRoundTiles);
-        const int lo = nr * warp / kConsumerWarps, hi = (p.debug & 1) ? lo : nr * (warp + 1) / kConsumerWarps;
-        if (hi > lo && !(p.debug & 2)) {
+        const int lo = nr * warp / kConsumerWarps, hi = nr * (warp + 1) / kConsumerWarps;
+        if (hi > lo) {
             bool ok = true;
 #pragma unroll 1
             for (int ls = lo / kStageTiles; ls <= (hi - 1) / kStageTiles; ++ls) {
@@ -274,13 +206,12 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             }
             if (!ok) {   // gave up: flag it, leave together below
                 if (lane == 0) {
-                    atomicExch(p.error_flag, 2);
+                    atomicExch(p.error_flag, kErrConsumerWait);
                     flag_s[0] = 1;
                 }
                 break;
             }
         }
-        if (r == 0) stamp(6);
         const int t_first = t0 + r * kRoundTiles + lo;
         int rg = t_first / p.k_tiles, kt = t_first - rg * p.k_tiles;
         const uint8_t* tile = ring + ((r * kRoundStages) % kStages) * kStageBytes + lo * kTileBytes + lane * 16;
@@ -314,10 +245,8 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
             for (int ls = 0; ls < kRoundStages; ++ls) mbar_arrive(&empty_bar[(r * kRoundStages + ls) % kStages]);
         }
     }
-    stamp(7);
     flush();
     consumer_sync();
-    stamp(4);
     if (flag_s[0] || n_tiles == 0) return;
 
     // ---- epilogue --------------------------------------------------------------------------
@@ -333,8 +262,6 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         const int rgi = rg_first + li, row = rgi * 16 + r;
         const bool partial = (li == 0 && part_first) || (li == n_rg - 1 && li > 0 && part_last);
         if (row >= p.N && !partial) continue;
-        float h_old = 0.f;
-        if (p.out && p.out_kind == kOutResidual && row < p.N) h_old = __bfloat162float(p.out[(int64_t)m * p.ldo + row]);
         int v = sacc[rem * 8 + m];
         if (partial) {
             // Row group shared with other CTAs: add this CTA's sum and a ticket to the 64-bit
@@ -355,13 +282,10 @@ __global__ void __launch_bounds__(kLinearThreads, 2) fused_linear_kernel(const F
         if (p.acc_out) p.acc_out[(int64_t)m * p.N + row] = v;
         if (p.out) {
             const int sg = segment_of(p.seg, row);
-            const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg]
-                                          : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : p.ws[sg]);
-            const float lin = lin_out(v, a_s[m], ws);
-            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(p.out_kind == kOutResidual ? h_old + lin : lin);
+            const float ws = p.ws_dev_f32 ? p.ws_dev_f32[sg] : (p.ws_dev_bf16 ? __bfloat162float(p.ws_dev_bf16[sg]) : 1.f);
+            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(lin_out(v, a_s[m], ws));
         }
     }
-    stamp(5);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -379,6 +303,10 @@ __global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const Attenti
     pdl_launch_dependents();
     pdl_wait();
     const int P = (int)p.pos[blockIdx.y];
+    if (P < 0 || P >= p.L) {      // outside the cache: flag it, touch nothing
+        if (threadIdx.x == 0 && blockIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, kErrPosition);
+        return;
+    }
     const AttnItem it = attention_item(p, blockIdx.x, P);
     if (it.G == 0) return;
     if (it.G == 1)
@@ -452,9 +380,7 @@ cudaError_t launch_k(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem,
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    // BITNET_NO_PDL=1 launches everything with ordinary stream ordering (for measurements)
-    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
-    cfg.numAttrs = (pdl && !no_pdl) ? 1 : 0;
+    cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
@@ -472,8 +398,8 @@ void plan_linear(FusedLinearParams& p, int n_sm) {
 
 size_t fused_linear_smem(const FusedLinearParams& p) {
     const size_t y_stride = (size_t)p.k_tiles * kTileCols + 16;
-    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + (16 + 64 + 8 * 3) * 4 + (size_t)p.r_max * 128 * 4 +
-           (p.src == kSrcQuantized ? 0 : (size_t)p.K_even * 6) + (size_t)(p.M + 1) * y_stride + 128;
+    return (size_t)kStages * kStageBytes + 2 * kStages * sizeof(uint64_t) + (64 + 8 * 3) * 4 + (size_t)p.r_max * 128 * 4 +
+           (size_t)(p.M + 1) * y_stride + 128;
 }
 
 int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t max_head_smem) {
@@ -493,12 +419,7 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
 }
 
 int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pdl) {
-    const size_t smem = fused_linear_smem(p);
-    cudaError_t e;
-    switch (p.src) {
-        default: e = launch_k(fused_linear_kernel, p.grid, kLinearThreads, smem, stream, p, pdl); break;
-    }
-    return check_cuda(e);
+    return check_cuda(launch_k(fused_linear_kernel, p.grid, kLinearThreads, fused_linear_smem(p), stream, p, pdl));
 }
 
 static size_t attention_smem_nw(const AttentionParams& p, int nw) {
@@ -525,7 +446,7 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     return check_cuda(e);
 }
 
-size_t head_smem(const HeadParams& p) { return sizeof(float) * ((size_t)p.M * p.K + 16 + 16 * 8 * 2) + 64; }
+size_t head_smem(const HeadParams& p) { return sizeof(float) * ((size_t)p.M * p.K + 32 + 16 * 8 * 2) + 64; }
 
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl) {
     return check_cuda(launch_k(output_head_kernel, grid, kHeadThreads, head_smem(p), stream, p, pdl));
@@ -547,17 +468,42 @@ namespace {
 
 constexpr int kStaticRowGroups = 1024;                      // outputs of up to 16384 rows
 constexpr int kStaticSlots = kStaticRowGroups * 128;        // one 64-bit slot per (row, token)
-// 1 MB of slots plus one word for the kernel's error flag.  Every GPU that loads the library
+// 1 MB of slots plus one word for the kernel's error code.  Every GPU that loads the library
 // holds this array until the process exits.
 static __device__ __align__(256) unsigned long long g_static_scratch[kStaticSlots + 32];
 
 struct StaticSetup {
-    bool ready = false;
+    bool ready = false;                      // written last, under the mutex
     unsigned long long* scratch = nullptr;   // device address of g_static_scratch on this device
     int n_sm = 0;
     int smem_optin = 0;
 };
 StaticSetup g_static_setup[64];
+std::mutex g_static_mutex;
+
+// The set-up of the calling thread's current device (done once per device, under a lock).
+StaticSetup* static_setup() {
+    int dev = 0;
+    if (check_cuda(cudaGetDevice(&dev))) return nullptr;
+    if (dev < 0 || dev >= 64) return set_status(kUnsupported), nullptr;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSetup& st = g_static_setup[dev];
+    if (st.ready) return &st;
+    // With that device current: the array's name is only a host-side handle, the kernel needs
+    // the address the runtime reports for it on this device.
+    void* ptr = nullptr;
+    int n_sm = 0, smem_optin = 0;
+    if (check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch))) return nullptr;
+    if (check_cuda(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev)) ||
+        check_cuda(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) ||
+        check_cuda(cudaFuncSetAttribute(fused_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin)))
+        return nullptr;
+    st.scratch = static_cast<unsigned long long*>(ptr);
+    st.n_sm = n_sm;
+    st.smem_optin = smem_optin;
+    st.ready = true;
+    return &st;
+}
 
 }  // namespace
 
@@ -570,46 +516,43 @@ extern "C" int bitlinear_int8xint2_noalloc(int8_t* input0, int8_t* input1, void*
     if (!input0 || !input1 || !output0 || !s || !ws || M < 1 || N < 1 || K < 1) return set_status(kBadArgument), kBadArgument;
     if (N % 16 != 0 || K % 128 != 0) return set_status(kUnsupported), kUnsupported;
     if (M > 8 || N / 16 > kStaticRowGroups) return set_status(kTooLarge), kTooLarge;   // beyond the fixed scratch
-    int dev = 0;
-    if (check_cuda(cudaGetDevice(&dev))) return kCudaError;
-    if (dev < 0 || dev >= 64) return set_status(kUnsupported), kUnsupported;
-    StaticSetup& st = g_static_setup[dev];
-    if (!st.ready) {
-        // Once per device, with that device current: the array's name is only a host-side
-        // handle, the kernel needs the address the runtime reports for it on this device.
-        void* ptr = nullptr;
-        if (check_cuda(cudaGetSymbolAddress(&ptr, g_static_scratch))) return kCudaError;
-        if (check_cuda(cudaDeviceGetAttribute(&st.n_sm, cudaDevAttrMultiProcessorCount, dev)) ||
-            check_cuda(cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) ||
-            check_cuda(cudaFuncSetAttribute(fused_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            st.smem_optin)))
-            return kCudaError;
-        st.scratch = static_cast<unsigned long long*>(ptr);
-        st.ready = true;
-    }
+    StaticSetup* st = static_setup();
+    if (!st) return bitnet_last_status();
     FusedLinearParams p{};
     p.w2t = reinterpret_cast<const uint8_t*>(input1);
     p.N = N; p.K = K; p.M = M;
-    p.src = kSrcQuantized; p.out_kind = kOutBf16;
-    plan_linear(p, st.n_sm);
-    if (fused_linear_smem(p) > (size_t)st.smem_optin) return set_status(kTooLarge), kTooLarge;
+    plan_linear(p, st->n_sm);
+    if (fused_linear_smem(p) > (size_t)st->smem_optin) return set_status(kTooLarge), kTooLarge;
     p.yq = input0; p.ldy = K;
     p.a_q_bf16 = static_cast<const __nv_bfloat16*>(s);
     p.out = static_cast<__nv_bfloat16*>(output0); p.ldo = N;
     p.ws_dev_bf16 = static_cast<const __nv_bfloat16*>(ws);
     // row segments of the reference's shape ladder (gpu/bitnet_kernels/bitnet_kernels.cu:4-33)
+    // for the shapes this entry point can take (N <= 16384)
     int ws_num = 1;
     if (N == 3840 && K == 2560) ws_num = 3;
-    else if ((N == 13824 && K == 2560) || (N == 20480 && K == 3200)) ws_num = 2;
+    else if (N == 13824 && K == 2560) ws_num = 2;
     else if (N == 4800 && K == 3200) ws_num = 6;
     p.seg.n_seg = ws_num;
     for (int i = 0; i < 8; ++i) p.seg.end[i] = i < ws_num ? (N / ws_num) * (i + 1) : N;
-    p.acc_scratch = st.scratch;
-    p.error_flag = reinterpret_cast<int*>(st.scratch + kStaticSlots);
+    p.acc_scratch = st->scratch;
+    p.error_flag = reinterpret_cast<int*>(st->scratch + kStaticSlots);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the last call left; the slots this call uses must start at zero.
-    if (check_cuda(cudaMemsetAsync(st.scratch, 0, (size_t)(N / 16) * 128 * sizeof(unsigned long long), cs)))
+    // The array keeps whatever the last call left (after a call that gave up on a wait: partly
+    // filled slots): the slots this call uses must start at zero.  The error word is not
+    // cleared here, so that bitlinear_int8xint2_noalloc_error can still report an earlier call.
+    if (check_cuda(cudaMemsetAsync(st->scratch, 0, (size_t)(N / 16) * 128 * sizeof(unsigned long long), cs)))
         return kCudaError;
     return launch_fused_linear(p, cs, false);
 }
 
+extern "C" int bitlinear_int8xint2_noalloc_error(int clear) {
+    using namespace bitnet;
+    set_status(kOk);
+    StaticSetup* st = static_setup();
+    if (!st) return -1;
+    int v = 0;
+    if (check_cuda(cudaMemcpy(&v, st->scratch + kStaticSlots, sizeof(int), cudaMemcpyDeviceToHost))) return -1;
+    if (v != 0 && clear && check_cuda(cudaMemset(st->scratch + kStaticSlots, 0, sizeof(unsigned long long)))) return -1;
+    return v;
+}

@@ -18,7 +18,6 @@
 // 32q+8j..32q+8j+7 of a K tile, so operand slab j holds those 4 x 8 = 32 columns of A, and
 // the activations are staged with the same column selection.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -291,8 +290,12 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
         };
         const bool stage_y = p.ycanon == nullptr;
         if (stage_y) load_y(0);
-        // optional cycle counters of warp 0 of CTA (0,0,0): a measurement aid behind error_flag
+        // cycle counters of warp 0 of CTA (0,0,0) in builds with BITNET_TRACE: a measurement aid behind error_flag
+#ifdef BITNET_TRACE
         const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+#else
+        constexpr bool tracing = false;
+#endif
         long long c_wfull = 0, c_oempty = 0, c_unpack = 0, c_stage = 0, c_fence = 0, c_t = clock64();
         auto lap = [&](long long& acc) {
             if (tracing) {
@@ -495,9 +498,7 @@ cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    // Both kernels are launched as programmatic dependents of whatever precedes them in the
-    // stream (BITNET_NO_PDL=1: ordinary stream order).
-    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
+    // Both kernels are launched as programmatic dependents of whatever precedes them in the stream.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -507,7 +508,7 @@ cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
     cfg.dynamicSmemBytes = TcSmem<TN>::kBytes + 1024;
     cfg.stream = stream;
     cfg.attrs = attr;
-    cfg.numAttrs = no_pdl ? 0 : 1;
+    cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, w2a8_gemm_tc_kernel<TN>, p);
     if (e != cudaSuccess) return e;
     if (p.k_splits > 1) {
@@ -537,8 +538,9 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t a
     p.k_tiles = (a.K + kTileCols - 1) / kTileCols;
     p.n_rowgroups = (a.N + 15) / 16;
     p.error_flag = error_flag;
-    static const bool trace_on = getenv("BITNET_TC_TRACE") != nullptr;
-    p.trace = trace_on ? reinterpret_cast<unsigned long long*>(error_flag + 16) : nullptr;   // spare words behind the flag
+#ifdef BITNET_TRACE
+    p.trace = reinterpret_cast<unsigned long long*>(error_flag + 16);   // spare words behind the flag
+#endif
     // Few output tiles (decode-sized M): split K over enough CTAs to occupy the SMs.
     const int tn = a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128);
     const int tiles = ((a.N + kRows - 1) / kRows) * ((a.M + tn - 1) / tn);
@@ -548,8 +550,7 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t a
     p.k_splits = ks;
     p.acc_ws = acc_ws;
     // Many tokens: lay the activations out for the tensor core once, instead of in every CTA.
-    static const bool no_prestage = getenv("BITNET_TC_NO_PRESTAGE") != nullptr;
-    if (a.M >= 128 && !no_prestage) {
+    if (a.M >= 128) {
         p.m_groups = (a.M + 127) / 128 * 16;
         p.ycanon = workspace_tc_activations((size_t)p.m_groups * 8 * p.k_tiles * kTileCols, stream);
     }

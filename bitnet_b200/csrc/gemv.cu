@@ -8,8 +8,6 @@
 // (mma.sync m16n8k32 u8 x s8): the four 2-bit fields of a byte are separated by masks
 // only, without shifts, by accumulating field j in its own accumulator (which then holds
 // 4^j times the true sum) and folding the four with exact arithmetic shifts at the end.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "kernels.h"
 
@@ -232,18 +230,14 @@ int w2a8_gemv(const LinearArgs& a, cudaStream_t stream) {
     // the fused kernel earns its keep inside the decode chain, where it also does the prologue and
     // overlaps its predecessor.  It stays ahead for one or two tokens on short, wide matrices
     // (2560 x 6912: 6.7 vs 8.2 us), where the direct kernel has too few row groups to fill the SMs.
-    // BITNET_GEMV_DIRECT=1 / BITNET_GEMV_FUSED=1 force one or the other (for comparisons).
-    static const bool direct = getenv("BITNET_GEMV_DIRECT") != nullptr;
-    static const bool fused = getenv("BITNET_GEMV_FUSED") != nullptr;
-    if (a.M <= 8 && !direct && a.K % 8 == 0 && (fused || (a.M <= 2 && a.K >= 2 * a.N && a.N <= 4096))) {
+    if (a.M <= 2 && a.K % 8 == 0 && a.K >= 2 * a.N && a.N <= 4096) {
         const int rc = fused_linear_quantized(a, stream);
         if (rc != kTooLarge) return rc;
         set_status(kOk);   // does not fit the fused kernel's shared memory: the direct kernel takes it
     }
     // Larger batches go to the tcgen05 kernel when the activations are laid out for it.
-    static const bool no_tc = getenv("BITNET_NO_TCGEN05") != nullptr;
     const int64_t k_pad = (a.K + kTileCols - 1) / kTileCols * kTileCols;
-    if (a.M >= 16 && !no_tc && a.ldy % 16 == 0 && a.ldy >= k_pad && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
+    if (a.M >= 16 && a.ldy % 16 == 0 && a.ldy >= k_pad && (reinterpret_cast<uintptr_t>(a.y) & 15) == 0) {
         WorkspaceView ws;
         if (!workspace_view(&ws)) return kCudaError;
         if (a.ysum) return w2a8_gemm_tc(a, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, stream);

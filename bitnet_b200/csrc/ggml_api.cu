@@ -264,4 +264,89 @@ void ggml_bitnet_mul_mat(const struct ggml_compute_params* params, struct ggml_t
                                      ne00, ne11, bits);
 }
 
+// ---- the TL2 kernel signatures (include/ggml-bitnet.h:46-47) ------------------------------------
+void ggml_preprocessor(int bs, int m, int three_k, int two_k, void* B, void* LUT_Scales, void* Three_QLUT,
+                       void* Two_QLUT) {
+    (void)m;
+    set_status(kOk);
+    const int k = three_k + two_k;
+    if (!B || !LUT_Scales || bs < 1 || three_k < 0 || two_k < 0 || k < 1 || three_k % 3 != 0 || two_k % 2 != 0 ||
+        (three_k && !Three_QLUT) || (two_k && !Two_QLUT)) {
+        set_status(kBadArgument);
+        return;
+    }
+    DevBuf d_x, d_y, d_s, d_b;
+    const size_t ne = (size_t)bs * k;
+    if (check_cuda(d_x.alloc(ne * 4)) || check_cuda(d_y.alloc(ne)) || check_cuda(d_s.alloc(bs * 4)) ||
+        check_cuda(d_b.alloc(bs * 4)))
+        return;
+    if (check_cuda(cudaMemcpy(d_x.p, B, ne * 4, cudaMemcpyHostToDevice))) return;
+    // per_tensor_quant of include/bitnet-lut-kernels.h (one scale 127/absmax per activation row)
+    quant_f32_rows_kernel<<<bs, 256>>>(static_cast<const float*>(d_x.p), static_cast<int8_t*>(d_y.p),
+                                       static_cast<float*>(d_s.p), static_cast<float*>(d_b.p), k);
+    if (check_cuda(cudaGetLastError())) return;
+    if (check_cuda(cudaMemcpy(LUT_Scales, d_s.p, bs * 4, cudaMemcpyDeviceToHost))) return;
+    const int8_t* y = static_cast<const int8_t*>(d_y.p);
+    if (three_k && check_cuda(cudaMemcpy2D(Three_QLUT, (size_t)three_k / 3 * 32, y, k, three_k, bs, cudaMemcpyDeviceToHost)))
+        return;
+    if (two_k && check_cuda(cudaMemcpy2D(Two_QLUT, (size_t)two_k / 2 * 32, y + three_k, k, two_k, bs, cudaMemcpyDeviceToHost)))
+        return;
+}
+
+void ggml_qgemm_lut(int bs, int m, int k, int BK, void* A, void* sign, void* LUT, void* Scales, void* LUT_Scales,
+                    void* C) {
+    (void)sign;
+    set_status(kOk);
+    if (!A || !Scales || !LUT_Scales || !C || bs < 1 || m < 1 || k < 1 || BK < 0 || BK > k || (BK > 0 && !LUT)) {
+        set_status(kBadArgument);
+        return;
+    }
+    const bool three = 2 * BK >= k;                  // the part of K grouped in threes comes first
+    const int col0 = three ? 0 : k - BK;             // the columns this call multiplies
+    const size_t stride = three ? (size_t)BK / 3 * 32 : (size_t)BK / 2 * 32;
+    std::vector<int32_t> part;
+    if (BK > 0) {
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            const Node* node = find_node(A);
+            if (!node || node->k != k || node->rows != m) {
+                set_status(kBadArgument);   // not a tensor ggml_bitnet_transform_tensor produced
+                return;
+            }
+        }
+        // The int8 activations of this call's columns, zero elsewhere: a zero activation adds
+        // nothing to the product nor to the row sum that the weight offset takes off.
+        DevBuf d_y, d_acc;
+        if (check_cuda(d_y.alloc((size_t)bs * k)) || check_cuda(d_acc.alloc((size_t)bs * m * 4))) return;
+        if (check_cuda(cudaMemset(d_y.p, 0, (size_t)bs * k)) ||
+            check_cuda(cudaMemcpy2D(static_cast<int8_t*>(d_y.p) + col0, k, LUT, stride, BK, bs, cudaMemcpyHostToDevice)))
+            return;
+        LinearArgs a;
+        a.w2t = A;
+        a.y = static_cast<const int8_t*>(d_y.p); a.ldy = k;
+        a.acc_out = static_cast<int32_t*>(d_acc.p);
+        a.M = bs; a.N = m; a.K = k;
+        a.seg.n_seg = 1;
+        if (w2a8_gemv(a, nullptr)) return;
+        part.resize((size_t)bs * m);
+        if (check_cuda(cudaMemcpy(part.data(), d_acc.p, part.size() * 4, cudaMemcpyDeviceToHost))) return;
+    }
+    int32_t* ci = static_cast<int32_t*>(C);
+    if (three) {                                     // first call of the pair: int32 sums
+        for (size_t i = 0; i < (size_t)bs * m; ++i) ci[i] = part[i];
+        return;
+    }
+    // second call: add this part's sums and finalise as include/bitnet-lut-kernels.h:993-999 does
+    const float ws = static_cast<const float*>(Scales)[0];
+    float* cf = static_cast<float*>(C);
+    for (int b = 0; b < bs; ++b) {
+        const float a_b = static_cast<const float*>(LUT_Scales)[b];
+        for (int i = 0; i < m; ++i) {
+            const size_t idx = (size_t)b * m + i;
+            const int32_t v = ci[idx] + (BK > 0 ? part[idx] : 0);
+            cf[idx] = (float)v / a_b * ws;
+        }
+    }
+}
+
 }  // extern "C"

@@ -2,9 +2,7 @@
 // the fused decode kernels so that both produce bit-identical int8 activations:
 // (optional) RMSNorm -> round to bf16 -> absmax -> a = 127 / max(absmax, 1e-5)
 // -> y = clamp(rint(x * a), -128, 127), following gpu/model.py:68-71 behind the norms of
-// gpu/model.py:159-160, 195-196, 237-242.  Executed by exactly 256 threads per token;
-// thread t owns the 8-element groups t, t + 256, ... in every pass, so the result does not
-// depend on which kernel runs it.
+// gpu/model.py:159-160, 195-196, 237-242.
 #pragma once
 #include "common.cuh"
 
@@ -60,27 +58,10 @@ __device__ __forceinline__ bool aligned16(const void* p, int64_t ld_elems, int e
     return ((reinterpret_cast<uintptr_t>(p) & 15) == 0) && ((ld_elems * elem_bytes) % 16 == 0);
 }
 
-// Sum or max over the 256 threads.  `sync` is a barrier over exactly those threads.
+// Sum of `ss` (double) and max of `mx` over the 256 threads in one round (two barriers).
+// `sd` holds 8 doubles, `sf` 8 floats.
 template <class Sync>
-__device__ __forceinline__ float reduce_256(float v, bool is_max, float* scratch, int tid, Sync sync) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float t = __shfl_xor_sync(0xffffffffu, v, o);
-        v = is_max ? fmaxf(v, t) : v + t;
-    }
-    sync();
-    if ((tid & 31) == 0) scratch[tid >> 5] = v;
-    sync();
-    float r = scratch[0];
-#pragma unroll
-    for (int i = 1; i < kPrologueThreads / 32; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
-    return r;
-}
-
-// Sum of `ss` and max of `mx` over the 256 threads in one round (two barriers).  `scratch`
-// holds 16 floats.
-template <class Sync>
-__device__ __forceinline__ void reduce2_256(float& ss, float& mx, float* scratch, int tid, Sync sync) {
+__device__ __forceinline__ void reduce_stats_256(double& ss, float& mx, double* sd, float* sf, int tid, Sync sync) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -88,43 +69,44 @@ __device__ __forceinline__ void reduce2_256(float& ss, float& mx, float* scratch
     }
     sync();
     if ((tid & 31) == 0) {
-        scratch[tid >> 5] = ss;
-        scratch[8 + (tid >> 5)] = mx;
+        sd[tid >> 5] = ss;
+        sf[tid >> 5] = mx;
     }
     sync();
-    ss = scratch[0];
-    mx = scratch[8];
+    ss = sd[0];
+    mx = sf[0];
 #pragma unroll
     for (int i = 1; i < kPrologueThreads / 32; ++i) {
-        ss += scratch[i];
-        mx = fmaxf(mx, scratch[8 + i]);
+        ss += sd[i];
+        mx = fmaxf(mx, sf[i]);
     }
 }
 
 // ---- the arithmetic of one token, shared by every kernel that quantises activations ----------
-// In f32: t = x * g; r = rsqrt(mean(x^2) + eps); xn = bf16(t * r); a = 127 / max(max|xn|, 1e-5);
-// y = clamp(rint(xn * a), -128, 127).  Because rounding and multiplication by r > 0 are
-// monotone, max|xn| = bf16(max|t| * r), so one reduction round (sum of squares and max|t|
-// together) and two passes over the values suffice.
+// t = x * g (f32); r = (float)(1 / sqrt(mean(x^2) + eps)) with the mean and the root in double
+// precision; xn = bf16(t * r); a = 127 / max(max|xn|, 1e-5); y = clamp(rint(xn * a), -128, 127).
+// Because rounding and multiplication by r > 0 are monotone, max|xn| = bf16(max|t| * r), so one
+// reduction round (sum of squares and max|t| together) and two passes over the values suffice.
 //
-// The sum of squares has a fixed association, independent of how many threads work on it:
-// p(v) = x0^2 + ... + x7^2 of group v (fused multiply-adds from zero, in order); "lane" L of 256
-// adds p(L), p(L + 256), ... in order; 32 consecutive lanes combine by a butterfly of shuffles;
-// the 8 results are added in order.
+// The sum of squares is accumulated in double precision (B200 runs it at half the f32 rate, and
+// a token has a few thousand values): its f32 rounding then does not depend on the order of the
+// additions, so every kernel - whatever its thread count, and however a producer kernel cut the
+// vector into slices - derives the same r, and r equals what a double-precision CPU evaluation
+// gives.  A quantiser turns a last-bit difference in r into different int8 values; this removes
+// that source of divergence between kernels, between GPUs of a tensor-parallel group, and
+// between the GPU and the CPU checker.
 
-// Sum of squares of a group, and max |x * g| (max |x| without norm weight).
-__device__ __forceinline__ void group_stats(const Vec8& x, const Vec8& g, bool use_g, float& p, float& m) {
-    p = 0.f;
-    m = 0.f;
+// Adds the squares of a group to ss and folds max |x * g| (max |x| without norm weight) into m.
+__device__ __forceinline__ void group_stats(const Vec8& x, const Vec8& g, bool use_g, double& ss, float& m) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        p = fmaf(x.v[e], x.v[e], p);
+        ss = fma((double)x.v[e], (double)x.v[e], ss);
         m = fmaxf(m, fabsf(use_g ? x.v[e] * g.v[e] : x.v[e]));
     }
 }
 // From the reduced statistics to the normalisation factor and the activation scale.
-__device__ __forceinline__ void finish_stats(float ss, float mt, int K, float eps, bool use_g, float& rinv, float& a) {
-    rinv = use_g ? rsqrtf(ss / (float)K + eps) : 1.f;
+__device__ __forceinline__ void finish_stats(double ss, float mt, int K, float eps, bool use_g, float& rinv, float& a) {
+    rinv = use_g ? (float)(1.0 / sqrt(ss / (double)K + (double)eps)) : 1.f;
     const float amax = use_g ? bf16_round(mt * rinv) : mt;
     a = 127.0f / fmaxf(amax, 1e-5f);
 }
@@ -145,15 +127,16 @@ __device__ __forceinline__ uint2 quant_group(const Vec8& x, const Vec8& g, bool 
 // One token whose source values already sit in shared memory, by 256 threads: xv holds ceil8(K)
 // bf16 values (zero beyond K).  y: destination row of k_pad bytes (shared or global), zero
 // filled beyond K.  On return every thread holds the activation scale; `sy_warp` is the sum of
-// y over the calling warp's elements (exact in f32), which the caller adds up over the eight
-// warps.  The loops are deliberately not unrolled: these kernels run for microseconds, and code
-// that does not fit the instruction cache costs more than the loop overhead saves.
+// y over the calling warp's elements, which the caller adds up over the eight warps.  `sd` holds
+// 8 doubles, `sf` 8 floats.  The loops are deliberately not unrolled: these kernels run for
+// microseconds, and code that does not fit the instruction cache costs more than the loop
+// overhead saves.
 // GVEC: gamma is 16-byte aligned and padded to whole groups of 8 (e.g. staged in shared memory),
 // so the element-wise fallback is left out of the code.
 template <bool GVEC = false, class Sync>
 __device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, int k_pad, const __nv_bfloat16* gamma,
-                                               float eps, int8_t* y, float* scratch, int tid, Sync sync, float& a_out,
-                                               float& sy_warp) {
+                                               float eps, int8_t* y, double* sd, float* sf, int tid, Sync sync,
+                                               float& a_out, int& sy_warp) {
     const int n_vec = (K + 7) / 8;
     const bool use_g = gamma != nullptr;
     const bool g_vec = GVEC || (use_g && aligned16(gamma, 8, 2));
@@ -161,15 +144,12 @@ __device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, i
         if (!use_g) return Vec8{};
         return GVEC ? unpack_bf16x8(*reinterpret_cast<const uint4*>(gamma + v * 8)) : load_bf16x8(gamma, v * 8, K, g_vec);
     };
-    float ss = 0.f, mt = 0.f;
+    double ss = 0.0;
+    float mt = 0.f;
 #pragma unroll 1
-    for (int v = tid; v < n_vec; v += kPrologueThreads) {
-        float p, m;
-        group_stats(unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8)), load_g(v), use_g, p, m);
-        ss += p;
-        mt = fmaxf(mt, m);
-    }
-    reduce2_256(ss, mt, scratch, tid, sync);
+    for (int v = tid; v < n_vec; v += kPrologueThreads)
+        group_stats(unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8)), load_g(v), use_g, ss, mt);
+    reduce_stats_256(ss, mt, sd, sf, tid, sync);
     float rinv, a;
     finish_stats(ss, mt, K, eps, use_g, rinv, a);
     int sy_i = 0;
@@ -182,7 +162,7 @@ __device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, i
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sy_i += __shfl_xor_sync(0xffffffffu, sy_i, o);
     a_out = a;
-    sy_warp = (float)sy_i;   // |sum| <= 128 * 8 * groups per warp: exact
+    sy_warp = sy_i;
 }
 
 }  // namespace bitnet

@@ -2,8 +2,6 @@
 // second half of the row), optional RMSNorm, then per-token absmax int8 quantisation (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242).
 // One CTA of 256 threads per token; the arithmetic lives in prologue.cuh, shared with the
 // fused decode kernels.
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "kernels.h"
 #include "prologue.cuh"
@@ -14,8 +12,9 @@ namespace {
 
 __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const QuantArgs p) {
     extern __shared__ __align__(16) uint8_t smem_q[];
-    __shared__ float scratch[16];
-    __shared__ float sy_part[kPrologueThreads / 32];
+    __shared__ double red_d[8];
+    __shared__ float red_f[8];
+    __shared__ int sy_part[kPrologueThreads / 32];
     __nv_bfloat16* xv = reinterpret_cast<__nv_bfloat16*>(smem_q);
     const int tok = blockIdx.x, tid = threadIdx.x;
     // launched as a programmatic dependent: the launch overlaps the tail of the kernel that
@@ -25,7 +24,8 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
     const __nv_bfloat16* row = p.x_bf16 + (int64_t)tok * p.ldx;
     const bool vec_ok = aligned16(p.x_bf16, p.ldx, 2);
     const int K = p.K;
-    float a, sy_warp;
+    float a;
+    int sy_warp;
 #pragma unroll 1
     for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads) {
         Vec8 x = load_bf16x8(row, v * 8, K, vec_ok);
@@ -39,13 +39,12 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
         }
         *reinterpret_cast<uint4*>(xv + v * 8) = pack_bf16x8(x);
     }
-    norm_quant_row(xv, K, (int)p.ldy, p.gamma, p.eps, p.y + (int64_t)tok * p.ldy, scratch, tid,
+    norm_quant_row(xv, K, (int)p.ldy, p.gamma, p.eps, p.y + (int64_t)tok * p.ldy, red_d, red_f, tid,
                    [] { __syncthreads(); }, a, sy_warp);
     if ((tid & 31) == 0) sy_part[tid >> 5] = sy_warp;
     __syncthreads();
-    float sy = 0.f;
-    for (int i = 0; i < kPrologueThreads / 32; ++i) sy += sy_part[i];
-    const int ysum = (int)sy;
+    int ysum = 0;
+    for (int i = 0; i < kPrologueThreads / 32; ++i) ysum += sy_part[i];
     if (tid == 0) {
         if (p.a_f32) p.a_f32[tok] = a;
         if (p.a_bf16) p.a_bf16[tok] = __float2bfloat16_rn(a);
@@ -65,7 +64,6 @@ int act_quant(const QuantArgs& a, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return check_cuda(e);
     }
-    static const bool no_pdl = getenv("BITNET_NO_PDL") != nullptr;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -75,7 +73,7 @@ int act_quant(const QuantArgs& a, cudaStream_t stream) {
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
-    cfg.numAttrs = no_pdl ? 0 : 1;
+    cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, act_quant_kernel, a));
 }
 

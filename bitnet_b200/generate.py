@@ -30,8 +30,7 @@ class _DecoderLayer(ctypes.Structure):
 
 class FusedDecoder:
     """One decode step for a batch of at most 8 through `bitnet_decoder_step`: the whole
-    step runs inside the library (see include/bitnet_b200.h), either as a chain of fused
-    kernels or, with `use_persistent(True)`, as one persistent kernel; both give the same bits."""
+    step runs inside the library (see include/bitnet_b200.h) as a chain of fused kernels."""
 
     MAX_BATCH = 8
 
@@ -70,13 +69,6 @@ class FusedDecoder:
             raise _lib.BitnetError("bitnet_decoder_create failed")
         self.kernels_per_step = _lib.lib.bitnet_decoder_kernels_per_step(self.handle)
 
-    def use_persistent(self, on: bool) -> bool:
-        """Switches between the single persistent kernel and the kernel chain; returns whether
-        the persistent kernel is now in use (False when it does not fit the model)."""
-        got = bool(_lib.lib.bitnet_decoder_use_persistent(self.handle, 1 if on else 0))
-        self.kernels_per_step = _lib.lib.bitnet_decoder_kernels_per_step(self.handle)
-        return got
-
     def step(self, tokens: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, logits: Optional[torch.Tensor] = None):
         """tokens int64 [B] (or [B,1]), pos int64 [B], out int64 [B] on the device; enqueued on the current stream."""
         _lib.check(_lib.lib.bitnet_decoder_step(self.handle, _lib.ptr(tokens), _lib.ptr(pos), _lib.ptr(out),
@@ -95,6 +87,15 @@ class FusedDecoder:
     def error_flag(self) -> int:
         return _lib.lib.bitnet_decoder_error_flag(self.handle)
 
+    def clear_error(self):
+        _lib.check(_lib.lib.bitnet_decoder_clear_error(self.handle))
+
+    def set_attention_tap(self, buffer: Optional[torch.Tensor]):
+        """bf16 [n_layers, batch, dim] that every attention kernel of later steps also writes
+        its output to (None switches it off): lets a checker follow the step layer by layer."""
+        self._tap = buffer
+        _lib.check(_lib.lib.bitnet_decoder_set_attention_tap(self.handle, _lib.ptr(buffer)))
+
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
         if h and _lib is not None and getattr(_lib, "lib", None) is not None:   # may run at interpreter exit
@@ -105,11 +106,9 @@ class Generator:
     AUTO_FUSED_MAX_BATCH = 2
 
     def __init__(self, model: Transformer, batch: int, max_seq_len: int, use_cuda_graph: bool = True,
-                 fused: Optional[bool] = None, persistent: Optional[bool] = None):
+                 fused: Optional[bool] = None):
         """fused=None picks the in-library decode step where it is the faster path (kernel model,
-        batch <= AUTO_FUSED_MAX_BATCH); fused=True asks for it up to batch 8.  persistent=True/False
-        chooses the single persistent kernel or the kernel chain for it; None leaves the library's
-        default."""
+        batch <= AUTO_FUSED_MAX_BATCH); fused=True asks for it up to batch 8."""
         self.model, self.batch, self.max_seq_len = model, batch, max_seq_len
         dev = model.tok_embeddings.weight.device
         self.device = dev
@@ -120,6 +119,7 @@ class Generator:
         self.host_in = torch.zeros((batch, 1), dtype=torch.int64).pin_memory()
         self.host_out = torch.zeros((batch,), dtype=torch.int64).pin_memory()
         self.use_cuda_graph = use_cuda_graph
+        self._pos_host = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.graph_host: Optional[torch.cuda.CUDAGraph] = None
         self._host_state = False
@@ -128,7 +128,6 @@ class Generator:
         if fused and not can_fuse:
             raise ValueError("the fused decode chain needs the kernel model and batch <= 8")
         self.fused: Optional[FusedDecoder] = None
-        self.persistent = False
         # fused=None: the in-library step where it is the faster path.  It repeats the activation
         # prologue of every token in every CTA, so beyond two sequences one launch per operation
         # wins (measured on B200, 2B architecture: batch 2: 1.66 vs 1.96 ms; batch 4: 2.38 vs
@@ -145,11 +144,6 @@ class Generator:
                 # op-by-op path (same kernels, one launch per operation) takes over
                 if fused:
                     raise
-            if self.fused is not None:
-                if persistent is not None:
-                    self.persistent = self.fused.use_persistent(persistent)
-                else:   # the library's choice
-                    self.persistent = self.fused.kernels_per_step == 1
 
     def _step(self):
         if self.fused is not None:
@@ -167,6 +161,7 @@ class Generator:
         token as the input of the next decode step."""
         B, T = prompt.shape
         assert B == self.batch and T < self.max_seq_len
+        self._pos_host = T                      # host mirror of the positions (all sequences advance together)
         self.pos.zero_()
         logits = self.model(prompt, self.pos, self.cache, kv_len=T, last_only=True)
         nxt = logits[:, -1].argmax(-1)
@@ -205,9 +200,17 @@ class Generator:
         self.tokens.copy_(saved[0]); self.pos.copy_(saved[1]); self.out.copy_(saved[2])
         torch.cuda.synchronize()
 
+    def _advance(self):
+        """Refuses a step that would write beyond the KV cache (the kernels would flag it and
+        skip the append; the host knows earlier)."""
+        if self._pos_host >= self.max_seq_len:
+            raise ValueError(f"decode step at position {self._pos_host} exceeds max_seq_len {self.max_seq_len}")
+        self._pos_host += 1
+
     @torch.no_grad()
     def decode_step(self):
         """One token for every sequence, device resident (input = previous output)."""
+        self._advance()
         if self._host_state:   # the last steps ran on the host buffers: take their state over
             self.tokens.copy_(self.host_in)
             self.out.copy_(self.host_out)
@@ -222,21 +225,18 @@ class Generator:
         """One token with host buffers on both sides: takes the input ids from pinned host
         memory (tokens_host, or the ids the previous step chose), runs the step, and returns
         the chosen ids in pinned host memory once they have arrived."""
+        self._advance()
         with torch.cuda.stream(self.stream):
             if tokens_host is not None:
                 self.host_in.copy_(tokens_host)
             elif not self._host_state:
                 self.host_in.copy_(self.tokens)
-            if self.fused is not None and self.fused.kernels_per_step == 1:
-                # one kernel: launching it directly costs less than replaying a graph
-                self.fused.step_sync(self.host_in, self.pos, self.host_out)
-                self._host_state = True
-                return self.host_out
             if self.graph_host is not None:
                 self.graph_host.replay()
                 self._host_state = self.fused is not None   # next input and result live in host_in / host_out
             else:
                 self.tokens.copy_(self.host_in, non_blocking=True)
+                self._pos_host -= 1             # decode_step counts the step itself
                 self.decode_step()
                 self.host_out.copy_(self.out, non_blocking=True)
             self.stream.synchronize()

@@ -74,6 +74,13 @@ void bitlinear_int8xint2(int8_t* input0, int8_t* input1, void* output0, void* s,
  * keep them on one stream per device.  Returns 0 or a BITNET_STATUS_* code. */
 int bitlinear_int8xint2_noalloc(int8_t* input0, int8_t* input1, void* output0, void* s, void* ws,
                                 int M, int N, int K, void* stream);
+/* The kernel behind bitlinear_int8xint2_noalloc bounds every wait; if one ever runs out, the
+ * kernel leaves a non-zero code in a word of the same fixed array and returns without
+ * storing results.  This reads that word on the current device (after synchronising it):
+ * 0 = no call gave up since the word was last cleared, 1 or 2 = the code of the wait that
+ * did; clear != 0 resets it.  Returns -1 if the word cannot be read.  Like the call itself it
+ * allocates nothing.  No counterpart in the reference. */
+int bitlinear_int8xint2_noalloc_error(int clear);
 
 /* ---- the same operation with explicit arguments ---------------------------------------
  * Serves gpu/model.py:54-75 (BitLinearKernel.forward) with the row segments stated by the
@@ -114,11 +121,10 @@ int bitnet_quant_input_glu(const void* x13_bf16, int64_t ldx, const void* gamma_
  * Counterpart of the decode model that the reference captures in a CUDA graph
  * (gpu/generate.py:159-213) around Transformer.forward_with_attn_bias (gpu/model.py:269-282):
  * one call enqueues, for every layer, wqkv -> attention -> wo -> w13 -> w2 (each BitLinear
- * fused with the rescale, residual, gate, RMSNorm and int8 quantisation in front of it),
- * then the bf16 output projection and the greedy choice.  Kernels are chained with
- * programmatic dependent launch; the call allocates nothing and may be captured in a
- * CUDA graph.  All pointers in the structs are device pointers that must stay valid for
- * the decoder's lifetime. */
+ * fused with the rescale, residual, gate, RMSNorm and int8 quantisation around it), then the
+ * bf16 output projection and the greedy choice.  Kernels are chained with programmatic
+ * dependent launch; the call allocates nothing and may be captured in a CUDA graph.  All
+ * pointers in the structs are device pointers that must stay valid for the decoder's lifetime. */
 typedef struct bitnet_decoder_config {
     int dim, n_layers, n_heads, n_kv_heads, head_dim, ffn_dim, vocab_size;
     float norm_eps;
@@ -134,24 +140,24 @@ typedef struct bitnet_decoder_layer {
 } bitnet_decoder_layer;
 
 /* tok_embeddings bf16 [vocab, dim]; norm bf16 [dim]; output bf16 [vocab, dim]; rope f32
- * [max_seq_len, head_dim/2, 2] (cos, sin).  Allocates the decoder's scratch buffers (the
- * only allocation; do it outside stream capture).  Returns NULL on failure (see
- * bitnet_last_status). */
+ * [max_seq_len, head_dim/2, 2] (cos, sin).  dim and ffn_dim must be multiples of 8 and 16.
+ * Allocates the decoder's scratch buffers (the only allocation; do it outside stream
+ * capture).  Returns NULL on failure (see bitnet_last_status). */
 void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
                             const void* tok_embeddings, const void* norm, const void* output, const float* rope);
 /* tokens int64 [batch]: ids to feed (overwritten with the chosen ids, so that the next
  * call continues the sequence); pos int64 [batch]: tokens already in the cache (incremented);
- * out int64 [batch]: chosen ids; logits f32 [batch, vocab] or NULL. */
+ * out int64 [batch]: chosen ids; logits f32 [batch, vocab] or NULL.
+ * A position outside [0, max_seq_len) or a token id outside the vocabulary is not an
+ * out-of-bounds access: the kernels leave a code in the decoder's error word (see
+ * bitnet_decoder_error_flag), append nothing to that sequence's cache (position) or use token 0
+ * (token id), and the step's results are meaningless. */
 int bitnet_decoder_step(void* decoder, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream);
 /* bitnet_decoder_step followed by a wait for the stream: returns when `out` (and `logits`)
  * hold the step's result.  With `tokens` and `out` in pinned host memory (which the device can
  * address) this is the whole host-in, host-out step in one call, without copy nodes.  Not for
  * use under stream capture.  No counterpart in the reference. */
 int bitnet_decoder_step_sync(void* decoder, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, void* stream);
-/* Measurement aid: enqueues only the four fused BitLinear kernels of every layer (no
- * attention, no output head), so that the BitLinear kernel can be timed alone on the
- * model's real weights.  The activations it leaves behind are meaningless. */
-int bitnet_decoder_bench_linears(void* decoder, int64_t* tokens, void* stream);
 /* The attention step of that chain on its own (batch sequences, one new token each), for
  * callers that run the decoder op by op: RoPE on q and k (adjacent pairs, as the
  * interleaved rope of gpu/model.py:144-152), append k and v to the cache at pos[b], then
@@ -159,34 +165,26 @@ int bitnet_decoder_bench_linears(void* decoder, int64_t* tokens, void* stream);
  *   xqkv bf16 [batch, ld_qkv]: q heads, k heads, v heads of the new token
  *   pos int64 [batch]; rope f32 [max_seq_len, head_dim/2, 2]
  *   cache_k, cache_v bf16 [batch, max_seq_len, n_kv_heads, head_dim]; out bf16 [batch, n_heads*head_dim]
- * Uses the workspace (see bitnet_init). */
+ * Uses the workspace (see bitnet_init).  A position outside the cache is flagged in the
+ * workspace's error word and skipped. */
 int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos, const float* rope, void* cache_k,
                             void* cache_v, void* out, int batch, int n_heads, int n_kv_heads, int head_dim,
                             int max_seq_len, void* stream);
-/* Measurement aid: when the decoder was created with the environment variable BITNET_TRACE
- * set, CTA 0 of every fused BitLinear launch records six %globaltimer stamps (start, weights
- * requested, dependency resolved, activations quantised, matmul done, results stored);
- * this copies them out, sixteen 64-bit values per launch: first the 4 BitLinear launches of
- * every layer, then one attention launch per layer. */
-int bitnet_decoder_read_trace(void* decoder, unsigned long long* host_out, int n_values);
-/* Measurement aid: copies out the spare words behind the workspace's error flag, where the
- * tcgen05 kernel leaves cycle counters of one warp when BITNET_TC_TRACE is set (waits for
- * weights, waits for operand buffers, unpack, activation staging, proxy fence, steps, epilogue). */
-int bitnet_debug_read_workspace_words(unsigned long long* host_out, int n_words);
-/* Non-zero if a kernel of this decoder gave up on a bounded wait (synchronises the device). */
+/* The decoder's error word (synchronises the device): 0, or the code of what a kernel of this
+ * decoder met - 1, 2: a bounded wait for weight tiles ran out; 4: a position outside the KV
+ * cache; 5: a token id outside the vocabulary. */
 int bitnet_decoder_error_flag(void* decoder);
+/* Clears the error word and the little state the kernels keep between launches, so that the
+ * next step starts clean after an error. */
+int bitnet_decoder_clear_error(void* decoder);
 /* Number of kernels one step launches. */
 int bitnet_decoder_kernels_per_step(void* decoder);
-/* Chooses how bitnet_decoder_step runs: on = 1, the whole step as one persistent kernel (one
- * CTA per SM, launched cooperatively, grid-wide barriers between the phases of a layer);
- * on = 0, a chain of five kernels per layer.  Both give the same bits.  Returns the mode in
- * effect afterwards: 0 when the persistent kernel does not fit the model (grouped-query ratio
- * above 4, or shared memory).  The chain is the default (measured faster on B200); a refused
- * cooperative launch also switches the decoder back to the chain for good.  Environment:
- * BITNET_PERSISTENT=1 starts with the persistent kernel, BITNET_NO_PERSISTENT=1 removes it.
- * No counterpart in the reference. */
-int bitnet_decoder_use_persistent(void* decoder, int on);
 void bitnet_decoder_destroy(void* decoder);
+/* The error word of the workspace behind the stand-alone entry points (bitlinear_int8xint2,
+ * bitnet_linear_w2a8, bitnet_attention_decode) on the current device, same codes (3: a bounded
+ * wait of the tensor-core kernel ran out); clear != 0 resets it together with the workspace's
+ * split-K scratch.  Synchronises the device.  -1 if it cannot be read. */
+int bitnet_workspace_error(int clear);
 
 /* ---- weight layout conversion ----------------------------------------------------------
  * Size in bytes of a W2T buffer for an [N,K] matrix: ceil16(N) * ceil128(K) / 4. */

@@ -90,6 +90,29 @@ int ggml_bitnet_get_type_bits(enum ggml_type type);
 /* Recorded only: the GPU path does not use ggml's threads. */
 void ggml_bitnet_set_n_threads(int n_threads);
 
+/* ---- the x86 TL2 kernel entry points (include/ggml-bitnet.h:46-47) on the GPU -------------
+ * The reference generates these two per model shape (include/bitnet-lut-kernels.h:1003-1124 is
+ * the preset for 3200/8640): the pre-processor quantises a batch of f32 activation rows and
+ * builds look-up tables; the matmul is then called twice per output tile, first for the part of
+ * K that is grouped in threes (BK = three_k; writes int32 sums to C), then for the remainder
+ * (BK = two_k; adds its sums and turns C into floats, (float)sum / LUT_Scales[b] * Scales[0],
+ * :993-999).  This library keeps the signatures and the two-call protocol, and gives them the
+ * same result, but the buffers carry its own data:
+ *   - A is bitnet_tensor_extra::qweights of a tensor that ggml_bitnet_transform_tensor of THIS
+ *     library transformed (an I2_S tensor; the TL2 byte layout that the reference's converter
+ *     writes into GGUF files is not decoded), and stands for the whole matrix, not one tile;
+ *   - Three_QLUT / Two_QLUT receive the int8 activations (row b at byte b*three_k/3*32 and
+ *     b*two_k/2*32, the reference's row strides; the first three_k / two_k bytes are used);
+ *   - C is f32/int32 [bs, m]; `sign` is ignored.
+ * The call with 2*BK >= k is the first of a pair (columns 0 .. BK-1, LUT = Three_QLUT), the other
+ * one the second (columns k-BK .. k-1, LUT = Two_QLUT; BK may be 0).  All pointers are host
+ * pointers.  How the llama.cpp fork drives these calls is not part of the reference
+ * checkout: compatibility with its caller is unverified. */
+void ggml_preprocessor(int bs, int m, int three_k, int two_k, void* B, void* LUT_Scales, void* Three_QLUT,
+                       void* Two_QLUT);
+void ggml_qgemm_lut(int bs, int m, int k, int BK, void* A, void* sign, void* LUT, void* Scales, void* LUT_Scales,
+                    void* C);
+
 #ifdef __cplusplus
 }
 #endif

@@ -129,12 +129,18 @@ class OracleDecoder:
         return O.to_bf16(out)
 
     # ---- one decoder layer, one decode step ------------------------------------------------
-    def layer_forward(self, li: int, h: np.ndarray, pos: np.ndarray) -> np.ndarray:
+    def layer_forward(self, li: int, h: np.ndarray, pos: np.ndarray, att_given: Optional[np.ndarray] = None) -> np.ndarray:
         """h f32 [B, dim] (bf16 values) -> the layer's output, TransformerBlock.forward of
-        gpu/model.py:231-243 for one new token per sequence."""
+        gpu/model.py:231-243 for one new token per sequence.  att_given: take this as the
+        attention output instead of computing it (the cache is still updated), so that a
+        comparison of the BitLinear path does not hinge on two softmax implementations
+        rounding alike."""
         L = self.layers[li]
         xqkv = self.bitlinear(L["wqkv"], h, L["attention_norm"], f"l{li}.wqkv")
         att = self.attention(li, xqkv, pos)
+        self.last_attention = att
+        if att_given is not None:
+            att = np.asarray(att_given, dtype=np.float32)
         h = O.to_bf16(h + self.bitlinear(L["wo"], att, L["attn_sub_norm"], f"l{li}.wo"))
         x13 = self.bitlinear(L["w13"], h, L["ffn_norm"], f"l{li}.w13")
         x1, x3 = x13[:, : self.F], x13[:, self.F:]
@@ -147,9 +153,13 @@ class OracleDecoder:
         xn = O.to_bf16(O.rmsnorm(h, self.final_norm, float(self.eps)))
         return O.to_bf16((xn.astype(np.float64) @ self.out_w.astype(np.float64).T).astype(np.float32))
 
-    def step(self, tokens: np.ndarray, pos: np.ndarray) -> np.ndarray:
-        """tokens int [B], pos int [B] (keys already cached).  Returns logits [B, V]."""
+    def step(self, tokens: np.ndarray, pos: np.ndarray, att_given: Optional[Sequence[np.ndarray]] = None) -> np.ndarray:
+        """tokens int [B], pos int [B] (keys already cached).  Returns logits [B, V].
+        att_given[l]: attention output to use in layer l (see layer_forward); the oracle's own
+        attention outputs of the step are kept in self.attention_outputs."""
         h = self.emb[np.asarray(tokens).reshape(-1)]
+        self.attention_outputs = []
         for li in range(len(self.layers)):
-            h = self.layer_forward(li, h, pos)
+            h = self.layer_forward(li, h, pos, None if att_given is None else att_given[li])
+            self.attention_outputs.append(self.last_attention)
         return self.head(h)

@@ -12,6 +12,9 @@ What it records (all inputs come from numpy's seeded PCG64 generator, seeds in t
 * ``ref_i2s.npz``       - src/ggml-bitnet-mad.cpp compiled in place (oracle/build_oracle.py):
   quantize_i2_s bytes and ggml_vec_dot_i2_i8_s results, including a ragged row count, a
   non-multiple-of-32 block count, and raw random bytes (so that code 3 occurs).
+* ``ref_converters.npz`` - utils/convert-hf-to-gguf-bitnet.py:quantize_to_i2_s (with and
+  without override_scale) and gpu/convert_safetensors.py:invert_convert_q, taken from their
+  files by name and run on small inputs.
 * ``ref_gpu_test_kat.npz`` - the inputs and expected bf16 outputs of the procedural
   known-answer test gpu/test.py:42-61 (ternary weights, int8 activations in [-128,126],
   all scales 1, expected = int32 matmul cast to bf16) on reduced shapes plus one real
@@ -98,7 +101,44 @@ def main():
             out[f"y_{i}"] = y
             out[f"ref_packed_{i}"] = ref_pack.convert_weight_int8_to_int2(torch.from_numpy(q.copy())).numpy()
     np.savez_compressed(os.path.join(HERE, "ref_gpu_test_kat.npz"), **out)
-    for f in ("ref_gpu_pack.npz", "ref_i2s.npz", "ref_gpu_test_kat.npz"):
+    # ---- the reference's Python converters (functions taken from their files by name: the
+    # modules themselves import the llama.cpp fork's gguf package, which is not in the checkout)
+    import ast
+
+    def ref_function(rel_path, name, env):
+        src = open(os.path.join(a.ref, rel_path)).read()
+        for node in ast.parse(src).body:
+            if isinstance(node, ast.FunctionDef) and node.name == name:
+                exec(compile(ast.Module([node], []), rel_path, "exec"), env)
+                return env[name]
+        raise KeyError(name)
+
+    env = {"np": np}
+    ref_quantize_to_i2_s = ref_function("utils/convert-hf-to-gguf-bitnet.py", "quantize_to_i2_s", env)
+    from einops import rearrange
+
+    env2 = {"torch": torch, "rearrange": rearrange}
+    ref_invert_q = ref_function("gpu/convert_safetensors.py", "invert_convert_q", env2)
+    out = {}
+    for i, (n, k) in enumerate([(4, 128), (16, 256), (24, 640)]):
+        rng = np.random.default_rng(4000 + i)
+        w = rng.standard_normal((n, k)).astype(np.float32)
+        s = np.float32(1.0) / max(np.abs(w).mean(dtype=np.float32), np.float32(1e-5))
+        wq = (np.clip(np.rint(w * s), -1, 1) / s).astype(np.float32)           # weight_quant, :1055-1060
+        out[f"wq_{i}"] = wq
+        out[f"i2s_{i}"] = ref_quantize_to_i2_s(wq)
+        tern = rng.integers(-1, 2, size=(n, k)).astype(np.float32)
+        out[f"tern_{i}"] = tern
+        out[f"i2s_override_{i}"] = ref_quantize_to_i2_s(tern, override_scale=0.625 + i)
+
+    class Cfg:
+        n_head = 4
+    wq = torch.arange(4 * 8 * 3, dtype=torch.float32).view(32, 3)
+    out["rope_in"] = wq.numpy()
+    out["rope_out"] = ref_invert_q(wq, Cfg()).numpy()
+    np.savez_compressed(os.path.join(HERE, "ref_converters.npz"), **out)
+
+    for f in ("ref_gpu_pack.npz", "ref_i2s.npz", "ref_gpu_test_kat.npz", "ref_converters.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
 
 

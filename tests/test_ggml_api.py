@@ -97,3 +97,45 @@ def test_transform_and_mul_mat_match_oracle(L, port_lib, rows, k, m):
     assert np.array_equal(work[m * k: m * k + 4 * m].view(np.float32), a)        # lut_scales
     assert np.array_equal(out, want)
     L.ggml_bitnet_free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,three_k,two_k", [(3200, 8640, 8640, 0), (3200, 3200, 3168, 32), (8640, 3200, 3168, 32)])
+@pytest.mark.parametrize("bs", [1, 8])
+def test_tl2_signature_entry_points_match_oracle(L, port_lib, m, k, three_k, two_k, bs):
+    """ggml_preprocessor + the pair of ggml_qgemm_lut calls (include/ggml-bitnet.h:46-47) on the
+    3B preset's shapes (include/bitnet-lut-kernels.h:1003-1124): C = (sum w*q) / LUT_Scales * Scales,
+    the rescale of :993-999, equal to the oracle's f32 result."""
+    q, ws = O.synth_weights(m, k, seed=m + k)
+    x = O.synth_acts(bs, k, seed=bs + k).astype(np.float32)
+    y, a, ysum = O.act_quant(x)
+    want = O.rescale(O.matmul_i32(y, q), a, [ws])
+    buf = port_lib.quantize_i2_s(q.astype(np.float32) * ws)
+
+    L.ggml_bitnet_init()
+    w_t = _tensor(GGML_TYPE_I2_S, k, m, buf)
+    L.ggml_bitnet_transform_tensor(ctypes.byref(w_t))
+    assert L.bitnet_last_status() == 0 and w_t.extra
+    extra = ctypes.cast(w_t.extra, ctypes.POINTER(Extra)).contents
+    lut_scales = np.zeros(bs, dtype=np.float32)
+    three = np.zeros(bs * three_k // 3 * 32, dtype=np.int8)
+    two = np.zeros(max(bs * two_k // 2 * 32, 1), dtype=np.int8)
+    vp = lambda arr: arr.ctypes.data_as(ctypes.c_void_p)
+    L.ggml_preprocessor(bs, m, three_k, two_k, vp(x), vp(lut_scales), vp(three), vp(two))
+    assert L.bitnet_last_status() == 0
+    assert np.array_equal(lut_scales, a)
+    assert np.array_equal(three.reshape(bs, -1)[:, :three_k], y[:, :three_k])
+    if two_k:
+        assert np.array_equal(two.reshape(bs, -1)[:, :two_k], y[:, three_k:])
+    c = np.zeros((bs, m), dtype=np.float32)
+    scales = np.array([ws], dtype=np.float32)
+    qw = ctypes.c_void_p(extra.qweights)
+    L.ggml_qgemm_lut(bs, m, k, three_k, qw, None, vp(three), vp(scales), vp(lut_scales), vp(c))
+    assert L.bitnet_last_status() == 0
+    L.ggml_qgemm_lut(bs, m, k, two_k, qw, None, vp(two), vp(scales), vp(lut_scales), vp(c))
+    assert L.bitnet_last_status() == 0
+    assert np.array_equal(c, want)
+    # a pointer that no transform produced is refused
+    L.ggml_qgemm_lut(bs, m, k, three_k, vp(three), None, vp(three), vp(scales), vp(lut_scales), vp(c))
+    assert L.bitnet_last_status() == 1
+    L.ggml_bitnet_free()

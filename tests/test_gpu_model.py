@@ -180,3 +180,51 @@ def test_fused_chain_odd_head_dim():
     agree, rel = _teacher_forced_agreement(model, args, batch=2, n_steps=64, prompt_len=5, max_seq=128, seed=13)
     assert sum(agree) / len(agree) >= 0.99
     assert max(rel) <= 1e-2
+
+
+def test_chain_flags_positions_and_tokens_outside_their_ranges(models):
+    """A position beyond the KV cache or a token id beyond the vocabulary must not become an
+    out-of-bounds access: the kernels skip the access and leave a code in the decoder's error
+    word; after clear_error the decoder works again and gives the same bits as a fresh one."""
+    from bitnet_b200.generate import Generator
+
+    args, kern, _ = models
+    max_seq = 32
+    prompt = torch.randint(0, args.vocab_size, (1, 6), device="cuda", generator=torch.Generator("cuda").manual_seed(8))
+    g = Generator(kern, 1, max_seq, use_cuda_graph=False, fused=True)
+    g.prefill(prompt)
+    good_tok, good_pos = g.tokens.clone(), g.pos.clone()
+    logits = torch.empty((1, args.vocab_size), dtype=torch.float32, device="cuda")
+    # position == max_seq_len: flagged (4), nothing appended
+    g.pos.fill_(max_seq)
+    cache_before = [(k.clone(), v.clone()) for k, v in g.cache]
+    g.fused.step(g.tokens, g.pos, g.out, logits)
+    assert g.fused.error_flag() == 4
+    for (k0, v0), (k1, v1) in zip(cache_before, g.cache):
+        assert torch.equal(k0, k1) and torch.equal(v0, v1)
+    g.fused.clear_error()
+    assert g.fused.error_flag() == 0
+    # token id == vocab_size: flagged (5)
+    g.tokens.fill_(args.vocab_size)
+    g.pos.copy_(good_pos)
+    g.fused.step(g.tokens, g.pos, g.out, logits)
+    assert g.fused.error_flag() == 5
+    g.fused.clear_error()
+    # a clean step afterwards equals a fresh decoder's (the first failed step appended nothing;
+    # the second one wrote position good_pos, which the clean step overwrites)
+    g.tokens.copy_(good_tok)
+    g.pos.copy_(good_pos)
+    g.fused.step(g.tokens, g.pos, g.out, logits)
+    fresh = Generator(kern, 1, max_seq, use_cuda_graph=False, fused=True)
+    fresh.prefill(prompt)
+    logits2 = torch.empty_like(logits)
+    fresh.fused.step(fresh.tokens, fresh.pos, fresh.out, logits2)
+    torch.cuda.synchronize()
+    assert g.fused.error_flag() == 0 and torch.equal(logits, logits2) and torch.equal(g.out, fresh.out)
+    # the host side refuses a step beyond the cache before anything is launched
+    h = Generator(kern, 1, 8, use_cuda_graph=False, fused=True)
+    h.prefill(prompt)               # 6 tokens: positions 6 and 7 are left
+    h.decode_step()
+    h.decode_step()
+    with pytest.raises(ValueError):
+        h.decode_step()
