@@ -44,6 +44,13 @@ SIGNATURES = {
     "bitnet_decoder_clear_error": (_i, [_vp]),
     "bitnet_decoder_kernels_per_step": (_i, [_vp]),
     "bitnet_workspace_error": (_i, [_i]),
+    "bitnet_tp_area_bytes": (ctypes.c_size_t, [_vp, _i]),
+    "bitnet_tp_area_create": (_i, [ctypes.c_size_t, _vp, _vp]),
+    "bitnet_tp_area_open": (_i, [_vp, _vp]),
+    "bitnet_tp_area_close": (_i, [_vp]),
+    "bitnet_tp_area_free": (_i, [_vp]),
+    "bitnet_decoder_set_wait_limit": (_i, [_vp, ctypes.c_double]),
+    "bitnet_decoder_create_tp": (_vp, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "bitnet_decoder_destroy": (None, [_vp]),
     "bitnet_w2t_bytes": (ctypes.c_size_t, [_i, _i]),
     "bitnet_pack_ternary": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -43,15 +43,17 @@ def is_stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """trace=True compiles the phase time stamps in (-DBITNET_TRACE; see
+    include/bitnet_b200_bench.h): a measurement build, not for deployment."""
+    if not force and not trace and not is_stale():
         return LIB
     objs = []
     os.makedirs(os.path.join(PKG, "build"), exist_ok=True)
     procs = []
     for src in sources():
         obj = os.path.join(PKG, "build", os.path.basename(src)[:-3] + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DBITNET_TRACE"] if trace else []), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -74,5 +76,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="compile the phase time stamps in (measurement build)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.trace))

@@ -1,21 +1,24 @@
-// The BitLinear and attention kernels of the decode chain (batches of at most 8 tokens):
+// The kernels of the decode chain (batches of at most 8 tokens):
 //
-//   per layer:  wqkv -> attention -> wo -> w13 (+ gate) -> w2          then:  output head -> argmax
+//   embed -> per layer: wqkv -> attention -> wo -> w13 (+ gate) -> w2 -> ... -> output head -> argmax
 //
 // A BitLinear at batch 1 moves 1.6-8.8 MB of packed weights: about a microsecond of HBM time,
 // as much as one kernel boundary costs (0.9 us measured on B200 with programmatic dependent
-// launch).  The step is therefore bound by the latency of its chain of dependent phases, and
-// these kernels are built to make each phase short:
+// launch).  The step is therefore bound by the latency of its chain of dependent phases and by
+// the number of instructions each phase executes on every SM, and these kernels are built to
+// keep both small:
 //  * every kernel lets its successor start at once (griddepcontrol.launch_dependents first);
 //    the successor's CTAs bring their share of the weight matrix into shared memory with bulk
 //    asynchronous copies - weights do not depend on the predecessor - and only then wait for it;
 //  * a CTA owns whole 16-row groups of the weight matrix, so no partial sums cross CTAs: no
-//    atomics on global memory, no scratch buffer, no tickets;
-//  * the statistics that the RMSNorm + absmax quantisation in front of the NEXT BitLinear needs
-//    (sum of squares, max |x * g|) are published by the kernel that produces the vector - one
-//    partial per 16 outputs, computed by the threads that hold those outputs anyway - so the
-//    consumer's prologue is one fetch of the vector and one pass over it, with no reduction over
-//    the vector (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242);
+//    atomics on sums in global memory, no scratch buffer, no tickets;
+//  * every CTA needs the whole quantised input vector, so the prologue is work that all SMs
+//    repeat: it is cut to the bone.  The producer of a vector x stores, next to x, the products
+//    t = x * g with the weight g of the RMSNorm in front of the NEXT BitLinear, and accumulates
+//    the statistics of x (sum of squares, max |t|) in one slot per token; the consumer's prologue
+//    is then one load of the slot, one rsqrt, and per element a multiply, a bf16 rounding, a
+//    multiply and a rounding to int8 - no reduction over the vector, no norm weight
+//    (gpu/model.py:68-71 behind the norms of :159-160, :195-196, :237-242);
 //  * the gate of the feed-forward block (gpu/model.py:193-195) is applied by w13's epilogue: a
 //    CTA owns gate row group u together with up row group u + F/16, so w2 reads a vector of F
 //    gated values instead of 2 F.
@@ -37,7 +40,6 @@ constexpr int kCWarps = 8;                                  // consumer warps
 constexpr int kCThreads = kCWarps * 32;
 constexpr int kCLinearThreads = kCThreads + 32;             // + one producer warp
 constexpr int kCMaxStages = 8;
-constexpr int kXvRows = 2;                                  // tokens whose source rows are staged together
 
 #ifdef BITNET_TRACE
 #define CHAIN_STAMP(i)                                                   \
@@ -51,58 +53,60 @@ constexpr int kXvRows = 2;                                  // tokens whose sour
 #endif
 
 __device__ __forceinline__ void chain_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kCThreads) : "memory"); }
-struct ChainSync {
-    __device__ __forceinline__ void operator()() const { chain_sync(); }
-};
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+
+// Adds a CTA's share to a statistics slot (device scope, or system scope for a slot in another
+// rank's memory).
+__device__ __forceinline__ void stat_add(StatPart* slot, double ss, float mx, bool system_scope) {
+    unsigned long long* mxp = reinterpret_cast<unsigned long long*>(&slot->mx);
+    const unsigned long long bits = (unsigned long long)__double_as_longlong((double)mx);   // mx >= 0: bit patterns order like values
+    if (system_scope) {
+        atomicAdd_system(&slot->ss, ss);
+        atomicMax_system(mxp, bits);
+    } else {
+        atomicAdd(&slot->ss, ss);
+        atomicMax(mxp, bits);
+    }
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 struct ChainSmem {
     uint8_t* ring;
     uint64_t *full_bar, *empty_bar;
-    float *rinv_s, *a_s, *red_f;
+    float *a_s, *stat_f;
     int *ysum_s, *flag_s, *sacc;
-    double* red_d;
-    __nv_bfloat16 *gs, *xv;
+    double* stat_d;
     int8_t* ys;
 };
 // Shared-memory layout (host and device use the same arithmetic).
 __host__ __device__ inline size_t chain_carve(const ChainLinearParams& p, uint8_t* base, ChainSmem* s) {
-    const size_t k_even = (size_t)(p.K + 7) / 8 * 8;
     const size_t k_pad = (size_t)p.k_tiles * kTileCols;
     size_t off = 0;
     auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 15) / 16 * 16; return o; };
     const size_t o_ring = take((size_t)p.ring_stages * kCStageBytes);
     const size_t o_bar = take(2 * kCMaxStages * sizeof(uint64_t));
-    const size_t o_misc = take(64 * sizeof(float));
-    const size_t o_redd = take(8 * sizeof(double));
+    const size_t o_misc = take(32 * sizeof(float));
+    const size_t o_statd = take((size_t)8 * p.units_max * sizeof(double));
+    const size_t o_statf = take((size_t)8 * p.units_max * sizeof(float));
     const size_t o_sacc = take((size_t)p.units_max * p.n_sub * 128 * sizeof(int));
-    const size_t o_gs = take(p.gamma ? k_even * 2 : 0);
-    const size_t o_xv = take((size_t)(p.M < kXvRows ? p.M : kXvRows) * k_even * 2);
     const size_t o_ys = take((size_t)(p.M + 1) * (k_pad + 16));
     if (s) {
         s->ring = base + o_ring;
         s->full_bar = reinterpret_cast<uint64_t*>(base + o_bar);
         s->empty_bar = s->full_bar + kCMaxStages;
         float* misc = reinterpret_cast<float*>(base + o_misc);
-        s->rinv_s = misc;
-        s->a_s = misc + 8;
-        s->ysum_s = reinterpret_cast<int*>(misc + 16);
-        s->red_f = misc + 24;
-        s->flag_s = reinterpret_cast<int*>(misc + 32);
-        s->red_d = reinterpret_cast<double*>(base + o_redd);
+        s->a_s = misc;
+        s->ysum_s = reinterpret_cast<int*>(misc + 8);
+        s->flag_s = reinterpret_cast<int*>(misc + 16);
+        s->stat_d = reinterpret_cast<double*>(base + o_statd);
+        s->stat_f = reinterpret_cast<float*>(base + o_statf);
         s->sacc = reinterpret_cast<int*>(base + o_sacc);
-        s->gs = reinterpret_cast<__nv_bfloat16*>(base + o_gs);
-        s->xv = reinterpret_cast<__nv_bfloat16*>(base + o_xv);
         s->ys = reinterpret_cast<int8_t*>(base + o_ys);
     }
     return off;
 }
 
 // ---------------------------------------------------------------------------------------
-// BitLinear of the chain.  288 threads: 8 consumer warps and one producer warp.
+// BitLinear of the chain.  288 threads: 8 consumer warps and one producer warp; two CTAs fit an SM, so
+// that the successor kernel's CTAs are resident, and past their set-up, while this kernel still runs.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const ChainLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -114,16 +118,16 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 
     // this CTA's units and the tile sequence they make: for each of the n_sub row-group sets,
     // the tiles of row groups u0 .. u1-1 (+ set * sub_stride), one contiguous range of the matrix
-    const int u0 = (int)((int64_t)p.n_units * cta / p.grid), u1 = (int)((int64_t)p.n_units * (cta + 1) / p.grid);
-    const int nu = u1 - u0;
+    const int u0 = cta * p.units_base + min(cta, p.units_rem);      // the first units_rem CTAs take one unit more
+    const int nu = p.units_base + (cta < p.units_rem ? 1 : 0);
     const int seg_tiles = nu * p.k_tiles;                  // tiles per contiguous range
     const int n_tiles = seg_tiles * p.n_sub;
     const int n_chunks = (n_tiles + kCStageTiles - 1) / kCStageTiles;
-    const int S = p.ring_stages;
+    const int s_mask = p.ring_stages - 1;                  // ring_stages is a power of two
 
     if (tid == 0) {
 #pragma unroll 1
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s <= s_mask; ++s) {
             mbar_init(&sm.full_bar[s], 1);
             mbar_init(&sm.empty_bar[s], kCWarps);
         }
@@ -138,8 +142,8 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
         if (lane == 0) {
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
-                const int s = c % S;
-                if (c >= S && !mbar_wait(&sm.empty_bar[s], ((c / S) - 1) & 1)) {
+                const int s = c & s_mask;
+                if (c > s_mask && !mbar_wait(&sm.empty_bar[s], ((c / p.ring_stages) - 1) & 1)) {
                     atomicExch(p.error_flag, kErrProducerWait);
                     break;
                 }
@@ -168,192 +172,148 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #pragma unroll 1
     for (int i = tid; i < n_lg * 128; i += kCThreads) sm.sacc[i] = 0;
     if (tid < 8) sm.ysum_s[tid] = 0;
-    const bool use_g = p.gamma != nullptr;
-    if (use_g) {   // the norm weight is a constant: stage it before the wait
-#pragma unroll 1
-        for (int v = tid; v < n_vec; v += kCThreads) cp_async16(sm.gs + v * 8, p.gamma + v * 8);
-    }
-    // the row of zeros that MMA columns without a token read
+    // the row of zeros that MMA columns without a token read, and the padding of the token rows
 #pragma unroll 1
     for (int v = tid; v < y_stride / 16; v += kCThreads)
         *reinterpret_cast<uint4*>(sm.ys + (size_t)p.M * y_stride + v * 16) = make_uint4(0, 0, 0, 0);
-    // epilogue inputs that do not depend on the predecessor: the next norm's weight for the
-    // first batch of outputs this thread finalises
+    if (k_pad > K) {
+#pragma unroll 1
+        for (int i = tid; i < p.M * ((k_pad - K) / 8); i += kCThreads) {
+            const int m = i / ((k_pad - K) / 8), v = i - m * ((k_pad - K) / 8);
+            *reinterpret_cast<uint2*>(sm.ys + (size_t)m * y_stride + K + v * 8) = make_uint2(0, 0);
+        }
+    }
+    // What the epilogue needs and the predecessor does not produce: this thread's first output
+    // (consecutive threads -> consecutive rows), its weight scales and the next norm's weight.
     const int total_out = nu * 16 * p.M;
     const int n_out_rows = p.out_kind == kOutGlu ? p.N / 2 : p.N;
-    auto out_index = [&](int idx, int& m, int& lu, int& r) {   // consecutive threads -> consecutive rows
-        m = idx / (nu * 16);
-        const int rem = idx - m * (nu * 16);
-        lu = rem >> 4;
-        r = rem & 15;
-    };
-    float g_pre = 1.f, h_pre = 0.f;
-    {
-        int m, lu, r;
-        out_index(tid, m, lu, r);
-        const int row = (u0 + lu) * 16 + r;
-        if (tid < total_out && row < n_out_rows && p.stats_out) g_pre = __bfloat162float(p.gamma_out[row]);
+    int e_m = 0, e_lu = 0, e_r = 0;
+    if (tid < total_out) {
+        e_m = tid / (nu * 16);
+        const int rem = tid - e_m * (nu * 16);
+        e_lu = rem >> 4;
+        e_r = rem & 15;
+    }
+    const int e_row = (u0 + e_lu) * 16 + e_r;
+    const bool e_live = tid < total_out && e_row < n_out_rows;
+    float e_ws0 = 0.f, e_ws1 = 0.f, e_g = 1.f;
+    if (e_live) {
+        e_ws0 = p.ws[segment_of(p.seg, e_row)];
+        if (p.out_kind == kOutGlu) e_ws1 = p.ws[segment_of(p.seg, e_row + p.sub_stride * 16)];
+        if (p.gamma_out) e_g = __bfloat162float(p.gamma_out[e_row]);
     }
 
-    CHAIN_STAMP(1)
-    pdl_wait();   // the predecessor's results are visible from here on
-    CHAIN_STAMP(2)
+    float e_h = 0.f;
+    constexpr bool real = true;
     {
-        int m, lu, r;
-        out_index(tid, m, lu, r);
-        const int row = (u0 + lu) * 16 + r;
-        if (tid < total_out && row < n_out_rows && p.out_kind == kOutResidual)
-            h_pre = __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(p.out) + (int64_t)m * p.ldo + row));
+    if (real) {
+        CHAIN_STAMP(1)
+        pdl_wait();   // the predecessor's results are visible from here on
+        CHAIN_STAMP(2)
+        if (e_live && p.out_kind == kOutResidual)
+            e_h = __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(p.out) + (int64_t)e_m * p.ldo + e_row));
+        if (p.zero_slot && cta == 0 && tid < p.M) {
+            p.zero_slot[tid].ss = 0.0;
+            p.zero_slot[tid].mx = 0.0;
+        }
+        if (p.stats_wait.flag) {      // tensor parallel: other ranks add to the statistics; every warp waits for itself
+            if (lane == 0 && !tp_wait(p.stats_wait)) atomicExch(p.error_flag, kErrPeerWait);
+            __syncwarp();
+        }
     }
 
     // ---- prologue: int8 activations of every token into shared memory ----------------------
+    // A thread takes 8 consecutive values of t (two 16-byte loads) and the token's statistics
+    // (one 16-byte load, the same for all threads), derives the factors itself and writes 8 bytes.
 #pragma unroll 1
-    for (int m0 = 0; m0 < p.M; m0 += kXvRows) {
-        const int nr = min(kXvRows, p.M - m0);
-        // source rows: asynchronous 16-byte copies, all in flight at once
-#pragma unroll 1
-        for (int r = 0; r < nr; ++r) {
-            const __nv_bfloat16* row;
-            if (p.src == kSrcEmbedding) {
-                int64_t tok = p.tokens[m0 + r];
-                if (tok < 0 || tok >= p.vocab) {
-                    if (tid == 0) atomicExch(p.error_flag, kErrToken);
-                    tok = 0;
-                }
-                row = p.emb + tok * (int64_t)K;
-            } else {
-                row = p.x + (int64_t)(m0 + r) * p.ldx;
-            }
-#pragma unroll 1
-            for (int v = tid; v < n_vec; v += kCThreads) cp_async16(sm.xv + (size_t)r * K + v * 8, row + v * 8);
-        }
-        if (p.stats_in && warp < nr) {
-            // warp w adds up the producer's partial statistics of token m0 + w
-            const StatPart* sp = p.stats_in + (size_t)(m0 + warp) * p.n_stats_in;
-            double ss = 0.0, mx = 0.0;
-#pragma unroll 1
-            for (int i = lane; i < p.n_stats_in; i += 32) {
-                const double2 v = __ldcg(reinterpret_cast<const double2*>(sp + i));
-                ss += v.x;
-                mx = fmax(mx, v.y);
-            }
+    for (int m = 0; m < p.M; ++m) {
+        const double2 st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
+        const float* tm = p.t + (int64_t)m * p.ldt;
+        constexpr int kIt = 1024 / kCThreads;               // vectors of up to 8192 values: all loads in flight at once
+        float4 lo[kIt], hi[kIt];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            }
-            if (lane == 0) {
-                float rinv, a;
-                finish_stats(ss, (float)mx, K, p.eps, use_g, rinv, a);
-                sm.rinv_s[m0 + warp] = rinv;
-                sm.a_s[m0 + warp] = a;
+        for (int it = 0; it < kIt; ++it) {
+            const int v = tid + it * kCThreads;
+            if (v < n_vec) {
+                lo[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8));
+                hi[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
             }
         }
-        cp_async_wait_all();
-        chain_sync();
-        if (!p.stats_in) {
-            // no producer statistics (first layer: the source is an embedding row): reduce here
-#pragma unroll 1
-            for (int r = 0; r < nr; ++r) {
-                double ss = 0.0;
-                float mt = 0.f;
-#pragma unroll 1
-                for (int v = tid; v < n_vec; v += kCThreads)
-                    group_stats(unpack_bf16x8(*reinterpret_cast<const uint4*>(sm.xv + (size_t)r * K + v * 8)),
-                                use_g ? unpack_bf16x8(*reinterpret_cast<const uint4*>(sm.gs + v * 8)) : Vec8{}, use_g, ss, mt);
-                reduce_stats_256(ss, mt, sm.red_d, sm.red_f, tid, ChainSync());
-                if (tid == 0) {
-                    float rinv, a;
-                    finish_stats(ss, mt, K, p.eps, use_g, rinv, a);
-                    sm.rinv_s[m0 + r] = rinv;
-                    sm.a_s[m0 + r] = a;
-                }
-            }
-            chain_sync();
-        }
-        if (p.src == kSrcEmbedding && p.h_copy && cta == 0) {   // the residual stream starts as the embedding row
-#pragma unroll 1
-            for (int r = 0; r < nr; ++r)
-#pragma unroll 1
-                for (int v = tid; v < n_vec; v += kCThreads)
-                    *reinterpret_cast<uint4*>(p.h_copy + (int64_t)(m0 + r) * K + v * 8) =
-                        *reinterpret_cast<const uint4*>(sm.xv + (size_t)r * K + v * 8);
-        }
-#pragma unroll 1
-        for (int r = 0; r < nr; ++r) {
-            const float rinv = sm.rinv_s[m0 + r], a = sm.a_s[m0 + r];
-            int8_t* ym = sm.ys + (size_t)(m0 + r) * y_stride;
-            int sy = 0;
-#pragma unroll 1
-            for (int v = tid; v < k_pad / 8; v += kCThreads) {
-                uint2 w = make_uint2(0, 0);
-                if (v < n_vec)
-                    w = quant_group(unpack_bf16x8(*reinterpret_cast<const uint4*>(sm.xv + (size_t)r * K + v * 8)),
-                                    use_g ? unpack_bf16x8(*reinterpret_cast<const uint4*>(sm.gs + v * 8)) : Vec8{}, use_g, rinv, a, sy);
-                *reinterpret_cast<uint2*>(ym + v * 8) = w;
-            }
+        float rinv, a;
+        finish_stats(st.x, (float)st.y, p.k_norm, p.eps, true, rinv, a);
+        int8_t* ym = sm.ys + (size_t)m * y_stride;
+        int sy = 0;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
-            if (lane == 0) atomicAdd(&sm.ysum_s[m0 + r], sy);
+        for (int it = 0; it < kIt; ++it) {
+            const int v = tid + it * kCThreads;
+            if (v < n_vec) {
+                const float f[8] = {lo[it].x, lo[it].y, lo[it].z, lo[it].w, hi[it].x, hi[it].y, hi[it].z, hi[it].w};
+                int q[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) q[e] = quant_s8(bf16_round(f[e] * rinv) * a);
+                const uint32_t w0 = pack_bytes(q[0], q[1], q[2], q[3]), w1 = pack_bytes(q[4], q[5], q[6], q[7]);
+                sy = __dp4a((int)w0, 0x01010101, sy);
+                sy = __dp4a((int)w1, 0x01010101, sy);
+                *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
+            }
         }
-        chain_sync();   // ys and ysum_s complete; xv may be overwritten by the next tokens
+#pragma unroll 1
+        for (int v = tid + kIt * kCThreads; v < n_vec; v += kCThreads) {    // vectors longer than 8192 values
+            const float4 l4 = __ldcg(reinterpret_cast<const float4*>(tm + v * 8)), h4 = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
+            const float f[8] = {l4.x, l4.y, l4.z, l4.w, h4.x, h4.y, h4.z, h4.w};
+            int q[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) q[e] = quant_s8(bf16_round(f[e] * rinv) * a);
+            const uint32_t w0 = pack_bytes(q[0], q[1], q[2], q[3]), w1 = pack_bytes(q[4], q[5], q[6], q[7]);
+            sy = __dp4a((int)w0, 0x01010101, sy);
+            sy = __dp4a((int)w1, 0x01010101, sy);
+            *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
+        if (lane == 0 && real) atomicAdd(&sm.ysum_s[m], sy);
+        if (tid == 0) sm.a_s[m] = a;
     }
-    CHAIN_STAMP(3)
+    if (real) { CHAIN_STAMP(8) }
+    chain_sync();   // ys, ysum_s, a_s complete
+    if (real) { CHAIN_STAMP(3) }
 
     // ---- matmul over the staged tiles ----------------------------------------------------
     // Per tile a lane holds the A fragments of rows g, g+8 for four m16n8k32 MMAs: each of its
     // four words is split into its four 2-bit fields by AND masks alone (field j stays scaled by
     // 4^j and has its own accumulator).  Tokens are the MMA's 8 columns, so any M <= 8 costs the
-    // same.  Two tiles are in flight per warp on separate accumulators, so that the second
-    // tile's MMAs do not wait for the first one's.
+    // same.  Within a round (two ring stages, up to 64 tiles) each warp takes one contiguous run.
     const int g = lane >> 2, q = lane & 3;
     const int8_t* y_lane = sm.ys + (size_t)(g < p.M ? g : p.M) * y_stride + 32 * q;
     constexpr int kRoundTiles = kCRoundStages * kCStageTiles;
     const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
-    int acc[2][4][4];
+    int acc[4][4];
 #pragma unroll
-    for (int s2 = 0; s2 < 2; ++s2)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[s2][j][e] = 0;
-    auto flush = [&](int lg) {   // this warp's sums of local row group lg into the CTA's accumulator
-        int* dst = sm.sacc + lg * 128;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int tok = 2 * q + (i & 1);
-            const int v = acc[0][0][i] + acc[1][0][i] + ((acc[0][1][i] + acc[1][1][i]) >> 2) + ((acc[0][2][i] + acc[1][2][i]) >> 4) +
-                          ((acc[0][3][i] + acc[1][3][i]) >> 6);
-            if (tok < p.M) atomicAdd(&dst[(g + 8 * (i >> 1)) * 8 + tok], v);
-        }
-#pragma unroll
-        for (int s2 = 0; s2 < 2; ++s2)
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[s2][j][e] = 0;
-    };
-    auto tile_mma = [&](int (&a4)[4][4], const uint4& wc, const uint4& y0, const uint4& y1) {
-        const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-        const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t msk = 0x03030303u << (2 * j);
-            mma_u8s8(a4[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
-        }
-    };
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0;
     bool gave_up = false;
+#ifdef BITNET_TRACE
+    long long tr_wait = 0, tr_flush = 0, tr_t0 = clock64(), tr_a;
+#define TR_BEGIN tr_a = clock64();
+#define TR_END(x) x += clock64() - tr_a;
+#else
+#define TR_BEGIN
+#define TR_END(x)
+#endif
 #pragma unroll 1
     for (int r = 0; r < n_rounds && !gave_up; ++r) {
         const int nr_t = min(kRoundTiles, n_tiles - r * kRoundTiles);
-        const int lo = nr_t * warp / kCWarps, hi = nr_t * (warp + 1) / kCWarps;
-        if (hi > lo) {
+        const int lo_t = nr_t * warp / kCWarps;
+        const int hi_t = nr_t * (warp + 1) / kCWarps;
+        const int c0 = r * kCRoundStages;                    // first chunk of the round
+        if (hi_t > lo_t && real) {
             bool ok = true;
+            TR_BEGIN
 #pragma unroll 1
-            for (int ls = lo / kCStageTiles; ls <= (hi - 1) / kCStageTiles; ++ls) {
-                const int c = r * kCRoundStages + ls;        // chunk number of the CTA's tile sequence
-                ok = ok && mbar_wait(&sm.full_bar[c % S], (c / S) & 1);
-            }
+            for (int ls = lo_t / kCStageTiles; ls <= (hi_t - 1) / kCStageTiles; ++ls)
+                ok = ok && mbar_wait(&sm.full_bar[(c0 + ls) & s_mask], ((c0 + ls) / p.ring_stages) & 1);
+            TR_END(tr_wait)
             if (!ok) {   // gave up: flag it, leave together below
                 if (lane == 0) {
                     atomicExch(p.error_flag, kErrConsumerWait);
@@ -362,96 +322,123 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 gave_up = true;
             }
         }
-        if (!gave_up && hi > lo) {
-            int t = r * kRoundTiles + lo;                    // local tile number
-            const int t_end = r * kRoundTiles + hi;
+        if (r == 0 && real) { CHAIN_STAMP(9) }
+        if (!gave_up && hi_t > lo_t) {
+            // the two stages of a round are adjacent in the ring (ring_stages is even)
+            const uint8_t* tile = sm.ring + (c0 & s_mask) * kCStageBytes + lo_t * kTileBytes + lane * 16;
+            int t = r * kRoundTiles + lo_t;                  // local tile number
             int lg = t / p.k_tiles, kt = t - lg * p.k_tiles;
-            // the ring slot of a tile: chunk c = t / 32 sits in stage c % S
-            auto tile_ptr = [&](int tt) -> const uint8_t* {
-                const int c = tt / kCStageTiles;
-                return sm.ring + (c % S) * kCStageBytes + (tt - c * kCStageTiles) * kTileBytes + lane * 16;
-            };
 #pragma unroll 1
-            while (t < t_end) {
-                const int n_here = min(t_end - t, p.k_tiles - kt);   // tiles of this row group in the run
-                int j = 0;
-#pragma unroll 1
-                for (; j + 2 <= n_here; j += 2) {
-                    const uint4 w0 = *reinterpret_cast<const uint4*>(tile_ptr(t + j));
-                    const uint4 w1 = *reinterpret_cast<const uint4*>(tile_ptr(t + j + 1));
-                    const uint4* yp0 = reinterpret_cast<const uint4*>(y_lane + (kt + j) * kTileCols);
-                    const uint4* yp1 = reinterpret_cast<const uint4*>(y_lane + (kt + j + 1) * kTileCols);
-                    const uint4 y00 = yp0[0], y01 = yp0[1], y10 = yp1[0], y11 = yp1[1];
-                    tile_mma(acc[0], w0, y00, y01);
-                    tile_mma(acc[1], w1, y10, y11);
+            for (int i = lo_t; i < hi_t; ++i, tile += kTileBytes) {
+                const uint4 wc = *reinterpret_cast<const uint4*>(tile);
+                const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
+                const uint4 y0 = yp[0], y1 = yp[1];
+                const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+                const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t msk = 0x03030303u << (2 * j);
+                    mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
                 }
-                if (j < n_here) {
-                    const uint4 w0 = *reinterpret_cast<const uint4*>(tile_ptr(t + j));
-                    const uint4* yp0 = reinterpret_cast<const uint4*>(y_lane + (kt + j) * kTileCols);
-                    const uint4 y00 = yp0[0], y01 = yp0[1];
-                    tile_mma(acc[0], w0, y00, y01);
-                }
-                flush(lg);
-                t += n_here;
-                kt += n_here;
-                if (kt == p.k_tiles) {
-                    kt = 0;
-                    ++lg;
+                if (++kt == p.k_tiles || i + 1 == hi_t) {
+                    // end of this row group's tiles in the run: the warp's sums into the CTA's accumulator
+                    TR_BEGIN
+                    int* dst = sm.sacc + lg * 128;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int tok = 2 * q + (e & 1);
+                        const int v = acc[0][e] + (acc[1][e] >> 2) + (acc[2][e] >> 4) + (acc[3][e] >> 6);
+                        if (tok < p.M && real) atomicAdd(&dst[(g + 8 * (e >> 1)) * 8 + tok], v);
+                        acc[0][e] = 0; acc[1][e] = 0; acc[2][e] = 0; acc[3][e] = 0;
+                    }
+                    TR_END(tr_flush)
+                    if (kt == p.k_tiles) {
+                        kt = 0;
+                        ++lg;
+                    }
                 }
             }
         }
         __syncwarp();
-        if (lane == 0 && !gave_up) {
+        if (lane == 0 && !gave_up && real) {
             // This warp is done with every stage of the round.  It releases a stage only after
             // having seen that stage's copy complete (usually it has, long ago), so that no warp
             // ever waits for a later fill of a stage whose earlier fill it has not observed.
 #pragma unroll 1
             for (int ls = 0; ls < kCRoundStages; ++ls) {
-                const int c = r * kCRoundStages + ls;
-                if (c < n_chunks && mbar_wait(&sm.full_bar[c % S], (c / S) & 1)) mbar_arrive(&sm.empty_bar[c % S]);
+                const int c = c0 + ls;
+                if (c < n_chunks && mbar_wait(&sm.full_bar[c & s_mask], (c / p.ring_stages) & 1)) mbar_arrive(&sm.empty_bar[c & s_mask]);
             }
         }
     }
-    CHAIN_STAMP(4)
+#ifdef BITNET_TRACE
+    if (real && p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+        p.trace[11] = (unsigned long long)tr_wait;
+        p.trace[12] = (unsigned long long)tr_flush;
+        p.trace[13] = (unsigned long long)(clock64() - tr_t0);
+        p.trace[14] = (unsigned long long)n_tiles;
+    }
+#endif
+    if (real) { CHAIN_STAMP(4) }
     chain_sync();
-    if (sm.flag_s[0] || n_tiles == 0) return;
+    if (real) { CHAIN_STAMP(10) }
+    if (real && (sm.flag_s[0] || n_tiles == 0)) return;
 
     // ---- epilogue --------------------------------------------------------------------------
     // Thread idx finalises output r of unit lu for token m; 16 consecutive threads hold the 16
     // outputs of one unit and token, and reduce their statistics by shuffles.
+    const bool want_stats = p.stats_out != nullptr;
 #pragma unroll 1
     for (int base = 0; base < total_out; base += kCThreads) {
         const int idx = base + tid;
         const bool valid = idx < total_out;
-        int m = 0, lu = 0, r = 0;
-        if (valid) out_index(idx, m, lu, r);
+        int m = e_m, lu = e_lu, r = e_r;
+        float ws0 = e_ws0, ws1 = e_ws1, gq = e_g, h_old = e_h;
+        bool live = e_live;
+        if (base > 0) {            // more than 512 outputs per CTA: the general form
+            m = 0; lu = 0; r = 0; live = false;
+            if (valid) {
+                m = idx / (nu * 16);
+                const int rem = idx - m * (nu * 16);
+                lu = rem >> 4;
+                r = rem & 15;
+                const int row = (u0 + lu) * 16 + r;
+                live = row < n_out_rows;
+                if (live) {
+                    ws0 = p.ws[segment_of(p.seg, row)];
+                    if (p.out_kind == kOutGlu) ws1 = p.ws[segment_of(p.seg, row + p.sub_stride * 16)];
+                    gq = p.gamma_out ? __bfloat162float(p.gamma_out[row]) : 1.f;
+                    if (p.out_kind == kOutResidual)
+                        h_old = __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(p.out) + (int64_t)m * p.ldo + row));
+                }
+            }
+        }
         const int row = (u0 + lu) * 16 + r;                 // output index (glu: index of the gated value)
-        const bool live = valid && row < n_out_rows;
-        float o = 0.f, gq = 1.f;
+        float o = 0.f;
         if (live) {
             const float a = sm.a_s[m];
             const int ys_m = sm.ysum_s[m];                  // fields hold weight + 1: take sum(y) off once per row
             const int v0 = sm.sacc[lu * 128 + r * 8 + m] - ys_m;
-            if (p.out_kind == kOutGlu) {
-                const int v1 = sm.sacc[(nu + lu) * 128 + r * 8 + m] - ys_m;
-                const int row_up = row + p.sub_stride * 16;
-                const float x1 = lin_out(v0, a, p.ws[segment_of(p.seg, row)]);
-                const float x3 = lin_out(v1, a, p.ws[segment_of(p.seg, row_up)]);
-                const float t = fmaxf(x1, 0.f);
-                o = bf16_round(bf16_round(t * t) * x3);     // rounded after each step, as bf16 tensor operations round
+            if (p.out_kind == kOutTpPartial) {
+                // this rank's exact partial sums, to slot [rank][m][row] of every rank's area
+                const size_t at = p.tp_part_off + (((size_t)p.tp.rank * p.M + m) * p.N + row) * sizeof(int32_t);
+#pragma unroll 1
+                for (int pr = 0; pr < p.tp.size && real; ++pr) *reinterpret_cast<int32_t*>(p.tp.area[pr] + at) = v0;
             } else {
-                const float lin = lin_out(v0, a, p.ws[segment_of(p.seg, row)]);
-                if (p.out_kind == kOutResidual) {
-                    const float h_old = base == 0 ? h_pre : __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(p.out) + (int64_t)m * p.ldo + row));
-                    o = bf16_round(h_old + lin);
+                if (p.out_kind == kOutGlu) {
+                    const int v1 = sm.sacc[(nu + lu) * 128 + r * 8 + m] - ys_m;
+                    const float x1 = lin_out(v0, a, ws0), x3 = lin_out(v1, a, ws1);
+                    const float tt = fmaxf(x1, 0.f);
+                    o = bf16_round(bf16_round(tt * tt) * x3);   // rounded after each step, as bf16 tensor operations round
                 } else {
-                    o = lin;
+                    const float lin = lin_out(v0, a, ws0);
+                    o = p.out_kind == kOutResidual ? bf16_round(h_old + lin) : lin;
+                    if (real) p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(o);
                 }
+                if (p.t_out && real) p.t_out[(int64_t)m * p.ldt_out + row] = o * gq;    // exact: both factors are bf16 values
             }
-            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(o);
-            if (p.stats_out) gq = base == 0 ? g_pre : __bfloat162float(p.gamma_out[row]);
         }
-        if (p.stats_out) {
+        if (want_stats) {
             double ss = (double)o * (double)o;
             float mx = fabsf(o * gq);
 #pragma unroll
@@ -459,15 +446,129 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 ss += __shfl_xor_sync(0xffffffffu, ss, off);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
             }
-            if (valid && (lane & 15) == 0) {
-                StatPart sp;
-                sp.ss = ss;
-                sp.mx = (double)mx;
-                p.stats_out[(size_t)m * p.n_units + u0 + lu] = sp;
+            if (valid && (lane & 15) == 0) {      // the unit's share, to be added up per token below
+                sm.stat_d[m * p.units_max + lu] = ss;
+                sm.stat_f[m * p.units_max + lu] = mx;
             }
         }
     }
+    if (want_stats) {
+        // one share per token and CTA: the units' shares added in their order, then one atomic pair
+        chain_sync();
+        if (tid < p.M && real) {
+            double ss = 0.0;
+            float mx = 0.f;
+#pragma unroll 1
+            for (int lu = 0; lu < nu; ++lu) {
+                ss += sm.stat_d[tid * p.units_max + lu];
+                mx = fmaxf(mx, sm.stat_f[tid * p.units_max + lu]);
+            }
+            if (p.tp.size > 1) {     // every rank normalises over the whole vector: the slot in every rank's area
+#pragma unroll 1
+                for (int pr = 0; pr < p.tp.size; ++pr)
+                    stat_add(reinterpret_cast<StatPart*>(p.tp.area[pr] + p.tp_stats_off) + tid, ss, mx, true);
+                __threadfence_system();
+            } else {
+                stat_add(p.stats_out + tid, ss, mx, false);
+            }
+        }
+        if (p.tp.size > 1 && real) {
+            __syncwarp();            // the M adding threads are lanes of warp 0
+            if (tid == 0) tp_signal(p.tp, p.tp_stats_flag_off);
+        }
+    }
+    if (p.out_kind == kOutTpPartial && real) {
+        if (cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
+        __threadfence_system();
+        chain_sync();
+        if (tid == 0) tp_signal(p.tp, p.tp_part_flag_off);
+    }
     CHAIN_STAMP(5)
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// First kernel of a step: the embedding rows of the new tokens start the residual stream; their
+// products with layer 0's attention_norm weight and their statistics go where wqkv expects them.
+// One CTA of 256 threads per token.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) embed_kernel(const EmbedParams p) {
+    __shared__ double sd[8];
+    __shared__ float sf[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int m = blockIdx.x, tid = threadIdx.x;
+    if (p.zero_slot && tid == 0) {
+        p.zero_slot[m].ss = 0.0;
+        p.zero_slot[m].mx = 0.0;
+    }
+    int64_t tok = p.tokens[m];
+    if (tok < 0 || tok >= p.vocab) {      // outside the vocabulary: flag it, use token 0
+        if (tid == 0) atomicExch(p.error_flag, kErrToken);
+        tok = 0;
+    }
+    const __nv_bfloat16* row = p.emb + tok * (int64_t)p.K;
+    double ss = 0.0;
+    float mx = 0.f;
+#pragma unroll 1
+    for (int v = tid; v < p.K / 8; v += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + v * 8);
+        const Vec8 x = unpack_bf16x8(raw), g = unpack_bf16x8(*reinterpret_cast<const uint4*>(p.gamma + v * 8));
+        *reinterpret_cast<uint4*>(p.h + (int64_t)m * p.K + v * 8) = raw;
+        float t[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            t[e] = x.v[e] * g.v[e];
+            ss = fma((double)x.v[e], (double)x.v[e], ss);
+            mx = fmaxf(mx, fabsf(t[e]));
+        }
+        *reinterpret_cast<float4*>(p.t + (int64_t)m * p.K + v * 8) = make_float4(t[0], t[1], t[2], t[3]);
+        *reinterpret_cast<float4*>(p.t + (int64_t)m * p.K + v * 8 + 4) = make_float4(t[4], t[5], t[6], t[7]);
+    }
+    reduce_stats<256>(ss, mx, sd, sf, tid, [] { __syncthreads(); });
+    if (tid == 0) {
+        p.stats_out[m].ss = ss;
+        p.stats_out[m].mx = (double)mx;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Second half of a row-parallel BitLinear under tensor parallelism: adds up the ranks' exact
+// int32 partial sums, rescales, adds the residual, and hands h, t = h * g and the statistics of h
+// to the next BitLinear.  Every rank does the whole vector (it needs all of h).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tp_reduce_kernel(const TpReduceParams p) {
+    __shared__ double sd[8];
+    __shared__ float sf[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    if (p.zero_slot && blockIdx.x == 0 && tid < p.M) {
+        p.zero_slot[tid].ss = 0.0;
+        p.zero_slot[tid].mx = 0.0;
+    }
+    if (tid == 0 && !tp_wait(p.wait)) atomicExch(p.error_flag, kErrPeerWait);
+    __syncthreads();
+    const int row = blockIdx.x * 256 + tid;
+    const float gq = row < p.N ? __bfloat162float(p.gamma_out[row]) : 0.f;
+#pragma unroll 1
+    for (int m = 0; m < p.M; ++m) {
+        float o = 0.f;
+        if (row < p.N) {
+            int v = 0;
+#pragma unroll 1
+            for (int r = 0; r < p.T; ++r) v += __ldcg(p.part + ((size_t)r * p.M + m) * p.N + row);   // integer sums: any order
+            const float h_old = __bfloat162float(p.out[(int64_t)m * p.ldo + row]);
+            o = bf16_round(h_old + lin_out(v, p.a[m], p.ws));
+            p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(o);
+            p.t_out[(int64_t)m * p.ldo + row] = o * gq;
+        }
+        double ss = (double)o * (double)o;
+        float mx = fabsf(o * gq);
+        reduce_stats<256>(ss, mx, sd, sf, tid, [] { __syncthreads(); });
+        if (tid == 0) stat_add(p.stats_out + m, ss, mx, false);
+        __syncthreads();
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -494,10 +595,11 @@ __device__ __forceinline__ void unpack8(const uint4& r, float (&f)[8]) {
 }
 
 // Statistics of one head's output for the next prologue: thread d < D holds value `val` of
-// dimension d (others hold 0).  `sd`/`sf` hold 16 entries; every thread of the CTA must call.
+// dimension d (others hold 0); the head's share goes to the sequence's slot.  `sd`/`sf` hold 16
+// entries; every thread of the CTA must call.
 template <class Sync>
-__device__ __forceinline__ void publish_head_stats(const AttentionParams& p, int b, int head, float val, float gq, int tid,
-                                                   double* sd, float* sf, Sync sync) {
+__device__ __forceinline__ void publish_head_stats(const AttentionParams& p, int b, float val, float gq, int tid, double* sd,
+                                                   float* sf, Sync sync) {
     double ss = (double)val * (double)val;
     float mx = fabsf(val * gq);
 #pragma unroll
@@ -512,10 +614,16 @@ __device__ __forceinline__ void publish_head_stats(const AttentionParams& p, int
     }
     sync();
     if (tid == 0) {
-        StatPart sp;
-        sp.ss = sd[0] + sd[1] + sd[2] + sd[3];      // D <= 128: the values sit in the first four warps
-        sp.mx = (double)fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3]));
-        p.stats_out[(size_t)b * p.H + head] = sp;
+        ss = sd[0] + sd[1] + sd[2] + sd[3];          // D <= 128: the values sit in the first four warps
+        mx = fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3]));
+        if (p.tp.size > 1) {     // every rank's wo normalises over all heads: the slot in every rank's area
+#pragma unroll 1
+            for (int pr = 0; pr < p.tp.size; ++pr)
+                stat_add(reinterpret_cast<StatPart*>(p.tp.area[pr] + p.tp_stats_off) + b, ss, mx, true);
+            tp_signal(p.tp, p.tp_stats_flag_off);
+        } else {
+            stat_add(p.stats_out + b, ss, mx, false);
+        }
     }
 }
 
@@ -533,11 +641,11 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
     const int D = p.D, G = p.H / p.Hkv, kvh = h / G;
     const int hw = tid >> 4, l16 = tid & 15, d0 = 8 * l16;
     const bool live = d0 < D;
-    float* red_m = reinterpret_cast<float*>(smem);      // [32]
-    float* red_l = red_m + 32;                          // [32]
+    float* red_m = reinterpret_cast<float*>(smem);      // [32] (16 used)
+    float* red_l = red_m + 32;                          // [32]: 16 sums, 16 normalised weights
     float* sf = red_l + 32;                             // [16]
     double* sd = reinterpret_cast<double*>(sf + 16);    // [16]
-    float* red_o = reinterpret_cast<float*>(sd + 16);   // [32][D]
+    float* red_o = reinterpret_cast<float*>(sd + 16);   // [16][D]
     const int64_t key_stride = (int64_t)p.Hkv * D;
     const __nv_bfloat16* ck = p.cache_k + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
@@ -557,8 +665,12 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
     };
     load_block(0, p.L);       // requested before P is known; rows >= P are masked below
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
-    uint4 q_raw = make_uint4(0, 0, 0, 0);
-    if (live) q_raw = __ldcg(reinterpret_cast<const uint4*>(x + h * D + d0));   // L2: written by other SMs
+    uint4 q_raw = make_uint4(0, 0, 0, 0), k_raw = make_uint4(0, 0, 0, 0), v_new = make_uint4(0, 0, 0, 0);
+    if (live) {      // L2: written by other SMs.  Every half-warp takes the new token's k and v: which one owns key P is not known yet
+        q_raw = __ldcg(reinterpret_cast<const uint4*>(x + h * D + d0));
+        k_raw = __ldcg(reinterpret_cast<const uint4*>(x + (p.H + kvh) * D + d0));
+        v_new = __ldcg(reinterpret_cast<const uint4*>(x + (p.H + p.Hkv + kvh) * D + d0));
+    }
     if (P < 0 || P >= p.L) {      // outside the cache: flag it, touch nothing
         if (tid == 0) atomicExch(p.error_flag, kErrPosition);
         return true;
@@ -591,12 +703,10 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
     // the new token is key P: its owner half-warp takes k (rotated) and v from xqkv, and the CTA
     // of the kv head's first query head appends them to the cache
     const bool own_new = (P & 31) == hw;
-    uint4 k_new = make_uint4(0, 0, 0, 0), v_new = make_uint4(0, 0, 0, 0);
+    uint4 k_new = make_uint4(0, 0, 0, 0);
     if (own_new && live) {
-        const uint4 kraw = __ldcg(reinterpret_cast<const uint4*>(x + (p.H + kvh) * D + d0));
-        v_new = __ldcg(reinterpret_cast<const uint4*>(x + (p.H + p.Hkv + kvh) * D + d0));
         float kf[8];
-        rotate(kraw, kf);
+        rotate(k_raw, kf);
         Vec8 kv8;
 #pragma unroll
         for (int e = 0; e < 8; ++e) kv8.v[e] = kf[e];
@@ -654,39 +764,54 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
             m_run = m_new;
         }
     }
-    // combine the 32 half-warps
-    if (l16 == 0) {
-        red_m[hw] = m_run;
-        red_l[hw] = l_run;
+    // combine: first the two half-warps of a warp by shuffles, then the 16 warps through shared memory
+    {
+        const float m_o = __shfl_xor_sync(0xffffffffu, m_run, 16), l_o = __shfl_xor_sync(0xffffffffu, l_run, 16);
+        const float m_n = fmaxf(m_run, m_o);
+        const float f_me = m_run > -INFINITY ? __expf(m_run - m_n) : 0.f, f_ot = m_o > -INFINITY ? __expf(m_o - m_n) : 0.f;
+        l_run = l_run * f_me + l_o * f_ot;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = o[e] * f_me + __shfl_xor_sync(0xffffffffu, o[e], 16) * f_ot;
+        m_run = m_n;
     }
-    if (live) {
-        *reinterpret_cast<float4*>(red_o + hw * D + d0) = make_float4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<float4*>(red_o + hw * D + d0 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    const int wp = tid >> 5;
+    if ((tid & 31) == 0) {
+        red_m[wp] = m_run;
+        red_l[wp] = l_run;
+    }
+    if ((tid & 16) == 0 && live) {
+        *reinterpret_cast<float4*>(red_o + wp * D + d0) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(red_o + wp * D + d0 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    __syncthreads();
+    if (tid < 32) {      // the warps' weights, normalised: exp(m_w - max) / sum
+        const float mw = tid < 16 ? red_m[tid] : -INFINITY, lw = tid < 16 ? red_l[tid] : 0.f;
+        float mx = mw;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float f = mw > -INFINITY ? __expf(mw - mx) : 0.f;
+        float l = lw * f;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+        if (tid < 16) red_l[16 + tid] = l > 0.f ? f / l : 0.f;
     }
     __syncthreads();
     float val = 0.f, gq = 1.f;
     if (tid < D) {
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int w = 0; w < 32; ++w) mx = fmaxf(mx, red_m[w]);
-        float l = 0.f, acc = 0.f;
-#pragma unroll 1
-        for (int w = 0; w < 32; ++w) {
-            const float lw = red_l[w];
-            if (lw > 0.f) {
-                const float f = __expf(red_m[w] - mx);
-                l = fmaf(lw, f, l);
-                acc = fmaf(red_o[w * D + tid], f, acc);
-            }
-        }
-        const __nv_bfloat16 ob = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 16; ++w) acc = fmaf(red_o[w * D + tid], red_l[16 + w], acc);
+        const __nv_bfloat16 ob = __float2bfloat16_rn(acc);
         const int64_t oi = (int64_t)b * p.H * D + h * D + tid;
         p.out[oi] = ob;
         if (p.tap) p.tap[oi] = ob;
         val = __bfloat162float(ob);
-        if (p.stats_out) gq = __bfloat162float(p.gamma_out[h * D + tid]);
+        if (p.stats_out) {
+            gq = __bfloat162float(p.gamma_out[h * D + tid]);
+            p.t_out[oi] = val * gq;                  // exact: both factors are bf16 values
+        }
     }
-    if (p.stats_out) publish_head_stats(p, b, h, val, gq, tid, sd, sf, [] { __syncthreads(); });
+    if (p.stats_out) publish_head_stats(p, b, val, gq, tid, sd, sf, [] { __syncthreads(); });
     return true;
 }
 
@@ -701,6 +826,10 @@ __global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const Attenti
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y, tid = threadIdx.x;
+    if (p.zero_slot && blockIdx.x == 0 && tid == 0) {
+        p.zero_slot[b].ss = 0.0;
+        p.zero_slot[b].mx = 0.0;
+    }
     if constexpr (NTHREADS == kAttnThreads) {
         // candidates for the short form: one CTA per query head (see attention_item)
         if ((int)blockIdx.x < p.H && p.S >= p.H / p.Hkv && (p.D & 7) == 0 && attention_short(p, smem, b, blockIdx.x, tid)) return;
@@ -736,10 +865,12 @@ __global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const Attenti
         const int head = it.kvh * Gfull + it.h0 + hh;
         float val = 0.f, gq = 1.f;
         if (tid < p.D) {
-            val = __bfloat162float(p.out[(int64_t)b * p.H * p.D + head * p.D + tid]);
+            const int64_t oi = (int64_t)b * p.H * p.D + head * p.D + tid;
+            val = __bfloat162float(p.out[oi]);
             gq = __bfloat162float(p.gamma_out[head * p.D + tid]);
+            p.t_out[oi] = val * gq;
         }
-        publish_head_stats(p, b, head, val, gq, tid, sd, sf, [] { __syncthreads(); });
+        publish_head_stats(p, b, val, gq, tid, sd, sf, [] { __syncthreads(); });
     }
 }
 
@@ -774,9 +905,11 @@ void plan_chain_linear(ChainLinearParams& p, int n_sm) {
         p.sub_stride = 0;
     }
     p.grid = p.n_units < n_sm ? p.n_units : n_sm;
+    p.units_base = p.n_units / p.grid;
+    p.units_rem = p.n_units % p.grid;
     p.units_max = (p.n_units + p.grid - 1) / p.grid;
-    if (p.ring_stages < 2 || p.ring_stages > kCMaxStages) p.ring_stages = 4;
-    p.ring_stages = p.ring_stages / kCRoundStages * kCRoundStages;
+    if (p.ring_stages != 2 && p.ring_stages != 4 && p.ring_stages != 8) p.ring_stages = 8;   // a power of two
+    if (p.k_norm == 0) p.k_norm = p.K;
 }
 
 size_t chain_linear_smem(const ChainLinearParams& p) { return chain_carve(p, nullptr, nullptr) + 128; }
@@ -800,6 +933,14 @@ int prepare_chain_kernels(size_t smem_optin) {
 
 int launch_chain_linear(const ChainLinearParams& p, cudaStream_t stream, bool pdl) {
     return check_cuda(launch_chain_k(chain_linear_kernel, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
+}
+
+int launch_embed(const EmbedParams& p, cudaStream_t stream, bool pdl) {
+    return check_cuda(launch_chain_k(embed_kernel, p.M, 256, 0, stream, p, pdl));
+}
+
+int launch_tp_reduce(const TpReduceParams& p, cudaStream_t stream, bool pdl) {
+    return check_cuda(launch_chain_k(tp_reduce_kernel, (p.N + 255) / 256, 256, 0, stream, p, pdl));
 }
 
 int launch_chain_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl) {

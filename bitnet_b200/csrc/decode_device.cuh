@@ -64,8 +64,36 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// ---- tensor-parallel exchange (see TpPeers in decode_fused.h) ---------------------------------
+constexpr long long kPeerWaitCycles = 600000000LL;       // default limit of a wait for another rank: about 0.3 s
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// One thread: waits until the arrival counter has reached this step's target.  False after the
+// time limit (the caller records kErrPeerWait and carries on with whatever is there, so that the
+// kernel ends and the host can read the error word).
+__device__ __noinline__ bool tp_wait(const TpWait& w) {
+    const unsigned long long target = __ldcg(w.step) * w.per_step + w.base;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(w.flag) < target) {
+        if (clock64() - t0 > w.limit_cycles) return false;
+    }
+    return true;
+}
+// One thread, after a CTA barrier behind which every thread that stored to the peers' areas has
+// executed __threadfence_system(): counts this CTA in on every rank.
+__device__ __forceinline__ void tp_signal(const TpPeers& tp, size_t flag_off) {
+    __threadfence_system();
+#pragma unroll 1
+    for (int r = 0; r < tp.size; ++r)
+        atomicAdd_system(reinterpret_cast<unsigned long long*>(tp.area[r] + flag_off), 1ull);
+}
+
 // bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
-__device__ __noinline__ float lin_out(int acc, float a, float ws) { return bf16_round((float)acc / a * ws); }
+__device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf16_round(__fdiv_rn((float)acc, a) * ws); }
 
 // ---------------------------------------------------------------------------------------
 // Attention for one new token per sequence: RoPE on q and k, append k, v to the cache,
@@ -443,9 +471,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
     // producer's partial statistics when it published them
     for (int m = 0; m < p.M; ++m) {
         double ss = 0.0;
-        if (p.stats_in) {
-            for (int i = tid; i < p.n_stats_in; i += kHeadThreads) ss += __ldcg(&p.stats_in[(size_t)m * p.n_stats_in + i].ss);
-        }
+        if (p.stats_in && tid == 0) ss = __ldcg(&p.stats_in[m].ss);
         for (int k = tid; k < p.K; k += kHeadThreads) {
             const float v = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(p.h + (int64_t)m * p.K + k)) << 16);   // L2: written by other SMs
             xs[(size_t)m * p.K + k] = v;
@@ -458,7 +484,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
         sync();
         double tot = 0.0;
         for (int i = 0; i < kHeadThreads / 32; ++i) tot += red_d[i];
-        const float rinv = (float)(1.0 / sqrt(tot / (double)p.K + (double)p.eps));
+        const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn((float)tot, (float)p.K), p.eps)));
         for (int k = tid; k < p.K; k += kHeadThreads)
             xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * __bfloat162float(p.gamma[k]) * rinv);
     }
@@ -522,8 +548,22 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
             const int wi = best_i[w * 8 + tid];
             if (wv > v || (wv == v && wi < i)) { v = wv; i = wi; }
         }
-        p.part_val[cta * 8 + tid] = v;
-        p.part_idx[cta * 8 + tid] = i;
+        if (p.tp.size > 1) {     // the slice's maxima go to slot [rank][cta] of every rank's area
+            const size_t at = ((size_t)p.tp.rank * n_cta + cta) * 8 + tid;
+#pragma unroll 1
+            for (int pr = 0; pr < p.tp.size; ++pr) {
+                reinterpret_cast<float*>(p.tp.area[pr] + p.tp_val_off)[at] = v;
+                reinterpret_cast<int*>(p.tp.area[pr] + p.tp_idx_off)[at] = i;
+            }
+            __threadfence_system();
+        } else {
+            p.part_val[cta * 8 + tid] = v;
+            p.part_idx[cta * 8 + tid] = i;
+        }
+    }
+    if (p.tp.size > 1 && tid < 32) {
+        __syncwarp();            // the M storing threads are lanes of warp 0
+        if (tid == 0) tp_signal(p.tp, p.tp_flag_off);
     }
 }
 

@@ -336,12 +336,16 @@ __global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
     __shared__ int si[256];
     pdl_launch_dependents();
     pdl_wait();
+    if (p.wait.flag) {      // tensor parallel: the maxima of all ranks' vocabulary slices
+        if (threadIdx.x == 0 && !tp_wait(p.wait)) atomicExch(p.error_flag, kErrPeerWait);
+        __syncthreads();
+    }
     for (int m = 0; m < p.M; ++m) {
         float v = -INFINITY;
         int i = 0x7fffffff;
         for (int c = threadIdx.x; c < p.n_part; c += 256) {
-            const float cv = p.part_val[c * 8 + m];
-            const int ci = p.part_idx[c * 8 + m];
+            const float cv = __ldcg(&p.part_val[c * 8 + m]);
+            const int ci = __ldcg(&p.part_idx[c * 8 + m]);
             if (cv > v || (cv == v && ci < i)) { v = cv; i = ci; }
         }
         sv[threadIdx.x] = v; si[threadIdx.x] = i;
@@ -363,6 +367,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
         }
         __syncthreads();
     }
+    if (p.step && threadIdx.x == 0) *p.step += 1;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -16,6 +16,8 @@ enum OutKind : int {
     kOutResidual = 1,    // out[m, n] = bf16(out[m, n] + bf16(acc / a * ws))   (gpu/model.py:237-243)
     kOutGlu = 2,         // rows n and n + N/2 are gate and up: out[m, n] = bf16(bf16(relu(g)^2) * u)
                          // (gpu/model.py:193-195), n < N/2
+    kOutTpPartial = 3,   // row-parallel shard: the exact int32 sums over this rank's K slice go to
+                         // every rank's exchange area; tp_reduce_kernel adds them up and rescales
 };
 
 // Error codes that kernels leave in their error word.
@@ -53,48 +55,114 @@ struct FusedLinearParams {
     int* error_flag;
 };
 
-// Partial statistics of a vector that a producer kernel publishes for the RMSNorm + int8
-// quantisation in front of the next BitLinear: the sum of squares of a slice of the vector
-// and the largest |x * norm weight| in it.  Sums are kept in double precision, which makes
-// the total independent (to the last bit of its f32 rounding, for all practical purposes) of
-// how the vector was cut into slices and of the order in which they are added.
+// Statistics of a vector that its producer kernel accumulates for the RMSNorm + int8
+// quantisation in front of the next BitLinear: the sum of squares of the vector and the largest
+// |x * norm weight| in it.  One slot per token; the producer's CTAs add their shares with
+// atomics (a double-precision add and a max on the bit pattern of a non-negative double), the
+// consumer reads one slot.  The sum is kept in double precision, which makes its f32 rounding
+// independent - for all practical purposes - of the order in which the shares arrive and equal
+// to what a double-precision CPU evaluation gives.  A slot is cleared by the kernel that runs
+// after its consumer.
 struct StatPart {
     double ss;
     double mx;
 };
 
 // ---------------------------------------------------------------------------------------
-// BitLinear of the decode chain (decode_chain.cu): prologue (RMSNorm + int8 quantisation of
-// the input vector) + W2A8 matmul + epilogue (rescale, residual or gate, statistics for the
-// next prologue).  Whole 16-row groups belong to one CTA, so no sums cross CTAs.
+// Tensor parallelism.  Every rank owns an exchange area in its own device memory that the other
+// ranks of the node map through CUDA IPC; producers store into every rank's area (plain peer
+// stores and atomics over NVLink) and then add to an arrival counter there; consumers poll their
+// own counter (bounded) and read their own memory.  No multicast loads, no bulk/TMA copies from
+// peer memory.  Counters only grow: the count a consumer waits for is step * per_step + base,
+// with `step` read from the rank's own step counter on the device, so that a captured CUDA
+// graph can be replayed.
+// ---------------------------------------------------------------------------------------
+constexpr int kMaxTp = 8;
+
+struct TpPeers {
+    int rank, size;                  // size <= 1: no tensor parallelism
+    uint8_t* area[kMaxTp];           // base of every rank's exchange area as mapped in this process
+};
+
+struct TpWait {                      // wait until *flag >= *step * per_step + base
+    const unsigned long long* flag;  // null: nothing to wait for
+    const unsigned long long* step;
+    unsigned long long per_step, base;
+    long long limit_cycles;          // give up after this many SM clock cycles
+};
+
+// ---------------------------------------------------------------------------------------
+// BitLinear of the decode chain (decode_chain.cu): prologue (int8 quantisation of the normalised
+// input vector) + W2A8 matmul + epilogue (rescale, residual or gate, and what the next prologue
+// needs).  Whole 16-row groups belong to one CTA, so no sums cross CTAs.
+//
+// The input arrives as t[m, k] = x[m, k] * g[k] in f32 (x the bf16 activation, g the weight of
+// the RMSNorm in front of this BitLinear, both factors bf16 values, so the product is exact)
+// with the statistics of x; the kernel computes r = rsqrt(mean(x^2) + eps), xn = bf16(t * r),
+// a = 127 / max|xn|, y = rint(xn * a) - the arithmetic of prologue.cuh - without touching x or g.
 // ---------------------------------------------------------------------------------------
 struct ChainLinearParams {
     const uint8_t* w2t;
     int N, K, k_tiles;
     int n_units, n_sub, sub_stride;  // unit u = row groups u + s * sub_stride, s < n_sub (2 for kOutGlu)
     int units_max;                   // most units a CTA owns
+    int units_base, units_rem;       // CTA c owns units_base units, one more if c < units_rem
     int grid, M, ring_stages;
-    int src, out_kind;
+    int out_kind;
     // source
-    const __nv_bfloat16* x;          // kSrcVector [M, ldx]
-    int64_t ldx;
-    const int64_t* tokens;           // kSrcEmbedding
-    const __nv_bfloat16* emb;
-    __nv_bfloat16* h_copy;           // [M, K]
-    int vocab;
-    const __nv_bfloat16* gamma;      // RMSNorm weight [K], null = no norm
+    const float* t;                  // [M, ldt]
+    int64_t ldt;
+    const StatPart* stats_in;        // [M]
+    int k_norm;                      // length of the whole normalised vector (K; more for a K slice)
     float eps;
-    const StatPart* stats_in;        // [M][n_stats_in] from the producer of x, null = computed here
-    int n_stats_in;
+    TpWait stats_wait;               // tensor parallel: statistics that other ranks contribute to
+    StatPart* zero_slot;             // [M] slot to clear (its consumer ran before this kernel), or null
     // output
-    __nv_bfloat16* out;              // [M, ldo]
+    __nv_bfloat16* out;              // [M, ldo] (kOutBf16: written; kOutResidual: updated in place; others: unused)
     int64_t ldo;
     ScaleSegments seg;
     float ws[8];                     // weight scale per segment
-    const __nv_bfloat16* gamma_out;  // norm weight of the next prologue over `out`, with stats_out
-    StatPart* stats_out;             // [M][n_units] or null
+    const __nv_bfloat16* gamma_out;  // with t_out and stats_out: the norm weight of the next prologue over the output
+    float* t_out;                    // [M, ldt_out] = output * gamma_out
+    int64_t ldt_out;
+    StatPart* stats_out;             // [M] slot the output's statistics are added to (in every rank's area when tp.size > 1)
+    // tensor parallel
+    TpPeers tp;
+    size_t tp_stats_off, tp_stats_flag_off;   // kOutGlu: statistics slot and arrival counter in every area
+    size_t tp_part_off, tp_part_flag_off;     // kOutTpPartial: int32 [size][M][N] and arrival counter in every area
+    float* a_out;                    // kOutTpPartial: [M] activation scales for the reduction kernel
     int* error_flag;
     unsigned long long* trace;       // phase timestamps of CTA 0 (only in builds with BITNET_TRACE)
+};
+
+// First kernel of a step: h[m] = embedding row of tokens[m]; t[m] = h[m] * gamma; statistics of h[m].
+struct EmbedParams {
+    const int64_t* tokens;
+    const __nv_bfloat16* emb;
+    const __nv_bfloat16* gamma;      // attention_norm of layer 0
+    __nv_bfloat16* h;                // [M, K]
+    float* t;                        // [M, K]
+    StatPart* stats_out;             // [M], written (not added to)
+    StatPart* zero_slot;             // [M] or null
+    int M, K, vocab;
+    int* error_flag;
+};
+
+// Second half of a row-parallel BitLinear: out[m, n] = bf16(out[m, n] + bf16(sum_r part[r][m][n] / a[m] * ws)),
+// t_out = out * gamma_out and the statistics of out.  One CTA of 256 threads per 256 rows.
+struct TpReduceParams {
+    const int32_t* part;             // [T][M][N] in this rank's exchange area
+    TpWait wait;
+    const float* a;                  // [M]
+    float ws;
+    __nv_bfloat16* out;              // [M, ldo], updated in place
+    int64_t ldo;
+    const __nv_bfloat16* gamma_out;
+    float* t_out;                    // [M, ldo]
+    StatPart* stats_out;             // [M], added to
+    StatPart* zero_slot;
+    int M, N, T;
+    int* error_flag;
 };
 
 struct AttentionParams {
@@ -109,8 +177,12 @@ struct AttentionParams {
     float* part_ml;                  // [B, H, S, 2]
     int* counters;                   // [B, Hkv], zero between launches
     int H, Hkv, D, L, S;
-    const __nv_bfloat16* gamma_out;  // norm weight over `out` (per sequence: H*D values), with stats_out
-    StatPart* stats_out;             // [B][H] or null
+    const __nv_bfloat16* gamma_out;  // norm weight over `out` (per sequence: H*D values), with t_out and stats_out
+    float* t_out;                    // [B, H*D] = out * gamma_out, or null
+    StatPart* stats_out;             // [B] slot the statistics of a sequence's output are added to
+    StatPart* zero_slot;             // [B] slot to clear, or null
+    TpPeers tp;                      // tensor parallel: the statistics go to the slot at this offset of every area
+    size_t tp_stats_off, tp_stats_flag_off;
     __nv_bfloat16* tap;              // optional second copy of `out` (for checkers)
     int* error_flag;
     unsigned long long* trace;
@@ -121,13 +193,14 @@ struct HeadParams {
     const __nv_bfloat16* gamma;      // final RMSNorm weight
     float eps;
     const __nv_bfloat16* h;          // [M, K]
-    const StatPart* stats_in;        // [M][n_stats_in] or null (sum of squares computed here)
-    int n_stats_in;
+    const StatPart* stats_in;        // [M] or null (sum of squares computed here)
     float* logits;                   // [M, V] or null
     float* part_val;                 // [grid, 8]
     int* part_idx;
     int M, K, V;
     int row_offset;                  // added to the reported indices (vocabulary slice of a rank)
+    TpPeers tp;                      // tensor parallel: the per-CTA maxima go to [size][grid][8] of every area
+    size_t tp_val_off, tp_idx_off, tp_flag_off;
 };
 
 struct ArgmaxParams {
@@ -137,6 +210,9 @@ struct ArgmaxParams {
     int64_t* out;
     int64_t* tokens;
     int64_t* pos;
+    TpWait wait;                     // tensor parallel: the maxima of all ranks
+    unsigned long long* step;        // this rank's step counter, incremented here (may be null)
+    int* error_flag;
 };
 
 void plan_linear(FusedLinearParams& p, int n_sm);
@@ -150,6 +226,8 @@ size_t chain_attention_smem(const AttentionParams& p);
 int prepare_chain_kernels(size_t smem_optin);
 int launch_chain_linear(const ChainLinearParams& p, cudaStream_t stream, bool pdl);
 int launch_chain_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl);
+int launch_tp_reduce(const TpReduceParams& p, cudaStream_t stream, bool pdl);
+int launch_embed(const EmbedParams& p, cudaStream_t stream, bool pdl);
 
 size_t attention_smem(const AttentionParams& p);
 size_t head_smem(const HeadParams& p);

@@ -121,6 +121,30 @@ int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream) {
     return launch_fused_linear(p, stream, false);
 }
 
+// Layout of a rank's exchange area (the same on every rank).
+struct TpLayout {
+    size_t flag_att, flag_o, flag_glu, flag_2, flag_head;   // arrival counters, one 128-byte line each
+    size_t stats;                                           // [n_layers][2][batch] StatPart: attention output, gated values
+    size_t part_o, part_2;                                  // int32 [size][batch][dim]
+    size_t head_val, head_idx;                              // [size][grid][8]
+    size_t total;
+};
+static TpLayout tp_layout(const bitnet_decoder_config& c, int size, int head_grid) {
+    TpLayout L{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
+    L.flag_att = take(128); L.flag_o = take(128); L.flag_glu = take(128); L.flag_2 = take(128); L.flag_head = take(128);
+    L.stats = take((size_t)c.n_layers * 2 * c.batch * sizeof(StatPart));
+    L.part_o = take((size_t)size * c.batch * c.dim * 4);
+    L.part_2 = take((size_t)size * c.batch * c.dim * 4);
+    L.head_val = take((size_t)size * head_grid * 8 * 4);
+    L.head_idx = take((size_t)size * head_grid * 8 * 4);
+    L.total = off;
+    return L;
+}
+constexpr long long kPeerWaitCyclesDefault = 600000000LL;   // about 0.3 s
+constexpr int kTpHeadGridMax = 256;     // upper bound of the output head's grid used for sizing the area
+
 struct Decoder {
     bitnet_decoder_config cfg{};
     std::vector<bitnet_decoder_layer> layers;
@@ -131,14 +155,25 @@ struct Decoder {
     int device = 0, n_sm = 0, kv_splits = 1, head_grid = 0;
     void* scratch = nullptr;
     int *attn_counters = nullptr, *error_flag = nullptr, *part_idx = nullptr;
-    __nv_bfloat16 *h = nullptr, *xqkv = nullptr, *attn_out = nullptr, *glu = nullptr;
-    StatPart *stats_h = nullptr, *stats_att = nullptr, *stats_glu = nullptr;
+    __nv_bfloat16 *h = nullptr, *xqkv = nullptr, *attn_out = nullptr;
+    float *t_h = nullptr, *t_att = nullptr, *t_glu = nullptr;   // x * (next norm weight), f32
+    StatPart* stats = nullptr;                    // [1 + 4 * n_layers][batch] statistics slots
     float *part_o = nullptr, *part_ml = nullptr, *part_val = nullptr;
     unsigned long long* trace = nullptr;          // [n_layers * 5][16] phase timestamps (builds with BITNET_TRACE)
     __nv_bfloat16* attn_tap = nullptr;            // optional [n_layers][batch][dim] copy of the attention outputs
     ChainLinearParams plan_qkv{}, plan_o{}, plan_13{}, plan_2{};
-    int64_t steps_enqueued = 0;                   // host mirror of the positions' advance (bounds check)
+    // tensor parallel (tp.size > 1): cfg holds the whole model's sizes, `loc` this rank's share
+    TpPeers tp{};
+    bitnet_decoder_config loc{};
+    unsigned long long* step_ctr = nullptr;       // steps this decoder has completed (device)
+    float *a_o = nullptr, *a_2 = nullptr;         // activation scales handed from wo / w2 to their reductions
+    long long wait_limit = kPeerWaitCyclesDefault;  // SM cycles a kernel waits for another rank before it gives up
+
+    // statistics slots: 0 = embedding; per layer: attention output, h after wo, gated values, h after w2
+    StatPart* slot_emb() const { return stats; }
+    StatPart* slot(int layer, int which) const { return stats + (size_t)(1 + 4 * layer + which) * cfg.batch; }
 };
+enum { kSlotAtt = 0, kSlotHo = 1, kSlotGlu = 2, kSlotH2 = 3 };
 
 static size_t align_up(size_t x) { return (x + 255) / 256 * 256; }
 
@@ -153,22 +188,40 @@ int bitnet_init(void) {
     return workspace() ? kOk : bitnet_last_status();
 }
 
-static void layer_params(const Decoder* d, int l, const int64_t* tokens, const int64_t* pos, ChainLinearParams lin[4],
-                         AttentionParams* ap);
 static HeadParams head_params(const Decoder* d, float* logits);
 
-void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
-                            const void* tok_embeddings, const void* norm, const void* output, const float* rope) {
+static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers, const void* tok_embeddings,
+                            const void* norm, const void* output, const float* rope, int rank, int size,
+                            void* const* areas) {
     set_status(kOk);
     if (!cfg || !layers || !tok_embeddings || !norm || !output || !rope) return set_status(kBadArgument), nullptr;
-    const int B = cfg->batch, D = cfg->head_dim, H = cfg->n_heads, Hkv = cfg->n_kv_heads;
-    if (B < 1 || B > 8 || cfg->n_layers < 1 || H < 1 || Hkv < 1 || H % Hkv != 0 || H / Hkv > 16 || D % 4 != 0 ||
-        D > 128 || cfg->dim % 8 != 0 || cfg->dim != H * D || cfg->ffn_dim % 16 != 0 || cfg->max_seq_len < 2 ||
-        cfg->vocab_size < 1)
+    if (size < 1 || size > kMaxTp || rank < 0 || rank >= size || (size > 1 && !areas)) return set_status(kBadArgument), nullptr;
+    const int B = cfg->batch, D = cfg->head_dim;
+    if (B < 1 || B > 8 || cfg->n_layers < 1 || cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->n_heads % cfg->n_kv_heads != 0 ||
+        cfg->n_heads / cfg->n_kv_heads > 16 || D % 4 != 0 || D > 128 || cfg->dim % 8 != 0 || cfg->dim != cfg->n_heads * D ||
+        cfg->ffn_dim % 16 != 0 || cfg->max_seq_len < 2 || cfg->vocab_size < 1)
+        return set_status(kUnsupported), nullptr;
+    // this rank's share: whole kv-head groups, a slice of the feed-forward width and of the vocabulary
+    if (cfg->n_kv_heads % size != 0 || cfg->ffn_dim % (16 * size) != 0 || cfg->vocab_size % size != 0 ||
+        (cfg->n_heads / size * D) % 8 != 0)
         return set_status(kUnsupported), nullptr;
     Decoder* d = new (std::nothrow) Decoder();
     if (!d) return set_status(kBadArgument), nullptr;
     d->cfg = *cfg;
+    d->loc = *cfg;
+    d->loc.n_heads = cfg->n_heads / size;
+    d->loc.n_kv_heads = cfg->n_kv_heads / size;
+    d->loc.ffn_dim = cfg->ffn_dim / size;
+    d->loc.vocab_size = cfg->vocab_size / size;
+    d->tp.rank = rank;
+    d->tp.size = size;
+    for (int r = 0; r < size && size > 1; ++r) {
+        if (!areas[r]) {
+            delete d;
+            return set_status(kBadArgument), nullptr;
+        }
+        d->tp.area[r] = static_cast<uint8_t*>(areas[r]);
+    }
     d->layers.assign(layers, layers + cfg->n_layers);
     d->emb = static_cast<const __nv_bfloat16*>(tok_embeddings);
     d->final_norm = static_cast<const __nv_bfloat16*>(norm);
@@ -180,27 +233,31 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         return nullptr;
     }
     d->n_sm = prop.multiProcessorCount;
+    const int H = d->loc.n_heads, Hkv = d->loc.n_kv_heads, F = d->loc.ffn_dim;
     int s = d->n_sm / (Hkv * B);
     d->kv_splits = s < 1 ? 1 : (s > 16 ? 16 : s);
-    d->head_grid = d->n_sm;
+    d->head_grid = d->n_sm < kTpHeadGridMax ? d->n_sm : kTpHeadGridMax;
 
-    const int dim = cfg->dim, F = cfg->ffn_dim, Nqkv = (H + 2 * Hkv) * D;
-    auto plan = [&](ChainLinearParams& p, int N, int K, int src, int out_kind, const void* gamma_probe) {
+    const int dim = cfg->dim, Nqkv = (H + 2 * Hkv) * D, Ko = H * D;
+    auto plan = [&](ChainLinearParams& p, int N, int K, int k_norm, int out_kind) {
         p = ChainLinearParams{};
-        p.N = N; p.K = K; p.src = src; p.out_kind = out_kind; p.M = B; p.eps = cfg->norm_eps;
-        p.gamma = static_cast<const __nv_bfloat16*>(gamma_probe);   // only whether there is one matters for the layout
+        p.N = N; p.K = K; p.k_norm = k_norm; p.out_kind = out_kind; p.M = B; p.eps = cfg->norm_eps;
         p.ring_stages = 4;
+#ifdef BITNET_TRACE
+        if (getenv("BITNET_RING_STAGES")) p.ring_stages = atoi(getenv("BITNET_RING_STAGES"));   // measurement builds only
+#endif
         plan_chain_linear(p, d->n_sm);
     };
-    plan(d->plan_qkv, Nqkv, dim, kSrcVector, kOutBf16, norm);
-    plan(d->plan_o, dim, dim, kSrcVector, kOutResidual, norm);
-    plan(d->plan_13, 2 * F, dim, kSrcVector, kOutGlu, norm);
-    plan(d->plan_2, dim, F, kSrcVector, kOutResidual, norm);
+    const bool tp = size > 1;
+    plan(d->plan_qkv, Nqkv, dim, dim, kOutBf16);
+    plan(d->plan_o, dim, Ko, dim, tp ? kOutTpPartial : kOutResidual);
+    plan(d->plan_13, 2 * F, dim, dim, kOutGlu);
+    plan(d->plan_2, dim, F, cfg->ffn_dim, tp ? kOutTpPartial : kOutResidual);
 
     AttentionParams ap{};
     ap.H = H; ap.Hkv = Hkv; ap.D = D; ap.S = d->kv_splits;
     HeadParams hp{};
-    hp.M = B; hp.K = dim; hp.V = cfg->vocab_size;
+    hp.M = B; hp.K = dim; hp.V = d->loc.vocab_size;
     size_t lin_smem = 0;
     for (const ChainLinearParams* p : {&d->plan_qkv, &d->plan_o, &d->plan_13, &d->plan_2})
         lin_smem = chain_linear_smem(*p) > lin_smem ? chain_linear_smem(*p) : lin_smem;
@@ -217,11 +274,10 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     // one zero-initialised scratch allocation
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return o; };
-    const size_t o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_h = take((size_t)B * dim * 2),
-                 o_qkv = take((size_t)B * Nqkv * 2), o_att = take((size_t)B * dim * 2), o_glu = take((size_t)B * F * 2),
-                 o_sh = take((size_t)B * d->plan_o.n_units * sizeof(StatPart)),
-                 o_sa = take((size_t)B * H * sizeof(StatPart)),
-                 o_sg = take((size_t)B * d->plan_13.n_units * sizeof(StatPart)),
+    const size_t o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_step = take(8), o_ao = take((size_t)B * 4),
+                 o_a2 = take((size_t)B * 4), o_h = take((size_t)B * dim * 2), o_qkv = take((size_t)B * Nqkv * 2),
+                 o_att = take((size_t)B * Ko * 2), o_th = take((size_t)B * dim * 4), o_tatt = take((size_t)B * Ko * 4),
+                 o_tglu = take((size_t)B * F * 4), o_st = take((size_t)(1 + 4 * cfg->n_layers) * B * sizeof(StatPart)),
                  o_po = take((size_t)B * H * d->kv_splits * D * 4),
                  o_pml = take((size_t)B * H * d->kv_splits * 2 * 4), o_pv = take((size_t)d->head_grid * 8 * 4),
                  o_pi = take((size_t)d->head_grid * 8 * 4), o_tr = take((size_t)cfg->n_layers * 5 * 16 * 8);
@@ -232,13 +288,16 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     uint8_t* base = static_cast<uint8_t*>(d->scratch);
     d->attn_counters = reinterpret_cast<int*>(base + o_actr);
     d->error_flag = reinterpret_cast<int*>(base + o_err);
+    d->step_ctr = reinterpret_cast<unsigned long long*>(base + o_step);
+    d->a_o = reinterpret_cast<float*>(base + o_ao);
+    d->a_2 = reinterpret_cast<float*>(base + o_a2);
     d->h = reinterpret_cast<__nv_bfloat16*>(base + o_h);
     d->xqkv = reinterpret_cast<__nv_bfloat16*>(base + o_qkv);
     d->attn_out = reinterpret_cast<__nv_bfloat16*>(base + o_att);
-    d->glu = reinterpret_cast<__nv_bfloat16*>(base + o_glu);
-    d->stats_h = reinterpret_cast<StatPart*>(base + o_sh);
-    d->stats_att = reinterpret_cast<StatPart*>(base + o_sa);
-    d->stats_glu = reinterpret_cast<StatPart*>(base + o_sg);
+    d->t_h = reinterpret_cast<float*>(base + o_th);
+    d->t_att = reinterpret_cast<float*>(base + o_tatt);
+    d->t_glu = reinterpret_cast<float*>(base + o_tglu);
+    d->stats = reinterpret_cast<StatPart*>(base + o_st);
     d->part_o = reinterpret_cast<float*>(base + o_po);
     d->part_ml = reinterpret_cast<float*>(base + o_pml);
     d->part_val = reinterpret_cast<float*>(base + o_pv);
@@ -247,31 +306,90 @@ void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     return d;
 }
 
-// Parameter blocks of layer l: lin[0..3] = wqkv, wo, w13, w2 and the attention between the
-// first two.
-static void layer_params(const Decoder* d, int l, const int64_t* tokens, const int64_t* pos, ChainLinearParams lin[4],
-                         AttentionParams* ap) {
+void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
+                            const void* tok_embeddings, const void* norm, const void* output, const float* rope) {
+    return decoder_create(cfg, layers, tok_embeddings, norm, output, rope, 0, 1, nullptr);
+}
+
+void* bitnet_decoder_create_tp(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
+                               const void* tok_embeddings, const void* norm, const void* output_slice, const float* rope,
+                               int rank, int size, void* const* areas) {
+    return decoder_create(cfg, layers, tok_embeddings, norm, output_slice, rope, rank, size, areas);
+}
+
+size_t bitnet_tp_area_bytes(const bitnet_decoder_config* cfg, int size) {
+    if (!cfg || size < 1 || size > kMaxTp) return 0;
+    return tp_layout(*cfg, size, kTpHeadGridMax).total;
+}
+
+int bitnet_tp_area_create(size_t bytes, void** area, void* ipc_handle_64) {
+    set_status(kOk);
+    if (!area || !ipc_handle_64 || bytes == 0) return set_status(kBadArgument), kBadArgument;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is handed over as 64 bytes");
+    void* p = nullptr;
+    if (check_cuda(cudaMalloc(&p, bytes)) || check_cuda(cudaMemset(p, 0, bytes))) return kCudaError;
+    cudaIpcMemHandle_t h;
+    if (check_cuda(cudaIpcGetMemHandle(&h, p))) {
+        cudaFree(p);
+        return kCudaError;
+    }
+    memcpy(ipc_handle_64, &h, 64);
+    *area = p;
+    return kOk;
+}
+
+int bitnet_tp_area_open(const void* ipc_handle_64, void** peer_area) {
+    set_status(kOk);
+    if (!ipc_handle_64 || !peer_area) return set_status(kBadArgument), kBadArgument;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle_64, 64);
+    return check_cuda(cudaIpcOpenMemHandle(peer_area, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int bitnet_tp_area_close(void* peer_area) {
+    set_status(kOk);
+    return peer_area ? check_cuda(cudaIpcCloseMemHandle(peer_area)) : kOk;
+}
+
+int bitnet_tp_area_free(void* area) {
+    set_status(kOk);
+    return area ? check_cuda(cudaFree(area)) : kOk;
+}
+
+// Parameter blocks of layer l: lin[0..3] = wqkv, wo, w13, w2, the attention between the first
+// two and, under tensor parallelism, the reductions behind wo and w2.  Every producer hands its
+// output on as t = output * (weight of the norm in front of the consumer) with the output's
+// statistics in a slot; a slot is cleared by the kernel that runs after its consumer.
+static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinearParams lin[4], AttentionParams* ap,
+                         TpReduceParams red[2]) {
     const bitnet_decoder_config& c = d->cfg;
-    const int D = c.head_dim, H = c.n_heads, Hkv = c.n_kv_heads, dim = c.dim, F = c.ffn_dim;
-    const int Nqkv = (H + 2 * Hkv) * D;
+    const int D = c.head_dim, H = d->loc.n_heads, Hkv = d->loc.n_kv_heads, dim = c.dim, F = d->loc.ffn_dim;
+    const int Nqkv = (H + 2 * Hkv) * D, Ko = H * D;
+    const int T = d->tp.size, rank = d->tp.rank;
+    const bool tp = T > 1;
+    const TpLayout lay = tp_layout(c, T, kTpHeadGridMax);
     const bitnet_decoder_layer& L = d->layers[l];
     const bool last = l + 1 == c.n_layers;
-    auto common = [&](ChainLinearParams& p, const void* w, const void* gamma) {
-        p.w2t = static_cast<const uint8_t*>(w);
-        p.gamma = static_cast<const __nv_bfloat16*>(gamma);
-        p.error_flag = d->error_flag;
+    const unsigned long long nl = (unsigned long long)c.n_layers;
+    auto bf = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
+    uint8_t* my = tp ? d->tp.area[rank] : nullptr;
+    auto area_slot = [&](int which) { return lay.stats + ((size_t)(2 * l + which) * c.batch) * sizeof(StatPart); };
+    auto wait_on = [&](size_t flag_off, unsigned long long per_layer) {
+        TpWait w{};
+        w.flag = reinterpret_cast<const unsigned long long*>(my + flag_off);
+        w.step = d->step_ctr;
+        w.per_step = nl * per_layer;
+        w.base = (unsigned long long)(l + 1) * per_layer;
+        w.limit_cycles = d->wait_limit;
+        return w;
     };
-    // wqkv: (embedding ->) h -> attention_norm -> wqkv -> xqkv
+    // wqkv: t_h (= h * attention_norm) -> xqkv
     ChainLinearParams& q = lin[0];
     q = d->plan_qkv;
-    common(q, L.wqkv, L.attention_norm);
-    if (l == 0) {
-        q.src = kSrcEmbedding;
-        q.tokens = tokens; q.emb = d->emb; q.h_copy = d->h; q.vocab = c.vocab_size;
-    } else {
-        q.x = d->h; q.ldx = dim;
-        q.stats_in = d->stats_h; q.n_stats_in = d->plan_o.n_units;
-    }
+    q.w2t = static_cast<const uint8_t*>(L.wqkv); q.error_flag = d->error_flag;
+    q.t = d->t_h; q.ldt = dim;
+    q.stats_in = l == 0 ? d->slot_emb() : d->slot(l - 1, kSlotH2);
+    if (!tp) q.zero_slot = d->slot(l == 0 ? c.n_layers - 1 : l - 1, kSlotGlu);     // its consumer, w2, has run
     q.out = d->xqkv; q.ldo = Nqkv;
     q.seg.n_seg = 3; q.seg.end[0] = H * D; q.seg.end[1] = (H + Hkv) * D; q.seg.end[2] = Nqkv;
     q.ws[0] = L.s_q; q.ws[1] = L.s_k; q.ws[2] = L.s_v;
@@ -281,72 +399,137 @@ static void layer_params(const Decoder* d, int l, const int64_t* tokens, const i
     ap->cache_k = static_cast<__nv_bfloat16*>(L.cache_k); ap->cache_v = static_cast<__nv_bfloat16*>(L.cache_v);
     ap->out = d->attn_out; ap->part_o = d->part_o; ap->part_ml = d->part_ml; ap->counters = d->attn_counters;
     ap->H = H; ap->Hkv = Hkv; ap->D = D; ap->L = c.max_seq_len; ap->S = d->kv_splits;
-    ap->gamma_out = static_cast<const __nv_bfloat16*>(L.attn_sub_norm); ap->stats_out = d->stats_att;
-    ap->tap = d->attn_tap ? d->attn_tap + (size_t)l * c.batch * dim : nullptr;
+    ap->gamma_out = bf(L.attn_sub_norm) + (size_t)rank * Ko; ap->t_out = d->t_att; ap->stats_out = d->slot(l, kSlotAtt);
+    ap->zero_slot = l == 0 ? nullptr : d->slot(l - 1, kSlotH2);           // its consumer, this layer's wqkv, has run
+    ap->tap = d->attn_tap ? d->attn_tap + (size_t)l * c.batch * Ko : nullptr;
     ap->error_flag = d->error_flag;
+    if (tp) {     // all ranks' wo normalise over all heads
+        ap->tp = d->tp; ap->tp_stats_off = area_slot(0); ap->tp_stats_flag_off = lay.flag_att;
+    }
 
-    // wo: attention output -> attn_sub_norm -> wo -> h += ...   (statistics for ffn_norm)
+    // wo: t_att (= attention output * attn_sub_norm) -> h += ...; t_h = h * ffn_norm
     ChainLinearParams& o = lin[1];
     o = d->plan_o;
-    common(o, L.wo, L.attn_sub_norm);
-    o.x = d->attn_out; o.ldx = dim;
-    o.stats_in = d->stats_att; o.n_stats_in = H;
-    o.out = d->h; o.ldo = dim;
+    o.w2t = static_cast<const uint8_t*>(L.wo); o.error_flag = d->error_flag;
+    o.t = d->t_att; o.ldt = Ko;
     o.seg.n_seg = 1; o.seg.end[0] = dim; o.ws[0] = L.s_o;
-    o.gamma_out = static_cast<const __nv_bfloat16*>(L.ffn_norm); o.stats_out = d->stats_h;
+    if (!tp) {
+        o.stats_in = d->slot(l, kSlotAtt);
+        o.out = d->h; o.ldo = dim;
+        o.gamma_out = bf(L.ffn_norm); o.t_out = d->t_h; o.ldt_out = dim; o.stats_out = d->slot(l, kSlotHo);
+    } else {
+        o.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(0));
+        o.stats_wait = wait_on(lay.flag_att, (unsigned long long)c.batch * c.n_heads);
+        o.tp = d->tp; o.tp_part_off = lay.part_o; o.tp_part_flag_off = lay.flag_o; o.a_out = d->a_o;
+        TpReduceParams& r = red[0];
+        r = TpReduceParams{};
+        r.part = reinterpret_cast<const int32_t*>(my + lay.part_o);
+        r.wait = wait_on(lay.flag_o, (unsigned long long)T * d->plan_o.grid);
+        r.a = d->a_o; r.ws = L.s_o; r.out = d->h; r.ldo = dim;
+        r.gamma_out = bf(L.ffn_norm); r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotHo);
+        r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(0));     // its consumer, wo, has run
+        r.M = c.batch; r.N = dim; r.T = T; r.error_flag = d->error_flag;
+    }
 
-    // w13: h -> ffn_norm -> w13 -> relu(x1)^2 * x3   (statistics for ffn_sub_norm)
+    // w13: t_h -> relu(x1)^2 * x3; t_glu = that * ffn_sub_norm
     ChainLinearParams& u = lin[2];
     u = d->plan_13;
-    common(u, L.w13, L.ffn_norm);
-    u.x = d->h; u.ldx = dim;
-    u.stats_in = d->stats_h; u.n_stats_in = d->plan_o.n_units;
-    u.out = d->glu; u.ldo = F;
+    u.w2t = static_cast<const uint8_t*>(L.w13); u.error_flag = d->error_flag;
+    u.t = d->t_h; u.ldt = dim;
+    u.stats_in = d->slot(l, kSlotHo);
+    if (!tp) u.zero_slot = d->slot(l, kSlotAtt);                          // its consumer, wo, has run
     u.seg.n_seg = 2; u.seg.end[0] = F; u.seg.end[1] = 2 * F; u.ws[0] = L.s_1; u.ws[1] = L.s_3;
-    u.gamma_out = static_cast<const __nv_bfloat16*>(L.ffn_sub_norm); u.stats_out = d->stats_glu;
+    u.gamma_out = bf(L.ffn_sub_norm) + (size_t)rank * F; u.t_out = d->t_glu; u.ldt_out = F; u.stats_out = d->slot(l, kSlotGlu);
+    if (tp) {     // all ranks' w2 normalise over the whole gated vector
+        u.tp = d->tp; u.tp_stats_off = area_slot(1); u.tp_stats_flag_off = lay.flag_glu;
+    }
 
-    // w2: gated values -> ffn_sub_norm -> w2 -> h += ...   (statistics for the next layer's
-    // attention_norm, or for the final norm)
+    // w2: t_glu -> h += ...; t_h = h * (the next layer's attention_norm, or the final norm)
     ChainLinearParams& w = lin[3];
     w = d->plan_2;
-    common(w, L.w2, L.ffn_sub_norm);
-    w.x = d->glu; w.ldx = F;
-    w.stats_in = d->stats_glu; w.n_stats_in = d->plan_13.n_units;
-    w.out = d->h; w.ldo = dim;
+    w.w2t = static_cast<const uint8_t*>(L.w2); w.error_flag = d->error_flag;
+    w.t = d->t_glu; w.ldt = F;
+    w.zero_slot = d->slot(l, kSlotHo);                                    // its consumer, w13, has run
     w.seg.n_seg = 1; w.seg.end[0] = dim; w.ws[0] = L.s_2;
-    w.gamma_out = last ? d->final_norm : static_cast<const __nv_bfloat16*>(d->layers[l + 1].attention_norm);
-    w.stats_out = d->stats_h;
+    const __nv_bfloat16* g_next = last ? d->final_norm : bf(d->layers[l + 1].attention_norm);
+    if (!tp) {
+        w.stats_in = d->slot(l, kSlotGlu);
+        w.out = d->h; w.ldo = dim;
+        w.gamma_out = g_next; w.t_out = d->t_h; w.ldt_out = dim; w.stats_out = d->slot(l, kSlotH2);
+    } else {
+        w.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(1));
+        w.stats_wait = wait_on(lay.flag_glu, (unsigned long long)T * d->plan_13.grid);
+        w.tp = d->tp; w.tp_part_off = lay.part_2; w.tp_part_flag_off = lay.flag_2; w.a_out = d->a_2;
+        TpReduceParams& r = red[1];
+        r = TpReduceParams{};
+        r.part = reinterpret_cast<const int32_t*>(my + lay.part_2);
+        r.wait = wait_on(lay.flag_2, (unsigned long long)T * d->plan_2.grid);
+        r.a = d->a_2; r.ws = L.s_2; r.out = d->h; r.ldo = dim;
+        r.gamma_out = g_next; r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotH2);
+        r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(1));     // its consumer, w2, has run
+        r.M = c.batch; r.N = dim; r.T = T; r.error_flag = d->error_flag;
+    }
 }
 
 static HeadParams head_params(const Decoder* d, float* logits) {
     HeadParams hp{};
     hp.w = d->output; hp.gamma = d->final_norm; hp.eps = d->cfg.norm_eps;
     hp.h = d->h; hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
-    hp.stats_in = d->stats_h; hp.n_stats_in = d->plan_2.n_units;
-    hp.M = d->cfg.batch; hp.K = d->cfg.dim; hp.V = d->cfg.vocab_size;
+    hp.stats_in = d->slot(d->cfg.n_layers - 1, kSlotH2);
+    hp.M = d->cfg.batch; hp.K = d->cfg.dim; hp.V = d->loc.vocab_size;
+    if (d->tp.size > 1) {
+        const TpLayout lay = tp_layout(d->cfg, d->tp.size, kTpHeadGridMax);
+        hp.row_offset = d->tp.rank * d->loc.vocab_size;
+        hp.tp = d->tp; hp.tp_val_off = lay.head_val; hp.tp_idx_off = lay.head_idx; hp.tp_flag_off = lay.flag_head;
+    }
     return hp;
 }
 
 static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out, float* logits, cudaStream_t stream,
                         bool linears_only) {
     const bitnet_decoder_config& c = d->cfg;
+    const bool tp = d->tp.size > 1;
+    if (tp && linears_only) return set_status(kUnsupported), kUnsupported;
+    EmbedParams ep{};
+    ep.tokens = tokens; ep.emb = d->emb; ep.gamma = static_cast<const __nv_bfloat16*>(d->layers[0].attention_norm);
+    ep.h = d->h; ep.t = d->t_h; ep.stats_out = d->slot_emb();
+    ep.zero_slot = d->slot(c.n_layers - 1, kSlotH2);        // its consumer, the previous step's output head, has run
+    ep.M = c.batch; ep.K = c.dim; ep.vocab = c.vocab_size; ep.error_flag = d->error_flag;
+    if (launch_embed(ep, stream, true)) return bitnet_last_status();
     for (int l = 0; l < c.n_layers; ++l) {
         ChainLinearParams lin[4];
         AttentionParams ap;
-        layer_params(d, l, tokens, pos, lin, &ap);
+        TpReduceParams red[2];
+        layer_params(d, l, pos, lin, &ap, red);
 #ifdef BITNET_TRACE
         for (int j = 0; j < 4; ++j) lin[j].trace = d->trace + 16 * (4 * l + j);
 #endif
         if (launch_chain_linear(lin[0], stream, true)) return bitnet_last_status();
         if (!linears_only && launch_chain_attention(ap, c.batch, stream, true)) return bitnet_last_status();
-        for (int j = 1; j < 4; ++j)
-            if (launch_chain_linear(lin[j], stream, true)) return bitnet_last_status();
+        if (launch_chain_linear(lin[1], stream, true)) return bitnet_last_status();
+        if (tp && launch_tp_reduce(red[0], stream, true)) return bitnet_last_status();
+        if (launch_chain_linear(lin[2], stream, true)) return bitnet_last_status();
+        if (launch_chain_linear(lin[3], stream, true)) return bitnet_last_status();
+        if (tp && launch_tp_reduce(red[1], stream, true)) return bitnet_last_status();
     }
     if (linears_only) return kOk;
     if (launch_head(head_params(d, logits), d->head_grid, stream, true)) return bitnet_last_status();
     ArgmaxParams am{};
     am.part_val = d->part_val; am.part_idx = d->part_idx; am.n_part = d->head_grid; am.M = c.batch;
-    am.out = out; am.tokens = tokens; am.pos = pos;
+    am.out = out; am.tokens = tokens; am.pos = pos; am.error_flag = d->error_flag;
+    am.step = d->step_ctr;
+    if (tp) {
+        const TpLayout lay = tp_layout(c, d->tp.size, kTpHeadGridMax);
+        uint8_t* my = d->tp.area[d->tp.rank];
+        am.part_val = reinterpret_cast<const float*>(my + lay.head_val);
+        am.part_idx = reinterpret_cast<const int*>(my + lay.head_idx);
+        am.n_part = d->tp.size * d->head_grid;
+        am.wait.flag = reinterpret_cast<const unsigned long long*>(my + lay.flag_head);
+        am.wait.step = d->step_ctr;
+        am.wait.per_step = (unsigned long long)d->tp.size * d->head_grid;
+        am.wait.base = am.wait.per_step;
+        am.wait.limit_cycles = d->wait_limit;
+    }
     return launch_argmax(am, stream, true);
 }
 
@@ -381,10 +564,21 @@ int bitnet_decoder_error_flag(void* dec) {
 int bitnet_decoder_clear_error(void* dec) {
     Decoder* d = static_cast<Decoder*>(dec);
     if (!d) return set_status(kBadArgument), kBadArgument;
-    // the kernels of the chain keep no state between launches besides the attention tickets
-    if (check_cuda(cudaMemset(d->error_flag, 0, sizeof(int))) ||
-        check_cuda(cudaMemset(d->attn_counters, 0, (size_t)d->cfg.batch * d->cfg.n_kv_heads * sizeof(int))))
+    // the state the kernels of the chain keep between launches: the attention tickets and the
+    // statistics slots (a step that ended early may have left shares in them)
+    if (check_cuda(cudaDeviceSynchronize()) || check_cuda(cudaMemset(d->error_flag, 0, sizeof(int))) ||
+        check_cuda(cudaMemset(d->attn_counters, 0, (size_t)d->cfg.batch * d->cfg.n_kv_heads * sizeof(int))) ||
+        check_cuda(cudaMemset(d->stats, 0, (size_t)(1 + 4 * d->cfg.n_layers) * d->cfg.batch * sizeof(StatPart))))
         return kCudaError;
+    return kOk;
+}
+
+int bitnet_decoder_set_wait_limit(void* dec, double milliseconds) {
+    Decoder* d = static_cast<Decoder*>(dec);
+    if (!d || !(milliseconds > 0.0)) return set_status(kBadArgument), kBadArgument;
+    cudaDeviceProp prop;
+    if (check_cuda(cudaGetDeviceProperties(&prop, d->device))) return kCudaError;
+    d->wait_limit = (long long)(milliseconds * (double)prop.clockRate);   // clockRate is in kHz: cycles per millisecond
     return kOk;
 }
 
@@ -411,7 +605,7 @@ int bitnet_decoder_read_trace(void* dec, unsigned long long* host_out, int n_val
 int bitnet_decoder_kernels_per_step(void* dec) {
     Decoder* d = static_cast<Decoder*>(dec);
     if (!d) return 0;
-    return 5 * d->cfg.n_layers + 2;
+    return (d->tp.size > 1 ? 7 : 5) * d->cfg.n_layers + 3;
 }
 
 void bitnet_decoder_destroy(void* dec) {

@@ -58,10 +58,10 @@ __device__ __forceinline__ bool aligned16(const void* p, int64_t ld_elems, int e
     return ((reinterpret_cast<uintptr_t>(p) & 15) == 0) && ((ld_elems * elem_bytes) % 16 == 0);
 }
 
-// Sum of `ss` (double) and max of `mx` over the 256 threads in one round (two barriers).
-// `sd` holds 8 doubles, `sf` 8 floats.
-template <class Sync>
-__device__ __forceinline__ void reduce_stats_256(double& ss, float& mx, double* sd, float* sf, int tid, Sync sync) {
+// Sum of `ss` (double) and max of `mx` over NT threads in one round (two barriers).
+// `sd` holds NT / 32 doubles, `sf` NT / 32 floats.
+template <int NT, class Sync>
+__device__ __forceinline__ void reduce_stats(double& ss, float& mx, double* sd, float* sf, int tid, Sync sync) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -76,23 +76,24 @@ __device__ __forceinline__ void reduce_stats_256(double& ss, float& mx, double* 
     ss = sd[0];
     mx = sf[0];
 #pragma unroll
-    for (int i = 1; i < kPrologueThreads / 32; ++i) {
+    for (int i = 1; i < NT / 32; ++i) {
         ss += sd[i];
         mx = fmaxf(mx, sf[i]);
     }
 }
 
 // ---- the arithmetic of one token, shared by every kernel that quantises activations ----------
-// t = x * g (f32); r = (float)(1 / sqrt(mean(x^2) + eps)) with the mean and the root in double
-// precision; xn = bf16(t * r); a = 127 / max(max|xn|, 1e-5); y = clamp(rint(xn * a), -128, 127).
+// t = x * g (f32); r = 1 / sqrt(sum(x^2) / K + eps) with the sum accumulated in double precision,
+// rounded to f32 once, and the rest in correctly rounded f32 operations; xn = bf16(t * r);
+// a = 127 / max(max|xn|, 1e-5); y = clamp(rint(xn * a), -128, 127).
 // Because rounding and multiplication by r > 0 are monotone, max|xn| = bf16(max|t| * r), so one
 // reduction round (sum of squares and max|t| together) and two passes over the values suffice.
 //
 // The sum of squares is accumulated in double precision (B200 runs it at half the f32 rate, and
 // a token has a few thousand values): its f32 rounding then does not depend on the order of the
 // additions, so every kernel - whatever its thread count, and however a producer kernel cut the
-// vector into slices - derives the same r, and r equals what a double-precision CPU evaluation
-// gives.  A quantiser turns a last-bit difference in r into different int8 values; this removes
+// vector into slices - derives the same r, and r equals what the CPU checker derives from a
+// double-precision sum.  A quantiser turns a last-bit difference in r into different int8 values; this removes
 // that source of divergence between kernels, between GPUs of a tensor-parallel group, and
 // between the GPU and the CPU checker.
 
@@ -106,7 +107,9 @@ __device__ __forceinline__ void group_stats(const Vec8& x, const Vec8& g, bool u
 }
 // From the reduced statistics to the normalisation factor and the activation scale.
 __device__ __forceinline__ void finish_stats(double ss, float mt, int K, float eps, bool use_g, float& rinv, float& a) {
-    rinv = use_g ? (float)(1.0 / sqrt(ss / (double)K + (double)eps)) : 1.f;
+    // the sum rounded to f32 once, then IEEE f32 operations (each correctly rounded, so a CPU
+    // evaluation in f32 gives the same bits): r = 1 / sqrt(sum / K + eps)
+    rinv = use_g ? __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn((float)ss, (float)K), eps))) : 1.f;
     const float amax = use_g ? bf16_round(mt * rinv) : mt;
     a = 127.0f / fmaxf(amax, 1e-5f);
 }
@@ -149,7 +152,7 @@ __device__ __forceinline__ void norm_quant_row(const __nv_bfloat16* xv, int K, i
 #pragma unroll 1
     for (int v = tid; v < n_vec; v += kPrologueThreads)
         group_stats(unpack_bf16x8(*reinterpret_cast<const uint4*>(xv + v * 8)), load_g(v), use_g, ss, mt);
-    reduce_stats_256(ss, mt, sd, sf, tid, sync);
+    reduce_stats<kPrologueThreads>(ss, mt, sd, sf, tid, sync);
     float rinv, a;
     finish_stats(ss, mt, K, eps, use_g, rinv, a);
     int sy_i = 0;

@@ -106,7 +106,11 @@ class TPDecoder:
     computes exactly what `model.build_synthetic(args, seed)` computes."""
 
     def __init__(self, args: ModelArgs, seed: int, rank: int, world: int, device, backend: str = "kernel",
-                 max_seq_len: int = 4096, group=None):
+                 max_seq_len: int = 4096, group=None, fast_random: bool = False):
+        """fast_random=True (for benchmarks of large models): every shard is drawn directly as
+        uniform ternary values with a fixed scale, seeded by (seed, layer, tensor, rank), instead
+        of being cut out of the ternarised whole matrix; the shards of different tp degrees then
+        do not make up the same model, which a throughput measurement does not need."""
         assert args.n_heads % world == 0 and args.n_kv_heads % world == 0, "heads must divide by the tp degree"
         assert args.ffn_dim % world == 0 and args.vocab_size % world == 0
         D = args.head_dim
@@ -129,16 +133,27 @@ class TPDecoder:
         self.final_norm = RMSNorm(args.dim, args.norm_eps).to(device)
         self.layers = []
         r = rank
+
+        def _rows(n, k, s, device, rows, cols=slice(None)):
+            if not fast_random:
+                return _ternary_rows(n, k, s, device, rows, cols)
+            nl = len(range(*rows.indices(n)))
+            kl = len(range(*cols.indices(k)))
+            g2 = torch.Generator(device=device)
+            g2.manual_seed(s * 131 + rank)
+            return (torch.randint(-1, 2, (nl, kl), generator=g2, device=device, dtype=torch.int8),
+                    torch.tensor([0.8], dtype=torch.bfloat16, device=device))
+
         for i in range(args.n_layers):
             qs, ks = slice(r * self.Hl * D, (r + 1) * self.Hl * D), slice(r * self.Hkvl * D, (r + 1) * self.Hkvl * D)
-            q_p, s_q = _ternary_rows(args.n_heads * D, args.dim, _seed(seed, i, 0, 0), device, qs)
-            k_p, s_k = _ternary_rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 1), device, ks)
-            v_p, s_v = _ternary_rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 2), device, ks)
-            wo_p, s_o = _ternary_rows(args.dim, args.n_heads * D, _seed(seed, i, 1, 0), device, slice(None), qs)
+            q_p, s_q = _rows(args.n_heads * D, args.dim, _seed(seed, i, 0, 0), device, qs)
+            k_p, s_k = _rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 1), device, ks)
+            v_p, s_v = _rows(args.n_kv_heads * D, args.dim, _seed(seed, i, 0, 2), device, ks)
+            wo_p, s_o = _rows(args.dim, args.n_heads * D, _seed(seed, i, 1, 0), device, slice(None), qs)
             fs = slice(r * Fl, (r + 1) * Fl)
-            g_p, s_1 = _ternary_rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 0), device, fs)
-            u_p, s_3 = _ternary_rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 1), device, fs)
-            w2_p, s_2 = _ternary_rows(args.dim, args.ffn_dim, _seed(seed, i, 3, 0), device, slice(None), fs)
+            g_p, s_1 = _rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 0), device, fs)
+            u_p, s_3 = _rows(args.ffn_dim, args.dim, _seed(seed, i, 2, 1), device, fs)
+            w2_p, s_2 = _rows(args.dim, args.ffn_dim, _seed(seed, i, 3, 0), device, slice(None), fs)
             norms = {}
             for name, nd in (("attention_norm", args.dim), ("ffn_norm", args.dim), ("attn_sub_norm", args.dim),
                              ("ffn_sub_norm", args.ffn_dim)):
@@ -282,3 +297,114 @@ class GraphedStep:
 
     def replay(self):
         self.graph.replay()
+
+
+class TPFusedStep:
+    """The tensor-parallel decode step inside the library (`bitnet_decoder_create_tp`): the
+    chain of fused kernels of `generate.FusedDecoder`, with the shards of a `TPDecoder`
+    (backend "kernel").  The ranks exchange through device memory mapped with CUDA IPC - the
+    statistics of the row-parallel BitLinears' inputs and their exact int32 partial sums - inside
+    the kernels; no collective library call is part of a step.  `group` is only used to hand
+    the IPC handles round when the step is built.  Bit-identical to the same class with one rank.
+
+    tokens int64 [B, 1] and pos int64 [B] live on the device and are advanced by the step;
+    `out` holds the chosen ids.  Every rank must build it and call `step()` in step."""
+
+    def __init__(self, dec: "TPDecoder", batch: int, max_seq_len: int, group=None, wait_limit_ms: Optional[float] = None,
+                 absent_peers: bool = False):
+        """absent_peers=True (for tests of the bounded waits): the other ranks' exchange areas are
+        plain buffers of this process that nobody ever writes to, and no process group is used."""
+        import ctypes
+
+        from . import _lib
+        from .generate import _DecoderConfig, _DecoderLayer
+
+        assert dec.backend == "kernel" and 1 <= batch <= 8
+        a, dev = dec.args, dec.device
+        self.dec, self.batch, self.max_seq_len = dec, batch, max_seq_len
+        self.cache = dec.make_cache(batch, max_seq_len)
+        self.tokens = torch.zeros((batch, 1), dtype=torch.int64, device=dev)
+        self.pos = torch.zeros((batch,), dtype=torch.int64, device=dev)
+        self.out = torch.zeros((batch,), dtype=torch.int64, device=dev)
+        cfg = _DecoderConfig(a.dim, a.n_layers, a.n_heads, a.n_kv_heads, a.head_dim, a.ffn_dim, a.vocab_size,
+                             a.norm_eps, batch, max_seq_len)
+        L = _lib.lib
+        world, rank = dec.world, dec.rank
+        self._area, self._peers = None, []
+        areas = (ctypes.c_void_p * max(world, 1))()
+        if world > 1:
+            nbytes = L.bitnet_tp_area_bytes(ctypes.byref(cfg), world)
+            area, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            _lib.check(L.bitnet_tp_area_create(nbytes, ctypes.byref(area), handle))
+            self._area = area
+            handles = [None] * world
+            if not absent_peers:
+                dist.all_gather_object(handles, handle.raw, group=group)
+            self._stand_ins = []
+            for r in range(world):
+                if r == rank:
+                    areas[r] = area.value
+                elif absent_peers:
+                    p, h2 = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                    _lib.check(L.bitnet_tp_area_create(nbytes, ctypes.byref(p), h2))
+                    self._stand_ins.append(p)
+                    areas[r] = p.value
+                else:
+                    p = ctypes.c_void_p()
+                    _lib.check(L.bitnet_tp_area_open(handles[r], ctypes.byref(p)))
+                    self._peers.append(p)
+                    areas[r] = p.value
+        layers = (_DecoderLayer * a.n_layers)()
+        self.rope = dec.rope[:max_seq_len].contiguous()
+        for i, (lay, (ck, cv)) in enumerate(zip(dec.layers, self.cache)):
+            S = layers[i]
+            S.wqkv, S.wo, S.w13, S.w2 = (lay["wqkv"].weight.data_ptr(), lay["wo"].weight.data_ptr(),
+                                         lay["w13"].weight.data_ptr(), lay["w2"].weight.data_ptr())
+            S.s_q, S.s_k, S.s_v = (float(x) for x in lay["wqkv"].scale.tolist())
+            S.s_o = float(lay["wo"].scale[0])
+            S.s_1, S.s_3 = (float(x) for x in lay["w13"].scale.tolist())
+            S.s_2 = float(lay["w2"].scale[0])
+            S.attention_norm = lay["attention_norm"].weight.data_ptr()
+            S.attn_sub_norm = lay["attn_sub_norm"].weight.data_ptr()
+            S.ffn_norm = lay["ffn_norm"].weight.data_ptr()
+            S.ffn_sub_norm = lay["ffn_sub_norm"].weight.data_ptr()
+            S.cache_k, S.cache_v = ck.data_ptr(), cv.data_ptr()
+        self.handle = L.bitnet_decoder_create_tp(ctypes.byref(cfg), layers, dec.emb.data_ptr(),
+                                                 dec.final_norm.weight.data_ptr(), dec.out_w.data_ptr(),
+                                                 self.rope.data_ptr(), rank, world, areas)
+        if not self.handle:
+            _lib.check()
+            raise _lib.BitnetError("bitnet_decoder_create_tp failed")
+        if wait_limit_ms is not None:
+            _lib.check(L.bitnet_decoder_set_wait_limit(self.handle, float(wait_limit_ms)))
+        if world > 1 and not absent_peers:
+            dist.barrier(group=group)       # every rank has mapped every area before anybody steps
+        self._lib = _lib
+        self.kernels_per_step = L.bitnet_decoder_kernels_per_step(self.handle)
+
+    def step(self, logits: Optional[torch.Tensor] = None):
+        """Enqueues one decode step on the current stream (may be captured in a CUDA graph)."""
+        _lib = self._lib
+        _lib.check(_lib.lib.bitnet_decoder_step(self.handle, _lib.ptr(self.tokens), _lib.ptr(self.pos), _lib.ptr(self.out),
+                                                _lib.ptr(logits), _lib.stream_ptr()))
+
+    def error_flag(self) -> int:
+        return self._lib.lib.bitnet_decoder_error_flag(self.handle)
+
+    def close(self):
+        h, self.handle = getattr(self, "handle", None), None
+        if h:
+            self._lib.lib.bitnet_decoder_destroy(h)
+        for p in getattr(self, "_peers", []):
+            self._lib.lib.bitnet_tp_area_close(p)
+        self._peers = []
+        for p in getattr(self, "_stand_ins", []):
+            self._lib.lib.bitnet_tp_area_free(p)
+        self._stand_ins = []
+        if getattr(self, "_area", None):
+            self._lib.lib.bitnet_tp_area_free(self._area)
+            self._area = None
+
+    def __del__(self):
+        if getattr(self, "_lib", None) is not None and getattr(self._lib, "lib", None) is not None:
+            self.close()

@@ -180,6 +180,38 @@ int bitnet_decoder_clear_error(void* decoder);
 /* Number of kernels one step launches. */
 int bitnet_decoder_kernels_per_step(void* decoder);
 void bitnet_decoder_destroy(void* decoder);
+/* ---- tensor-parallel decode: one process per GPU of one node ----------------------------
+ * The reference has no multi-GPU path (gpu/generate.py:324-326 fixes local_rank = 0); this is
+ * the partition its fused layout invites (gpu/model.py:103-118 names the per-rank head counts):
+ * wqkv and w13 are split over their output rows (whole kv-head groups; matching gate and up
+ * rows), wo and w2 over their input columns.  A rank gives its own shards in `layers` - wqkv
+ * [(H/size + 2 Hkv/size) D, dim], wo [dim, H/size D], w13 [2 F/size, dim] (gate rows, then up
+ * rows), w2 [dim, F/size], norm weights whole, its slice of the KV cache [batch, max_seq_len,
+ * Hkv/size, D] - and rows [rank V/size, (rank+1) V/size) of the output projection; `cfg` holds
+ * the sizes of the whole model.  The ranks exchange through device memory mapped with CUDA IPC:
+ * every rank creates one exchange area (bitnet_tp_area_create), passes the 64-byte handle to
+ * the others by any host channel, opens theirs (bitnet_tp_area_open) and hands all `size`
+ * pointers, its own at index `rank`, to bitnet_decoder_create_tp.  Per layer a step then
+ * exchanges the statistics of the attention output and of the gated vector (one slot per
+ * token, added to with atomics over NVLink) and the exact int32 partial sums of wo and w2
+ * (plain peer stores), each followed by an arrival counter that the consumer polls with a
+ * bounded wait; the greedy choice exchanges one (value, index) pair per CTA of the output head.
+ * Results are bit-identical to a single GPU's.  bitnet_decoder_step / _step_sync / _error_flag
+ * (code 6: an exchange did not arrive in time) / _destroy work as for a single GPU; all ranks
+ * must enqueue the same steps. */
+size_t bitnet_tp_area_bytes(const bitnet_decoder_config* cfg, int size);
+int bitnet_tp_area_create(size_t bytes, void** area, void* ipc_handle_64);
+int bitnet_tp_area_open(const void* ipc_handle_64, void** peer_area);
+int bitnet_tp_area_close(void* peer_area);
+int bitnet_tp_area_free(void* area);
+void* bitnet_decoder_create_tp(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,
+                               const void* tok_embeddings, const void* norm, const void* output_slice, const float* rope,
+                               int rank, int size, void* const* areas);
+/* How long a kernel of a tensor-parallel decoder waits for another rank's contribution before it
+ * gives up, records code 6 in the error word and carries on so that the step ends (default about
+ * 300 ms).  Takes effect for steps enqueued (or captured) afterwards. */
+int bitnet_decoder_set_wait_limit(void* decoder, double milliseconds);
+
 /* The error word of the workspace behind the stand-alone entry points (bitlinear_int8xint2,
  * bitnet_linear_w2a8, bitnet_attention_decode) on the current device, same codes (3: a bounded
  * wait of the tensor-core kernel ran out); clear != 0 resets it together with the workspace's

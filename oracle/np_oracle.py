@@ -48,10 +48,14 @@ def act_quant(x: np.ndarray):
 
 def rmsnorm(x: np.ndarray, g: np.ndarray, eps: float = 1e-5):
     """RMSNorm as the reference's decode model applies it before each BitLinear
-    (gpu/model.py:159-160,195-196,237-242): (x * g) * rsqrt(mean(x^2) + eps), in f32."""
+    (gpu/model.py:159-160,195-196,237-242): (x * g) * rsqrt(mean(x^2) + eps) in f32.  The
+    sum of squares is taken in f64 (so that it does not depend on the order of addition) and
+    rounded to f32 once; the mean, the root and the reciprocal are IEEE f32 operations."""
     x = np.asarray(x, dtype=np.float32)
-    ms = (x.astype(np.float64) ** 2).mean(axis=-1, keepdims=True)
-    return (x * g.astype(np.float32) * (1.0 / np.sqrt(ms + eps)).astype(np.float32)).astype(np.float32)
+    ss = (x.astype(np.float64) ** 2).sum(axis=-1, keepdims=True).astype(np.float32)
+    v = (ss / np.float32(x.shape[-1])).astype(np.float32) + np.float32(eps)
+    r = (np.float32(1.0) / np.sqrt(v.astype(np.float32))).astype(np.float32)
+    return (x * g.astype(np.float32) * r).astype(np.float32)
 
 
 def to_bf16(x: np.ndarray) -> np.ndarray:

@@ -137,7 +137,7 @@ def test_convert_checkpoint_scale_assembly_and_model_equivalence():
         b = f"layers.{i}."
         state[b + "attention.wqkv.weight"] = torch.randn((args.n_heads + 2 * args.n_kv_heads) * hd, d, generator=g)
         state[b + "attention.wo.weight"] = torch.randn(d, d, generator=g) * 0.3
-        state[b + "feed_forward.w13.weight"] = torch.randn(2 * F, d, generator=g) * 2.0
+        state[b + "feed_forward.w13.weight"] = torch.cat([torch.randn(F, d, generator=g) * 2.0, torch.randn(F, d, generator=g) * 0.5])
         state[b + "feed_forward.w2.weight"] = torch.randn(d, F, generator=g)
         for nm, n in (("attention_norm", d), ("ffn_norm", d), ("attention.attn_sub_norm", d), ("feed_forward.ffn_sub_norm", F)):
             state[b + nm + ".weight"] = (1 + 0.1 * torch.randn(n, generator=g)).bfloat16()

@@ -58,6 +58,50 @@ def greedy_loop(graph):
             outs.append(nxt.clone())
     return torch.stack(outs)
 assert torch.equal(greedy_loop(True), greedy_loop(False))
+
+# the in-library step (peer-memory exchange inside the kernels, no collective call in the step):
+# logits and tokens bit-identical to the same step on one rank, eagerly and replayed from a graph
+from bitnet_b200.tensor_parallel import TPFusedStep
+def fused_loop(dec, graph, steps=12):
+    st = TPFusedStep(dec, 2, 64)
+    g = torch.Generator().manual_seed(8)
+    st.tokens.copy_(torch.randint(0, args.vocab_size, (2, 1), generator=g).cuda())
+    st.pos.zero_()
+    Vl = args.vocab_size // dec.world
+    logits = torch.zeros((2, Vl), dtype=torch.float32, device="cuda")
+    toks, lgs = [], []
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        if graph:
+            st.step(logits); stream.synchronize()
+            st.tokens.copy_(torch.randint(0, args.vocab_size, (2, 1), generator=torch.Generator().manual_seed(8)).cuda()); st.pos.zero_()
+            for c in st.cache:
+                c[0].zero_(); c[1].zero_()
+            cg = torch.cuda.CUDAGraph()
+            stream.synchronize()
+            if dec.world > 1: dist.barrier()
+            with torch.cuda.graph(cg, stream=stream):
+                st.step(logits)
+        for s in range(steps):
+            if graph: cg.replay()
+            else: st.step(logits)
+            stream.synchronize()
+            toks.append(st.out.clone()); lgs.append(logits.clone())
+    assert st.error_flag() == 0
+    out = torch.stack(toks), torch.stack(lgs)
+    if dec.world > 1: dist.barrier()
+    st.close()
+    return out
+t2, l2 = fused_loop(dec_tp, False)
+t2g, l2g = fused_loop(dec_tp, True)
+assert torch.equal(t2, t2g) and torch.equal(l2, l2g)
+gathered = [torch.zeros_like(l2) for _ in range(world)]
+dist.all_gather(gathered, l2)
+if rank == 0:
+    t1, l1 = fused_loop(TPDecoder(args, 7, 0, 1, "cuda", backend="kernel", max_seq_len=64), False)
+    assert torch.equal(t2, t1), (t2, t1)
+    assert torch.equal(torch.cat(gathered, dim=-1), l1), float((torch.cat(gathered, dim=-1) - l1).abs().max())
+    print("TP_FUSED_OK")
 if rank == 0:
     one = run(TPDecoder(args, 7, 0, 1, "cuda", backend="kernel", max_seq_len=64))
     assert torch.equal(tp[0], one[0]), float((tp[0] - one[0]).abs().max())
@@ -79,4 +123,27 @@ def test_two_rank_nccl_equals_single_gpu(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                        capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.returncode == 0 and "TP_OK" in r.stdout and "TP_FUSED_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_bounded_wait_for_an_absent_rank_returns_an_error_status():
+    """A tensor-parallel step whose peer never contributes must end by itself: the kernels' waits
+    for the other rank run out (here after 2 ms each), the decoder's error word holds code 6, the
+    call returns, and the GPU keeps working (a single-GPU decoder gives its usual bits)."""
+    from bitnet_b200.generate import Generator
+    from bitnet_b200.model import build_synthetic, preset
+    from bitnet_b200.tensor_parallel import TPDecoder, TPFusedStep
+
+    args = preset("tiny", n_heads=4, n_kv_heads=2, ffn_dim=512)
+    dec = TPDecoder(args, 3, 0, 2, "cuda", backend="kernel", max_seq_len=32)    # rank 0 of 2; rank 1 does not exist
+    st = TPFusedStep(dec, 1, 32, wait_limit_ms=2.0, absent_peers=True)
+    st.tokens.fill_(5)
+    st.step()
+    torch.cuda.synchronize()
+    assert st.error_flag() == 6
+    st.close()
+    model = build_synthetic(preset("tiny"), seed=5, device="cuda", max_seq_len=32)
+    prompt = torch.randint(0, 512, (1, 6), device="cuda", generator=torch.Generator("cuda").manual_seed(2))
+    a = Generator(model, 1, 32, use_cuda_graph=False, fused=True).generate(prompt, 8)
+    b = Generator(model, 1, 32, use_cuda_graph=True, fused=True).generate(prompt, 8)
+    assert torch.equal(a, b)
