@@ -279,14 +279,15 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     if (real) { CHAIN_STAMP(3) }
 
     // ---- matmul over the staged tiles ----------------------------------------------------
-    // Per tile a lane holds the A fragments of rows g, g+8 for four m16n8k32 MMAs: each of its
-    // four words is split into its four 2-bit fields by AND masks alone (field j stays scaled by
-    // 4^j and has its own accumulator).  Tokens are the MMA's 8 columns, so any M <= 8 costs the
-    // same.  Within a round (two ring stages, up to 64 tiles) each warp takes one contiguous run.
+    // Per tile a lane holds the weights of rows g, g+8 in columns 32q .. 32q+31: four words whose
+    // four 2-bit fields are separated by AND masks alone (field j stays scaled by 4^j and has its
+    // own accumulator, folded by exact shifts at the end).  One token: eight dp4a per field pair
+    // against the lane's 32 activation bytes (cheaper than tensor-core MMAs that would leave seven
+    // of eight columns empty).  Two to eight tokens: four m16n8k32 MMAs per tile with the tokens as
+    // the MMA's columns, so that any such M costs the same.
     const int g = lane >> 2, q = lane & 3;
-    const int8_t* y_lane = sm.ys + (size_t)(g < p.M ? g : p.M) * y_stride + 32 * q;
-    constexpr int kRoundTiles = kCRoundStages * kCStageTiles;
-    const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
+    const bool one_token = p.M == 1;
+    const int8_t* y_lane = sm.ys + (size_t)((one_token || g < p.M) ? (one_token ? 0 : g) : p.M) * y_stride + 32 * q;
     int acc[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -301,73 +302,122 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #define TR_BEGIN
 #define TR_END(x)
 #endif
+    // n consecutive tiles, the first one local tile number t_first at `tile` (this lane's 16 bytes)
+    auto run_tiles = [&](const uint8_t* tile, int n, int t_first) {
+        int lg = t_first / p.k_tiles, kt = t_first - lg * p.k_tiles;
 #pragma unroll 1
-    for (int r = 0; r < n_rounds && !gave_up; ++r) {
-        const int nr_t = min(kRoundTiles, n_tiles - r * kRoundTiles);
-        const int lo_t = nr_t * warp / kCWarps;
-        const int hi_t = nr_t * (warp + 1) / kCWarps;
-        const int c0 = r * kCRoundStages;                    // first chunk of the round
-        if (hi_t > lo_t && real) {
-            bool ok = true;
-            TR_BEGIN
-#pragma unroll 1
-            for (int ls = lo_t / kCStageTiles; ls <= (hi_t - 1) / kCStageTiles; ++ls)
-                ok = ok && mbar_wait(&sm.full_bar[(c0 + ls) & s_mask], ((c0 + ls) / p.ring_stages) & 1);
-            TR_END(tr_wait)
-            if (!ok) {   // gave up: flag it, leave together below
-                if (lane == 0) {
-                    atomicExch(p.error_flag, kErrConsumerWait);
-                    sm.flag_s[0] = 1;
+        for (int i = 0; i < n; ++i, tile += kTileBytes) {
+            const uint4 wc = *reinterpret_cast<const uint4*>(tile);
+            const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
+            const uint4 y0 = yp[0], y1 = yp[1];
+            const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+            const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
+            if (one_token) {
+                // acc[j][0], acc[j][1]: rows g, g+8 of field j, summed over this lane's columns
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t msk = 0x03030303u << (2 * j);
+                    acc[j][0] = dp4a_u8s8(w[0] & msk, b[2 * j], acc[j][0]);
+                    acc[j][1] = dp4a_u8s8(w[1] & msk, b[2 * j], acc[j][1]);
+                    acc[j][0] = dp4a_u8s8(w[2] & msk, b[2 * j + 1], acc[j][0]);
+                    acc[j][1] = dp4a_u8s8(w[3] & msk, b[2 * j + 1], acc[j][1]);
                 }
-                gave_up = true;
-            }
-        }
-        if (r == 0 && real) { CHAIN_STAMP(9) }
-        if (!gave_up && hi_t > lo_t) {
-            // the two stages of a round are adjacent in the ring (ring_stages is even)
-            const uint8_t* tile = sm.ring + (c0 & s_mask) * kCStageBytes + lo_t * kTileBytes + lane * 16;
-            int t = r * kRoundTiles + lo_t;                  // local tile number
-            int lg = t / p.k_tiles, kt = t - lg * p.k_tiles;
-#pragma unroll 1
-            for (int i = lo_t; i < hi_t; ++i, tile += kTileBytes) {
-                const uint4 wc = *reinterpret_cast<const uint4*>(tile);
-                const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
-                const uint4 y0 = yp[0], y1 = yp[1];
-                const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-                const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
+            } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t msk = 0x03030303u << (2 * j);
                     mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
                 }
-                if (++kt == p.k_tiles || i + 1 == hi_t) {
-                    // end of this row group's tiles in the run: the warp's sums into the CTA's accumulator
-                    TR_BEGIN
-                    int* dst = sm.sacc + lg * 128;
+            }
+            if (++kt == p.k_tiles || i + 1 == n) {
+                // end of this row group's tiles in the run: the warp's sums into the CTA's accumulator
+                TR_BEGIN
+                int* dst = sm.sacc + lg * 128;
+                if (one_token) {
+                    int v0 = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
+                    int v1 = acc[0][1] + (acc[1][1] >> 2) + (acc[2][1] >> 4) + (acc[3][1] >> 6);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+                    if (q == 0) {
+                        atomicAdd(&dst[g * 8], v0);
+                        atomicAdd(&dst[(g + 8) * 8], v1);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { acc[j][0] = 0; acc[j][1] = 0; }
+                } else {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int tok = 2 * q + (e & 1);
                         const int v = acc[0][e] + (acc[1][e] >> 2) + (acc[2][e] >> 4) + (acc[3][e] >> 6);
-                        if (tok < p.M && real) atomicAdd(&dst[(g + 8 * (e >> 1)) * 8 + tok], v);
+                        if (tok < p.M) atomicAdd(&dst[(g + 8 * (e >> 1)) * 8 + tok], v);
                         acc[0][e] = 0; acc[1][e] = 0; acc[2][e] = 0; acc[3][e] = 0;
                     }
-                    TR_END(tr_flush)
-                    if (kt == p.k_tiles) {
-                        kt = 0;
-                        ++lg;
-                    }
+                }
+                TR_END(tr_flush)
+                if (kt == p.k_tiles) {
+                    kt = 0;
+                    ++lg;
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0 && !gave_up && real) {
-            // This warp is done with every stage of the round.  It releases a stage only after
-            // having seen that stage's copy complete (usually it has, long ago), so that no warp
-            // ever waits for a later fill of a stage whose earlier fill it has not observed.
+    };
+    if (n_chunks <= p.ring_stages) {
+        // The CTA's whole share sits in the ring (the usual case up to a few billion parameters):
+        // every warp takes one contiguous run of it, nothing is released or refilled.
+        const int lo_t = n_tiles * warp / kCWarps, hi_t = n_tiles * (warp + 1) / kCWarps;
+        if (hi_t > lo_t) {
+            bool ok = true;
+            TR_BEGIN
 #pragma unroll 1
-            for (int ls = 0; ls < kCRoundStages; ++ls) {
-                const int c = c0 + ls;
-                if (c < n_chunks && mbar_wait(&sm.full_bar[c & s_mask], (c / p.ring_stages) & 1)) mbar_arrive(&sm.empty_bar[c & s_mask]);
+            for (int c = lo_t / kCStageTiles; c <= (hi_t - 1) / kCStageTiles; ++c) ok = ok && mbar_wait(&sm.full_bar[c], 0);
+            TR_END(tr_wait)
+            CHAIN_STAMP(9)
+            if (ok) {
+                run_tiles(sm.ring + lo_t * kTileBytes + lane * 16, hi_t - lo_t, lo_t);
+            } else if (lane == 0) {
+                atomicExch(p.error_flag, kErrConsumerWait);
+                sm.flag_s[0] = 1;
+            }
+        }
+    } else {
+        // Larger shares stream through the ring in rounds of two stages (up to 64 tiles); within
+        // a round each warp takes one contiguous run.
+        constexpr int kRoundTiles = kCRoundStages * kCStageTiles;
+        const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
+#pragma unroll 1
+        for (int r = 0; r < n_rounds && !gave_up; ++r) {
+            const int nr_t = min(kRoundTiles, n_tiles - r * kRoundTiles);
+            const int lo_t = nr_t * warp / kCWarps, hi_t = nr_t * (warp + 1) / kCWarps;
+            const int c0 = r * kCRoundStages;                    // first chunk of the round
+            if (hi_t > lo_t) {
+                bool ok = true;
+                TR_BEGIN
+#pragma unroll 1
+                for (int ls = lo_t / kCStageTiles; ls <= (hi_t - 1) / kCStageTiles; ++ls)
+                    ok = ok && mbar_wait(&sm.full_bar[(c0 + ls) & s_mask], ((c0 + ls) / p.ring_stages) & 1);
+                TR_END(tr_wait)
+                if (!ok) {   // gave up: flag it, leave together below
+                    if (lane == 0) {
+                        atomicExch(p.error_flag, kErrConsumerWait);
+                        sm.flag_s[0] = 1;
+                    }
+                    gave_up = true;
+                }
+            }
+            if (r == 0) { CHAIN_STAMP(9) }
+            // the two stages of a round are adjacent in the ring (ring_stages is even)
+            if (!gave_up && hi_t > lo_t)
+                run_tiles(sm.ring + (c0 & s_mask) * kCStageBytes + lo_t * kTileBytes + lane * 16, hi_t - lo_t, r * kRoundTiles + lo_t);
+            __syncwarp();
+            if (lane == 0 && !gave_up) {
+                // This warp is done with every stage of the round.  It releases a stage only after
+                // having seen that stage's copy complete (usually it has, long ago), so that no warp
+                // ever waits for a later fill of a stage whose earlier fill it has not observed.
+#pragma unroll 1
+                for (int ls = 0; ls < kCRoundStages; ++ls) {
+                    const int c = c0 + ls;
+                    if (c < n_chunks && mbar_wait(&sm.full_bar[c & s_mask], (c / p.ring_stages) & 1)) mbar_arrive(&sm.empty_bar[c & s_mask]);
+                }
             }
         }
     }
