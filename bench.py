@@ -19,7 +19,9 @@ token per sequence) through the whole model.  One JSON line is printed by rank 0
 
 With N > 1 every rank runs an independent replica of the same workload (weak scaling; the
 2B architecture has 5 KV heads, which no tensor-parallel degree of 2, 4 or 8 divides) and
-the time is the maximum over ranks.
+the time is the maximum over ranks.  The line then also carries a `tp` object: the 8B and the
+~100B architectures decoded tensor-parallel over the N GPUs by the in-library step (peer-memory
+exchange inside the kernels), with their fraction of the aggregate HBM roofline.
 """
 from __future__ import annotations
 
@@ -55,12 +57,11 @@ def parse_args():
     ap.add_argument("--sweep-only", default="", metavar="N,K,M",
                     help="run only the isolated BitLinear call for one shape and token count (for profilers) and exit")
     ap.add_argument("--tp", action="store_true",
-                    help="shard one model tensor-parallel over the ranks (strong scaling) instead of replicas; "
-                         "needs head counts divisible by the rank count (8b, 100b presets)")
-    ap.add_argument("--no-graph", action="store_true", help="with --tp: issue the step op by op instead of replaying a graph")
-    ap.add_argument("--graph", action="store_true",
-                    help="with --tp on several ranks: replay the step (collectives included) from a CUDA graph; the "
-                         "default there is op by op")
+                    help="only the tensor-parallel measurement of --workload (8b, 100b) over the ranks, as its own line")
+    ap.add_argument("--tp-engine", choices=["fused", "nccl"], default="fused",
+                    help="with --tp: the in-library step (peer-memory exchange inside the kernels) or the op-by-op "
+                         "decoder with NCCL collectives (the bring-up arm)")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tp object of a multi-GPU run")
     ap.add_argument("--layers", type=int, default=0, help="use only the first LAYERS layers (0 = all): a small case for profilers, or with --tp")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="tokens in the KV cache when decode starts (with --tp)")
     return ap.parse_args()
@@ -251,31 +252,142 @@ def kernel_sweep(dev, peak_gbs, shapes=None, ms=None):
     return rows
 
 
-def decode_batch(model, args_model, dev, batch, steps, warmup):
-    """Decode tokens/s at a larger batch through the op-by-op path (tcgen05 BitLinear kernel,
-    library attention), captured in a CUDA graph; device-resident."""
+def reference_gpu_kernel_us(dev):
+    """The reference's own GPU kernel (its gpu/bitnet_kernels source built with its own command
+    line as compute_80 PTX, compiled for this GPU by the driver when the library loads) on the
+    four 2B shapes at M = 1: distinct weight buffers (> 2 x L2) cycled inside a CUDA graph, time
+    per launch from CUDA events.  A baseline beside the sweep; nothing of it is on the product path."""
+    import ctypes
+
+    import torch
+
+    from bitnet_b200 import _lib
+    from oracle import build_oracle
+
+    path = build_oracle.build_ref_gpu()
+    if not path:
+        return {"unavailable": "the reference's GPU kernel library was not built"}
+    try:
+        ref = ctypes.CDLL(path)
+    except OSError as exc:
+        return {"unavailable": f"load failed: {exc}"[:200]}
+    ref.bitlinear_int8xint2.restype = None
+    ref.bitlinear_int8xint2.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p]
+    g = torch.Generator(device=dev).manual_seed(2)
+    stream = torch.cuda.Stream(device=dev)
+    rows = []
+    for n, k in [(3840, 2560), (2560, 2560), (13824, 2560), (2560, 6912)]:
+        nbytes = n * k // 4
+        copies = max(2, int(300e6 // nbytes))
+        ws = [torch.randint(-128, 127, (n, k // 4), dtype=torch.int8, device=dev, generator=g) for _ in range(copies)]
+        y = torch.randint(-127, 127, (1, k), dtype=torch.int8, device=dev, generator=g)
+        s = torch.ones(1, dtype=torch.bfloat16, device=dev)
+        wsc = torch.ones(4, dtype=torch.bfloat16, device=dev)
+        out = torch.zeros((1, n), dtype=torch.bfloat16, device=dev)
+
+        def run():
+            st = _lib.stream_ptr()
+            for w in ws:
+                ref.bitlinear_int8xint2(_lib.ptr(y), _lib.ptr(w), _lib.ptr(out), _lib.ptr(s), _lib.ptr(wsc), 1, n, k, st)
+
+        with torch.cuda.stream(stream):
+            run()
+            stream.synchronize()
+            if not out.any():
+                return {"unavailable": "the reference kernel's PTX produced no output on this GPU"}
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                run()
+            for _ in range(3):
+                graph.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(3):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (3 * copies)
+        rows.append({"N": n, "K": k, "M": 1, "us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1)})
+        del ws
+    return {"kernel": "ladder_int8xint2_kernel (reference, compute_80 PTX)", "rows": rows}
+
+
+def decode_batch(model, args_model, dev, batch, steps, warmup, peak, prompt_len=PROMPT_LEN, want_e2e=True):
+    """Prefill `prompt_len` random tokens for `batch` sequences, then greedy decode steps from a
+    CUDA graph: device-resident tokens/s, the same with host buffers (ids copied in from pinned
+    memory and copied back every step), prefill tokens/s, and the step's bytes (packed weights +
+    bf16 output projection + the keys and values read) over the HBM peak."""
     import torch
 
     from bitnet_b200.generate import Generator
 
-    max_seq = (PROMPT_LEN + steps + warmup + 64 + 127) // 128 * 128
+    max_seq = (prompt_len + 2 * (steps + warmup) + 64 + 127) // 128 * 128
     gen = Generator(model, batch, max_seq)
     g = torch.Generator(device=dev).manual_seed(SEED + 5)
-    prompt = torch.randint(0, args_model.vocab_size, (batch, PROMPT_LEN), generator=g, device=dev)
+    prompt = torch.randint(0, args_model.vocab_size, (batch, prompt_len), generator=g, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gen.prefill(prompt)                       # warm-up of the prefill kernels
+    torch.cuda.synchronize()
+    e0.record()
     gen.prefill(prompt)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_prefill = e0.elapsed_time(e1)
     gen.capture()
     with torch.cuda.stream(gen.stream):
         for _ in range(warmup):
             gen.decode_step()
         gen.stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(gen.stream)
         for _ in range(steps):
             gen.decode_step()
         e1.record(gen.stream)
         gen.stream.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    return {"batch": batch, "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "steps": steps}
+    weights, kv = arch_step_bytes(args_model, batch, prompt_len + warmup + steps // 2)
+    gbs = (weights + kv) / (ms * 1e-3) / 1e9
+    out = {"batch": batch, "value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "steps": steps,
+           "prompt_len": prompt_len, "prefill_tok_s": batch * prompt_len / (ms_prefill * 1e-3),
+           "engine": "kernel chain" if gen.fused is not None else "op by op (tcgen05 BitLinear, library attention)",
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                        "bytes_per_step": weights + kv, "traffic": None}}
+    if want_e2e:
+        host_tok = gen.host_out.clone()
+        for _ in range(warmup):
+            host_tok = gen.decode_step_host(host_tok[:, None]).clone()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(gen.stream):
+            e0.record(gen.stream)
+        for _ in range(steps):
+            host_tok = gen.decode_step_host(host_tok[:, None]).clone()
+        with torch.cuda.stream(gen.stream):
+            e1.record(gen.stream)
+        torch.cuda.synchronize()
+        out["e2e"] = {"value": batch * steps / (e0.elapsed_time(e1) * 1e-3), "unit": "tok/s",
+                      "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch}
+    return out
+
+
+def config3_report(dev, peak, steps):
+    """The 3B architecture (hidden 3200, FFN 8640, head_dim 100: K is padded to the 128-column
+    tile): prefill of 512 random tokens, then decode, at batch 1, 16 and 64."""
+    import torch
+
+    from bitnet_b200.config import preset
+    from bitnet_b200.model import build_synthetic
+
+    am = preset("3b")
+    model = build_synthetic(am, seed=SEED + 3, device=dev, max_seq_len=1024)
+    rows = []
+    for batch in (1, 16, 64):
+        try:
+            rows.append(decode_batch(model, am, dev, batch, steps, 3, peak, prompt_len=512, want_e2e=False))
+        except Exception as exc:
+            rows.append({"batch": batch, "error": repr(exc)[:300]})
+    del model
+    torch.cuda.empty_cache()
+    return rows
 
 
 # ----------------------------------------------------------------------------------------
@@ -294,6 +406,9 @@ def run_ours(a, args_model):
     if world > 1:
         import torch.distributed as dist
 
+        # the ranks share exchange areas through CUDA IPC; collectives are used for set-up, barriers and
+        # the maximum over ranks only, and need no NVLink multicast objects
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from bitnet_b200 import ops
@@ -369,6 +484,7 @@ def run_ours(a, args_model):
             inputs[lin.in_features] = ops.quant_input(x)
     outs = {lin.out_features: torch.empty((B, lin.out_features), dtype=torch.bfloat16, device=dev) for lin in lins}
     weight_bytes = sum(l.out_features * l.in_features // 4 for l in lins)
+    n_lin = len(lins)
 
     def linears_once():
         if fused:                      # the fused BitLinear kernels (prologue + matmul), chained
@@ -396,31 +512,45 @@ def run_ours(a, args_model):
     barrier()
     ms_lin = e0.elapsed_time(e1) / reps
     clocks = sampler.stop() if sampler else None
+    peak, measured = hbm_peak()
+    n_launches = (gen.fused.kernels_per_step if fused else 2 * len(lins)) * K
+
+    # ---- several GPUs: the 8B and ~100B architectures sharded tensor-parallel over them --------
+    tp_rows = None
+    if world > 1 and not a.no_tp:
+        del gl, gen, model, lins
+        torch.cuda.empty_cache()
+        tp_rows = sharded_report(rank, world, dev, peak, steps=min(K, 32))
+        lins = []
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except (OSError, ValueError):
-        pass
-    peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = weight_bytes / (ms_lin * 1e-3) / 1e9
     cpu = None
+    extras = {}
     if world == 1 and not a.no_cpu_baseline:
         tok_s, info, _ = cpu_i2s_tokens_per_s(args_model, B, steps=3, warmup=1, layers_sampled=min(args_model.n_layers, 4))
         cpu = dict(info, value=tok_s, unit="tok/s")
-    extras = {}
+        try:       # the other baseline: the reference's GPU kernel on this GPU
+            extras["reference_gpu_kernel"] = reference_gpu_kernel_us(dev)
+        except Exception as exc:
+            extras["reference_gpu_kernel"] = {"unavailable": repr(exc)[:200]}
     if world == 1 and not a.no_extras:
         try:
-            extras["decode_bs64"] = decode_batch(model, args_model, dev, 64, steps=min(K, 16), warmup=3)
+            extras["decode_bs64"] = decode_batch(model, args_model, dev, 64, steps=min(K, 16), warmup=3, peak=peak)
             extras["kernel_sweep"] = kernel_sweep(dev, peak)
+            del gen, model
+            torch.cuda.empty_cache()
+            # the other architectures the benchmark configurations name, on this one GPU
+            extras["config3_3b"] = config3_report(dev, peak, steps=min(K, 16))
+            extras["tp"] = sharded_report(0, 1, dev, peak, steps=min(K, 32))
         except Exception as exc:   # the headline stands on its own
             extras["extras_error"] = repr(exc)[:300]
-    n_lin = len(lins)
+    if tp_rows is not None:
+        extras["tp"] = tp_rows
     # every byte a decode step must read: packed BitLinear weights + the bf16 output projection
     step_bytes = weight_bytes + 2 * args_model.vocab_size * args_model.dim
     step_gbs = step_bytes / (ms / K * 1e-3) / 1e9
@@ -431,7 +561,7 @@ def run_ours(a, args_model):
                      # dram__bytes_read + write per launch from one ncu capture of the four 2B shapes
                      # (profiles/fused_linear_kernel_2b_m1.md), averaged as the launches are mixed
                      "traffic": 4.50e6 if (fused and a.workload == "2b" and B == 1) else None}
-    roofline = dict(chain_linears, bound="hbm", peak=peak, unit="GB/s", peak_source="measured" if peaks else "fallback",
+    roofline = dict(chain_linears, bound="hbm", peak=peak, unit="GB/s", peak_source="measured" if measured else "fallback",
                     step_bytes=step_bytes, step_gbs=step_gbs, step_frac=step_gbs / peak)
     line = {
         "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{B})", "value": world * B * K / (ms * 1e-3),
@@ -446,7 +576,7 @@ def run_ours(a, args_model):
                          % (weight_bytes / 1e6)},
         "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8 * B,
                 "d2h_bytes_per_step": 8 * B},
-        "gpu_launches": (gen.fused.kernels_per_step if fused else 2 * n_lin) * K,
+        "gpu_launches": n_launches,
         "roofline": roofline,
         "cpu_baseline": cpu, "clocks": clocks, **extras,
     }
@@ -455,102 +585,207 @@ def run_ours(a, args_model):
         dist.destroy_process_group()
 
 
-def run_tp(a, args_model):
-    """One model sharded over the ranks (bitnet_b200.tensor_parallel): column-parallel wqkv/w13,
-    row-parallel wo/w2 with an all-gather and an exact int32 all-reduce each; the decode step
-    (kernels and collectives) is captured in a CUDA graph (--no-graph: issued op by op), timed
-    with CUDA events, maximum over ranks."""
+def arch_step_bytes(args_model, batch, context):
+    """Bytes one decode step must read: packed BitLinear weights, the bf16 output projection and
+    the bf16 keys and values of `context` positions for every sequence."""
+    D = args_model.head_dim
+    per_layer = ((args_model.n_heads + 2 * args_model.n_kv_heads) * D * args_model.dim
+                 + args_model.n_heads * D * args_model.dim + 3 * args_model.ffn_dim * args_model.dim) // 4
+    weights = per_layer * args_model.n_layers + 2 * args_model.vocab_size * args_model.dim
+    kv = 2 * 2 * args_model.n_kv_heads * D * context * batch * args_model.n_layers
+    return weights, kv
+
+
+def measure_sharded_decode(name, args_model, batch, context, steps, warmup, rank, world, dev, peak, want_local=True,
+                           dec=None):
+    """Decode steps of one model sharded tensor-parallel over the ranks (one rank: the whole
+    model), at a KV cache already holding `context` positions per sequence.
+
+    Batches up to 8 run the in-library step (`TPFusedStep`: the chain of fused kernels, the
+    exchange between ranks inside the kernels through peer memory), replayed from a CUDA graph.
+    Larger batches run the op-by-op decoder (`TPDecoder.decode_step`; with several ranks its NCCL
+    collectives are issued eagerly, never from a graph).  Time from CUDA events, maximum over
+    ranks.  `exchange_share` = 1 - (the same shards stepped with no exchange) / (the real step)."""
     import torch
     import torch.distributed as dist
 
-    from bitnet_b200.tensor_parallel import GraphedStep, TPDecoder
+    from bitnet_b200.tensor_parallel import GraphedStep, TPDecoder, TPFusedStep
+
+    max_seq = (context + 2 * (steps + warmup) + 16 + 127) // 128 * 128
+    if dec is None:
+        dec = TPDecoder(args_model, SEED, rank, world, dev, backend="kernel", max_seq_len=max_seq, fast_random=True)
+    assert dec.max_seq_len >= max_seq
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    fused = batch <= 8
+
+    def fill(cache):
+        for ck, cv in cache:     # a context of random keys and values stands in for a prefill
+            ck[:, :context].copy_(torch.randn(ck[:, :context].shape, generator=g, device=dev, dtype=torch.bfloat16))
+            cv[:, :context].copy_(torch.randn(cv[:, :context].shape, generator=g, device=dev, dtype=torch.bfloat16))
+
+    def max_ms(ms):
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, stream):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+        barrier()
+        return max_ms(e0.elapsed_time(e1)) / steps
+
+    out = {"model": name, "batch": batch, "context": context, "tp": world, "steps": steps}
+    if fused:
+        def fused_ms(local_only):
+            st = TPFusedStep(dec, batch, max_seq, local_only=local_only)
+            fill(st.cache)
+            st.tokens.copy_(torch.randint(0, args_model.vocab_size, (batch, 1), generator=g, device=dev))
+            st.pos.fill_(context)
+            stream = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(stream):
+                st.step()
+                stream.synchronize()
+                barrier()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    st.step()
+            ms = timed(graph.replay, stream)
+            err, launches = st.error_flag(), st.kernels_per_step
+            barrier()
+            del graph
+            st.close()
+            return ms, err, launches
+
+        from bitnet_b200._lib import BitnetError
+
+        try:
+            ms, err, launches = fused_ms(False)
+            out.update(engine="in-library chain, peer-memory exchange inside the kernels, CUDA graph",
+                       kernels_per_step=launches, error_flag=err)
+            if world > 1 and want_local:
+                try:
+                    ms_local, _, _ = fused_ms(True)
+                    out.update(ms_per_step_no_exchange=ms_local, exchange_share=max(0.0, 1.0 - ms_local / ms))
+                except BitnetError as exc:
+                    out["no_exchange_error"] = str(exc)[:160]
+        except BitnetError as exc:
+            # refused when the step is built (the same on every rank), e.g. batch x K of a BitLinear beyond
+            # the shared memory that holds a CTA's quantised activations: the op-by-op decoder takes the case
+            out["chain_refused"] = str(exc)[:160]
+            fused = False
+    if not fused:
+        cache = dec.make_cache(batch, max_seq)
+        fill(cache)
+        tok = torch.randint(0, args_model.vocab_size, (batch, 1), generator=g, device=dev)
+        pos = torch.full((batch,), context, dtype=torch.int64, device=dev)
+        if world == 1:
+            step = GraphedStep(dec, tok, pos, cache)
+            ms = timed(step.replay, step.stream)
+            out.update(engine="op by op (tcgen05 BitLinear, library attention), CUDA graph")
+        else:
+            def one():
+                nonlocal tok
+                tok = dec.decode_step(tok, pos, cache).view(batch, 1)
+                pos.add_(1)
+
+            ms = timed(one, torch.cuda.current_stream())
+            out.update(engine="op by op with NCCL all-gather / all-reduce, issued eagerly")
+        del cache
+    weights, kv = arch_step_bytes(args_model, batch, context)
+    gbs = (weights + kv) / (ms * 1e-3) / 1e9
+    out.update(ms_per_step=ms, value=batch / (ms * 1e-3), unit="tok/s", step_bytes=weights + kv,
+               achieved_gbs=gbs, peak_gbs=peak * world, frac=gbs / (peak * world))
+    torch.cuda.empty_cache()
+    return out
+
+
+# (model, batch, context): the 8B architecture at a 2048-token context and the ~100B architecture
+# at a 4096-token context; batches above 8 take the op-by-op decoder
+SHARDED_CASES = [("8b", 1, 2048), ("8b", 8, 2048), ("8b", 64, 2048), ("100b", 1, 4096), ("100b", 8, 4096),
+                 ("100b", 32, 4096)]
+
+
+def sharded_report(rank, world, dev, peak, steps, cases=None):
+    """The cases of SHARDED_CASES that the rank count divides; one decoder per model."""
+    import torch
+
+    from bitnet_b200.config import preset
+    from bitnet_b200.tensor_parallel import TPDecoder
+
+    rows, dec, dec_name = [], None, None
+    for name, batch, context in (cases or SHARDED_CASES):
+        am = preset(name)
+        if am.n_heads % world or am.n_kv_heads % world:
+            continue
+        k = steps if batch <= 8 else max(2, steps // 4)
+        try:
+            if dec_name != name:
+                dec = None
+                torch.cuda.empty_cache()
+                dec = TPDecoder(am, SEED, rank, world, dev, backend="kernel", max_seq_len=context + 2 * steps + 256,
+                                fast_random=True)
+                dec_name = name
+            rows.append(measure_sharded_decode(name, am, batch, context, k, 3, rank, world, dev, peak, dec=dec))
+        except Exception as exc:      # one case must not take the line with it
+            rows.append({"model": name, "batch": batch, "context": context, "tp": world, "error": repr(exc)[:300]})
+            break                     # the ranks may no longer be in step: stop here
+    dec = None
+    torch.cuda.empty_cache()
+    return rows
+
+
+def run_tp(a, args_model):
+    """Only the tensor-parallel measurement of --workload, as a line of its own."""
+    import torch
+    import torch.distributed as dist
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    # One rank: the step is replayed from a CUDA graph.  Several ranks: op by op unless --graph
-    # (a two-rank graph of 2 layers replays correctly in tests/test_tensor_parallel_gpu.py, but the
-    # 8-layer bench configuration did not finish on this pool, cause not found: left off by default).
-    if world > 1 and not a.graph:
-        a.no_graph = True
     if world > 1:
-        if not a.no_graph:
-            # collectives replayed from a CUDA graph: plain ring/tree algorithms (no NVLink SHARP
-            # multicast objects bound to graph nodes)
-            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-    B, K, W = a.batch, a.steps, a.warmup
-    max_seq = (a.context + K + W + 8 + 127) // 128 * 128
-    dec = TPDecoder(args_model, SEED, rank, world, dev, backend="kernel", max_seq_len=max_seq)
-    cache = dec.make_cache(B, max_seq)
-    g = torch.Generator(device=dev).manual_seed(SEED)
-    for ck, cv in cache:     # a context of random keys and values stands in for a prefill
-        ck[:, : a.context].copy_(torch.randn(ck[:, : a.context].shape, generator=g, device=dev).to(torch.bfloat16))
-        cv[:, : a.context].copy_(torch.randn(cv[:, : a.context].shape, generator=g, device=dev).to(torch.bfloat16))
-    tok = torch.randint(0, args_model.vocab_size, (B, 1), generator=g, device=dev)
-    pos = torch.full((B,), a.context, dtype=torch.int64, device=dev)
-    step = None if a.no_graph else GraphedStep(dec, tok, pos, cache)
-    stream = step.stream if step else torch.cuda.current_stream()
-
-    def one_step():
-        nonlocal tok
-        if step:
-            step.replay()
-        else:
-            tok = dec.decode_step(tok, pos, cache).view(B, 1)
-            pos.add_(1)
-
-    with torch.cuda.stream(stream):
-        for _ in range(W):
-            one_step()
-    # The barrier's collective runs on another stream than the step's: the device is drained
-    # first, so that collectives of one communicator never overlap on two streams (their order
-    # on the GPUs could then differ between the ranks).
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(K):
-            one_step()
-        e1.record(stream)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    peak, measured = hbm_peak()
+    r = measure_sharded_decode(a.workload, args_model, a.batch, a.context, a.steps, max(a.warmup, 3), rank, world, dev, peak)
     if rank == 0:
-        D = args_model.head_dim
-        per_layer = ((args_model.n_heads + 2 * args_model.n_kv_heads) * D * args_model.dim + args_model.dim * args_model.dim
-                     + 3 * args_model.ffn_dim * args_model.dim) // 4
-        step_bytes = per_layer * args_model.n_layers + 2 * args_model.vocab_size * args_model.dim
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        gbs = step_bytes / (ms / K * 1e-3) / 1e9
         print(json.dumps({
-            "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{B}, tp{world})", "value": B * K / (ms * 1e-3),
-            "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x 2-bit ternary -> int32 (bf16 elsewhere)",
-            "data": "synthetic",
-            "config": {"workload": f"{a.workload} architecture ({args_model.n_layers} layers) random-init, batch {B}, "
-                                   f"context {a.context}, tensor parallel x{world}, "
-                                   f"{'op by op' if a.no_graph else 'CUDA graph'}", "batch": B},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak * world, "unit": "GB/s",
-                         "frac": gbs / (peak * world), "traffic": None,
-                         "note": "whole step: packed weights + bf16 output projection over aggregate HBM bandwidth"},
-            "gpu_launches": None}), flush=True)
+            "metric": f"BitNet-{a.workload.upper()} decode tok/s (bs{a.batch}, tp{world})", "value": r["value"],
+            "unit": "tok/s", "n_gpus": world, "steps": r["steps"], "warmup": max(a.warmup, 3), "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 x 2-bit ternary -> int32 (bf16 elsewhere)", "data": "synthetic",
+            "config": {"workload": f"{a.workload} architecture ({args_model.n_layers} layers) random ternary shards, batch "
+                                   f"{a.batch}, context {a.context}, tensor parallel x{world}; {r['engine']}",
+                       "batch": a.batch},
+            "roofline": {"bound": "hbm", "achieved": r["achieved_gbs"], "peak": r["peak_gbs"], "unit": "GB/s",
+                         "frac": r["frac"], "traffic": None, "peak_source": "measured" if measured else "fallback",
+                         "note": "whole step: packed weights + bf16 output projection + KV cache over aggregate HBM bandwidth"},
+            "tp": r, "gpu_launches": r.get("kernels_per_step", 0) * r["steps"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def hbm_peak():
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(peaks["hbm_gbs"]), True
+    except (OSError, ValueError, KeyError):
+        return 6650.0, False
 
 
 def main():

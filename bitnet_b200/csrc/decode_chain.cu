@@ -35,7 +35,6 @@ namespace {
 
 constexpr int kCStageTiles = 32;
 constexpr int kCStageBytes = kCStageTiles * kTileBytes;     // 16 KB
-constexpr int kCRoundStages = 2;                            // stages a round of the consumers spans
 constexpr int kCWarps = 8;                                  // consumer warps
 constexpr int kCThreads = kCWarps * 32;
 constexpr int kCLinearThreads = kCThreads + 32;             // + one producer warp
@@ -108,6 +107,7 @@ __host__ __device__ inline size_t chain_carve(const ChainLinearParams& p, uint8_
 // BitLinear of the chain.  288 threads: 8 consumer warps and one producer warp; two CTAs fit an SM, so
 // that the successor kernel's CTAs are resident, and past their set-up, while this kernel still runs.
 // ---------------------------------------------------------------------------------------
+template <bool kOneToken>
 __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const ChainLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     ChainSmem sm;
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     // of eight columns empty).  Two to eight tokens: four m16n8k32 MMAs per tile with the tokens as
     // the MMA's columns, so that any such M costs the same.
     const int g = lane >> 2, q = lane & 3;
-    const bool one_token = p.M == 1;
+    constexpr bool one_token = kOneToken;                  // the launcher picks the instantiation by M
     const int8_t* y_lane = sm.ys + (size_t)((one_token || g < p.M) ? (one_token ? 0 : g) : p.M) * y_stride + 32 * q;
     int acc[4][4];
 #pragma unroll
@@ -302,62 +302,96 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #define TR_BEGIN
 #define TR_END(x)
 #endif
-    // n consecutive tiles, the first one local tile number t_first at `tile` (this lane's 16 bytes)
+    // The warp's sums of one row group into the CTA's accumulator.
+    auto flush = [&](int lg) {
+        TR_BEGIN
+        int* dst = sm.sacc + lg * 128;
+        if (one_token) {
+            int v0 = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
+            int v1 = acc[0][1] + (acc[1][1] >> 2) + (acc[2][1] >> 4) + (acc[3][1] >> 6);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (q == 0) {
+                atomicAdd(&dst[g * 8], v0);
+                atomicAdd(&dst[(g + 8) * 8], v1);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { acc[j][0] = 0; acc[j][1] = 0; }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int tok = 2 * q + (e & 1);
+                const int v = acc[0][e] + (acc[1][e] >> 2) + (acc[2][e] >> 4) + (acc[3][e] >> 6);
+                if (tok < p.M) atomicAdd(&dst[(g + 8 * (e >> 1)) * 8 + tok], v);
+                acc[0][e] = 0; acc[1][e] = 0; acc[2][e] = 0; acc[3][e] = 0;
+            }
+        }
+        TR_END(tr_flush)
+    };
+    // One tile: the lane's 16 weight bytes against its 32 activation bytes.
+    auto one_tile = [&](const uint4 wc, const uint4 y0, const uint4 y1) {
+        const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+        const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
+        if (one_token) {
+            // acc[j][0], acc[j][1]: rows g, g+8 of field j, summed over this lane's columns
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t msk = 0x03030303u << (2 * j);
+                acc[j][0] = dp4a_u8s8(w[0] & msk, b[2 * j], acc[j][0]);
+                acc[j][1] = dp4a_u8s8(w[1] & msk, b[2 * j], acc[j][1]);
+                acc[j][0] = dp4a_u8s8(w[2] & msk, b[2 * j + 1], acc[j][0]);
+                acc[j][1] = dp4a_u8s8(w[3] & msk, b[2 * j + 1], acc[j][1]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t msk = 0x03030303u << (2 * j);
+                mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
+            }
+        }
+    };
+    // n consecutive tiles, the first one local tile number t_first at `tile` (this lane's 16 bytes).
+    // The run is cut where a row group ends; within a piece four tiles are loaded before any is used.
     auto run_tiles = [&](const uint8_t* tile, int n, int t_first) {
         int lg = t_first / p.k_tiles, kt = t_first - lg * p.k_tiles;
 #pragma unroll 1
-        for (int i = 0; i < n; ++i, tile += kTileBytes) {
-            const uint4 wc = *reinterpret_cast<const uint4*>(tile);
-            const uint4* yp = reinterpret_cast<const uint4*>(y_lane + kt * kTileCols);
-            const uint4 y0 = yp[0], y1 = yp[1];
-            const uint32_t b[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-            const uint32_t w[4] = {wc.x, wc.y, wc.z, wc.w};
-            if (one_token) {
-                // acc[j][0], acc[j][1]: rows g, g+8 of field j, summed over this lane's columns
+        while (n > 0) {
+            const int piece = min(n, p.k_tiles - kt);
+            const uint8_t* yk = reinterpret_cast<const uint8_t*>(y_lane) + kt * kTileCols;
+            int i = 0;
+#pragma unroll 1
+            for (; i + 4 <= piece; i += 4, tile += 4 * kTileBytes, yk += 4 * kTileCols) {
+                uint4 wc[4], y0[4], y1[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t msk = 0x03030303u << (2 * j);
-                    acc[j][0] = dp4a_u8s8(w[0] & msk, b[2 * j], acc[j][0]);
-                    acc[j][1] = dp4a_u8s8(w[1] & msk, b[2 * j], acc[j][1]);
-                    acc[j][0] = dp4a_u8s8(w[2] & msk, b[2 * j + 1], acc[j][0]);
-                    acc[j][1] = dp4a_u8s8(w[3] & msk, b[2 * j + 1], acc[j][1]);
+                for (int u = 0; u < 4; ++u) {
+                    wc[u] = *reinterpret_cast<const uint4*>(tile + u * kTileBytes);
+                    y0[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols);
+                    y1[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16);
                 }
-            } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t msk = 0x03030303u << (2 * j);
-                    mma_u8s8(acc[j], w[0] & msk, w[1] & msk, w[2] & msk, w[3] & msk, b[2 * j], b[2 * j + 1]);
-                }
+                for (int u = 0; u < 4; ++u) one_tile(wc[u], y0[u], y1[u]);
             }
-            if (++kt == p.k_tiles || i + 1 == n) {
-                // end of this row group's tiles in the run: the warp's sums into the CTA's accumulator
-                TR_BEGIN
-                int* dst = sm.sacc + lg * 128;
-                if (one_token) {
-                    int v0 = acc[0][0] + (acc[1][0] >> 2) + (acc[2][0] >> 4) + (acc[3][0] >> 6);
-                    int v1 = acc[0][1] + (acc[1][1] >> 2) + (acc[2][1] >> 4) + (acc[3][1] >> 6);
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-                    v0 += __shfl_xor_sync(0xffffffffu, v0, 2); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-                    if (q == 0) {
-                        atomicAdd(&dst[g * 8], v0);
-                        atomicAdd(&dst[(g + 8) * 8], v1);
-                    }
+            if (i < piece) {     // up to three tiles left: again all loads first
+                uint4 wc[3], y0[3], y1[3];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) { acc[j][0] = 0; acc[j][1] = 0; }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int tok = 2 * q + (e & 1);
-                        const int v = acc[0][e] + (acc[1][e] >> 2) + (acc[2][e] >> 4) + (acc[3][e] >> 6);
-                        if (tok < p.M) atomicAdd(&dst[(g + 8 * (e >> 1)) * 8 + tok], v);
-                        acc[0][e] = 0; acc[1][e] = 0; acc[2][e] = 0; acc[3][e] = 0;
+                for (int u = 0; u < 3; ++u) {
+                    if (i + u < piece) {
+                        wc[u] = *reinterpret_cast<const uint4*>(tile + u * kTileBytes);
+                        y0[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols);
+                        y1[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16);
                     }
                 }
-                TR_END(tr_flush)
-                if (kt == p.k_tiles) {
-                    kt = 0;
-                    ++lg;
-                }
+#pragma unroll
+                for (int u = 0; u < 3; ++u)
+                    if (i + u < piece) one_tile(wc[u], y0[u], y1[u]);
+                tile += (piece - i) * kTileBytes;
+            }
+            flush(lg);
+            n -= piece;
+            kt += piece;
+            if (kt == p.k_tiles) {
+                kt = 0;
+                ++lg;
             }
         }
     };
@@ -382,13 +416,14 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     } else {
         // Larger shares stream through the ring in rounds of two stages (up to 64 tiles); within
         // a round each warp takes one contiguous run.
-        constexpr int kRoundTiles = kCRoundStages * kCStageTiles;
+        const int round_stages = p.ring_stages >> 1;         // half of the ring is worked on, the other half in flight
+        const int kRoundTiles = round_stages * kCStageTiles;
         const int n_rounds = (n_tiles + kRoundTiles - 1) / kRoundTiles;
 #pragma unroll 1
         for (int r = 0; r < n_rounds && !gave_up; ++r) {
             const int nr_t = min(kRoundTiles, n_tiles - r * kRoundTiles);
             const int lo_t = nr_t * warp / kCWarps, hi_t = nr_t * (warp + 1) / kCWarps;
-            const int c0 = r * kCRoundStages;                    // first chunk of the round
+            const int c0 = r * round_stages;                     // first chunk of the round
             if (hi_t > lo_t) {
                 bool ok = true;
                 TR_BEGIN
@@ -414,7 +449,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 // having seen that stage's copy complete (usually it has, long ago), so that no warp
                 // ever waits for a later fill of a stage whose earlier fill it has not observed.
 #pragma unroll 1
-                for (int ls = 0; ls < kCRoundStages; ++ls) {
+                for (int ls = 0; ls < round_stages; ++ls) {
                     const int c = c0 + ls;
                     if (c < n_chunks && mbar_wait(&sm.full_bar[c & s_mask], (c / p.ring_stages) & 1)) mbar_arrive(&sm.empty_bar[c & s_mask]);
                 }
@@ -894,7 +929,14 @@ __global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const Attenti
     // the split-KV body runs on the first AttnCfg<GMAX>::kThreads threads
     constexpr int NT = AttnCfg<GMAX>::kThreads, NW = AttnCfg<GMAX>::kWarps;
     bool wrote = false;
-    if (tid < NT) {
+    if (GMAX > 4 && it.G > 1 && p.D == 128) {
+        // whole groups of more than four query heads at head_dim 128: the key loop on tensor cores, by
+        // four warps (the 512-thread form of this kernel leaves a thread too few registers for it)
+        if (tid < 128) {
+            auto sync = [] { asm volatile("bar.sync 3, 128;\n" ::: "memory"); };
+            wrote = attention_body<16, 4, true>(p, smem, &is_last, b, it.kvh, it.h0, it.G, it.split, it.S, P, tid, sync, [] {});
+        }
+    } else if (tid < NT) {
         auto sync = [] { asm volatile("bar.sync 2, %0;\n" ::"n"(NT) : "memory"); };
         if (it.G == 1)
             wrote = attention_body<1, NW>(p, smem, &is_last, b, it.kvh, it.h0, 1, it.split, it.S, P, tid, sync, [] {});
@@ -959,6 +1001,10 @@ void plan_chain_linear(ChainLinearParams& p, int n_sm) {
     p.units_rem = p.n_units % p.grid;
     p.units_max = (p.n_units + p.grid - 1) / p.grid;
     if (p.ring_stages != 2 && p.ring_stages != 4 && p.ring_stages != 8) p.ring_stages = 8;   // a power of two
+    // A share that passes through the ring more than once is bound by instruction throughput, not by
+    // latency: it takes the tensor-core form of the tile loop whatever M (16 logic operations and 4
+    // MMAs per tile instead of 16 + 16 on the integer pipe, which issues two warp instructions per clock).
+    p.big_share = p.units_max * p.n_sub * p.k_tiles > p.ring_stages * kCStageTiles;
     if (p.k_norm == 0) p.k_norm = p.K;
 }
 
@@ -971,7 +1017,8 @@ size_t chain_attention_smem(const AttentionParams& p) {
 }
 
 int prepare_chain_kernels(size_t smem_optin) {
-    cudaError_t e = cudaFuncSetAttribute(chain_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    cudaError_t e = cudaFuncSetAttribute(chain_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chain_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
     if (e != cudaSuccess) return check_cuda(e);
     const int attn = 96 * 1024;
     if ((e = cudaFuncSetAttribute(chain_attention_kernel<4, kAttnThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn)) != cudaSuccess ||
@@ -982,7 +1029,9 @@ int prepare_chain_kernels(size_t smem_optin) {
 }
 
 int launch_chain_linear(const ChainLinearParams& p, cudaStream_t stream, bool pdl) {
-    return check_cuda(launch_chain_k(chain_linear_kernel, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
+    if (p.M == 1 && !p.big_share)
+        return check_cuda(launch_chain_k(chain_linear_kernel<true>, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
+    return check_cuda(launch_chain_k(chain_linear_kernel<false>, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
 }
 
 int launch_embed(const EmbedParams& p, cudaStream_t stream, bool pdl) {

@@ -103,7 +103,7 @@ __device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf
 // ---------------------------------------------------------------------------------------
 template <int GMAX>
 struct AttnCfg {
-    static constexpr int kWarps = GMAX <= 4 ? 16 : (GMAX <= 8 ? 8 : 4);   // bounded by registers
+    static constexpr int kWarps = GMAX <= 4 ? 16 : 4;   // bounded by registers (the tensor-core key loop wants 4)
     static constexpr int kThreads = kWarps * 32;
 };
 
@@ -131,6 +131,152 @@ __device__ __forceinline__ AttnItem attention_item(const AttentionParams& p, int
     return it;
 }
 
+// The key loop of the split-KV body on tensor cores, for head_dim 128 and up to 16 query heads
+// per kv head: the heads of the group are the 16 rows of m16n8k16 bf16 MMAs (rows beyond G are
+// zero), a warp takes 16 keys per step.  S = Q K^T: the dot product over the 128 dims may be summed
+// in any order of the dims, so a lane loads the 16-byte pieces of a key row that it can use as B
+// fragments directly - piece i*4 + q of key g for lane 4g+q - and Q's A fragments are arranged to
+// match.  O += P V: the B fragment wants two keys' values of one dim in a register; a lane loads
+// 32 contiguous bytes of its four keys and pairs them with byte permutes, the dims being assigned
+// to the MMA's columns so that those loads are contiguous.  P is rounded to bf16 for the second
+// product (as flash attention kernels do), sums and maxima stay in f32.  Leaves each warp's
+// (max, sum, unnormalised output) where the scalar body leaves them.
+//   q_s [G][128] rotated queries (bf16 values, not yet scaled); knew / vnew: the new token's key and
+//   value (bf16 values), attended by warp 0 when with_new; ck / cv: row 0 of this (sequence, kv head).
+template <int NW, int GMAX>
+__device__ __forceinline__ void attention_keys_mma(const float* q_s, int G, const float* knew, const float* vnew, bool with_new,
+                                                   const __nv_bfloat16* ck, const __nv_bfloat16* cv, int64_t key_stride, int lo,
+                                                   int hi, int warp, int lane, float* red_m, float* red_l, float* red_o) {
+    constexpr int D = 128;
+    const int g = lane >> 2, q = lane & 3;
+    const float scale = rsqrtf((float)D);
+    auto pack = [](float lo_v, float hi_v) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo_v, hi_v);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    };
+    // A fragments of Q: k-step 2i+h covers dims i*32 + q*8 + h*4 .. +3 for this lane
+    uint32_t qa[8][4];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const int d = (s >> 1) * 32 + q * 8 + (s & 1) * 4;
+        const float* r0 = q_s + g * D + d;
+        const float* r1 = q_s + (g + 8) * D + d;
+        const bool v0 = g < G, v1 = g + 8 < G;
+        qa[s][0] = v0 ? pack(r0[0], r0[1]) : 0u;
+        qa[s][2] = v0 ? pack(r0[2], r0[3]) : 0u;
+        qa[s][1] = v1 ? pack(r1[0], r1[1]) : 0u;
+        qa[s][3] = v1 ? pack(r1[2], r1[3]) : 0u;
+    }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows g and g+8
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) { o[nt][0] = 0.f; o[nt][1] = 0.f; o[nt][2] = 0.f; o[nt][3] = 0.f; }
+
+#pragma unroll 1
+    for (int j0 = lo + warp * 16; j0 < hi; j0 += NW * 16) {
+        uint4 kk[2][4], vv[4][2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int key = j0 + t * 8 + g;
+            const uint4* src = reinterpret_cast<const uint4*>(ck + (int64_t)key * key_stride) + q;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kk[t][i] = key < hi ? src[i * 4] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int key = j0 + (x >> 1) * 8 + 2 * q + (x & 1);
+            const uint4* src = reinterpret_cast<const uint4*>(cv + (int64_t)key * key_stride) + g;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) vv[x][j] = key < hi ? src[j * 8] : make_uint4(0, 0, 0, 0);
+        }
+        float s[2][4];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            s[t][0] = 0.f; s[t][1] = 0.f; s[t][2] = 0.f; s[t][3] = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                mma_bf16(s[t], qa[2 * i], kk[t][i].x, kk[t][i].y);
+                mma_bf16(s[t], qa[2 * i + 1], kk[t][i].z, kk[t][i].w);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[t][c] = (j0 + t * 8 + 2 * q + (c & 1) < hi) ? s[t][c] * scale : -INFINITY;
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);          // finite: key j0 is inside the slice
+        const float c0 = __expf(m0 - mn0), c1 = __expf(m1 - mn1);
+        m0 = mn0; m1 = mn1;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            s[t][0] = __expf(s[t][0] - mn0); s[t][1] = __expf(s[t][1] - mn0);
+            s[t][2] = __expf(s[t][2] - mn1); s[t][3] = __expf(s[t][3] - mn1);
+        }
+        l0 = l0 * c0 + (s[0][0] + s[0][1]) + (s[1][0] + s[1][1]);
+        l1 = l1 * c1 + (s[0][2] + s[0][3]) + (s[1][2] + s[1][3]);
+        const uint32_t pa[4] = {pack(s[0][0], s[0][1]), pack(s[0][2], s[0][3]), pack(s[1][0], s[1][1]), pack(s[1][2], s[1][3])};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t wa[4] = {vv[0][j].x, vv[0][j].y, vv[0][j].z, vv[0][j].w};
+            const uint32_t wb[4] = {vv[1][j].x, vv[1][j].y, vv[1][j].z, vv[1][j].w};
+            const uint32_t wc[4] = {vv[2][j].x, vv[2][j].y, vv[2][j].z, vv[2][j].w};
+            const uint32_t wd[4] = {vv[3][j].x, vv[3][j].y, vv[3][j].z, vv[3][j].w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int nt = j * 8 + e;
+                const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(wa[e >> 1], wb[e >> 1], sel);
+                const uint32_t b1 = __byte_perm(wc[e >> 1], wd[e >> 1], sel);
+                o[nt][0] *= c0; o[nt][1] *= c0; o[nt][2] *= c1; o[nt][3] *= c1;
+                mma_bf16(o[nt], pa, b0, b1);
+            }
+        }
+    }
+    if (with_new && warp == 0) {     // the new token attends to itself: one more key, from shared memory
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const int d = (s >> 1) * 32 + q * 8 + (s & 1) * 4;
+            const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][0]));
+            const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][2]));
+            const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][1]));
+            const float2 a3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][3]));
+            s0 += a0.x * knew[d] + a0.y * knew[d + 1] + a2.x * knew[d + 2] + a2.y * knew[d + 3];
+            s1 += a1.x * knew[d] + a1.y * knew[d + 1] + a3.x * knew[d + 2] + a3.y * knew[d + 3];
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        s0 *= scale; s1 *= scale;
+        const float mn0 = fmaxf(m0, s0), mn1 = fmaxf(m1, s1);
+        const float c0 = __expf(m0 - mn0), c1 = __expf(m1 - mn1);
+        const float p0 = __expf(s0 - mn0), p1 = __expf(s1 - mn1);
+        m0 = mn0; m1 = mn1;
+        l0 = l0 * c0 + (q == 0 ? p0 : 0.f);          // the lanes' sums are added up below
+        l1 = l1 * c1 + (q == 0 ? p1 : 0.f);
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+            const int d = ((nt >> 3) * 8 + 2 * q) * 8 + (nt & 7);
+            o[nt][0] = o[nt][0] * c0 + p0 * vnew[d]; o[nt][1] = o[nt][1] * c0 + p0 * vnew[d + 8];
+            o[nt][2] = o[nt][2] * c1 + p1 * vnew[d]; o[nt][3] = o[nt][3] * c1 + p1 * vnew[d + 8];
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (q == 0) {
+        if (g < G) { red_m[warp * GMAX + g] = m0; red_l[warp * GMAX + g] = l0; }
+        if (g + 8 < G) { red_m[warp * GMAX + g + 8] = m1; red_l[warp * GMAX + g + 8] = l1; }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+        const int d = ((nt >> 3) * 8 + 2 * q) * 8 + (nt & 7);
+        if (g < G) { red_o[(warp * G + g) * D + d] = o[nt][0]; red_o[(warp * G + g) * D + d + 8] = o[nt][1]; }
+        if (g + 8 < G) { red_o[(warp * G + g + 8) * D + d] = o[nt][2]; red_o[(warp * G + g + 8) * D + d + 8] = o[nt][3]; }
+    }
+}
+
 // Attention of query heads h0 .. h0+G-1 of kv head kvh of sequence b over KV slice `split` of S,
 // by NW warps, with P keys already in the cache (the caller reads p.pos[b]; the body does not).
 // A subset of the heads (G < H / Hkv) is only allowed with S = 1.  `smem` needs
@@ -139,7 +285,7 @@ __device__ __forceinline__ AttnItem attention_item(const AttentionParams& p, int
 // q, k, v (xqkv) are visible: the cache rows and the positions must not change meanwhile.
 // Returns true when this CTA wrote p.out for its heads (always with S == 1; with several slices
 // only the CTA that combined them).
-template <int GMAX, int NW, class Sync, class Wait>
+template <int GMAX, int NW, bool kMma = false, class Sync, class Wait>
 __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t* smem, int* is_last_s, int b, int kvh,
                                                int h0, int G, int split, int S, int P, int tid, Sync sync, Wait wait) {
     constexpr int NT = NW * 32;
@@ -170,12 +316,13 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
             }
         }
     };
-    request(lo + warp * U);
+    if constexpr (!kMma) request(lo + warp * U);
     wait();
     const __nv_bfloat16* x = p.xqkv + (int64_t)b * p.ld_qkv;
     const float* rope = p.rope + (int64_t)P * D;           // [D/2][2] cos, sin of position P
     const float qscale = rsqrtf((float)D);
     // vectors: G query heads, then k, then v; pairs (2i, 2i+1) rotate together
+#pragma unroll 4
     for (int idx = tid; idx < (G + 2) * (D / 2); idx += NT) {
         const int vec = idx / (D / 2), i = idx - vec * (D / 2);
         int col;
@@ -190,7 +337,10 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
             const float r1 = bf16_round(__fmul_rn(x0, sn) + __fmul_rn(x1, cs));
             x0 = r0; x1 = r1;
         }
-        if (vec < G) { q_s[vec * D + 2 * i] = x0 * qscale; q_s[vec * D + 2 * i + 1] = x1 * qscale; }
+        if (vec < G) {     // the tensor-core loop scales the scores instead (its queries must stay bf16 values)
+            q_s[vec * D + 2 * i] = kMma ? x0 : x0 * qscale;
+            q_s[vec * D + 2 * i + 1] = kMma ? x1 : x1 * qscale;
+        }
         else {
             float* dst = vec == G ? knew : vnew;
             dst[2 * i] = x0; dst[2 * i + 1] = x1;
@@ -203,6 +353,10 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
     }
     sync();
 
+    if constexpr (kMma) {
+        attention_keys_mma<NW, GMAX>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,
+                                     red_l, red_o);
+    } else {
     // Online softmax state of the G query heads; a lane owns dims d0..d0+3 of q, k, v and o.
     float m_h[GMAX], l_h[GMAX], o_h[GMAX][4], q_r[GMAX][4];
 #pragma unroll
@@ -376,6 +530,7 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
             }
         }
     }
+    }
     sync();
     for (int idx = tid; idx < G * D; idx += NT) {
         const int h = idx / D, d = idx - h * D;
@@ -414,35 +569,71 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
     if (!*is_last_s) return false;
     __threadfence();
     // weights of the slices per head, then one pass over the partial outputs
-    float* sl_m = red_o;                  // [G][S] max, then weight
-    float* sl_l = red_o + G * p.S;        // [G][S] sum
+    float* sl_m = red_o;                  // [G][S] weight of slice s for head h
     const int64_t head0 = (int64_t)b * p.H + kvh * Gfull + h0;
-    for (int idx = tid; idx < G * S; idx += NT) {
-        const int h = idx / S, sidx = idx - h * S;
-        sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
-        sl_l[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2 + 1]);
-    }
-    sync();
-    if (tid < G) {
-        float mx = -INFINITY, den = 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, sl_m[tid * p.S + sidx]);
-        for (int sidx = 0; sidx < S; ++sidx) {
-            const float l = sl_l[tid * p.S + sidx];
-            const float w = l > 0.f ? __expf(sl_m[tid * p.S + sidx] - mx) * l : 0.f;
-            sl_m[tid * p.S + sidx] = w;
-            den += w;
+    if (S <= 32) {
+        // a warp per head, a lane per slice: maximum, weights and their sum by shuffles
+        for (int h = warp; h < G; h += NW) {
+            float m = -INFINITY, l = 0.f;
+            if (lane < S) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((head0 + h) * p.S + lane) * 2));
+                m = ml.x; l = ml.y;
+            }
+            float mx = m;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float w = l > 0.f ? __expf(m - mx) * l : 0.f;
+            float den = w;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+            if (lane < S) sl_m[h * p.S + lane] = den > 0.f ? w / den : 0.f;
         }
-        const float inv = den > 0.f ? 1.f / den : 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) sl_m[tid * p.S + sidx] *= inv;
+    } else {
+        float* sl_l = red_o + G * p.S;    // [G][S] sum
+        for (int idx = tid; idx < G * S; idx += NT) {
+            const int h = idx / S, sidx = idx - h * S;
+            sl_m[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2]);
+            sl_l[h * p.S + sidx] = __ldcg(&p.part_ml[((head0 + h) * p.S + sidx) * 2 + 1]);
+        }
+        sync();
+        if (tid < G) {
+            float mx = -INFINITY, den = 0.f;
+            for (int sidx = 0; sidx < S; ++sidx) mx = fmaxf(mx, sl_m[tid * p.S + sidx]);
+            for (int sidx = 0; sidx < S; ++sidx) {
+                const float l = sl_l[tid * p.S + sidx];
+                const float w = l > 0.f ? __expf(sl_m[tid * p.S + sidx] - mx) * l : 0.f;
+                sl_m[tid * p.S + sidx] = w;
+                den += w;
+            }
+            const float inv = den > 0.f ? 1.f / den : 0.f;
+            for (int sidx = 0; sidx < S; ++sidx) sl_m[tid * p.S + sidx] *= inv;
+        }
     }
     sync();
-    for (int idx = tid; idx < G * D; idx += NT) {
-        const int h = idx / D, d = idx - h * D;
+    // four dims per thread and sixteen slices per batch of loads: the partial outputs come from L2,
+    // and one CTA reads all of them, so as many loads as possible are in flight at once
+    const int D4 = D >> 2;                   // D is a multiple of 4
+    for (int idx = tid; idx < G * D4; idx += NT) {
+        const int h = idx / D4, d = (idx - h * D4) * 4;
         const float* po = p.part_o + (head0 + h) * p.S * D + d;
-        float num = 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) num += sl_m[h * p.S + sidx] * __ldcg(po + (int64_t)sidx * D);
-        p.out[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(num);
-        if (p.tap) p.tap[(int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d] = __float2bfloat16_rn(num);
+        float num[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s0 = 0; s0 < S; s0 += 16) {
+            float4 v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                v[u] = s0 + u < S ? __ldcg(reinterpret_cast<const float4*>(po + (int64_t)(s0 + u) * D)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {       // slices in their order, as a scalar loop would add them
+                const float w = s0 + u < S ? sl_m[h * p.S + s0 + u] : 0.f;
+                num[0] += w * v[u].x; num[1] += w * v[u].y; num[2] += w * v[u].z; num[3] += w * v[u].w;
+            }
+        }
+        const int64_t oi = (int64_t)b * p.H * D + (kvh * Gfull + h0 + h) * D + d;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            p.out[oi + e] = __float2bfloat16_rn(num[e]);
+            if (p.tap) p.tap[oi + e] = __float2bfloat16_rn(num[e]);
+        }
     }
     return true;
 }

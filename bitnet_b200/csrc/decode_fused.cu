@@ -433,7 +433,7 @@ static size_t attention_smem_nw(const AttentionParams& p, int nw) {
 }
 size_t attention_smem(const AttentionParams& p) {
     const int G = p.H / p.Hkv;
-    return attention_smem_nw(p, G <= 4 ? 16 : (G <= 8 ? 8 : 4));
+    return attention_smem_nw(p, G <= 4 ? 16 : 4);
 }
 
 int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, bool pdl, bool many_sequences) {

@@ -108,6 +108,7 @@ struct ChainLinearParams {
     int units_max;                   // most units a CTA owns
     int units_base, units_rem;       // CTA c owns units_base units, one more if c < units_rem
     int grid, M, ring_stages;
+    int big_share;                   // a CTA's share passes through the ring more than once (set by plan_chain_linear)
     int out_kind;
     // source
     const float* t;                  // [M, ldt]

@@ -198,7 +198,7 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     if (size < 1 || size > kMaxTp || rank < 0 || rank >= size || (size > 1 && !areas)) return set_status(kBadArgument), nullptr;
     const int B = cfg->batch, D = cfg->head_dim;
     if (B < 1 || B > 8 || cfg->n_layers < 1 || cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->n_heads % cfg->n_kv_heads != 0 ||
-        cfg->n_heads / cfg->n_kv_heads > 16 || D % 4 != 0 || D > 128 || cfg->dim % 8 != 0 || cfg->dim != cfg->n_heads * D ||
+        cfg->n_heads / cfg->n_kv_heads > 16 || D % 4 != 0 || D > 128 || cfg->dim % 8 != 0 || (cfg->n_heads * D) % 8 != 0 ||
         cfg->ffn_dim % 16 != 0 || cfg->max_seq_len < 2 || cfg->vocab_size < 1)
         return set_status(kUnsupported), nullptr;
     // this rank's share: whole kv-head groups, a slice of the feed-forward width and of the vocabulary
@@ -235,7 +235,7 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->n_sm = prop.multiProcessorCount;
     const int H = d->loc.n_heads, Hkv = d->loc.n_kv_heads, F = d->loc.ffn_dim;
     int s = d->n_sm / (Hkv * B);
-    d->kv_splits = s < 1 ? 1 : (s > 16 ? 16 : s);
+    d->kv_splits = s < 1 ? 1 : (s > 32 ? 32 : s);
     d->head_grid = d->n_sm < kTpHeadGridMax ? d->n_sm : kTpHeadGridMax;
 
     const int dim = cfg->dim, Nqkv = (H + 2 * Hkv) * D, Ko = H * D;
@@ -247,6 +247,14 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         if (getenv("BITNET_RING_STAGES")) p.ring_stages = atoi(getenv("BITNET_RING_STAGES"));   // measurement builds only
 #endif
         plan_chain_linear(p, d->n_sm);
+        if (p.big_share) {     // a long stream per CTA: the larger ring, where shared memory allows it
+            p.ring_stages = 8;
+            plan_chain_linear(p, d->n_sm);
+            if (chain_linear_smem(p) > (size_t)prop.sharedMemPerBlockOptin) {
+                p.ring_stages = 4;
+                plan_chain_linear(p, d->n_sm);
+            }
+        }
     };
     const bool tp = size > 1;
     plan(d->plan_qkv, Nqkv, dim, dim, kOutBf16);
@@ -645,7 +653,7 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
     Workspace* w = workspace();
     if (!w) return bitnet_last_status();
     int s = w->n_sm / (n_kv_heads * batch);
-    s = s < 1 ? 1 : (s > 16 ? 16 : s);
+    s = s < 1 ? 1 : (s > 32 ? 32 : s);
     const size_t need = (size_t)batch * n_heads * s * (head_dim + 2) * sizeof(float);
     if (need > w->attn_part_bytes) {      // grows outside stream capture only (cudaMalloc)
         std::lock_guard<std::mutex> lock(g_ws_mutex);

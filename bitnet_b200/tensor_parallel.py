@@ -311,9 +311,12 @@ class TPFusedStep:
     `out` holds the chosen ids.  Every rank must build it and call `step()` in step."""
 
     def __init__(self, dec: "TPDecoder", batch: int, max_seq_len: int, group=None, wait_limit_ms: Optional[float] = None,
-                 absent_peers: bool = False):
+                 absent_peers: bool = False, local_only: bool = False):
         """absent_peers=True (for tests of the bounded waits): the other ranks' exchange areas are
-        plain buffers of this process that nobody ever writes to, and no process group is used."""
+        plain buffers of this process that nobody ever writes to, and no process group is used.
+        local_only=True (for timing): this rank's shards run as a model of their own, with no
+        exchange at all - the same weight bytes and kernels minus the peer traffic and the waits,
+        so that the difference to the real step is the cost of the exchange."""
         import ctypes
 
         from . import _lib
@@ -330,6 +333,10 @@ class TPFusedStep:
                              a.norm_eps, batch, max_seq_len)
         L = _lib.lib
         world, rank = dec.world, dec.rank
+        if local_only:
+            cfg = _DecoderConfig(a.dim, a.n_layers, dec.Hl, dec.Hkvl, a.head_dim, a.ffn_dim // world,
+                                 a.vocab_size // world, a.norm_eps, batch, max_seq_len)
+            world, rank = 1, 0
         self._area, self._peers = None, []
         areas = (ctypes.c_void_p * max(world, 1))()
         if world > 1:
@@ -379,6 +386,7 @@ class TPFusedStep:
             _lib.check(L.bitnet_decoder_set_wait_limit(self.handle, float(wait_limit_ms)))
         if world > 1 and not absent_peers:
             dist.barrier(group=group)       # every rank has mapped every area before anybody steps
+        self.world = world
         self._lib = _lib
         self.kernels_per_step = L.bitnet_decoder_kernels_per_step(self.handle)
 

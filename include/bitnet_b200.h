@@ -141,6 +141,8 @@ typedef struct bitnet_decoder_layer {
 
 /* tok_embeddings bf16 [vocab, dim]; norm bf16 [dim]; output bf16 [vocab, dim]; rope f32
  * [max_seq_len, head_dim/2, 2] (cos, sin).  dim and ffn_dim must be multiples of 8 and 16.
+ * wo maps n_heads*head_dim values to dim; the two need not be equal (a tensor-parallel shard of a
+ * model, run on its own, is a valid configuration).
  * Allocates the decoder's scratch buffers (the only allocation; do it outside stream
  * capture).  Returns NULL on failure (see bitnet_last_status). */
 void* bitnet_decoder_create(const bitnet_decoder_config* cfg, const bitnet_decoder_layer* layers,

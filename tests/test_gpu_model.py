@@ -46,7 +46,12 @@ def test_attention_kernel_matches_pytorch_attention(models):
 
     for B, H, Hkv, D, L, P in [(1, 20, 5, 128, 256, 200), (3, 8, 2, 64, 64, 5), (2, 32, 32, 100, 96, 37),
                                (2, 80, 8, 128, 128, 0), (64, 8, 8, 128, 64, 33), (64, 20, 5, 128, 256, 140),
-                               (70, 32, 8, 128, 640, 600)]:
+                               (70, 32, 8, 128, 640, 600),
+                               # groups of more than four query heads: the tensor-core key loop, one and several
+                               # slices, slice ends inside and at the end of a 16-key step
+                               (1, 10, 1, 128, 4224, 4096), (2, 80, 8, 128, 1100, 1000), (1, 16, 2, 128, 512, 15),
+                               (1, 16, 2, 128, 512, 16), (3, 12, 2, 128, 512, 17), (1, 10, 1, 128, 512, 383),
+                               (2, 20, 2, 128, 2176, 2049), (8, 10, 1, 128, 640, 531)]:
         g = torch.Generator("cuda").manual_seed(B * 100 + H)
         xqkv = torch.randn((B, (H + 2 * Hkv) * D), device="cuda", generator=g).bfloat16()
         ck = torch.randn((B, L, Hkv, D), device="cuda", generator=g).bfloat16()
