@@ -67,6 +67,17 @@ __device__ __forceinline__ void stat_add(StatPart* slot, double ss, float mx, bo
     }
 }
 
+// Tensor parallel, last CTA of a grid: this GPU's total in `local` goes to the slot at `off` of
+// every rank's area, and `local` is cleared for its next use.
+__device__ __forceinline__ void stat_forward(const TpPeers& tp, size_t off, int m, StatPart* local) {
+    const double ss = __ldcg(&local[m].ss);
+    const double mxd = __ldcg(&local[m].mx);
+    local[m].ss = 0.0;
+    local[m].mx = 0.0;
+#pragma unroll 1
+    for (int pr = 0; pr < tp.size; ++pr) stat_add(reinterpret_cast<StatPart*>(tp.area[pr] + off) + m, ss, (float)mxd, true);
+}
+
 struct ChainSmem {
     uint8_t* ring;
     uint64_t *full_bar, *empty_bar;
@@ -548,25 +559,27 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 ss += sm.stat_d[tid * p.units_max + lu];
                 mx = fmaxf(mx, sm.stat_f[tid * p.units_max + lu]);
             }
-            if (p.tp.size > 1) {     // every rank normalises over the whole vector: the slot in every rank's area
-#pragma unroll 1
-                for (int pr = 0; pr < p.tp.size; ++pr)
-                    stat_add(reinterpret_cast<StatPart*>(p.tp.area[pr] + p.tp_stats_off) + tid, ss, mx, true);
-                __threadfence_system();
-            } else {
-                stat_add(p.stats_out + tid, ss, mx, false);
-            }
+            stat_add(p.stats_out + tid, ss, mx, false);
         }
-        if (p.tp.size > 1 && real) {
-            __syncwarp();            // the M adding threads are lanes of warp 0
-            if (tid == 0) tp_signal(p.tp, p.tp_stats_flag_off);
+        if (p.tp.size > 1 && real && warp == 0) {
+            // Every rank normalises over the whole vector.  This GPU's CTAs add up in its own slot;
+            // the last of them forwards the total to the slot in every rank's area and signals.
+            __syncwarp();            // the M adding threads are lanes of this warp
+            int last = 0;
+            if (lane == 0) last = tp_last_cta(p.tp_ticket, (unsigned int)gridDim.x, false) ? 1 : 0;
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                if (lane < p.M) stat_forward(p.tp, p.tp_stats_off, lane, p.stats_out);
+                __threadfence_system();
+                __syncwarp();
+                if (lane == 0) tp_signal(p.tp, p.tp_stats_flag_off);
+            }
         }
     }
     if (p.out_kind == kOutTpPartial && real) {
         if (cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
-        __threadfence_system();
         chain_sync();
-        if (tid == 0) tp_signal(p.tp, p.tp_part_flag_off);
+        if (tid == 0 && tp_last_cta(p.tp_ticket, (unsigned int)gridDim.x, true)) tp_signal(p.tp, p.tp_part_flag_off);
     }
     CHAIN_STAMP(5)
     }
@@ -701,13 +714,14 @@ __device__ __forceinline__ void publish_head_stats(const AttentionParams& p, int
     if (tid == 0) {
         ss = sd[0] + sd[1] + sd[2] + sd[3];          // D <= 128: the values sit in the first four warps
         mx = fmaxf(fmaxf(sf[0], sf[1]), fmaxf(sf[2], sf[3]));
-        if (p.tp.size > 1) {     // every rank's wo normalises over all heads: the slot in every rank's area
+        stat_add(p.stats_out + b, ss, mx, false);
+        // Tensor parallel: every rank's wo normalises over all heads.  This GPU's heads add up in its
+        // own slots; the CTA that delivers the last head forwards the totals of all sequences to the
+        // slots in every rank's area and signals.
+        if (p.tp.size > 1 && tp_last_cta(p.tp_ticket, (unsigned int)(gridDim.y * p.H), false)) {
 #pragma unroll 1
-            for (int pr = 0; pr < p.tp.size; ++pr)
-                stat_add(reinterpret_cast<StatPart*>(p.tp.area[pr] + p.tp_stats_off) + b, ss, mx, true);
+            for (int m = 0; m < (int)gridDim.y; ++m) stat_forward(p.tp, p.tp_stats_off, m, p.stats_out);
             tp_signal(p.tp, p.tp_stats_flag_off);
-        } else {
-            stat_add(p.stats_out + b, ss, mx, false);
         }
     }
 }

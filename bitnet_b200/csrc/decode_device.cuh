@@ -92,6 +92,23 @@ __device__ __forceinline__ void tp_signal(const TpPeers& tp, size_t flag_off) {
         atomicAdd_system(reinterpret_cast<unsigned long long*>(tp.area[r] + flag_off), 1ull);
 }
 
+// One thread per CTA, after a CTA barrier: counts the CTA in on a ticket in this GPU's own memory
+// and returns true for the last of n_cta, which then speaks for the whole grid to the other ranks.
+// (One arrival per rank instead of one per CTA: atomics of many CTAs on one address in another
+// GPU's memory are served one NVLink round trip after the other.)  remote_data: threads of the CTA
+// stored to other ranks' areas before the barrier; this thread's system-scope fence then orders
+// those stores (which happen before it through the barrier) ahead of the ticket, so that the last
+// CTA's signal covers them - one fence per CTA instead of one per storing thread.
+__device__ __forceinline__ bool tp_last_cta(unsigned int* ticket, unsigned int n_cta, bool remote_data) {
+    if (remote_data) __threadfence_system();
+    else __threadfence();
+    const unsigned int t = atomicAdd(ticket, 1u);
+    if (t + 1 != n_cta) return false;
+    atomicExch(ticket, 0u);          // every CTA has drawn: ready for the kernel's next launch
+    __threadfence();
+    return true;
+}
+
 // bf16( float(acc) / a * ws ): the rescale of gpu/bitnet_kernels/bitnet_kernels.h:82
 __device__ __forceinline__ float lin_out(int acc, float a, float ws) { return bf16_round(__fdiv_rn((float)acc, a) * ws); }
 
@@ -746,7 +763,6 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
                 reinterpret_cast<float*>(p.tp.area[pr] + p.tp_val_off)[at] = v;
                 reinterpret_cast<int*>(p.tp.area[pr] + p.tp_idx_off)[at] = i;
             }
-            __threadfence_system();
         } else {
             p.part_val[cta * 8 + tid] = v;
             p.part_idx[cta * 8 + tid] = i;
@@ -754,7 +770,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
     }
     if (p.tp.size > 1 && tid < 32) {
         __syncwarp();            // the M storing threads are lanes of warp 0
-        if (tid == 0) tp_signal(p.tp, p.tp_flag_off);
+        if (tid == 0 && tp_last_cta(p.tp_ticket, (unsigned int)n_cta, true)) tp_signal(p.tp, p.tp_flag_off);
     }
 }
 

@@ -132,6 +132,7 @@ struct ChainLinearParams {
     size_t tp_stats_off, tp_stats_flag_off;   // kOutGlu: statistics slot and arrival counter in every area
     size_t tp_part_off, tp_part_flag_off;     // kOutTpPartial: int32 [size][M][N] and arrival counter in every area
     float* a_out;                    // kOutTpPartial: [M] activation scales for the reduction kernel
+    unsigned int* tp_ticket;         // tensor parallel: this GPU's count of CTAs that have delivered (see tp_last_cta)
     int* error_flag;
     unsigned long long* trace;       // phase timestamps of CTA 0 (only in builds with BITNET_TRACE)
 };
@@ -184,6 +185,7 @@ struct AttentionParams {
     StatPart* zero_slot;             // [B] slot to clear, or null
     TpPeers tp;                      // tensor parallel: the statistics go to the slot at this offset of every area
     size_t tp_stats_off, tp_stats_flag_off;
+    unsigned int* tp_ticket;         // tensor parallel: this GPU's count of heads whose statistics are in stats_out
     __nv_bfloat16* tap;              // optional second copy of `out` (for checkers)
     int* error_flag;
     unsigned long long* trace;
@@ -202,6 +204,7 @@ struct HeadParams {
     int row_offset;                  // added to the reported indices (vocabulary slice of a rank)
     TpPeers tp;                      // tensor parallel: the per-CTA maxima go to [size][grid][8] of every area
     size_t tp_val_off, tp_idx_off, tp_flag_off;
+    unsigned int* tp_ticket;         // tensor parallel: this GPU's count of CTAs that have delivered
 };
 
 struct ArgmaxParams {

@@ -166,6 +166,8 @@ struct Decoder {
     TpPeers tp{};
     bitnet_decoder_config loc{};
     unsigned long long* step_ctr = nullptr;       // steps this decoder has completed (device)
+    unsigned int* tickets = nullptr;              // tensor parallel: per exchange point, CTAs of this GPU that have delivered (64 bytes apart)
+    unsigned int* ticket(int which) const { return tickets + 16 * which; }
     float *a_o = nullptr, *a_2 = nullptr;         // activation scales handed from wo / w2 to their reductions
     long long wait_limit = kPeerWaitCyclesDefault;  // SM cycles a kernel waits for another rank before it gives up
 
@@ -174,6 +176,7 @@ struct Decoder {
     StatPart* slot(int layer, int which) const { return stats + (size_t)(1 + 4 * layer + which) * cfg.batch; }
 };
 enum { kSlotAtt = 0, kSlotHo = 1, kSlotGlu = 2, kSlotH2 = 3 };
+enum { kTickAtt = 0, kTickO = 1, kTickGlu = 2, kTick2 = 3, kTickHead = 4 };
 
 static size_t align_up(size_t x) { return (x + 255) / 256 * 256; }
 
@@ -282,7 +285,7 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     // one zero-initialised scratch allocation
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += align_up(bytes); return o; };
-    const size_t o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_step = take(8), o_ao = take((size_t)B * 4),
+    const size_t o_actr = take((size_t)B * Hkv * 4), o_err = take(4), o_step = take(8), o_tick = take(8 * 64), o_ao = take((size_t)B * 4),
                  o_a2 = take((size_t)B * 4), o_h = take((size_t)B * dim * 2), o_qkv = take((size_t)B * Nqkv * 2),
                  o_att = take((size_t)B * Ko * 2), o_th = take((size_t)B * dim * 4), o_tatt = take((size_t)B * Ko * 4),
                  o_tglu = take((size_t)B * F * 4), o_st = take((size_t)(1 + 4 * cfg->n_layers) * B * sizeof(StatPart)),
@@ -297,6 +300,7 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
     d->attn_counters = reinterpret_cast<int*>(base + o_actr);
     d->error_flag = reinterpret_cast<int*>(base + o_err);
     d->step_ctr = reinterpret_cast<unsigned long long*>(base + o_step);
+    d->tickets = reinterpret_cast<unsigned int*>(base + o_tick);
     d->a_o = reinterpret_cast<float*>(base + o_ao);
     d->a_2 = reinterpret_cast<float*>(base + o_a2);
     d->h = reinterpret_cast<__nv_bfloat16*>(base + o_h);
@@ -412,7 +416,7 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
     ap->tap = d->attn_tap ? d->attn_tap + (size_t)l * c.batch * Ko : nullptr;
     ap->error_flag = d->error_flag;
     if (tp) {     // all ranks' wo normalise over all heads
-        ap->tp = d->tp; ap->tp_stats_off = area_slot(0); ap->tp_stats_flag_off = lay.flag_att;
+        ap->tp = d->tp; ap->tp_stats_off = area_slot(0); ap->tp_stats_flag_off = lay.flag_att; ap->tp_ticket = d->ticket(kTickAtt);
     }
 
     // wo: t_att (= attention output * attn_sub_norm) -> h += ...; t_h = h * ffn_norm
@@ -427,12 +431,12 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
         o.gamma_out = bf(L.ffn_norm); o.t_out = d->t_h; o.ldt_out = dim; o.stats_out = d->slot(l, kSlotHo);
     } else {
         o.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(0));
-        o.stats_wait = wait_on(lay.flag_att, (unsigned long long)c.batch * c.n_heads);
-        o.tp = d->tp; o.tp_part_off = lay.part_o; o.tp_part_flag_off = lay.flag_o; o.a_out = d->a_o;
+        o.stats_wait = wait_on(lay.flag_att, (unsigned long long)T);     // one arrival per rank and exchange
+        o.tp = d->tp; o.tp_part_off = lay.part_o; o.tp_part_flag_off = lay.flag_o; o.a_out = d->a_o; o.tp_ticket = d->ticket(kTickO);
         TpReduceParams& r = red[0];
         r = TpReduceParams{};
         r.part = reinterpret_cast<const int32_t*>(my + lay.part_o);
-        r.wait = wait_on(lay.flag_o, (unsigned long long)T * d->plan_o.grid);
+        r.wait = wait_on(lay.flag_o, (unsigned long long)T);
         r.a = d->a_o; r.ws = L.s_o; r.out = d->h; r.ldo = dim;
         r.gamma_out = bf(L.ffn_norm); r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotHo);
         r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(0));     // its consumer, wo, has run
@@ -449,7 +453,7 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
     u.seg.n_seg = 2; u.seg.end[0] = F; u.seg.end[1] = 2 * F; u.ws[0] = L.s_1; u.ws[1] = L.s_3;
     u.gamma_out = bf(L.ffn_sub_norm) + (size_t)rank * F; u.t_out = d->t_glu; u.ldt_out = F; u.stats_out = d->slot(l, kSlotGlu);
     if (tp) {     // all ranks' w2 normalise over the whole gated vector
-        u.tp = d->tp; u.tp_stats_off = area_slot(1); u.tp_stats_flag_off = lay.flag_glu;
+        u.tp = d->tp; u.tp_stats_off = area_slot(1); u.tp_stats_flag_off = lay.flag_glu; u.tp_ticket = d->ticket(kTickGlu);
     }
 
     // w2: t_glu -> h += ...; t_h = h * (the next layer's attention_norm, or the final norm)
@@ -466,12 +470,12 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
         w.gamma_out = g_next; w.t_out = d->t_h; w.ldt_out = dim; w.stats_out = d->slot(l, kSlotH2);
     } else {
         w.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(1));
-        w.stats_wait = wait_on(lay.flag_glu, (unsigned long long)T * d->plan_13.grid);
-        w.tp = d->tp; w.tp_part_off = lay.part_2; w.tp_part_flag_off = lay.flag_2; w.a_out = d->a_2;
+        w.stats_wait = wait_on(lay.flag_glu, (unsigned long long)T);
+        w.tp = d->tp; w.tp_part_off = lay.part_2; w.tp_part_flag_off = lay.flag_2; w.a_out = d->a_2; w.tp_ticket = d->ticket(kTick2);
         TpReduceParams& r = red[1];
         r = TpReduceParams{};
         r.part = reinterpret_cast<const int32_t*>(my + lay.part_2);
-        r.wait = wait_on(lay.flag_2, (unsigned long long)T * d->plan_2.grid);
+        r.wait = wait_on(lay.flag_2, (unsigned long long)T);
         r.a = d->a_2; r.ws = L.s_2; r.out = d->h; r.ldo = dim;
         r.gamma_out = g_next; r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotH2);
         r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(1));     // its consumer, w2, has run
@@ -489,6 +493,7 @@ static HeadParams head_params(const Decoder* d, float* logits) {
         const TpLayout lay = tp_layout(d->cfg, d->tp.size, kTpHeadGridMax);
         hp.row_offset = d->tp.rank * d->loc.vocab_size;
         hp.tp = d->tp; hp.tp_val_off = lay.head_val; hp.tp_idx_off = lay.head_idx; hp.tp_flag_off = lay.flag_head;
+        hp.tp_ticket = d->ticket(kTickHead);
     }
     return hp;
 }
@@ -534,7 +539,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
         am.n_part = d->tp.size * d->head_grid;
         am.wait.flag = reinterpret_cast<const unsigned long long*>(my + lay.flag_head);
         am.wait.step = d->step_ctr;
-        am.wait.per_step = (unsigned long long)d->tp.size * d->head_grid;
+        am.wait.per_step = (unsigned long long)d->tp.size;
         am.wait.base = am.wait.per_step;
         am.wait.limit_cycles = d->wait_limit;
     }
@@ -576,6 +581,7 @@ int bitnet_decoder_clear_error(void* dec) {
     // statistics slots (a step that ended early may have left shares in them)
     if (check_cuda(cudaDeviceSynchronize()) || check_cuda(cudaMemset(d->error_flag, 0, sizeof(int))) ||
         check_cuda(cudaMemset(d->attn_counters, 0, (size_t)d->cfg.batch * d->cfg.n_kv_heads * sizeof(int))) ||
+        check_cuda(cudaMemset(d->tickets, 0, 8 * 64)) ||
         check_cuda(cudaMemset(d->stats, 0, (size_t)(1 + 4 * d->cfg.n_layers) * d->cfg.batch * sizeof(StatPart))))
         return kCudaError;
     return kOk;
