@@ -67,15 +67,14 @@ __device__ __forceinline__ void stat_add(StatPart* slot, double ss, float mx, bo
     }
 }
 
-// Tensor parallel, last CTA of a grid: this GPU's total in `local` goes to the slot at `off` of
+// Tensor parallel, last CTA of a grid: this GPU's total of token m in `local` goes to its packets in
 // every rank's area, and `local` is cleared for its next use.
-__device__ __forceinline__ void stat_forward(const TpPeers& tp, size_t off, int m, StatPart* local) {
+__device__ __forceinline__ void stat_forward(const TpPeers& tp, size_t off, int M, int m, StatPart* local, unsigned int tag) {
     const double ss = __ldcg(&local[m].ss);
     const double mxd = __ldcg(&local[m].mx);
     local[m].ss = 0.0;
     local[m].mx = 0.0;
-#pragma unroll 1
-    for (int pr = 0; pr < tp.size; ++pr) stat_add(reinterpret_cast<StatPart*>(tp.area[pr] + off) + m, ss, (float)mxd, true);
+    tp_put_stats(tp, off, M, m, ss, (float)mxd, tag);
 }
 
 struct ChainSmem {
@@ -227,10 +226,6 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             p.zero_slot[tid].ss = 0.0;
             p.zero_slot[tid].mx = 0.0;
         }
-        if (p.stats_wait.flag) {      // tensor parallel: other ranks add to the statistics; every warp waits for itself
-            if (lane == 0 && !tp_wait(p.stats_wait)) atomicExch(p.error_flag, kErrPeerWait);
-            __syncwarp();
-        }
     }
 
     // ---- prologue: int8 activations of every token into shared memory ----------------------
@@ -238,7 +233,8 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     // (one 16-byte load, the same for all threads), derives the factors itself and writes 8 bytes.
 #pragma unroll 1
     for (int m = 0; m < p.M; ++m) {
-        const double2 st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
+        double2 st = make_double2(0.0, 0.0);
+        if (!p.tp_stats_in) st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
         const float* tm = p.t + (int64_t)m * p.ldt;
         constexpr int kIt = 1024 / kCThreads;               // vectors of up to 8192 values: all loads in flight at once
         float4 lo[kIt], hi[kIt];
@@ -249,6 +245,18 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 lo[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8));
                 hi[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
             }
+        }
+        if (p.tp_stats_in) {
+            // tensor parallel: the statistics are the sum over all ranks' packets; lane 0 of every warp
+            // gathers them (this rank's own vector is already on its way: the loads above)
+            double ss = 0.0;
+            float mx = 0.f;
+            // (a step that has already given up somewhere does not wait again)
+            if (lane == 0 && !tp_get_stats(p.tp_stats_in, p.tp.size, p.M, m, tp_tag(p.tp_tag_in),
+                                           __ldcg(p.error_flag) ? 0 : p.tp_tag_in.limit_cycles, ss, mx))
+                atomicExch(p.error_flag, kErrPeerWait);
+            st.x = __shfl_sync(0xffffffffu, ss, 0);
+            st.y = (double)__shfl_sync(0xffffffffu, mx, 0);
         }
         float rinv, a;
         finish_stats(st.x, (float)st.y, p.k_norm, p.eps, true, rinv, a);
@@ -484,6 +492,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     // Thread idx finalises output r of unit lu for token m; 16 consecutive threads hold the 16
     // outputs of one unit and token, and reduce their statistics by shuffles.
     const bool want_stats = p.stats_out != nullptr;
+    const unsigned int part_tag = p.out_kind == kOutTpPartial ? tp_tag(p.tp_tag_out) : 0u;
 #pragma unroll 1
     for (int base = 0; base < total_out; base += kCThreads) {
         const int idx = base + tid;
@@ -516,10 +525,10 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             const int ys_m = sm.ysum_s[m];                  // fields hold weight + 1: take sum(y) off once per row
             const int v0 = sm.sacc[lu * 128 + r * 8 + m] - ys_m;
             if (p.out_kind == kOutTpPartial) {
-                // this rank's exact partial sums, to slot [rank][m][row] of every rank's area
-                const size_t at = p.tp_part_off + (((size_t)p.tp.rank * p.M + m) * p.N + row) * sizeof(int32_t);
+                // this rank's exact partial sums, as packets [rank][m][row] of every rank's area
+                const size_t at = p.tp_part_off + (((size_t)p.tp.rank * p.M + m) * p.N + row) * sizeof(uint2);
 #pragma unroll 1
-                for (int pr = 0; pr < p.tp.size && real; ++pr) *reinterpret_cast<int32_t*>(p.tp.area[pr] + at) = v0;
+                for (int pr = 0; pr < p.tp.size && real; ++pr) tp_put(p.tp.area[pr] + at, (unsigned int)v0, part_tag);
             } else {
                 if (p.out_kind == kOutGlu) {
                     const int v1 = sm.sacc[(nu + lu) * 128 + r * 8 + m] - ys_m;
@@ -563,24 +572,15 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
         }
         if (p.tp.size > 1 && real && warp == 0) {
             // Every rank normalises over the whole vector.  This GPU's CTAs add up in its own slot;
-            // the last of them forwards the total to the slot in every rank's area and signals.
+            // the last of them forwards the total to its packets in every rank's area.
             __syncwarp();            // the M adding threads are lanes of this warp
             int last = 0;
-            if (lane == 0) last = tp_last_cta(p.tp_ticket, (unsigned int)gridDim.x, false) ? 1 : 0;
+            if (lane == 0) last = tp_last_cta(p.tp_ticket, (unsigned int)gridDim.x) ? 1 : 0;
             last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                if (lane < p.M) stat_forward(p.tp, p.tp_stats_off, lane, p.stats_out);
-                __threadfence_system();
-                __syncwarp();
-                if (lane == 0) tp_signal(p.tp, p.tp_stats_flag_off);
-            }
+            if (last && lane < p.M) stat_forward(p.tp, p.tp_stats_off, p.M, lane, p.stats_out, tp_tag(p.tp_tag_out));
         }
     }
-    if (p.out_kind == kOutTpPartial && real) {
-        if (cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
-        chain_sync();
-        if (tid == 0 && tp_last_cta(p.tp_ticket, (unsigned int)gridDim.x, true)) tp_signal(p.tp, p.tp_part_flag_off);
-    }
+    if (p.out_kind == kOutTpPartial && real && cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
     CHAIN_STAMP(5)
     }
 }
@@ -641,12 +641,8 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpReduceParams p) 
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x;
-    if (p.zero_slot && blockIdx.x == 0 && tid < p.M) {
-        p.zero_slot[tid].ss = 0.0;
-        p.zero_slot[tid].mx = 0.0;
-    }
-    if (tid == 0 && !tp_wait(p.wait)) atomicExch(p.error_flag, kErrPeerWait);
-    __syncthreads();
+    const unsigned int tag = tp_tag(p.tag);
+    long long limit = __ldcg(p.error_flag) ? 0 : p.tag.limit_cycles;    // a step that has already given up does not wait again
     const int row = blockIdx.x * 256 + tid;
     const float gq = row < p.N ? __bfloat162float(p.gamma_out[row]) : 0.f;
 #pragma unroll 1
@@ -654,8 +650,17 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpReduceParams p) 
         float o = 0.f;
         if (row < p.N) {
             int v = 0;
+            bool ok = true;
 #pragma unroll 1
-            for (int r = 0; r < p.T; ++r) v += __ldcg(p.part + ((size_t)r * p.M + m) * p.N + row);   // integer sums: any order
+            for (int r = 0; r < p.T; ++r) {          // every thread waits for its own packets; integer sums: any order
+                unsigned int x;
+                ok = tp_get(p.part + ((size_t)r * p.M + m) * p.N + row, tag, limit, x) && ok;
+                v += (int)x;
+            }
+            if (!ok) {
+                atomicExch(p.error_flag, kErrPeerWait);
+                limit = 0;
+            }
             const float h_old = __bfloat162float(p.out[(int64_t)m * p.ldo + row]);
             o = bf16_round(h_old + lin_out(v, p.a[m], p.ws));
             p.out[(int64_t)m * p.ldo + row] = __float2bfloat16_rn(o);
@@ -717,11 +722,11 @@ __device__ __forceinline__ void publish_head_stats(const AttentionParams& p, int
         stat_add(p.stats_out + b, ss, mx, false);
         // Tensor parallel: every rank's wo normalises over all heads.  This GPU's heads add up in its
         // own slots; the CTA that delivers the last head forwards the totals of all sequences to the
-        // slots in every rank's area and signals.
-        if (p.tp.size > 1 && tp_last_cta(p.tp_ticket, (unsigned int)(gridDim.y * p.H), false)) {
+        // packets in every rank's area.
+        if (p.tp.size > 1 && tp_last_cta(p.tp_ticket, (unsigned int)(gridDim.y * p.H))) {
+            const unsigned int tag = tp_tag(p.tp_tag_out);
 #pragma unroll 1
-            for (int m = 0; m < (int)gridDim.y; ++m) stat_forward(p.tp, p.tp_stats_off, m, p.stats_out);
-            tp_signal(p.tp, p.tp_stats_flag_off);
+            for (int m = 0; m < (int)gridDim.y; ++m) stat_forward(p.tp, p.tp_stats_off, (int)gridDim.y, m, p.stats_out, tag);
         }
     }
 }

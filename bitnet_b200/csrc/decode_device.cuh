@@ -64,44 +64,69 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
-// ---- tensor-parallel exchange (see TpPeers in decode_fused.h) ---------------------------------
+// ---- tensor-parallel exchange (see TpPeers and TpTag in decode_fused.h) ------------------------
 constexpr long long kPeerWaitCycles = 600000000LL;       // default limit of a wait for another rank: about 0.3 s
 
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ unsigned int tp_tag(const TpTag& t) {
+    return (unsigned int)(__ldcg(t.step) * t.mul + t.add);
 }
-// One thread: waits until the arrival counter has reached this step's target.  False after the
-// time limit (the caller records kErrPeerWait and carries on with whatever is there, so that the
-// kernel ends and the host can read the error word).
-__device__ __noinline__ bool tp_wait(const TpWait& w) {
-    const unsigned long long target = __ldcg(w.step) * w.per_step + w.base;
-    const long long t0 = clock64();
-    while (ld_acquire_sys(w.flag) < target) {
-        if (clock64() - t0 > w.limit_cycles) return false;
+// One packet into (possibly another rank's) memory: a single 8-byte store, nothing to follow it.
+__device__ __forceinline__ void tp_put(void* addr, unsigned int value, unsigned int tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(addr), "r"(value), "r"(tag) : "memory");
+}
+// Reads a packet of this rank's area once it carries `tag`.  False after the time limit (the caller
+// records kErrPeerWait and carries on with whatever is there, so that the kernel ends and the host
+// can read the error word).
+__device__ __forceinline__ bool tp_get(const void* addr, unsigned int tag, long long limit_cycles, unsigned int& value) {
+    unsigned int v, t;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(v), "=r"(t) : "l"(addr) : "memory");
+    if (t != tag) {
+        const long long t0 = clock64();
+        do {
+            if (clock64() - t0 > limit_cycles) { value = v; return false; }
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(v), "=r"(t) : "l"(addr) : "memory");
+        } while (t != tag);
     }
+    value = v;
     return true;
 }
-// One thread, after a CTA barrier behind which every thread that stored to the peers' areas has
-// executed __threadfence_system(): counts this CTA in on every rank.
-__device__ __forceinline__ void tp_signal(const TpPeers& tp, size_t flag_off) {
-    __threadfence_system();
+// A rank's statistics of one token to slot [rank][m] of every rank's area.
+__device__ __forceinline__ void tp_put_stats(const TpPeers& tp, size_t off, int M, int m, double ss, float mx, unsigned int tag) {
+    const unsigned long long b = (unsigned long long)__double_as_longlong(ss);
 #pragma unroll 1
-    for (int r = 0; r < tp.size; ++r)
-        atomicAdd_system(reinterpret_cast<unsigned long long*>(tp.area[r] + flag_off), 1ull);
+    for (int pr = 0; pr < tp.size; ++pr) {
+        TpStatPackets* dst = reinterpret_cast<TpStatPackets*>(tp.area[pr] + off) + (size_t)tp.rank * M + m;
+        tp_put(&dst->w[0], (unsigned int)b, tag);
+        tp_put(&dst->w[2], (unsigned int)(b >> 32), tag);
+        tp_put(&dst->w[4], __float_as_uint(mx), tag);
+    }
+}
+// All ranks' statistics of token m from this rank's area, added in the order of the ranks (the same
+// sum on every rank).  False if a packet did not arrive in time.
+__device__ __forceinline__ bool tp_get_stats(const TpStatPackets* slots, int size, int M, int m, unsigned int tag,
+                                             long long limit_cycles, double& ss, float& mx) {
+    bool ok = true;
+    ss = 0.0;
+    mx = 0.f;
+#pragma unroll 1
+    for (int r = 0; r < size; ++r) {
+        const TpStatPackets* src = slots + (size_t)r * M + m;
+        unsigned int lo, hi, mb;
+        ok = tp_get(&src->w[0], tag, limit_cycles, lo) && ok;
+        ok = tp_get(&src->w[2], tag, limit_cycles, hi) && ok;
+        ok = tp_get(&src->w[4], tag, limit_cycles, mb) && ok;
+        ss += __longlong_as_double((long long)(((unsigned long long)hi << 32) | lo));
+        mx = fmaxf(mx, __uint_as_float(mb));
+    }
+    return ok;
 }
 
 // One thread per CTA, after a CTA barrier: counts the CTA in on a ticket in this GPU's own memory
-// and returns true for the last of n_cta, which then speaks for the whole grid to the other ranks.
-// (One arrival per rank instead of one per CTA: atomics of many CTAs on one address in another
-// GPU's memory are served one NVLink round trip after the other.)  remote_data: threads of the CTA
-// stored to other ranks' areas before the barrier; this thread's system-scope fence then orders
-// those stores (which happen before it through the barrier) ahead of the ticket, so that the last
-// CTA's signal covers them - one fence per CTA instead of one per storing thread.
-__device__ __forceinline__ bool tp_last_cta(unsigned int* ticket, unsigned int n_cta, bool remote_data) {
-    if (remote_data) __threadfence_system();
-    else __threadfence();
+// and returns true for the last of n_cta, which then speaks for the whole grid to the other ranks
+// (this GPU's share of the statistics is added up in its own memory first: atomics of many CTAs on
+// one address in another GPU's memory are served one NVLink round trip after the other).
+__device__ __forceinline__ bool tp_last_cta(unsigned int* ticket, unsigned int n_cta) {
+    __threadfence();
     const unsigned int t = atomicAdd(ticket, 1u);
     if (t + 1 != n_cta) return false;
     atomicExch(ticket, 0u);          // every CTA has drawn: ready for the kernel's next launch
@@ -756,21 +781,18 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
             const int wi = best_i[w * 8 + tid];
             if (wv > v || (wv == v && wi < i)) { v = wv; i = wi; }
         }
-        if (p.tp.size > 1) {     // the slice's maxima go to slot [rank][cta] of every rank's area
+        if (p.tp.size > 1) {     // the slice's maxima go to packets [rank][cta] of every rank's area
             const size_t at = ((size_t)p.tp.rank * n_cta + cta) * 8 + tid;
+            const unsigned int tag = tp_tag(p.tp_tag_out);
 #pragma unroll 1
             for (int pr = 0; pr < p.tp.size; ++pr) {
-                reinterpret_cast<float*>(p.tp.area[pr] + p.tp_val_off)[at] = v;
-                reinterpret_cast<int*>(p.tp.area[pr] + p.tp_idx_off)[at] = i;
+                tp_put(reinterpret_cast<uint2*>(p.tp.area[pr] + p.tp_val_off) + at, __float_as_uint(v), tag);
+                tp_put(reinterpret_cast<uint2*>(p.tp.area[pr] + p.tp_idx_off) + at, (unsigned int)i, tag);
             }
         } else {
             p.part_val[cta * 8 + tid] = v;
             p.part_idx[cta * 8 + tid] = i;
         }
-    }
-    if (p.tp.size > 1 && tid < 32) {
-        __syncwarp();            // the M storing threads are lanes of warp 0
-        if (tid == 0 && tp_last_cta(p.tp_ticket, (unsigned int)n_cta, true)) tp_signal(p.tp, p.tp_flag_off);
     }
 }
 

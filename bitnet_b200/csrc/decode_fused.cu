@@ -336,16 +336,29 @@ __global__ void __launch_bounds__(256) argmax_kernel(const ArgmaxParams p) {
     __shared__ int si[256];
     pdl_launch_dependents();
     pdl_wait();
-    if (p.wait.flag) {      // tensor parallel: the maxima of all ranks' vocabulary slices
-        if (threadIdx.x == 0 && !tp_wait(p.wait)) atomicExch(p.error_flag, kErrPeerWait);
-        __syncthreads();
-    }
+    const bool packets = p.tag.step != nullptr;     // tensor parallel: the maxima of all ranks' vocabulary slices
+    const unsigned int tag = packets ? tp_tag(p.tag) : 0u;
+    long long limit = (packets && __ldcg(p.error_flag) == 0) ? p.tag.limit_cycles : 0;
     for (int m = 0; m < p.M; ++m) {
         float v = -INFINITY;
         int i = 0x7fffffff;
         for (int c = threadIdx.x; c < p.n_part; c += 256) {
-            const float cv = __ldcg(&p.part_val[c * 8 + m]);
-            const int ci = __ldcg(&p.part_idx[c * 8 + m]);
+            float cv;
+            int ci;
+            if (packets) {
+                unsigned int vb, ib;
+                const bool ok = tp_get(reinterpret_cast<const uint2*>(p.part_val) + c * 8 + m, tag, limit, vb) &&
+                                tp_get(reinterpret_cast<const uint2*>(p.part_idx) + c * 8 + m, tag, limit, ib);
+                if (!ok) {
+                    atomicExch(p.error_flag, kErrPeerWait);
+                    limit = 0;
+                }
+                cv = __uint_as_float(vb);
+                ci = (int)ib;
+            } else {
+                cv = __ldcg(&p.part_val[c * 8 + m]);
+                ci = __ldcg(&p.part_idx[c * 8 + m]);
+            }
             if (cv > v || (cv == v && ci < i)) { v = cv; i = ci; }
         }
         sv[threadIdx.x] = v; si[threadIdx.x] = i;

@@ -84,12 +84,19 @@ struct TpPeers {
     uint8_t* area[kMaxTp];           // base of every rank's exchange area as mapped in this process
 };
 
-struct TpWait {                      // wait until *flag >= *step * per_step + base
-    const unsigned long long* flag;  // null: nothing to wait for
-    const unsigned long long* step;
-    unsigned long long per_step, base;
-    long long limit_cycles;          // give up after this many SM clock cycles
+// What crosses between ranks travels as 8-byte packets {value, tag}: one store that no fence has
+// to follow, since a packet whose tag is this exchange's tag carries its value with it (8-byte
+// stores arrive whole).  tag = (uint32)(*step * mul + add) is different for every exchange that
+// reuses a packet's address (mul = exchanges of this kind per step, add = 1 + its number within the
+// step); memory starts out zero and no tag is zero... until the counter wraps after 2^32 exchanges,
+// by which time the address has long held other tags.
+struct TpTag {
+    const unsigned long long* step;  // this rank's step counter (device); null: no exchange
+    unsigned int mul, add;
+    long long limit_cycles;          // a reader gives up after this many SM clock cycles
 };
+// Statistics of one (rank, token): three packets {ss low word, ss high word, mx bits} + padding.
+struct TpStatPackets { unsigned int w[8]; };
 
 // ---------------------------------------------------------------------------------------
 // BitLinear of the decode chain (decode_chain.cu): prologue (int8 quantisation of the normalised
@@ -116,7 +123,8 @@ struct ChainLinearParams {
     const StatPart* stats_in;        // [M]
     int k_norm;                      // length of the whole normalised vector (K; more for a K slice)
     float eps;
-    TpWait stats_wait;               // tensor parallel: statistics that other ranks contribute to
+    const TpStatPackets* tp_stats_in; // tensor parallel: [size][M] packets in this rank's area instead of stats_in
+    TpTag tp_tag_in;                 //   and their tag
     StatPart* zero_slot;             // [M] slot to clear (its consumer ran before this kernel), or null
     // output
     __nv_bfloat16* out;              // [M, ldo] (kOutBf16: written; kOutResidual: updated in place; others: unused)
@@ -129,8 +137,9 @@ struct ChainLinearParams {
     StatPart* stats_out;             // [M] slot the output's statistics are added to (in every rank's area when tp.size > 1)
     // tensor parallel
     TpPeers tp;
-    size_t tp_stats_off, tp_stats_flag_off;   // kOutGlu: statistics slot and arrival counter in every area
-    size_t tp_part_off, tp_part_flag_off;     // kOutTpPartial: int32 [size][M][N] and arrival counter in every area
+    size_t tp_stats_off;             // kOutGlu: TpStatPackets [size][M] in every area
+    size_t tp_part_off;              // kOutTpPartial: packets {int32, tag} [size][M][N] in every area
+    TpTag tp_tag_out;                // tag of what this kernel sends
     float* a_out;                    // kOutTpPartial: [M] activation scales for the reduction kernel
     unsigned int* tp_ticket;         // tensor parallel: this GPU's count of CTAs that have delivered (see tp_last_cta)
     int* error_flag;
@@ -153,8 +162,8 @@ struct EmbedParams {
 // Second half of a row-parallel BitLinear: out[m, n] = bf16(out[m, n] + bf16(sum_r part[r][m][n] / a[m] * ws)),
 // t_out = out * gamma_out and the statistics of out.  One CTA of 256 threads per 256 rows.
 struct TpReduceParams {
-    const int32_t* part;             // [T][M][N] in this rank's exchange area
-    TpWait wait;
+    const uint2* part;               // packets {int32, tag} [T][M][N] in this rank's exchange area
+    TpTag tag;
     const float* a;                  // [M]
     float ws;
     __nv_bfloat16* out;              // [M, ldo], updated in place
@@ -162,7 +171,6 @@ struct TpReduceParams {
     const __nv_bfloat16* gamma_out;
     float* t_out;                    // [M, ldo]
     StatPart* stats_out;             // [M], added to
-    StatPart* zero_slot;
     int M, N, T;
     int* error_flag;
 };
@@ -184,7 +192,8 @@ struct AttentionParams {
     StatPart* stats_out;             // [B] slot the statistics of a sequence's output are added to
     StatPart* zero_slot;             // [B] slot to clear, or null
     TpPeers tp;                      // tensor parallel: the statistics go to the slot at this offset of every area
-    size_t tp_stats_off, tp_stats_flag_off;
+    size_t tp_stats_off;             // TpStatPackets [size][B] in every area
+    TpTag tp_tag_out;
     unsigned int* tp_ticket;         // tensor parallel: this GPU's count of heads whose statistics are in stats_out
     __nv_bfloat16* tap;              // optional second copy of `out` (for checkers)
     int* error_flag;
@@ -202,9 +211,9 @@ struct HeadParams {
     int* part_idx;
     int M, K, V;
     int row_offset;                  // added to the reported indices (vocabulary slice of a rank)
-    TpPeers tp;                      // tensor parallel: the per-CTA maxima go to [size][grid][8] of every area
-    size_t tp_val_off, tp_idx_off, tp_flag_off;
-    unsigned int* tp_ticket;         // tensor parallel: this GPU's count of CTAs that have delivered
+    TpPeers tp;                      // tensor parallel: the per-CTA maxima go to packets [size][grid][8] of every area
+    size_t tp_val_off, tp_idx_off;
+    TpTag tp_tag_out;
 };
 
 struct ArgmaxParams {
@@ -214,7 +223,7 @@ struct ArgmaxParams {
     int64_t* out;
     int64_t* tokens;
     int64_t* pos;
-    TpWait wait;                     // tensor parallel: the maxima of all ranks
+    TpTag tag;                       // tensor parallel: part_val / part_idx hold packets {bits, tag} of all ranks' maxima
     unsigned long long* step;        // this rank's step counter, incremented here (may be null)
     int* error_flag;
 };

@@ -121,24 +121,23 @@ int fused_linear_quantized(const LinearArgs& a, cudaStream_t stream) {
     return launch_fused_linear(p, stream, false);
 }
 
-// Layout of a rank's exchange area (the same on every rank).
+// Layout of a rank's exchange area (the same on every rank).  Everything in it is 8-byte packets
+// {value, tag} written by all ranks (see TpTag).
 struct TpLayout {
-    size_t flag_att, flag_o, flag_glu, flag_2, flag_head;   // arrival counters, one 128-byte line each
-    size_t stats;                                           // [n_layers][2][batch] StatPart: attention output, gated values
-    size_t part_o, part_2;                                  // int32 [size][batch][dim]
-    size_t head_val, head_idx;                              // [size][grid][8]
+    size_t stats;                                           // TpStatPackets [n_layers][2][size][batch]: attention output, gated values
+    size_t part_o, part_2;                                  // packets [size][batch][dim]
+    size_t head_val, head_idx;                              // packets [size][grid][8]
     size_t total;
 };
 static TpLayout tp_layout(const bitnet_decoder_config& c, int size, int head_grid) {
     TpLayout L{};
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
-    L.flag_att = take(128); L.flag_o = take(128); L.flag_glu = take(128); L.flag_2 = take(128); L.flag_head = take(128);
-    L.stats = take((size_t)c.n_layers * 2 * c.batch * sizeof(StatPart));
-    L.part_o = take((size_t)size * c.batch * c.dim * 4);
-    L.part_2 = take((size_t)size * c.batch * c.dim * 4);
-    L.head_val = take((size_t)size * head_grid * 8 * 4);
-    L.head_idx = take((size_t)size * head_grid * 8 * 4);
+    L.stats = take((size_t)c.n_layers * 2 * size * c.batch * sizeof(TpStatPackets));
+    L.part_o = take((size_t)size * c.batch * c.dim * 8);
+    L.part_2 = take((size_t)size * c.batch * c.dim * 8);
+    L.head_val = take((size_t)size * head_grid * 8 * 8);
+    L.head_idx = take((size_t)size * head_grid * 8 * 8);
     L.total = off;
     return L;
 }
@@ -176,7 +175,7 @@ struct Decoder {
     StatPart* slot(int layer, int which) const { return stats + (size_t)(1 + 4 * layer + which) * cfg.batch; }
 };
 enum { kSlotAtt = 0, kSlotHo = 1, kSlotGlu = 2, kSlotH2 = 3 };
-enum { kTickAtt = 0, kTickO = 1, kTickGlu = 2, kTick2 = 3, kTickHead = 4 };
+enum { kTickAtt = 0, kTickGlu = 1 };
 
 static size_t align_up(size_t x) { return (x + 255) / 256 * 256; }
 
@@ -385,15 +384,15 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
     const unsigned long long nl = (unsigned long long)c.n_layers;
     auto bf = [](const void* p) { return static_cast<const __nv_bfloat16*>(p); };
     uint8_t* my = tp ? d->tp.area[rank] : nullptr;
-    auto area_slot = [&](int which) { return lay.stats + ((size_t)(2 * l + which) * c.batch) * sizeof(StatPart); };
-    auto wait_on = [&](size_t flag_off, unsigned long long per_layer) {
-        TpWait w{};
-        w.flag = reinterpret_cast<const unsigned long long*>(my + flag_off);
-        w.step = d->step_ctr;
-        w.per_step = nl * per_layer;
-        w.base = (unsigned long long)(l + 1) * per_layer;
-        w.limit_cycles = d->wait_limit;
-        return w;
+    auto area_slot = [&](int which) { return lay.stats + ((size_t)(2 * l + which) * T * c.batch) * sizeof(TpStatPackets); };
+    // four exchanges per layer (attention statistics, wo sums, gate statistics, w2 sums)
+    auto tag_of = [&](int which) {
+        TpTag t{};
+        t.step = d->step_ctr;
+        t.mul = 4u * (unsigned int)nl;
+        t.add = 4u * (unsigned int)l + (unsigned int)which + 1u;
+        t.limit_cycles = d->wait_limit;
+        return t;
     };
     // wqkv: t_h (= h * attention_norm) -> xqkv
     ChainLinearParams& q = lin[0];
@@ -416,7 +415,7 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
     ap->tap = d->attn_tap ? d->attn_tap + (size_t)l * c.batch * Ko : nullptr;
     ap->error_flag = d->error_flag;
     if (tp) {     // all ranks' wo normalise over all heads
-        ap->tp = d->tp; ap->tp_stats_off = area_slot(0); ap->tp_stats_flag_off = lay.flag_att; ap->tp_ticket = d->ticket(kTickAtt);
+        ap->tp = d->tp; ap->tp_stats_off = area_slot(0); ap->tp_tag_out = tag_of(0); ap->tp_ticket = d->ticket(kTickAtt);
     }
 
     // wo: t_att (= attention output * attn_sub_norm) -> h += ...; t_h = h * ffn_norm
@@ -430,16 +429,14 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
         o.out = d->h; o.ldo = dim;
         o.gamma_out = bf(L.ffn_norm); o.t_out = d->t_h; o.ldt_out = dim; o.stats_out = d->slot(l, kSlotHo);
     } else {
-        o.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(0));
-        o.stats_wait = wait_on(lay.flag_att, (unsigned long long)T);     // one arrival per rank and exchange
-        o.tp = d->tp; o.tp_part_off = lay.part_o; o.tp_part_flag_off = lay.flag_o; o.a_out = d->a_o; o.tp_ticket = d->ticket(kTickO);
+        o.tp_stats_in = reinterpret_cast<const TpStatPackets*>(my + area_slot(0)); o.tp_tag_in = tag_of(0);
+        o.tp = d->tp; o.tp_part_off = lay.part_o; o.tp_tag_out = tag_of(1); o.a_out = d->a_o;
         TpReduceParams& r = red[0];
         r = TpReduceParams{};
-        r.part = reinterpret_cast<const int32_t*>(my + lay.part_o);
-        r.wait = wait_on(lay.flag_o, (unsigned long long)T);
+        r.part = reinterpret_cast<const uint2*>(my + lay.part_o);
+        r.tag = tag_of(1);
         r.a = d->a_o; r.ws = L.s_o; r.out = d->h; r.ldo = dim;
         r.gamma_out = bf(L.ffn_norm); r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotHo);
-        r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(0));     // its consumer, wo, has run
         r.M = c.batch; r.N = dim; r.T = T; r.error_flag = d->error_flag;
     }
 
@@ -453,7 +450,7 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
     u.seg.n_seg = 2; u.seg.end[0] = F; u.seg.end[1] = 2 * F; u.ws[0] = L.s_1; u.ws[1] = L.s_3;
     u.gamma_out = bf(L.ffn_sub_norm) + (size_t)rank * F; u.t_out = d->t_glu; u.ldt_out = F; u.stats_out = d->slot(l, kSlotGlu);
     if (tp) {     // all ranks' w2 normalise over the whole gated vector
-        u.tp = d->tp; u.tp_stats_off = area_slot(1); u.tp_stats_flag_off = lay.flag_glu; u.tp_ticket = d->ticket(kTickGlu);
+        u.tp = d->tp; u.tp_stats_off = area_slot(1); u.tp_tag_out = tag_of(2); u.tp_ticket = d->ticket(kTickGlu);
     }
 
     // w2: t_glu -> h += ...; t_h = h * (the next layer's attention_norm, or the final norm)
@@ -469,16 +466,14 @@ static void layer_params(const Decoder* d, int l, const int64_t* pos, ChainLinea
         w.out = d->h; w.ldo = dim;
         w.gamma_out = g_next; w.t_out = d->t_h; w.ldt_out = dim; w.stats_out = d->slot(l, kSlotH2);
     } else {
-        w.stats_in = reinterpret_cast<const StatPart*>(my + area_slot(1));
-        w.stats_wait = wait_on(lay.flag_glu, (unsigned long long)T);
-        w.tp = d->tp; w.tp_part_off = lay.part_2; w.tp_part_flag_off = lay.flag_2; w.a_out = d->a_2; w.tp_ticket = d->ticket(kTick2);
+        w.tp_stats_in = reinterpret_cast<const TpStatPackets*>(my + area_slot(1)); w.tp_tag_in = tag_of(2);
+        w.tp = d->tp; w.tp_part_off = lay.part_2; w.tp_tag_out = tag_of(3); w.a_out = d->a_2;
         TpReduceParams& r = red[1];
         r = TpReduceParams{};
-        r.part = reinterpret_cast<const int32_t*>(my + lay.part_2);
-        r.wait = wait_on(lay.flag_2, (unsigned long long)T);
+        r.part = reinterpret_cast<const uint2*>(my + lay.part_2);
+        r.tag = tag_of(3);
         r.a = d->a_2; r.ws = L.s_2; r.out = d->h; r.ldo = dim;
         r.gamma_out = g_next; r.t_out = d->t_h; r.stats_out = d->slot(l, kSlotH2);
-        r.zero_slot = reinterpret_cast<StatPart*>(my + area_slot(1));     // its consumer, w2, has run
         r.M = c.batch; r.N = dim; r.T = T; r.error_flag = d->error_flag;
     }
 }
@@ -492,8 +487,8 @@ static HeadParams head_params(const Decoder* d, float* logits) {
     if (d->tp.size > 1) {
         const TpLayout lay = tp_layout(d->cfg, d->tp.size, kTpHeadGridMax);
         hp.row_offset = d->tp.rank * d->loc.vocab_size;
-        hp.tp = d->tp; hp.tp_val_off = lay.head_val; hp.tp_idx_off = lay.head_idx; hp.tp_flag_off = lay.flag_head;
-        hp.tp_ticket = d->ticket(kTickHead);
+        hp.tp = d->tp; hp.tp_val_off = lay.head_val; hp.tp_idx_off = lay.head_idx;
+        hp.tp_tag_out.step = d->step_ctr; hp.tp_tag_out.mul = 1; hp.tp_tag_out.add = 1; hp.tp_tag_out.limit_cycles = d->wait_limit;
     }
     return hp;
 }
@@ -537,11 +532,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
         am.part_val = reinterpret_cast<const float*>(my + lay.head_val);
         am.part_idx = reinterpret_cast<const int*>(my + lay.head_idx);
         am.n_part = d->tp.size * d->head_grid;
-        am.wait.flag = reinterpret_cast<const unsigned long long*>(my + lay.flag_head);
-        am.wait.step = d->step_ctr;
-        am.wait.per_step = (unsigned long long)d->tp.size;
-        am.wait.base = am.wait.per_step;
-        am.wait.limit_cycles = d->wait_limit;
+        am.tag.step = d->step_ctr; am.tag.mul = 1; am.tag.add = 1; am.tag.limit_cycles = d->wait_limit;
     }
     return launch_argmax(am, stream, true);
 }
