@@ -64,6 +64,7 @@ def parse_args():
     ap.add_argument("--no-tp", action="store_true", help="skip the tp object of a multi-GPU run")
     ap.add_argument("--layers", type=int, default=0, help="use only the first LAYERS layers (0 = all): a small case for profilers, or with --tp")
     ap.add_argument("--context", type=int, default=PROMPT_LEN, help="tokens in the KV cache when decode starts (with --tp)")
+    ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0 = the preset's): a small case for profilers")
     return ap.parse_args()
 
 
@@ -559,8 +560,8 @@ def run_ours(a, args_model):
                      "launches_per_step": n_lin, "bytes_per_launch": weight_bytes / n_lin,
                      "us_per_launch": 1e3 * ms_lin / n_lin, "achieved": achieved, "frac": achieved / peak,
                      # dram__bytes_read + write per launch from one ncu capture of the four 2B shapes
-                     # (profiles/fused_linear_kernel_2b_m1.md), averaged as the launches are mixed
-                     "traffic": 4.50e6 if (fused and a.workload == "2b" and B == 1) else None}
+                     # (profiles/chain_linear_kernel_2b_m1.md), averaged as the launches are mixed
+                     "traffic": 4.41e6 if (fused and a.workload == "2b" and B == 1) else None}
     roofline = dict(chain_linears, bound="hbm", peak=peak, unit="GB/s", peak_source="measured" if measured else "fallback",
                     step_bytes=step_bytes, step_gbs=step_gbs, step_frac=step_gbs / peak)
     line = {
@@ -792,7 +793,12 @@ def main():
     a = parse_args()
     from bitnet_b200.config import preset   # no torch, no CUDA library: the reference arm loads neither
 
-    args_model = preset(a.workload, n_layers=a.layers) if a.layers else preset(a.workload)
+    over = {}
+    if a.layers:
+        over["n_layers"] = a.layers
+    if a.vocab:
+        over["vocab_size"] = a.vocab
+    args_model = preset(a.workload, **over)
     if a.sweep_only:
         import torch
 

@@ -249,12 +249,29 @@ static void* decoder_create(const bitnet_decoder_config* cfg, const bitnet_decod
         if (getenv("BITNET_RING_STAGES")) p.ring_stages = atoi(getenv("BITNET_RING_STAGES"));   // measurement builds only
 #endif
         plan_chain_linear(p, d->n_sm);
-        if (p.big_share) {     // a long stream per CTA: the larger ring, where shared memory allows it
-            p.ring_stages = 8;
-            plan_chain_linear(p, d->n_sm);
-            if (chain_linear_smem(p) > (size_t)prop.sharedMemPerBlockOptin) {
-                p.ring_stages = 4;
+        if (p.big_share) {
+            // A long stream per CTA is bound by how many warps an SM has to issue from, not by latency:
+            // two CTAs per SM (16 consumer warps) with the largest ring that lets two fit; failing that,
+            // one CTA with the largest ring.
+            const size_t half = (size_t)prop.sharedMemPerMultiprocessor / 2 - 1024 - 256;
+            bool two = false;
+            for (int rs : {4, 2}) {
+                ChainLinearParams q = p;
+                q.ring_stages = rs;
+                plan_chain_linear(q, 2 * d->n_sm);
+                if (chain_linear_smem(q) <= half) {
+                    p = q;
+                    two = true;
+                    break;
+                }
+            }
+            if (!two) {
+                p.ring_stages = 8;
                 plan_chain_linear(p, d->n_sm);
+                if (chain_linear_smem(p) > (size_t)prop.sharedMemPerBlockOptin) {
+                    p.ring_stages = 4;
+                    plan_chain_linear(p, d->n_sm);
+                }
             }
         }
     };
@@ -338,7 +355,8 @@ int bitnet_tp_area_create(size_t bytes, void** area, void* ipc_handle_64) {
     if (!area || !ipc_handle_64 || bytes == 0) return set_status(kBadArgument), kBadArgument;
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is handed over as 64 bytes");
     void* p = nullptr;
-    if (check_cuda(cudaMalloc(&p, bytes)) || check_cuda(cudaMemset(p, 0, bytes))) return kCudaError;
+    // zero-filled before anybody can see it: no packet of a fresh area carries a valid tag
+    if (check_cuda(cudaMalloc(&p, bytes)) || check_cuda(cudaMemset(p, 0, bytes)) || check_cuda(cudaDeviceSynchronize())) return kCudaError;
     cudaIpcMemHandle_t h;
     if (check_cuda(cudaIpcGetMemHandle(&h, p))) {
         cudaFree(p);

@@ -194,10 +194,14 @@ void bitnet_decoder_destroy(void* decoder);
  * every rank creates one exchange area (bitnet_tp_area_create), passes the 64-byte handle to
  * the others by any host channel, opens theirs (bitnet_tp_area_open) and hands all `size`
  * pointers, its own at index `rank`, to bitnet_decoder_create_tp.  Per layer a step then
- * exchanges the statistics of the attention output and of the gated vector (one slot per
- * token, added to with atomics over NVLink) and the exact int32 partial sums of wo and w2
- * (plain peer stores), each followed by an arrival counter that the consumer polls with a
- * bounded wait; the greedy choice exchanges one (value, index) pair per CTA of the output head.
+ * exchanges the statistics of the attention output and of the gated vector (each rank's total
+ * of sum(x^2) and max|x g| per token, 24 bytes) and the exact int32 partial sums of wo and w2;
+ * the greedy choice exchanges one (value, index) pair per CTA of the output head.  Everything
+ * travels as 8-byte packets {value, tag} stored into every rank's area with plain peer stores;
+ * the tag numbers the exchange (it is derived from a step counter on the device, so a CUDA graph
+ * of the step replays), a reader polls the packet itself, bounded in time: no collective call,
+ * flag, fence or atomic is on the path between two GPUs.  Every decoder needs areas of its own,
+ * freshly created (bitnet_tp_area_create zero-fills them; the tags start over with each decoder).
  * Results are bit-identical to a single GPU's.  bitnet_decoder_step / _step_sync / _error_flag
  * (code 6: an exchange did not arrive in time) / _destroy work as for a single GPU; all ranks
  * must enqueue the same steps. */
