@@ -96,7 +96,7 @@ __host__ __device__ inline size_t chain_carve(const ChainLinearParams& p, uint8_
     const size_t o_statd = take((size_t)8 * p.units_max * sizeof(double));
     const size_t o_statf = take((size_t)8 * p.units_max * sizeof(float));
     const size_t o_sacc = take((size_t)p.units_max * p.n_sub * 128 * sizeof(int));
-    const size_t o_ys = take((size_t)(p.M + 1) * (k_pad + 16));
+    const size_t o_ys = take((size_t)p.M * (k_pad + 16));
     if (s) {
         s->ring = base + o_ring;
         s->full_bar = reinterpret_cast<uint64_t*>(base + o_bar);
@@ -182,10 +182,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #pragma unroll 1
     for (int i = tid; i < n_lg * 128; i += kCThreads) sm.sacc[i] = 0;
     if (tid < 8) sm.ysum_s[tid] = 0;
-    // the row of zeros that MMA columns without a token read, and the padding of the token rows
-#pragma unroll 1
-    for (int v = tid; v < y_stride / 16; v += kCThreads)
-        *reinterpret_cast<uint4*>(sm.ys + (size_t)p.M * y_stride + v * 16) = make_uint4(0, 0, 0, 0);
+    // the padding of the token rows
     if (k_pad > K) {
 #pragma unroll 1
         for (int i = tid; i < p.M * ((k_pad - K) / 8); i += kCThreads) {
@@ -236,16 +233,19 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
         double2 st = make_double2(0.0, 0.0);
         if (!p.tp_stats_in) st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
         const float* tm = p.t + (int64_t)m * p.ldt;
-        constexpr int kIt = 1024 / kCThreads;               // vectors of up to 8192 values: all loads in flight at once
+        constexpr int kIt = 1024 / kCThreads;               // 8192 values per pass: all of a pass's loads in flight at once
         float4 lo[kIt], hi[kIt];
+        auto fetch = [&](int v0) {
 #pragma unroll
-        for (int it = 0; it < kIt; ++it) {
-            const int v = tid + it * kCThreads;
-            if (v < n_vec) {
-                lo[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8));
-                hi[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
+            for (int it = 0; it < kIt; ++it) {
+                const int v = v0 + tid + it * kCThreads;
+                if (v < n_vec) {
+                    lo[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8));
+                    hi[it] = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
+                }
             }
-        }
+        };
+        fetch(0);
         if (p.tp_stats_in) {
             // tensor parallel: the statistics are the sum over all ranks' packets; lane 0 of every warp
             // gathers them (this rank's own vector is already on its way: the loads above)
@@ -262,31 +262,26 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
         finish_stats(st.x, (float)st.y, p.k_norm, p.eps, true, rinv, a);
         int8_t* ym = sm.ys + (size_t)m * y_stride;
         int sy = 0;
-#pragma unroll
-        for (int it = 0; it < kIt; ++it) {
-            const int v = tid + it * kCThreads;
-            if (v < n_vec) {
-                const float f[8] = {lo[it].x, lo[it].y, lo[it].z, lo[it].w, hi[it].x, hi[it].y, hi[it].z, hi[it].w};
-                int q[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) q[e] = quant_s8(bf16_round(f[e] * rinv) * a);
-                const uint32_t w0 = pack_bytes(q[0], q[1], q[2], q[3]), w1 = pack_bytes(q[4], q[5], q[6], q[7]);
-                sy = __dp4a((int)w0, 0x01010101, sy);
-                sy = __dp4a((int)w1, 0x01010101, sy);
-                *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
-            }
-        }
 #pragma unroll 1
-        for (int v = tid + kIt * kCThreads; v < n_vec; v += kCThreads) {    // vectors longer than 8192 values
-            const float4 l4 = __ldcg(reinterpret_cast<const float4*>(tm + v * 8)), h4 = __ldcg(reinterpret_cast<const float4*>(tm + v * 8 + 4));
-            const float f[8] = {l4.x, l4.y, l4.z, l4.w, h4.x, h4.y, h4.z, h4.w};
-            int q[8];
+        for (int v0 = 0; v0 < n_vec; v0 += kIt * kCThreads) {
+            float4 cl[kIt], ch[kIt];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) q[e] = quant_s8(bf16_round(f[e] * rinv) * a);
-            const uint32_t w0 = pack_bytes(q[0], q[1], q[2], q[3]), w1 = pack_bytes(q[4], q[5], q[6], q[7]);
-            sy = __dp4a((int)w0, 0x01010101, sy);
-            sy = __dp4a((int)w1, 0x01010101, sy);
-            *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
+            for (int it = 0; it < kIt; ++it) { cl[it] = lo[it]; ch[it] = hi[it]; }
+            if (v0 + kIt * kCThreads < n_vec) fetch(v0 + kIt * kCThreads);     // the next pass, in flight during this one
+#pragma unroll
+            for (int it = 0; it < kIt; ++it) {
+                const int v = v0 + tid + it * kCThreads;
+                if (v < n_vec) {
+                    const float f[8] = {cl[it].x, cl[it].y, cl[it].z, cl[it].w, ch[it].x, ch[it].y, ch[it].z, ch[it].w};
+                    int q[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) q[e] = quant_s8(bf16_round(f[e] * rinv) * a);
+                    const uint32_t w0 = pack_bytes(q[0], q[1], q[2], q[3]), w1 = pack_bytes(q[4], q[5], q[6], q[7]);
+                    sy = __dp4a((int)w0, 0x01010101, sy);
+                    sy = __dp4a((int)w1, 0x01010101, sy);
+                    *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
+                }
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sy += __shfl_xor_sync(0xffffffffu, sy, o);
@@ -306,7 +301,10 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     // the MMA's columns, so that any such M costs the same.
     const int g = lane >> 2, q = lane & 3;
     constexpr bool one_token = kOneToken;                  // the launcher picks the instantiation by M
-    const int8_t* y_lane = sm.ys + (size_t)((one_token || g < p.M) ? (one_token ? 0 : g) : p.M) * y_stride + 32 * q;
+    // MMA column g is token g; lanes whose column has no token feed zeros and load nothing
+    const bool has_token = one_token || g < p.M;
+    const int8_t* y_lane = sm.ys + (size_t)((!one_token && has_token) ? g : 0) * y_stride + 32 * q;
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
     int acc[4][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -384,8 +382,8 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     wc[u] = *reinterpret_cast<const uint4*>(tile + u * kTileBytes);
-                    y0[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols);
-                    y1[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16);
+                    y0[u] = has_token ? *reinterpret_cast<const uint4*>(yk + u * kTileCols) : zero4;
+                    y1[u] = has_token ? *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16) : zero4;
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) one_tile(wc[u], y0[u], y1[u]);
@@ -396,8 +394,8 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                 for (int u = 0; u < 3; ++u) {
                     if (i + u < piece) {
                         wc[u] = *reinterpret_cast<const uint4*>(tile + u * kTileBytes);
-                        y0[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols);
-                        y1[u] = *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16);
+                        y0[u] = has_token ? *reinterpret_cast<const uint4*>(yk + u * kTileCols) : zero4;
+                        y1[u] = has_token ? *reinterpret_cast<const uint4*>(yk + u * kTileCols + 16) : zero4;
                     }
                 }
 #pragma unroll

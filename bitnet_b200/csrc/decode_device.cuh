@@ -162,9 +162,12 @@ struct AttnItem {
 };
 __device__ __forceinline__ AttnItem attention_item(const AttentionParams& p, int x, int P) {
     const int Gfull = p.H / p.Hkv;
-    const int S = attention_slices(p.S, P);
+    // Groups of more than four query heads at head_dim 128 always go as whole groups (the
+    // tensor-core key loop of the chain's kernel), in slices of 64 keys or more.
+    const bool whole_groups = p.D == 128 && Gfull > 4 && p.S > 1;
+    const int S = whole_groups ? (P <= 64 ? 1 : min(p.S, (P + 63) / 64)) : attention_slices(p.S, P);
     AttnItem it{0, 0, 0, 0, S};
-    if (S == 1 && p.S >= Gfull) {
+    if (!whole_groups && S == 1 && p.S >= Gfull) {
         if (x < p.H) { it.kvh = x / Gfull; it.h0 = x - it.kvh * Gfull; it.G = 1; }
     } else {
         it.kvh = x / p.S; it.split = x - it.kvh * p.S;

@@ -441,7 +441,7 @@ int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pd
 }
 
 static size_t attention_smem_nw(const AttentionParams& p, int nw) {
-    const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : (G <= 8 ? 8 : 16);
+    const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : 16;     // the tensor-core key loop keeps 16 rows per warp
     return sizeof(float) * ((size_t)(G + 2) * p.D + 2 * nw * gmax + (size_t)nw * G * p.D) + 64;
 }
 size_t attention_smem(const AttentionParams& p) {
