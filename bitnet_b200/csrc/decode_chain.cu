@@ -262,12 +262,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
         finish_stats(st.x, (float)st.y, p.k_norm, p.eps, true, rinv, a);
         int8_t* ym = sm.ys + (size_t)m * y_stride;
         int sy = 0;
-#pragma unroll 1
-        for (int v0 = 0; v0 < n_vec; v0 += kIt * kCThreads) {
-            float4 cl[kIt], ch[kIt];
-#pragma unroll
-            for (int it = 0; it < kIt; ++it) { cl[it] = lo[it]; ch[it] = hi[it]; }
-            if (v0 + kIt * kCThreads < n_vec) fetch(v0 + kIt * kCThreads);     // the next pass, in flight during this one
+        auto quantise = [&](const float4 (&cl)[kIt], const float4 (&ch)[kIt], int v0) {
 #pragma unroll
             for (int it = 0; it < kIt; ++it) {
                 const int v = v0 + tid + it * kCThreads;
@@ -281,6 +276,18 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                     sy = __dp4a((int)w1, 0x01010101, sy);
                     *reinterpret_cast<uint2*>(ym + v * 8) = make_uint2(w0, w1);
                 }
+            }
+        };
+        if (n_vec <= kIt * kCThreads) {
+            quantise(lo, hi, 0);             // the usual case: one pass
+        } else {
+#pragma unroll 1
+            for (int v0 = 0; v0 < n_vec; v0 += kIt * kCThreads) {
+                float4 cl[kIt], ch[kIt];
+#pragma unroll
+                for (int it = 0; it < kIt; ++it) { cl[it] = lo[it]; ch[it] = hi[it]; }
+                if (v0 + kIt * kCThreads < n_vec) fetch(v0 + kIt * kCThreads);     // the next pass, in flight during this one
+                quantise(cl, ch, v0);
             }
         }
 #pragma unroll
@@ -917,11 +924,19 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
     return true;
 }
 
+// The 8-row tensor-core split-KV body of the 512-thread kernel, out of line: its register
+// allocation (and what it spills at 128 registers) must not touch the short form's code.
+__device__ __noinline__ bool attention_groups8(const AttentionParams& p, uint8_t* smem, int* is_last, int b, int kvh, int h0, int G,
+                                               int split, int S, int P, int tid) {
+    auto sync = [] { asm volatile("bar.sync 2, 512;\n" ::: "memory"); };
+    return attention_body<8, 16, true>(p, smem, is_last, b, kvh, h0, G, split, S, P, tid, sync, [] {});
+}
+
 // NTHREADS = 512 (grouped-query ratios up to 4: short form and split-KV body share the CTA) or
 // the split-KV body's own thread count (larger ratios: its register budget rules out 512
 // threads, and the short form is left out).
 template <int GMAX, int NTHREADS>
-__global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const AttentionParams p) {
+__global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const __grid_constant__ AttentionParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
     static_assert(AttnCfg<GMAX>::kThreads <= NTHREADS, "the split-KV body uses a prefix of the CTA's warps");
@@ -953,6 +968,11 @@ __global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const Attenti
             auto sync = [] { asm volatile("bar.sync 3, 128;\n" ::: "memory"); };
             wrote = attention_body<16, 4, true>(p, smem, &is_last, b, it.kvh, it.h0, it.G, it.split, it.S, P, tid, sync, [] {});
         }
+    } else if (GMAX <= 4 && it.G > 1 && p.D == 128) {
+        // whole groups of up to four query heads (long contexts, or many sequences): the 8-row form of
+        // the tensor-core key loop, which fits this 512-thread kernel's 128 registers, on all 16 warps
+        static_assert(GMAX > 4 || NT == 512, "attention_groups8 synchronises 512 threads");
+        if (tid < NT) wrote = attention_groups8(p, smem, &is_last, b, it.kvh, it.h0, it.G, it.split, it.S, P, tid);
     } else if (tid < NT) {
         auto sync = [] { asm volatile("bar.sync 2, %0;\n" ::"n"(NT) : "memory"); };
         if (it.G == 1)

@@ -1,6 +1,7 @@
 // Device code shared by the decode kernels (decode_fused.cu, decode_chain.cu): PTX helpers,
 // the split-KV attention body and the output-head body.
 #pragma once
+#include <type_traits>
 #include "common.cuh"
 #include "decode_fused.h"
 #include "prologue.cuh"
@@ -322,6 +323,134 @@ __device__ __forceinline__ void attention_keys_mma(const float* q_s, int G, cons
     }
 }
 
+// The same loop for groups of at most 8 query heads, within 128 registers per thread (so that it
+// can run inside a 512-thread CTA): only rows 0..7 of the MMAs are kept - the other half of every
+// accumulator goes to two scratch registers - and the values are requested after the scores have
+// been issued instead of together with the keys.
+template <int NW, int GMAX>
+__device__ __forceinline__ void attention_keys_mma8(const float* q_s, int G, const float* knew, const float* vnew, bool with_new,
+                                                    const __nv_bfloat16* ck, const __nv_bfloat16* cv, int64_t key_stride, int lo,
+                                                    int hi, int warp, int lane, float* red_m, float* red_l, float* red_o) {
+    constexpr int D = 128;
+    const int g = lane >> 2, q = lane & 3;
+    const float scale = rsqrtf((float)D);
+    auto pack = [](float lo_v, float hi_v) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo_v, hi_v);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    };
+    auto mma_half = [](float& d0, float& d1, float& j0, float& j1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};\n"
+            : "+f"(d0), "+f"(d1), "+f"(j0), "+f"(j1)
+            : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+    };
+    uint32_t qa[8][2];                       // rows g (a0, a2); rows g+8 are zero
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        const int d = (s >> 1) * 32 + q * 8 + (s & 1) * 4;
+        const float* r0 = q_s + g * D + d;
+        const bool v0 = g < G;
+        qa[s][0] = v0 ? pack(r0[0], r0[1]) : 0u;
+        qa[s][1] = v0 ? pack(r0[2], r0[3]) : 0u;
+    }
+    float m0 = -INFINITY, l0 = 0.f;
+    float jk[4][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};   // the unused halves; four pairs keep four MMAs independent
+    float o[16][2];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) { o[nt][0] = 0.f; o[nt][1] = 0.f; }
+
+#pragma unroll 1
+    for (int k0 = lo + warp * 16; k0 < hi; k0 += NW * 16) {
+        float s[2][2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {        // the two 8-key halves one after the other: registers
+            uint4 kk[4];
+            const int key = k0 + t * 8 + g;
+            const uint4* src = reinterpret_cast<const uint4*>(ck + (int64_t)key * key_stride) + q;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kk[i] = key < hi ? src[i * 4] : make_uint4(0, 0, 0, 0);
+            s[t][0] = 0.f; s[t][1] = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                mma_half(s[t][0], s[t][1], jk[2 * t][0], jk[2 * t][1], qa[2 * i][0], qa[2 * i][1], kk[i].x, kk[i].y);
+                mma_half(s[t][0], s[t][1], jk[2 * t][0], jk[2 * t][1], qa[2 * i + 1][0], qa[2 * i + 1][1], kk[i].z, kk[i].w);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) s[t][c] = (k0 + t * 8 + 2 * q + c < hi) ? s[t][c] * scale : -INFINITY;
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        const float mn0 = fmaxf(m0, mx0);                               // finite: key k0 is inside the slice
+        const float c0 = __expf(m0 - mn0);
+        m0 = mn0;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) { s[t][0] = __expf(s[t][0] - mn0); s[t][1] = __expf(s[t][1] - mn0); }
+        l0 = l0 * c0 + (s[0][0] + s[0][1]) + (s[1][0] + s[1][1]);
+        const uint32_t pa0 = pack(s[0][0], s[0][1]), pa2 = pack(s[1][0], s[1][1]);
+        // the values, in two halves of 64 dims (registers): 16 bytes of each of the lane's four keys
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint4 vv[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int key = k0 + (x >> 1) * 8 + 2 * q + (x & 1);
+                const uint4* src = reinterpret_cast<const uint4*>(cv + (int64_t)key * key_stride) + g;
+                vv[x] = key < hi ? src[j * 8] : make_uint4(0, 0, 0, 0);
+            }
+            const uint32_t wa[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w};
+            const uint32_t wb[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
+            const uint32_t wc[4] = {vv[2].x, vv[2].y, vv[2].z, vv[2].w};
+            const uint32_t wd[4] = {vv[3].x, vv[3].y, vv[3].z, vv[3].w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int nt = j * 8 + e;
+                const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(wa[e >> 1], wb[e >> 1], sel);
+                const uint32_t b1 = __byte_perm(wc[e >> 1], wd[e >> 1], sel);
+                o[nt][0] *= c0; o[nt][1] *= c0;
+                mma_half(o[nt][0], o[nt][1], jk[nt & 3][0], jk[nt & 3][1], pa0, pa2, b0, b1);
+            }
+        }
+    }
+    if (with_new && warp == 0) {     // the new token attends to itself: one more key, from shared memory
+        float s0 = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const int d = (s >> 1) * 32 + q * 8 + (s & 1) * 4;
+            const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][0]));
+            const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[s][1]));
+            s0 += a0.x * knew[d] + a0.y * knew[d + 1] + a2.x * knew[d + 2] + a2.y * knew[d + 3];
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s0 *= scale;
+        const float mn0 = fmaxf(m0, s0);
+        const float c0 = __expf(m0 - mn0), p0 = __expf(s0 - mn0);
+        m0 = mn0;
+        l0 = l0 * c0 + (q == 0 ? p0 : 0.f);          // the lanes' sums are added up below
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+            const int d = ((nt >> 3) * 8 + 2 * q) * 8 + (nt & 7);
+            o[nt][0] = o[nt][0] * c0 + p0 * vnew[d];
+            o[nt][1] = o[nt][1] * c0 + p0 * vnew[d + 8];
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    if (q == 0 && g < G) { red_m[warp * GMAX + g] = m0; red_l[warp * GMAX + g] = l0; }
+    if (g < G) {
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+            const int d = ((nt >> 3) * 8 + 2 * q) * 8 + (nt & 7);
+            red_o[(warp * G + g) * D + d] = o[nt][0];
+            red_o[(warp * G + g) * D + d + 8] = o[nt][1];
+        }
+    }
+}
+
 // Attention of query heads h0 .. h0+G-1 of kv head kvh of sequence b over KV slice `split` of S,
 // by NW warps, with P keys already in the cache (the caller reads p.pos[b]; the body does not).
 // A subset of the heads (G < H / Hkv) is only allowed with S = 1.  `smem` needs
@@ -398,7 +527,10 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
     }
     sync();
 
-    if constexpr (kMma) {
+    if constexpr (kMma && GMAX <= 8) {
+        attention_keys_mma8<NW, GMAX>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,
+                                      red_l, red_o);
+    } else if constexpr (kMma) {
         attention_keys_mma<NW, GMAX>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,
                                      red_l, red_o);
     } else {
@@ -694,23 +826,34 @@ constexpr int kHeadMaxLoads = 10;   // 16-byte loads per lane per pass over a ro
 // The output head over this CTA's slice of the vocabulary by 512 threads; `smem` needs
 // head_smem() bytes, `sync` is a barrier over those threads.  Leaves the slice's best
 // (value, index) per token in part_val / part_idx[cta].
-template <class Sync>
+// kCompact: the normalised activations (bf16 values) are kept as bf16 instead of f32, for batch x
+// hidden sizes whose f32 form does not fit shared memory; the products are the same.
+template <bool kCompact, class Sync>
 __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, int cta, int n_cta, int tid, Sync sync) {
-    float* xs = reinterpret_cast<float*>(smem);                 // [M][K]
-    double* red_d = reinterpret_cast<double*>(xs + (size_t)p.M * p.K);   // [16] (M * K is even)
+    using XT = typename std::conditional<kCompact, __nv_bfloat16, float>::type;
+    XT* xs = reinterpret_cast<XT*>(smem);                         // [M][K]
+    double* red_d = reinterpret_cast<double*>(xs + (size_t)p.M * p.K);   // [16] (K is a multiple of 8)
+    auto put = [&](size_t i, float v) {          // v is a bf16 value: exact either way
+        if constexpr (kCompact) xs[i] = __float2bfloat16_rn(v);
+        else xs[i] = v;
+    };
+    auto get = [&](size_t i) -> float {
+        if constexpr (kCompact) return __bfloat162float(xs[i]);
+        else return xs[i];
+    };
     float* best_v = reinterpret_cast<float*>(red_d + 16);       // [16 warps][8]
     int* best_i = reinterpret_cast<int*>(best_v + 16 * 8);      // [16 warps][8]
     const int warp = tid >> 5, lane = tid & 31;
 
-    // final RMSNorm (gpu/model.py:280) of every token into shared memory, as f32 values of the
-    // bf16 result; the sum of squares in double precision (see prologue.cuh), taken from the
+    // final RMSNorm (gpu/model.py:280) of every token into shared memory, as its bf16
+    // result; the sum of squares in double precision (see prologue.cuh), taken from the
     // producer's partial statistics when it published them
     for (int m = 0; m < p.M; ++m) {
         double ss = 0.0;
         if (p.stats_in && tid == 0) ss = __ldcg(&p.stats_in[m].ss);
         for (int k = tid; k < p.K; k += kHeadThreads) {
             const float v = __uint_as_float((unsigned int)__ldcg(reinterpret_cast<const unsigned short*>(p.h + (int64_t)m * p.K + k)) << 16);   // L2: written by other SMs
-            xs[(size_t)m * p.K + k] = v;
+            put((size_t)m * p.K + k, v);
             if (!p.stats_in) ss = fma((double)v, (double)v, ss);
         }
 #pragma unroll
@@ -722,7 +865,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
         for (int i = 0; i < kHeadThreads / 32; ++i) tot += red_d[i];
         const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn((float)tot, (float)p.K), p.eps)));
         for (int k = tid; k < p.K; k += kHeadThreads)
-            xs[(size_t)m * p.K + k] = bf16_round(xs[(size_t)m * p.K + k] * __bfloat162float(p.gamma[k]) * rinv);
+            put((size_t)m * p.K + k, bf16_round(get((size_t)m * p.K + k) * __bfloat162float(p.gamma[k]) * rinv));
     }
     const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
     float bv[8];
@@ -750,10 +893,17 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
 #pragma unroll
                     for (int m = 0; m < 8; ++m) {
                         if (m < p.M) {
-                            const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8);
-                            const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8 + 4);
-                            dot[m] += wf.v[0] * x0.x + wf.v[1] * x0.y + wf.v[2] * x0.z + wf.v[3] * x0.w +
-                                      wf.v[4] * x1.x + wf.v[5] * x1.y + wf.v[6] * x1.z + wf.v[7] * x1.w;
+                            Vec8 xf;
+                            if constexpr (kCompact) {
+                                xf = unpack_bf16x8(*reinterpret_cast<const uint4*>(xs + (size_t)m * p.K + v * 8));
+                            } else {
+                                const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8);
+                                const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * p.K + v * 8 + 4);
+                                xf.v[0] = x0.x; xf.v[1] = x0.y; xf.v[2] = x0.z; xf.v[3] = x0.w;
+                                xf.v[4] = x1.x; xf.v[5] = x1.y; xf.v[6] = x1.z; xf.v[7] = x1.w;
+                            }
+                            dot[m] += wf.v[0] * xf.v[0] + wf.v[1] * xf.v[1] + wf.v[2] * xf.v[2] + wf.v[3] * xf.v[3] +
+                                      wf.v[4] * xf.v[4] + wf.v[5] * xf.v[5] + wf.v[6] * xf.v[6] + wf.v[7] * xf.v[7];
                         }
                     }
                 }

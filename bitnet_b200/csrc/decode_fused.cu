@@ -317,16 +317,35 @@ __global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const Attenti
                                  [] { __syncthreads(); }, [] {});
 }
 
+// The same for whole groups of 2 to 16 query heads at head_dim 128, with the key loop on tensor
+// cores (attention_keys_mma): four warps, 16 keys per warp and step.
+__global__ void __launch_bounds__(128) attention_decode_mma_kernel(const AttentionParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int is_last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int P = (int)p.pos[blockIdx.y];
+    if (P < 0 || P >= p.L) {      // outside the cache: flag it, touch nothing
+        if (threadIdx.x == 0 && blockIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, kErrPosition);
+        return;
+    }
+    const AttnItem it = attention_item(p, blockIdx.x, P);
+    if (it.G == 0) return;
+    attention_body<16, 4, true>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
+                                [] { __syncthreads(); }, [] {});
+}
+
 // ---------------------------------------------------------------------------------------
 // Output head: final RMSNorm, then logits = x . E^T over this CTA's slice of the vocabulary
 // (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281) and the
 // slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
 // ---------------------------------------------------------------------------------------
+template <bool kCompact>
 __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const HeadParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
-    head_body(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
+    head_body<kCompact>(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
 }
 
 // Greedy choice over the per-CTA maxima; writes the chosen ids, feeds them back as the next
@@ -431,7 +450,9 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
-    SET_SMEM(output_head_kernel, max_head_smem)
+    SET_SMEM(attention_decode_mma_kernel, max_attn_smem)
+    SET_SMEM(output_head_kernel<false>, max_head_smem)
+    SET_SMEM(output_head_kernel<true>, max_head_smem)
 #undef SET_SMEM
     return kOk;
 }
@@ -441,7 +462,7 @@ int launch_fused_linear(const FusedLinearParams& p, cudaStream_t stream, bool pd
 }
 
 static size_t attention_smem_nw(const AttentionParams& p, int nw) {
-    const int G = p.H / p.Hkv, gmax = G <= 4 ? 4 : 16;     // the tensor-core key loop keeps 16 rows per warp
+    const int G = p.H / p.Hkv, gmax = G <= 4 ? 8 : 16;     // the tensor-core key loops keep 8 or 16 rows per warp
     return sizeof(float) * ((size_t)(G + 2) * p.D + 2 * nw * gmax + (size_t)nw * G * p.D) + 64;
 }
 size_t attention_smem(const AttentionParams& p) {
@@ -454,7 +475,10 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (many_sequences && G <= 4)
+    if (many_sequences && p.S == 1 && G > 1 && p.D == 128)      // one CTA per (sequence, kv head): whole groups, tensor cores
+        e = launch_k(attention_decode_mma_kernel, grid, 128,
+                     sizeof(float) * ((size_t)(G + 2) * p.D + 2 * 4 * 16 + (size_t)4 * G * p.D) + 64, stream, p, pdl);
+    else if (many_sequences && G <= 4)
         e = launch_k(attention_decode_kernel<4, 4>, grid, 4 * 32, attention_smem_nw(p, 4), stream, p, pdl);
     else if (many_sequences && G <= 8)
         e = launch_k(attention_decode_kernel<8, 4>, grid, 4 * 32, attention_smem_nw(p, 4), stream, p, pdl);
@@ -464,10 +488,15 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     return check_cuda(e);
 }
 
-size_t head_smem(const HeadParams& p) { return sizeof(float) * ((size_t)p.M * p.K + 32 + 16 * 8 * 2) + 64; }
+// The activations of all tokens as f32 where that fits well into shared memory, else as bf16.
+static bool head_compact(const HeadParams& p) { return (size_t)p.M * p.K * sizeof(float) > 160 * 1024; }
+size_t head_smem(const HeadParams& p) {
+    return (head_compact(p) ? 2 : 4) * (size_t)p.M * p.K + sizeof(float) * (32 + 16 * 8 * 2) + 64;
+}
 
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl) {
-    return check_cuda(launch_k(output_head_kernel, grid, kHeadThreads, head_smem(p), stream, p, pdl));
+    if (head_compact(p)) return check_cuda(launch_k(output_head_kernel<true>, grid, kHeadThreads, head_smem(p), stream, p, pdl));
+    return check_cuda(launch_k(output_head_kernel<false>, grid, kHeadThreads, head_smem(p), stream, p, pdl));
 }
 
 int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl) {
