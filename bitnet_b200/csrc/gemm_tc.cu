@@ -373,6 +373,22 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
             const float ws = p.ws_f32 ? p.ws_f32[sg] : (p.ws_bf16 ? __bfloat162float(p.ws_bf16[sg]) : 1.f);
             constexpr int kCols = TN / 4;                 // tokens per warp: 8, 16 or 32
             constexpr int kChunk = kCols < 16 ? 8 : 16;
+            // per-token sum(y) and scale of this warp's tokens: lane t holds token t's, shuffles hand them round
+            int ys_l = 0;
+            float as_l = 1.f;
+            {
+                const int tok = tok0 + quarter * kCols + lane;
+                if (lane < kCols && tok < p.M) {
+                    ys_l = p.ysum[tok];
+                    as_l = p.a_f32 ? p.a_f32[tok] : (p.a_bf16 ? __bfloat162float(p.a_bf16[tok]) : 1.f);
+                }
+            }
+            // bf16 results leave through shared memory (the operand buffers are free by now): the warp's
+            // 32 rows x kCols tokens are written row by row and stored as 16-byte pieces, 64 contiguous
+            // bytes per token, instead of one 2-byte store per value.
+            const bool vec_out = p.k_splits == 1 && p.out && (p.ldo & 7) == 0 &&
+                                 (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && rb * kRows + kRows <= p.N;
+            __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(ops) + warp * (kCols * 32);
 #pragma unroll 1
             for (int cb = quarter * kCols; cb < (quarter + 1) * kCols; cb += kChunk) {
                 int c0[16], c1[16], c2[16], c3[16];
@@ -382,29 +398,37 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
                 } else {
                     tmem_ld8(ta, c0); tmem_ld8(ta + TN, c1); tmem_ld8(ta + 2 * TN, c2); tmem_ld8(ta + 3 * TN, c3);
                 }
-                // per-token sum(y) and scale of this chunk (the same for every lane)
-                int ys[16];
-                float as[16];
-#pragma unroll
-                for (int e = 0; e < kChunk; ++e) {
-                    const int tok = tok0 + cb + e;
-                    const bool ok = tok < p.M;
-                    ys[e] = ok ? p.ysum[tok] : 0;
-                    as[e] = ok ? (p.a_f32 ? p.a_f32[tok] : (p.a_bf16 ? __bfloat162float(p.a_bf16[tok]) : 1.f)) : 1.f;
-                }
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
                 for (int e = 0; e < kChunk; ++e) {
+                    const int tl = cb - quarter * kCols + e;          // token within the warp's share
                     const int tok = tok0 + cb + e;
-                    if (tok < p.M && row < p.N) {
-                        int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6);
-                        if (p.k_splits > 1) {      // partial sum over this CTA's K share
-                            atomicAdd(&p.acc_ws[(int64_t)tok * p.N + row], v);
-                            continue;
-                        }
-                        v -= ys[e];
-                        if (p.acc_out) p.acc_out[(int64_t)tok * p.N + row] = v;
-                        if (p.out) p.out[(int64_t)tok * p.ldo + row] = __float2bfloat16_rn((float)v / as[e] * ws);
+                    const int ysum_e = __shfl_sync(0xffffffffu, ys_l, tl);
+                    const float a_e = __shfl_sync(0xffffffffu, as_l, tl);
+                    int v = c0[e] + (c1[e] >> 2) + (c2[e] >> 4) + (c3[e] >> 6);
+                    if (p.k_splits > 1) {      // partial sum over this CTA's K share
+                        if (tok < p.M && row < p.N) atomicAdd(&p.acc_ws[(int64_t)tok * p.N + row], v);
+                        continue;
+                    }
+                    v -= ysum_e;
+                    const __nv_bfloat16 o = __float2bfloat16_rn((float)v / a_e * ws);
+                    if (vec_out) {
+                        stg[tl * 32 + lane] = o;
+                    } else if (tok < p.M && row < p.N) {
+                        if (p.out) p.out[(int64_t)tok * p.ldo + row] = o;
+                    }
+                    if (p.acc_out && tok < p.M && row < p.N) p.acc_out[(int64_t)tok * p.N + row] = v;
+                }
+            }
+            if (vec_out) {
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < kCols / 8; ++it) {
+                    const int tl = it * 8 + (lane >> 2), part = lane & 3;
+                    const int tok = tok0 + quarter * kCols + tl;
+                    if (tok < p.M) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + tl * 32 + part * 8);
+                        *reinterpret_cast<uint4*>(p.out + (int64_t)tok * p.ldo + rb * kRows + lane_blk * 32 + part * 8) = v;
                     }
                 }
             }

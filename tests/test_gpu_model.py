@@ -51,7 +51,10 @@ def test_attention_kernel_matches_pytorch_attention(models):
                                # slices, slice ends inside and at the end of a 16-key step
                                (1, 10, 1, 128, 4224, 4096), (2, 80, 8, 128, 1100, 1000), (1, 16, 2, 128, 512, 15),
                                (1, 16, 2, 128, 512, 16), (3, 12, 2, 128, 512, 17), (1, 10, 1, 128, 512, 383),
-                               (2, 20, 2, 128, 2176, 2049), (8, 10, 1, 128, 640, 531)]:
+                               (2, 20, 2, 128, 2176, 2049), (8, 10, 1, 128, 640, 531),
+                               # ratios up to four at long contexts and with several sequences: the 8-row tensor-core loop
+                               (1, 20, 5, 128, 1024, 900), (2, 32, 8, 128, 2176, 2049), (8, 32, 8, 128, 640, 500),
+                               (1, 4, 1, 128, 2176, 2100), (3, 8, 4, 128, 512, 385), (1, 4, 2, 128, 4224, 4099)]:
         g = torch.Generator("cuda").manual_seed(B * 100 + H)
         xqkv = torch.randn((B, (H + 2 * Hkv) * D), device="cuda", generator=g).bfloat16()
         ck = torch.randn((B, L, Hkv, D), device="cuda", generator=g).bfloat16()
