@@ -32,6 +32,7 @@ SIGNATURES = {
     "bitlinear_int8xint2_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bitlinear_int8xint2_noalloc_error": (_i, [_i]),
     "bitnet_linear_w2a8": (_i, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, ctypes.POINTER(_i), _i, _i, _i, _i, _vp]),
+    "bitnet_linear_w2a8_add_quant": (_i, [_vp, _i64, _vp, _vp, _vp, _f, _i, _i, _i, _vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp]),
     "bitnet_quant_input": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
     "bitnet_quant_input_glu": (_i, [_vp, _i64, _vp, _f, _vp, _i64, _vp, _vp, _vp, _i, _i, _vp]),
     "bitnet_decoder_create": (_vp, [_vp, _vp, _vp, _vp, _vp, _vp]),

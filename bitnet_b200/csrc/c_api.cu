@@ -112,6 +112,40 @@ int bitnet_linear_w2a8(const int8_t* y, int64_t ldy, const void* w2t, void* out_
     return w2a8_gemv(a, static_cast<cudaStream_t>(stream));
 }
 
+int bitnet_linear_w2a8_add_quant(const int8_t* y, int64_t ldy, const void* w2t, const float* act_scale, const int32_t* ysum,
+                                 float w_scale, int M, int N, int K, void* h_bf16, int64_t ldh, const void* gamma_bf16,
+                                 float eps, int8_t* y_next, int64_t ldy_next, float* act_scale_next, int32_t* ysum_next,
+                                 void* stream) {
+    g_status = kOk;
+    if (!y || !w2t || !act_scale || !ysum || !h_bf16 || M < 16 || N < 8 || K < 1 || ldy < K || ldh < N) return fail(kBadArgument);
+    if (N % 8 != 0 || ldh % 8 != 0 || (reinterpret_cast<uintptr_t>(h_bf16) & 15) != 0) return fail(kUnsupported);
+    const int64_t k_pad = (K + kTileCols - 1) / kTileCols * kTileCols;
+    if (ldy % 16 != 0 || ldy < k_pad || (reinterpret_cast<uintptr_t>(y) & 15) != 0) return fail(kUnsupported);
+    if (y_next && (ldy_next < N || ldy_next % 8 != 0 || (reinterpret_cast<uintptr_t>(y_next) & 7) != 0)) return fail(kBadArgument);
+    WorkspaceView ws;
+    if (!workspace_view(&ws)) return kCudaError;
+    const int32_t* sums = nullptr;
+    bool raw = false;
+    LinearArgs a;
+    a.w2t = w2t;
+    a.y = y; a.ldy = ldy; a.ysum = ysum;
+    a.a_f32 = act_scale; a.a_stride = 1;
+    a.seg.n_seg = 1;
+    for (int i = 0; i < 8; ++i) a.seg.end[i] = N;
+    a.M = M; a.N = N; a.K = K;
+    a.sums = &sums; a.sums_raw = &raw;
+    const int rc = w2a8_gemm_tc(a, ws.error_flag, ws.tc_acc, ws.tc_acc_ints, ws.n_sm, static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    QuantArgs q;
+    q.x_bf16 = static_cast<const __nv_bfloat16*>(h_bf16); q.ldx = ldh;
+    q.gamma = static_cast<const __nv_bfloat16*>(gamma_bf16); q.eps = eps;
+    q.y = y_next; q.ldy = y_next ? ldy_next : N;
+    q.a_f32 = act_scale_next; q.ysum = ysum_next;
+    q.M = M; q.K = N;
+    q.lin_acc = const_cast<int32_t*>(sums); q.lin_ysum = raw ? ysum : nullptr; q.lin_a = act_scale; q.lin_ws = w_scale;
+    return act_quant(q, static_cast<cudaStream_t>(stream));
+}
+
 int bitnet_quant_input(const void* x_bf16, int64_t ldx, const void* gamma_bf16, float eps, int8_t* y, int64_t ldy,
                        float* act_scale, void* s_bf16, int32_t* ysum, int M, int K, void* stream) {
     g_status = kOk;

@@ -785,6 +785,7 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
         return true;
     }
     if (attention_slices(p.S, P) != 1) return false;
+    CHAIN_STAMP(1)
     // rotation of position P for this lane's pairs d0/2 .. d0/2+3
     const float* rope = p.rope + (int64_t)P * D + d0;
     float cs[8] = {1.f, 0.f, 1.f, 0.f, 1.f, 0.f, 1.f, 0.f};
@@ -830,6 +831,7 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = 0.f;
     const int n_keys = P + 1;
+    CHAIN_STAMP(2)
 #pragma unroll 1
     for (int j0 = 0; j0 < n_keys; j0 += 32 * kKeyRounds) {
         if (j0 > 0) load_block(j0, P);
@@ -873,6 +875,7 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
             m_run = m_new;
         }
     }
+    CHAIN_STAMP(3)
     // combine: first the two half-warps of a warp by shuffles, then the 16 warps through shared memory
     {
         const float m_o = __shfl_xor_sync(0xffffffffu, m_run, 16), l_o = __shfl_xor_sync(0xffffffffu, l_run, 16);
@@ -920,7 +923,9 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
             p.t_out[oi] = val * gq;                  // exact: both factors are bf16 values
         }
     }
+    CHAIN_STAMP(4)
     if (p.stats_out) publish_head_stats(p, b, val, gq, tid, sd, sf, [] { __syncthreads(); });
+    CHAIN_STAMP(5)
     return true;
 }
 
@@ -942,6 +947,7 @@ __global__ void __launch_bounds__(NTHREADS) chain_attention_kernel(const __grid_
     static_assert(AttnCfg<GMAX>::kThreads <= NTHREADS, "the split-KV body uses a prefix of the CTA's warps");
     pdl_launch_dependents();
     pdl_wait();
+    CHAIN_STAMP(0)
     const int b = blockIdx.y, tid = threadIdx.x;
     if (p.zero_slot && blockIdx.x == 0 && tid == 0) {
         p.zero_slot[b].ss = 0.0;

@@ -529,6 +529,7 @@ static int enqueue_step(Decoder* d, int64_t* tokens, int64_t* pos, int64_t* out,
         layer_params(d, l, pos, lin, &ap, red);
 #ifdef BITNET_TRACE
         for (int j = 0; j < 4; ++j) lin[j].trace = d->trace + 16 * (4 * l + j);
+        ap.trace = d->trace + 16 * (4 * c.n_layers + l);
 #endif
         if (launch_chain_linear(lin[0], stream, true)) return bitnet_last_status();
         if (!linears_only && launch_chain_attention(ap, c.batch, stream, true)) return bitnet_last_status();

@@ -63,6 +63,7 @@ struct TcParams {
     // that a bulk copy drops into the operand buffer.  Null: worker warps stage them from y.
     const uint8_t* ycanon;
     int m_groups;
+    bool defer_finalize;         // split K: no second pass here, the caller's next kernel finalises acc_ws
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -535,7 +536,7 @@ cudaError_t launch_tc(const TcParams& p, cudaStream_t stream) {
     cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, w2a8_gemm_tc_kernel<TN>, p);
     if (e != cudaSuccess) return e;
-    if (p.k_splits > 1) {
+    if (p.k_splits > 1 && !p.defer_finalize) {
         const int bx = (p.N + 1023) / 1024;   // four rows per thread
         cfg.gridDim = dim3((unsigned)(bx < 64 ? bx : 64), (unsigned)p.M);
         cfg.blockDim = dim3(256);
@@ -573,6 +574,16 @@ int w2a8_gemm_tc(const LinearArgs& a, int* error_flag, int32_t* acc_ws, size_t a
     if (ks < 1 || !acc_ws || (size_t)a.M * a.N > acc_ws_ints) ks = 1;
     p.k_splits = ks;
     p.acc_ws = acc_ws;
+    if (a.sums) {
+        // the caller finalises: the sums stay in the work space (raw partial sums with split K; with
+        // one CTA per output tile the epilogue stores them there with sum(y) already taken off)
+        if (!acc_ws || (size_t)a.M * a.N > acc_ws_ints) return set_status(kTooLarge), kTooLarge;
+        p.defer_finalize = true;
+        p.out = nullptr;
+        p.acc_out = ks > 1 ? nullptr : acc_ws;
+        *a.sums = acc_ws;
+        *a.sums_raw = ks > 1;
+    }
     // Many tokens: lay the activations out for the tensor core once, instead of in every CTA.
     if (a.M >= 128) {
         p.m_groups = (a.M + 127) / 128 * 16;

@@ -20,6 +20,11 @@ struct LinearArgs {
     const __nv_bfloat16* ws_bf16 = nullptr;
     ScaleSegments seg{1, {0, 0, 0, 0, 0, 0, 0, 0}};
     int M = 0, N = 0, K = 0;
+    // tcgen05 path only: leave the exact integer sums in the work space (`sums`: [M, N]) for a
+    // kernel of the caller's that finalises them, instead of finalising here.  *sums_raw tells
+    // whether sum(y) still has to be taken off (split K) or already is (one CTA per output tile).
+    const int32_t** sums = nullptr;
+    bool* sums_raw = nullptr;
 };
 
 int w2a8_gemv(const LinearArgs& a, cudaStream_t stream);
@@ -65,6 +70,13 @@ struct QuantArgs {
     int32_t* ysum = nullptr;                 // optional [M]
     int M = 0, K = 0;
     bool glu = false;                        // rows hold 2K values: quantise relu(x[k])^2 * x[K + k] (gpu/model.py:193-195)
+    // Fused form behind a BitLinear whose result is added to the residual stream: the row is
+    // x[m, k] += bf16( (lin_acc[m, k] - lin_ysum[m]?) / lin_a[m] * lin_ws ) first (x_bf16 is then
+    // updated in place and lin_acc is cleared), and quantised afterwards unless y is null.
+    int32_t* lin_acc = nullptr;              // [M, K] integer sums of the preceding BitLinear, or null
+    const int32_t* lin_ysum = nullptr;       // [M] sums still to be taken off, or null
+    const float* lin_a = nullptr;            // [M] its activation scales
+    float lin_ws = 1.f;                      // its weight scale
 };
 int act_quant(const QuantArgs& a, cudaStream_t stream);
 

@@ -26,8 +26,30 @@ __global__ void __launch_bounds__(kPrologueThreads) act_quant_kernel(const Quant
     const int K = p.K;
     float a;
     int sy_warp;
+    if (p.lin_acc) {
+        // x += rescaled sums of the preceding BitLinear (K % 8 == 0 and aligned rows: checked by the host)
+        int32_t* acc = p.lin_acc + (int64_t)tok * K;
+        const int ys = p.lin_ysum ? p.lin_ysum[tok] : 0;
+        const float la = p.lin_a[tok];
+        __nv_bfloat16* hrow = const_cast<__nv_bfloat16*>(row);
 #pragma unroll 1
-    for (int v = tid; v < (K + 7) / 8; v += kPrologueThreads) {
+        for (int v = tid; v < K / 8; v += kPrologueThreads) {
+            const int4 s0 = *reinterpret_cast<const int4*>(acc + v * 8), s1 = *reinterpret_cast<const int4*>(acc + v * 8 + 4);
+            *reinterpret_cast<int4*>(acc + v * 8) = make_int4(0, 0, 0, 0);
+            *reinterpret_cast<int4*>(acc + v * 8 + 4) = make_int4(0, 0, 0, 0);
+            const int sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            Vec8 x = unpack_bf16x8(*reinterpret_cast<const uint4*>(hrow + v * 8));
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x.v[e] = bf16_round(x.v[e] + bf16_round((float)(sv[e] - ys) / la * p.lin_ws));
+            const uint4 packed = pack_bf16x8(x);
+            *reinterpret_cast<uint4*>(hrow + v * 8) = packed;
+            *reinterpret_cast<uint4*>(xv + v * 8) = packed;
+        }
+        if (!p.y) return;
+        __syncthreads();
+    }
+#pragma unroll 1
+    for (int v = tid; v < (K + 7) / 8 && !p.lin_acc; v += kPrologueThreads) {
         Vec8 x = load_bf16x8(row, v * 8, K, vec_ok);
         if (p.glu) {   // relu(x1)^2 * x3 with bf16 rounding after each step, as the bf16 tensor ops round
             const Vec8 x3 = load_bf16x8(row + K, v * 8, K, vec_ok && K % 8 == 0);

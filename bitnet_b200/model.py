@@ -92,6 +92,22 @@ class BitLinearKernel(nn.Module):
                               self.in_features)
         return out.view(*x.shape[:-1], self.out_features)
 
+    def from_quantised(self, qa) -> torch.Tensor:
+        """The matmul alone on already quantised activations (y, act_scale, ysum) -> bf16 [M, N]."""
+        y, a, ysum = qa
+        return ops.linear_w2a8(y, a, ysum, self.weight, self.scale_f32, self.seg_end, self.out_features, self.in_features)
+
+    def add_into(self, qa, h: torch.Tensor, next_norm: Optional[RMSNorm]):
+        """h += self(qa) in place, then quant_input(next_norm(h)) in the same launch (None without a
+        next norm): ops.linear_w2a8_add_quant.  One row segment only (wo, w2)."""
+        assert len(self.segments) == 1
+        if getattr(self, "_host_scale", None) is None:       # read once, outside any stream capture
+            self._host_scale = float(self.scale_f32[0])
+        y, a, ysum = qa
+        return ops.linear_w2a8_add_quant(y, a, ysum, self.weight, self._host_scale, self.out_features, self.in_features, h,
+                                         None if next_norm is None else next_norm.weight,
+                                         0.0 if next_norm is None else next_norm.eps)
+
     def forward_glu(self, x13: torch.Tensor, norm: Optional[RMSNorm] = None) -> torch.Tensor:
         """forward(squared_relu(x1) * x3, norm) for x13 = [x1 | x3], the gate fused into the
         quantisation kernel."""
@@ -226,6 +242,21 @@ class TransformerBlock(nn.Module):
         h = x + self.attention(x, self.attention_norm, cache, pos, rope, kv_len)
         return h + self.feed_forward(h, self.ffn_norm)
 
+    def decode_fused(self, h: torch.Tensor, qa, cache, pos, rope, next_norm: Optional[RMSNorm]):
+        """One decode step of the layer for 16 sequences or more on the kernel path, with the
+        residual additions, the norms and the quantisations behind wo and w2 fused into their
+        BitLinears: the same arithmetic as forward(), 10 launches instead of 15.
+        h bf16 [B, dim] (updated in place); qa = quant_input(attention_norm(h)); returns the
+        quantised input of the next layer (None behind the last one)."""
+        att, ff = self.attention, self.feed_forward
+        xqkv = att.wqkv.from_quantised(qa)
+        out = ops.attention_decode(xqkv, pos, rope, cache[0], cache[1], att.n_local_heads, att.n_local_kv_heads, att.head_dim)
+        qo = ops.quant_input(out, att.attn_sub_norm.weight, att.attn_sub_norm.eps)
+        q13 = att.wo.add_into(qo, h, self.ffn_norm)
+        x13 = ff.w13.from_quantised(q13)
+        q2 = ops.quant_input_glu(x13, ff.ffn_sub_norm.weight, ff.ffn_sub_norm.eps)
+        return ff.w2.add_into(q2, h, next_norm)
+
 
 class Transformer(nn.Module):
     """gpu/model.py:246-296."""
@@ -243,6 +274,7 @@ class Transformer(nn.Module):
             self.output.weight = self.tok_embeddings.weight
         self.max_seq_len = max_seq_len
         self.rope: Optional[torch.Tensor] = None
+        self.fused_decode = True      # False: batched decode through the plain per-module path (for comparisons)
 
     @torch.no_grad()
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, cache: List[LayerCache],
@@ -252,6 +284,17 @@ class Transformer(nn.Module):
         if self.rope is None or self.rope.device != tokens.device:
             self.rope = rope_table(self.args.head_dim, self.max_seq_len, self.args.rope_theta, tokens.device)
         h = self.tok_embeddings(tokens)
+        B, T = tokens.shape
+        if (self.fused_decode and T == 1 and kv_len is None and B >= 16 and self.args.use_kernel and self.args.dim % 8 == 0
+                and all(l.attention.kernel_attention for l in self.layers)):
+            # batched decode on the kernel path: residual, norm and quantisation fused behind wo and w2
+            h = h.view(B, self.args.dim).contiguous()
+            first = self.layers[0].attention_norm
+            qa = ops.quant_input(h, first.weight, first.eps)
+            for i, (layer, c) in enumerate(zip(self.layers, cache)):
+                nxt = self.layers[i + 1].attention_norm if i + 1 < len(self.layers) else None
+                qa = layer.decode_fused(h, qa, c, pos, self.rope, nxt)
+            return self.output(self.norm(h.view(B, 1, self.args.dim))).float()
         for layer, c in zip(self.layers, cache):
             h = layer(h, c, pos, self.rope, kv_len)
         if last_only:

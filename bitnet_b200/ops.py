@@ -82,6 +82,31 @@ def linear_w2a8(y: torch.Tensor, act_scale: torch.Tensor, ysum: Optional[torch.T
     return acc if want_acc else out
 
 
+def linear_w2a8_add_quant(y: torch.Tensor, act_scale: torch.Tensor, ysum: torch.Tensor, weight: torch.Tensor,
+                          w_scale: float, n: int, k: int, h: torch.Tensor, gamma: Optional[torch.Tensor],
+                          eps: float = 1e-5, pad_to: int = 128):
+    """h += BitLinear(y) in place (h bf16 [M, N], contiguous), then - with gamma - RMSNorm and
+    quant_input of the new h: returns (y_next int8 [M, N_pad], act_scale f32 [M], ysum int32 [M]),
+    or None without gamma.  The fused form of `h = h + linear(...)` followed by the next
+    BitLinear's quant_input, for 16 tokens or more (bitnet_linear_w2a8_add_quant)."""
+    m = y.shape[0]
+    assert h.dtype == torch.bfloat16 and h.dim() == 2 and h.shape == (m, n) and h.stride(1) == 1
+    if gamma is None:
+        _lib.check(_lib.lib.bitnet_linear_w2a8_add_quant(_lib.ptr(y), y.stride(0), _lib.ptr(weight), _lib.ptr(act_scale),
+                                                         _lib.ptr(ysum), float(w_scale), m, n, k, _lib.ptr(h), h.stride(0),
+                                                         None, 0.0, None, 0, None, None, _lib.stream_ptr()))
+        return None
+    n_pad = (n + pad_to - 1) // pad_to * pad_to
+    y2 = torch.empty((m, n_pad), dtype=torch.int8, device=y.device)
+    a2 = torch.empty((m,), dtype=torch.float32, device=y.device)
+    s2 = torch.empty((m,), dtype=torch.int32, device=y.device)
+    _lib.check(_lib.lib.bitnet_linear_w2a8_add_quant(_lib.ptr(y), y.stride(0), _lib.ptr(weight), _lib.ptr(act_scale),
+                                                     _lib.ptr(ysum), float(w_scale), m, n, k, _lib.ptr(h), h.stride(0),
+                                                     _lib.ptr(gamma), eps, _lib.ptr(y2), n_pad, _lib.ptr(a2), _lib.ptr(s2),
+                                                     _lib.stream_ptr()))
+    return y2, a2, s2
+
+
 def attention_decode(xqkv: torch.Tensor, pos: torch.Tensor, rope: torch.Tensor, cache_k: torch.Tensor,
                      cache_v: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
     """One new token per sequence: RoPE, append to the KV cache, attention over the cache.

@@ -99,6 +99,20 @@ int bitnet_linear_w2a8(const int8_t* y, int64_t ldy, const void* w2t, void* out_
                        const float* w_scale, const int* seg_end, int n_seg,
                        int M, int N, int K, void* stream);
 
+/* A BitLinear whose result is added to the residual stream, fused with what follows it in a
+ * decoder layer (gpu/model.py:225-227, 236-242: h = h + wo(...), then ffn_norm and the next
+ * BitLinear's quant_input; likewise behind w2): h[m, :] += bf16(acc / act_scale[m] * w_scale),
+ * rounded to bf16 as the reference's tensor addition rounds, and then - unless y_next is NULL -
+ * the RMSNorm with gamma_bf16 and the int8 quantisation of the new h, exactly as
+ * bitnet_quant_input computes them.  Two launches (tensor-core matmul, one kernel for the rest)
+ * instead of four.  M >= 16; N % 8 == 0; y as for the tensor-core path of bitnet_linear_w2a8
+ * (16-byte aligned rows, ldy a multiple of 16 and >= ceil128(K), zero filled beyond K); ysum is
+ * required; one weight scale (wo and w2 have one row segment).  Uses the workspace. */
+int bitnet_linear_w2a8_add_quant(const int8_t* y, int64_t ldy, const void* w2t, const float* act_scale,
+                                 const int32_t* ysum, float w_scale, int M, int N, int K, void* h_bf16, int64_t ldh,
+                                 const void* gamma_bf16, float eps, int8_t* y_next, int64_t ldy_next,
+                                 float* act_scale_next, int32_t* ysum_next, void* stream);
+
 /* Activation prologue: optional RMSNorm (gamma_bf16 != NULL; gpu/model.py:159-160,
  * 195-196, 237-242) followed by BitLinearKernel.quant_input (gpu/model.py:68-71):
  * a = 127 / max(absmax, 1e-5), y = clamp(round_half_even(x*a), -128, 127).

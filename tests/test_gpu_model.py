@@ -236,3 +236,33 @@ def test_chain_flags_positions_and_tokens_outside_their_ranges(models):
     h.decode_step()
     with pytest.raises(ValueError):
         h.decode_step()
+
+
+@pytest.mark.parametrize("batch,over", [(16, {}), (33, {}), (64, dict(dim=384, n_heads=3, n_kv_heads=3, ffn_dim=200 * 4))])
+def test_batched_decode_with_fused_residual_norm_quant_equals_plain_path(batch, over):
+    """Batches of 16 and more decode with the residual addition, the RMSNorm and the next
+    quantisation fused behind wo and w2 (bitnet_linear_w2a8_add_quant): logits and KV caches must be
+    bit-identical to the same steps through the per-module path."""
+    from bitnet_b200.model import build_synthetic, make_cache, preset
+
+    args = preset("tiny", n_layers=3, **over)
+    model = build_synthetic(args, seed=11, device="cuda", max_seq_len=64)
+    g = torch.Generator("cuda").manual_seed(batch)
+    prompt = torch.randint(0, args.vocab_size, (batch, 5), device="cuda", generator=g)
+    outs = []
+    for fused in (True, False):
+        model.fused_decode = fused
+        cache = make_cache(args, batch, 64, "cuda")
+        pos = torch.zeros(batch, dtype=torch.int64, device="cuda")
+        lg = model(prompt, pos, cache, kv_len=5, last_only=True)
+        tok = lg[:, -1].argmax(-1, keepdim=True)
+        steps = []
+        for s in range(6):
+            lg = model(tok, pos + 5 + s, cache)
+            steps.append(lg.clone())
+            tok = lg[:, -1].argmax(-1, keepdim=True)
+        outs.append((torch.stack(steps), [c[0].clone() for c in cache], [c[1].clone() for c in cache]))
+    model.fused_decode = True
+    assert torch.equal(outs[0][0], outs[1][0])
+    for a, b in zip(outs[0][1] + outs[0][2], outs[1][1] + outs[1][2]):
+        assert torch.equal(a, b)
