@@ -318,8 +318,11 @@ __global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const Attenti
 }
 
 // The same for whole groups of 2 to 16 query heads at head_dim 128, with the key loop on tensor
-// cores (attention_keys_mma): four warps, 16 keys per warp and step.
-__global__ void __launch_bounds__(128) attention_decode_mma_kernel(const AttentionParams p) {
+// cores (attention_keys_mma / attention_keys_mma8): four warps, 16 keys per warp and step.  Groups
+// of up to 8 heads take the 8-row loop, whose 128 registers let four CTAs share an SM (with
+// hundreds of (sequence, kv head) pairs the number of CTAs in flight sets the pace).
+template <int ROWS>
+__global__ void __launch_bounds__(128, ROWS == 8 ? 4 : 1) attention_decode_mma_kernel(const AttentionParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
     pdl_launch_dependents();
@@ -331,8 +334,8 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const Attenti
     }
     const AttnItem it = attention_item(p, blockIdx.x, P);
     if (it.G == 0) return;
-    attention_body<16, 4, true>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
-                                [] { __syncthreads(); }, [] {});
+    attention_body<ROWS, 4, true>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
+                                  [] { __syncthreads(); }, [] {});
 }
 
 // ---------------------------------------------------------------------------------------
@@ -450,7 +453,8 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     SET_SMEM(attention_decode_kernel<4>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
-    SET_SMEM(attention_decode_mma_kernel, max_attn_smem)
+    SET_SMEM(attention_decode_mma_kernel<8>, max_attn_smem)
+    SET_SMEM(attention_decode_mma_kernel<16>, max_attn_smem)
     SET_SMEM(output_head_kernel<false>, max_head_smem)
     SET_SMEM(output_head_kernel<true>, max_head_smem)
 #undef SET_SMEM
@@ -475,9 +479,11 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (many_sequences && p.S == 1 && G > 1 && p.D == 128)      // one CTA per (sequence, kv head): whole groups, tensor cores
-        e = launch_k(attention_decode_mma_kernel, grid, 128,
-                     sizeof(float) * ((size_t)(G + 2) * p.D + 2 * 4 * 16 + (size_t)4 * G * p.D) + 64, stream, p, pdl);
+    if (many_sequences && p.S == 1 && G > 1 && p.D == 128) {    // one CTA per (sequence, kv head): whole groups, tensor cores
+        const size_t sm = sizeof(float) * ((size_t)(G + 2) * p.D + 2 * 4 * 16 + (size_t)4 * G * p.D) + 64;
+        e = G <= 8 ? launch_k(attention_decode_mma_kernel<8>, grid, 128, sm, stream, p, pdl)
+                   : launch_k(attention_decode_mma_kernel<16>, grid, 128, sm, stream, p, pdl);
+    }
     else if (many_sequences && G <= 4)
         e = launch_k(attention_decode_kernel<4, 4>, grid, 4 * 32, attention_smem_nw(p, 4), stream, p, pdl);
     else if (many_sequences && G <= 8)
