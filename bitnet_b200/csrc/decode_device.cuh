@@ -327,7 +327,7 @@ __device__ __forceinline__ void attention_keys_mma(const float* q_s, int G, cons
 // can run inside a 512-thread CTA): only rows 0..7 of the MMAs are kept - the other half of every
 // accumulator goes to two scratch registers - and the values are requested after the scores have
 // been issued instead of together with the keys.
-template <int NW, int GMAX>
+template <int NW, int GMAX, bool kEager>
 __device__ __forceinline__ void attention_keys_mma8(const float* q_s, int G, const float* knew, const float* vnew, bool with_new,
                                                     const __nv_bfloat16* ck, const __nv_bfloat16* cv, int64_t key_stride, int lo,
                                                     int hi, int warp, int lane, float* red_m, float* red_l, float* red_o) {
@@ -362,13 +362,35 @@ __device__ __forceinline__ void attention_keys_mma8(const float* q_s, int G, con
 #pragma unroll 1
     for (int k0 = lo + warp * 16; k0 < hi; k0 += NW * 16) {
         float s[2][2];
+        // kEager (CTAs of their own, 170 registers): every load of the step is issued before the first
+        // is used, as in the 16-row loop.  Otherwise halves one after the other: registers.
+        uint4 kkE[kEager ? 2 : 1][4], vvE[kEager ? 4 : 1][2];
+        if constexpr (kEager) {
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {        // the two 8-key halves one after the other: registers
+            for (int t = 0; t < 2; ++t) {
+                const int key = k0 + t * 8 + g;
+                const uint4* src = reinterpret_cast<const uint4*>(ck + (int64_t)key * key_stride) + q;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) kkE[t][i] = key < hi ? src[i * 4] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int key = k0 + (x >> 1) * 8 + 2 * q + (x & 1);
+                const uint4* src = reinterpret_cast<const uint4*>(cv + (int64_t)key * key_stride) + g;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) vvE[x][j] = key < hi ? src[j * 8] : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
             uint4 kk[4];
             const int key = k0 + t * 8 + g;
             const uint4* src = reinterpret_cast<const uint4*>(ck + (int64_t)key * key_stride) + q;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) kk[i] = key < hi ? src[i * 4] : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (kEager) kk[i] = kkE[t][i];
+                else kk[i] = key < hi ? src[i * 4] : make_uint4(0, 0, 0, 0);
+            }
             s[t][0] = 0.f; s[t][1] = 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -398,7 +420,8 @@ __device__ __forceinline__ void attention_keys_mma8(const float* q_s, int G, con
             for (int x = 0; x < 4; ++x) {
                 const int key = k0 + (x >> 1) * 8 + 2 * q + (x & 1);
                 const uint4* src = reinterpret_cast<const uint4*>(cv + (int64_t)key * key_stride) + g;
-                vv[x] = key < hi ? src[j * 8] : make_uint4(0, 0, 0, 0);
+                if constexpr (kEager) vv[x] = vvE[x][j];
+                else vv[x] = key < hi ? src[j * 8] : make_uint4(0, 0, 0, 0);
             }
             const uint32_t wa[4] = {vv[0].x, vv[0].y, vv[0].z, vv[0].w};
             const uint32_t wb[4] = {vv[1].x, vv[1].y, vv[1].z, vv[1].w};
@@ -459,7 +482,7 @@ __device__ __forceinline__ void attention_keys_mma8(const float* q_s, int G, con
 // q, k, v (xqkv) are visible: the cache rows and the positions must not change meanwhile.
 // Returns true when this CTA wrote p.out for its heads (always with S == 1; with several slices
 // only the CTA that combined them).
-template <int GMAX, int NW, bool kMma = false, class Sync, class Wait>
+template <int GMAX, int NW, bool kMma = false, bool kEager = false, class Sync, class Wait>
 __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t* smem, int* is_last_s, int b, int kvh,
                                                int h0, int G, int split, int S, int P, int tid, Sync sync, Wait wait) {
     constexpr int NT = NW * 32;
@@ -528,7 +551,7 @@ __device__ __forceinline__ bool attention_body(const AttentionParams& p, uint8_t
     sync();
 
     if constexpr (kMma && GMAX <= 8) {
-        attention_keys_mma8<NW, GMAX>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,
+        attention_keys_mma8<NW, GMAX, kEager>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,
                                       red_l, red_o);
     } else if constexpr (kMma) {
         attention_keys_mma<NW, GMAX>(q_s, G, knew, vnew, split == S - 1, ck - d0, cv - d0, key_stride, lo, hi, warp, lane, red_m,

@@ -319,10 +319,10 @@ __global__ void __launch_bounds__(NW * 32) attention_decode_kernel(const Attenti
 
 // The same for whole groups of 2 to 16 query heads at head_dim 128, with the key loop on tensor
 // cores (attention_keys_mma / attention_keys_mma8): four warps, 16 keys per warp and step.  Groups
-// of up to 8 heads take the 8-row loop, whose 128 registers let four CTAs share an SM (with
+// of up to 8 heads take the 8-row loop with all loads of a step in flight, three CTAs to an SM (with
 // hundreds of (sequence, kv head) pairs the number of CTAs in flight sets the pace).
 template <int ROWS>
-__global__ void __launch_bounds__(128, ROWS == 8 ? 4 : 1) attention_decode_mma_kernel(const AttentionParams p) {
+__global__ void __launch_bounds__(128, ROWS == 8 ? 3 : 1) attention_decode_mma_kernel(const AttentionParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
     pdl_launch_dependents();
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(128, ROWS == 8 ? 4 : 1) attention_decode_mma_k
     }
     const AttnItem it = attention_item(p, blockIdx.x, P);
     if (it.G == 0) return;
-    attention_body<ROWS, 4, true>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
+    attention_body<ROWS, 4, true, true>(p, smem, &is_last, blockIdx.y, it.kvh, it.h0, it.G, it.split, it.S, P, threadIdx.x,
                                   [] { __syncthreads(); }, [] {});
 }
 
@@ -479,7 +479,7 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     const dim3 grid(p.Hkv * p.S, batch);
     const size_t smem = attention_smem(p);
     cudaError_t e;
-    if (many_sequences && p.S == 1 && G > 1 && p.D == 128) {    // one CTA per (sequence, kv head): whole groups, tensor cores
+    if (many_sequences && p.S < G && G > 1 && p.D == 128) {     // whole groups per CTA (and slice), tensor cores
         const size_t sm = sizeof(float) * ((size_t)(G + 2) * p.D + 2 * 4 * 16 + (size_t)4 * G * p.D) + 64;
         e = G <= 8 ? launch_k(attention_decode_mma_kernel<8>, grid, 128, sm, stream, p, pdl)
                    : launch_k(attention_decode_mma_kernel<16>, grid, 128, sm, stream, p, pdl);

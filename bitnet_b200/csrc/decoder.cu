@@ -670,6 +670,13 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
     if (!w) return bitnet_last_status();
     int s = w->n_sm / (n_kv_heads * batch);
     s = s < 1 ? 1 : (s > 32 ? 32 : s);
+    // Many sequences (at least two CTAs per SM without any split) take the op-by-op path's own
+    // kernels.  Whole groups of query heads on the tensor-core loop may still be cut into up to
+    // three slices at long contexts (fewer than the heads of a group, so that a group stays in
+    // one CTA): hundreds of long CTAs in a wave and a fraction end in a long tail otherwise.
+    const bool many = s == 1 && batch * n_kv_heads >= 2 * w->n_sm;
+    const int G = n_heads / n_kv_heads;
+    if (many && G > 1 && head_dim == 128) s = G - 1 < 3 ? G - 1 : 3;
     const size_t need = (size_t)batch * n_heads * s * (head_dim + 2) * sizeof(float);
     if (need > w->attn_part_bytes) {      // grows outside stream capture only (cudaMalloc)
         std::lock_guard<std::mutex> lock(g_ws_mutex);
@@ -693,8 +700,7 @@ int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos
     // Many sequences (at least two CTAs per SM without any split): the 4-warp form of the
     // split-KV kernel.  Otherwise the decode chain's attention kernel, so that a decoder run op
     // by op and the in-library chain compute the very same attention.
-    if (s == 1 && batch * n_kv_heads >= 2 * w->n_sm)
-        return launch_attention(ap, batch, static_cast<cudaStream_t>(stream), false, true);
+    if (many) return launch_attention(ap, batch, static_cast<cudaStream_t>(stream), false, true);
     return launch_chain_attention(ap, batch, static_cast<cudaStream_t>(stream), false);
 }
 
