@@ -69,9 +69,17 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
     const int g = lane >> 2, q = lane & 3;
     const int row_group = blockIdx.x;
     const int tok0 = blockIdx.y * (8 * MB);
-    // Launched as a programmatic dependent: the activations may be the predecessor's output.
-    // (The weights are constants, but this kernel loads them straight into registers, where
-    // only a few fit, so nothing is fetched ahead of the wait.)
+    // Launched as a programmatic dependent: the activations may be the predecessor's output, the
+    // weights are constants.  The first tiles of every warp (most of a row group for K up to a few
+    // thousand) are therefore requested before the wait, while the predecessor still runs.
+    constexpr int U = 4;   // weight tiles in flight per warp
+    const uint4* wrow = p.w + (int64_t)row_group * p.k_tiles * 32 + lane;
+    uint4 wv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int kt = warp + u * kWarps;
+        if (kt < p.k_tiles) wv[u] = ldg_stream(wrow + (int64_t)kt * 32);
+    }
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
@@ -86,16 +94,15 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
 #pragma unroll
     for (int nb = 0; nb < MB; ++nb) ys[nb] = 0;
 
-    const uint4* wrow = p.w + (int64_t)row_group * p.k_tiles * 32 + lane;
     const bool vec_ok = (p.ldy % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
 
-    constexpr int U = 4;   // weight tiles in flight per warp
     for (int kt0 = warp; kt0 < p.k_tiles; kt0 += kWarps * U) {
-        uint4 wv[U];
+        if (kt0 != warp) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int kt = kt0 + u * kWarps;
-            if (kt < p.k_tiles) wv[u] = ldg_stream(wrow + (int64_t)kt * 32);
+            for (int u = 0; u < U; ++u) {
+                const int kt = kt0 + u * kWarps;
+                if (kt < p.k_tiles) wv[u] = ldg_stream(wrow + (int64_t)kt * 32);
+            }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
