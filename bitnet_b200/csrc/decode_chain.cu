@@ -150,6 +150,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     if (warp == kCWarps) {
         // ---- producer: streams the weight tiles; independent of the predecessor kernel ----
         if (lane == 0) {
+            const uint64_t policy = l2_evict_first_policy();
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
                 const int s = c & s_mask;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
                     const int n = min(end - t, seg_tiles - off);
                     const uint8_t* src = p.w2t + ((int64_t)(u0 + set * p.sub_stride) * p.k_tiles + off) * kTileBytes;
                     bulk_g2s(sm.ring + s * kCStageBytes + (t - c * kCStageTiles) * kTileBytes, src, (uint32_t)n * kTileBytes,
-                             &sm.full_bar[s]);
+                             &sm.full_bar[s], policy);
                     t += n;
                 }
             }
@@ -760,6 +761,7 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
     const __nv_bfloat16* cv = p.cache_v + ((int64_t)b * p.L * p.Hkv + kvh) * D + d0;
     const int P = (int)__ldcg(p.pos + b);
     uint4 kr[kKeyRounds], vr[kKeyRounds];
+    const uint64_t keep = l2_evict_last_policy();
     auto load_block = [&](int j0, int j_end) {   // cache rows j0 + 32 r + hw, r < 8, below j_end
 #pragma unroll
         for (int r = 0; r < kKeyRounds; ++r) {
@@ -767,8 +769,8 @@ __device__ __forceinline__ bool attention_short(const AttentionParams& p, uint8_
             kr[r] = make_uint4(0, 0, 0, 0);
             vr[r] = make_uint4(0, 0, 0, 0);
             if (j < j_end && live) {
-                kr[r] = __ldcg(reinterpret_cast<const uint4*>(ck + j * key_stride));   // L2: rows appended by earlier steps
-                vr[r] = __ldcg(reinterpret_cast<const uint4*>(cv + j * key_stride));
+                kr[r] = ldcg_keep(reinterpret_cast<const uint4*>(ck + j * key_stride), keep);   // L2: rows appended by earlier steps
+                vr[r] = ldcg_keep(reinterpret_cast<const uint4*>(cv + j * key_stride), keep);
             }
         }
     };

@@ -56,6 +56,35 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return mbar_test_wait(bar, parity) || mbar_wait_slow(bar, parity);   // usually complete already
 }
+// Weight tiles are read once per step and a step's weights are many times the L2: they are marked
+// evict-first so that what is read again soon (KV cache rows, activations, statistics) stays.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_evict_last_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol));
+    return pol;
+}
+// 16-byte load through L2 (the data was written by other SMs) that asks L2 to keep the line:
+// KV cache rows, which every step reads again.
+__device__ __forceinline__ uint4 ldcg_keep(const uint4* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(policy)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
                      smem_u32(dst)),
@@ -896,6 +925,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
 #pragma unroll
     for (int m = 0; m < 8; ++m) { bv[m] = -INFINITY; bi[m] = 0x7fffffff; }
     const int vec_per_row = p.K / 8;     // 16-byte pieces
+    const uint64_t w_policy = l2_evict_first_policy();    // the projection is read once per step: first out of L2
     for (int row = r0 + warp; row < r1; row += kHeadThreads / 32) {
         const uint4* wr = reinterpret_cast<const uint4*>(p.w + (int64_t)row * p.K);
         float dot[8];
@@ -906,7 +936,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
 #pragma unroll
             for (int u = 0; u < kHeadMaxLoads; ++u) {
                 const int v = base + u * 32 + lane;
-                if (v < vec_per_row) wv[u] = ldg_stream(wr + v);
+                if (v < vec_per_row) wv[u] = ldg_stream_hint(wr + v, w_policy);
             }
 #pragma unroll
             for (int u = 0; u < kHeadMaxLoads; ++u) {

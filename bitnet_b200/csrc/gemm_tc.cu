@@ -101,6 +101,14 @@ __device__ __noinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatile i
     }
     return true;
 }
+// The same with an L2 eviction policy: packed weights are read once per call and leave L2 first.
+__device__ __forceinline__ void bulk_load_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::"r"(
+            smem_addr(dst)),
+        "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
                      smem_addr(dst)),
@@ -220,15 +228,17 @@ __global__ void __launch_bounds__(kThreadsTc, 1) w2a8_gemm_tc_kernel(const TcPar
     if (warp == kProducerWarp) {
         // ---- producer ---------------------------------------------------------------------
         if (lane == 0) {
+            uint64_t w_policy;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(w_policy));
             for (int c = 0; c < n_pack; ++c) {
                 const int s = c % kPackStages;
                 if (c >= kPackStages && !bar_wait(&wempty[s], ((c / kPackStages) - 1) & 1, abort_flag)) break;
                 const int i0 = c * kPackTiles, nt = min(kPackTiles, nk - i0);
                 bar_expect_tx(&wfull[s], (uint32_t)(n_rg * nt * kTileBytes));
                 for (int r = 0; r < n_rg; ++r)
-                    bulk_load(pack + s * kPackStageBytes + r * kPackTiles * kTileBytes,
-                              p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt_lo + i0) * kTileBytes,
-                              (uint32_t)(nt * kTileBytes), &wfull[s]);
+                    bulk_load_hint(pack + s * kPackStageBytes + r * kPackTiles * kTileBytes,
+                                   p.w2t + ((int64_t)(rg0 + r) * k_tiles + kt_lo + i0) * kTileBytes,
+                                   (uint32_t)(nt * kTileBytes), &wfull[s], w_policy);
             }
         } else if (lane == 1 && p.ycanon) {
             // the activation slabs of every pipeline step, straight into the operand buffers

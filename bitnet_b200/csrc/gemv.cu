@@ -75,10 +75,12 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
     constexpr int U = 4;   // weight tiles in flight per warp
     const uint4* wrow = p.w + (int64_t)row_group * p.k_tiles * 32 + lane;
     uint4 wv[U];
+    uint64_t w_policy;      // weights are read once per call: first out of L2
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(w_policy));
 #pragma unroll
     for (int u = 0; u < U; ++u) {
         const int kt = warp + u * kWarps;
-        if (kt < p.k_tiles) wv[u] = ldg_stream(wrow + (int64_t)kt * 32);
+        if (kt < p.k_tiles) wv[u] = ldg_stream_hint(wrow + (int64_t)kt * 32, w_policy);
     }
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(kThreads) w2a8_gemv_kernel(const GemvParams p)
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int kt = kt0 + u * kWarps;
-                if (kt < p.k_tiles) wv[u] = ldg_stream(wrow + (int64_t)kt * 32);
+                if (kt < p.k_tiles) wv[u] = ldg_stream_hint(wrow + (int64_t)kt * 32, w_policy);
             }
         }
 #pragma unroll
