@@ -168,6 +168,7 @@ class TPDecoder:
                 w2=_Linear([w2_p], [s_2], args.ffn_dim, backend, cols=(fs.start, fs.stop)), **norms))
         self.rope = rope_table(D, max_seq_len, args.rope_theta, device)
         self.max_seq_len = max_seq_len
+        self.fused_one_rank = True      # False: batched decode on one rank through the per-op path as well (for comparisons)
 
     # ---- collectives --------------------------------------------------------------------
     def _all_gather_cols(self, x: torch.Tensor) -> torch.Tensor:
@@ -216,9 +217,44 @@ class TPDecoder:
         return out.transpose(1, 2).reshape(B * T, Hl * D)
 
     @torch.no_grad()
+    def _hidden_one_rank(self, tokens: torch.Tensor, pos: torch.Tensor, cache) -> torch.Tensor:
+        """Batched decode on one rank: the same arithmetic as `hidden`, with the library's fused calls
+        (matmul + rescale in one call; residual, norm and next quantisation behind wo and w2 in one
+        kernel, as model.TransformerBlock.decode_fused)."""
+        from . import ops
+
+        a, B = self.args, tokens.shape[0]
+        h = self.emb[tokens.reshape(-1)].contiguous()
+        first = self.layers[0]["attention_norm"]
+        qa = ops.quant_input(h, first.weight, first.eps)
+
+        def mm(lin, q):
+            return ops.linear_w2a8(q[0], q[1], q[2], lin.weight, lin.scale, lin.seg_end, lin.n, lin.in_features)
+
+        def add_into(lin, q, nxt):
+            if getattr(lin, "_host_scale", None) is None:       # read once, outside any stream capture
+                lin._host_scale = float(lin.scale[0])
+            return ops.linear_w2a8_add_quant(q[0], q[1], q[2], lin.weight, lin._host_scale, lin.n, lin.in_features, h,
+                                             None if nxt is None else nxt.weight, 0.0 if nxt is None else nxt.eps)
+
+        for i, (L, c) in enumerate(zip(self.layers, cache)):
+            xqkv = mm(L["wqkv"], qa)
+            att = ops.attention_decode(xqkv, pos, self.rope, c[0], c[1], self.Hl, self.Hkvl, a.head_dim)
+            qo = ops.quant_input(att, L["attn_sub_norm"].weight, L["attn_sub_norm"].eps)
+            q13 = add_into(L["wo"], qo, L["ffn_norm"])
+            x13 = mm(L["w13"], q13)
+            q2 = ops.quant_input_glu(x13, L["ffn_sub_norm"].weight, L["ffn_sub_norm"].eps)
+            nxt = self.layers[i + 1]["attention_norm"] if i + 1 < len(self.layers) else None
+            qa = add_into(L["w2"], q2, nxt)
+        return h
+
+    @torch.no_grad()
     def hidden(self, tokens: torch.Tensor, pos: torch.Tensor, cache, kv_len: Optional[int] = None) -> torch.Tensor:
         """tokens int64 [B, T] -> final hidden state bf16 [B*T, dim] (identical on every rank)."""
         B, T = tokens.shape
+        if (self.world == 1 and self.backend == "kernel" and T == 1 and kv_len is None and B >= 16
+                and self.args.dim % 8 == 0 and self.fused_one_rank):
+            return self._hidden_one_rank(tokens, pos, cache)
         h = self.emb[tokens.reshape(-1)]
         for L, c in zip(self.layers, cache):
             xqkv = L["wqkv"](h, L["attention_norm"])

@@ -147,3 +147,29 @@ def test_bounded_wait_for_an_absent_rank_returns_an_error_status():
     a = Generator(model, 1, 32, use_cuda_graph=False, fused=True).generate(prompt, 8)
     b = Generator(model, 1, 32, use_cuda_graph=True, fused=True).generate(prompt, 8)
     assert torch.equal(a, b)
+
+
+def test_one_rank_batched_decode_fused_calls_equal_per_op_path():
+    """On one rank, batches of 16 or more take the library's fused calls (matmul + rescale,
+    residual + norm + quantisation behind wo and w2): same hidden states and tokens, bit for bit,
+    as the per-op path that the multi-rank decoder uses."""
+    from bitnet_b200.model import preset
+    from bitnet_b200.tensor_parallel import TPDecoder
+
+    args = preset("tiny", n_heads=4, n_kv_heads=2, ffn_dim=512, n_layers=3)
+    dec = TPDecoder(args, 9, 0, 1, "cuda", backend="kernel", max_seq_len=64)
+    outs = []
+    for fused in (True, False):
+        dec.fused_one_rank = fused
+        cache = dec.make_cache(24, 64)
+        g = torch.Generator("cuda").manual_seed(4)
+        tok = torch.randint(0, args.vocab_size, (24, 1), device="cuda", generator=g)
+        pos = torch.zeros(24, dtype=torch.int64, device="cuda")
+        hs = []
+        for s in range(5):
+            h = dec.hidden(tok, pos + s, cache)
+            hs.append(h.clone())
+            tok = dec.greedy(h).view(24, 1)
+        outs.append(torch.stack(hs))
+    dec.fused_one_rank = True
+    assert torch.equal(outs[0], outs[1])
