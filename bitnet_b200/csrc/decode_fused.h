@@ -70,11 +70,10 @@ struct StatPart {
 
 // ---------------------------------------------------------------------------------------
 // Tensor parallelism.  Every rank owns an exchange area in its own device memory that the other
-// ranks of the node map through CUDA IPC; producers store into every rank's area (plain peer
-// stores and atomics over NVLink) and then add to an arrival counter there; consumers poll their
-// own counter (bounded) and read their own memory.  No multicast loads, no bulk/TMA copies from
-// peer memory.  Counters only grow: the count a consumer waits for is step * per_step + base,
-// with `step` read from the rank's own step counter on the device, so that a captured CUDA
+// ranks of the node map through CUDA IPC; producers store tagged packets into every rank's area
+// (plain 8-byte peer stores over NVLink), consumers poll the packets in their own memory, bounded
+// in time.  No multicast loads, no bulk/TMA copies from peer memory, no atomics or fences between
+// GPUs.  The tags derive from the rank's own step counter on the device, so that a captured CUDA
 // graph can be replayed.
 // ---------------------------------------------------------------------------------------
 constexpr int kMaxTp = 8;
