@@ -117,7 +117,9 @@ __host__ __device__ inline size_t chain_carve(const ChainLinearParams& p, uint8_
 // BitLinear of the chain.  288 threads: 8 consumer warps and one producer warp; two CTAs fit an SM, so
 // that the successor kernel's CTAs are resident, and past their set-up, while this kernel still runs.
 // ---------------------------------------------------------------------------------------
-template <bool kOneToken>
+// kTp: the tensor-parallel paths (packets from and to other ranks) exist only in the instantiations
+// that a tensor-parallel decoder launches, so that they cost the single-GPU kernels nothing.
+template <bool kOneToken, bool kTp>
 __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const ChainLinearParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     ChainSmem sm;
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
 #pragma unroll 1
     for (int m = 0; m < p.M; ++m) {
         double2 st = make_double2(0.0, 0.0);
-        if (!p.tp_stats_in) st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
+        if (!kTp || !p.tp_stats_in) st = __ldcg(reinterpret_cast<const double2*>(p.stats_in + m));
         const float* tm = p.t + (int64_t)m * p.ldt;
         constexpr int kIt = 1024 / kCThreads;               // 8192 values per pass: all of a pass's loads in flight at once
         float4 lo[kIt], hi[kIt];
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             }
         };
         fetch(0);
-        if (p.tp_stats_in) {
+        if (kTp && p.tp_stats_in) {
             // tensor parallel: the statistics are the sum over all ranks' packets; lane 0 of every warp
             // gathers them (this rank's own vector is already on its way: the loads above)
             double ss = 0.0;
@@ -498,7 +500,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
     // Thread idx finalises output r of unit lu for token m; 16 consecutive threads hold the 16
     // outputs of one unit and token, and reduce their statistics by shuffles.
     const bool want_stats = p.stats_out != nullptr;
-    const unsigned int part_tag = p.out_kind == kOutTpPartial ? tp_tag(p.tp_tag_out) : 0u;
+    const unsigned int part_tag = (kTp && p.out_kind == kOutTpPartial) ? tp_tag(p.tp_tag_out) : 0u;
 #pragma unroll 1
     for (int base = 0; base < total_out; base += kCThreads) {
         const int idx = base + tid;
@@ -530,7 +532,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             const float a = sm.a_s[m];
             const int ys_m = sm.ysum_s[m];                  // fields hold weight + 1: take sum(y) off once per row
             const int v0 = sm.sacc[lu * 128 + r * 8 + m] - ys_m;
-            if (p.out_kind == kOutTpPartial) {
+            if (kTp && p.out_kind == kOutTpPartial) {
                 // this rank's exact partial sums, as packets [rank][m][row] of every rank's area
                 const size_t at = p.tp_part_off + (((size_t)p.tp.rank * p.M + m) * p.N + row) * sizeof(uint2);
 #pragma unroll 1
@@ -576,7 +578,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             }
             stat_add(p.stats_out + tid, ss, mx, false);
         }
-        if (p.tp.size > 1 && real && warp == 0) {
+        if (kTp && p.tp.size > 1 && real && warp == 0) {
             // Every rank normalises over the whole vector.  This GPU's CTAs add up in its own slot;
             // the last of them forwards the total to its packets in every rank's area.
             __syncwarp();            // the M adding threads are lanes of this warp
@@ -586,7 +588,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             if (last && lane < p.M) stat_forward(p.tp, p.tp_stats_off, p.M, lane, p.stats_out, tp_tag(p.tp_tag_out));
         }
     }
-    if (p.out_kind == kOutTpPartial && real && cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
+    if (kTp && p.out_kind == kOutTpPartial && real && cta == 0 && tid < p.M) p.a_out[tid] = sm.a_s[tid];
     CHAIN_STAMP(5)
     }
 }
@@ -657,11 +659,18 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpReduceParams p) 
         if (row < p.N) {
             int v = 0;
             bool ok = true;
-#pragma unroll 1
-            for (int r = 0; r < p.T; ++r) {          // every thread waits for its own packets; integer sums: any order
-                unsigned int x;
-                ok = tp_get(p.part + ((size_t)r * p.M + m) * p.N + row, tag, limit, x) && ok;
-                v += (int)x;
+            // every thread takes its own packets: all requested first, those still missing waited for;
+            // integer sums: any order
+            unsigned int xv[kMaxTp], xt[kMaxTp];
+#pragma unroll
+            for (int r = 0; r < kMaxTp; ++r)
+                if (r < p.T) tp_peek(p.part + ((size_t)r * p.M + m) * p.N + row, xv[r], xt[r]);
+#pragma unroll
+            for (int r = 0; r < kMaxTp; ++r) {
+                if (r < p.T) {
+                    if (xt[r] != tag) ok = tp_get(p.part + ((size_t)r * p.M + m) * p.N + row, tag, limit, xv[r]) && ok;
+                    v += (int)xv[r];
+                }
             }
             if (!ok) {
                 atomicExch(p.error_flag, kErrPeerWait);
@@ -1062,8 +1071,10 @@ size_t chain_attention_smem(const AttentionParams& p) {
 }
 
 int prepare_chain_kernels(size_t smem_optin) {
-    cudaError_t e = cudaFuncSetAttribute(chain_linear_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(chain_linear_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    cudaError_t e = cudaFuncSetAttribute(chain_linear_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chain_linear_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chain_linear_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chain_linear_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_optin);
     if (e != cudaSuccess) return check_cuda(e);
     const int attn = 96 * 1024;
     if ((e = cudaFuncSetAttribute(chain_attention_kernel<4, kAttnThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn)) != cudaSuccess ||
@@ -1074,9 +1085,14 @@ int prepare_chain_kernels(size_t smem_optin) {
 }
 
 int launch_chain_linear(const ChainLinearParams& p, cudaStream_t stream, bool pdl) {
-    if (p.M == 1 && !p.big_share)
-        return check_cuda(launch_chain_k(chain_linear_kernel<true>, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
-    return check_cuda(launch_chain_k(chain_linear_kernel<false>, p.grid, kCLinearThreads, chain_linear_smem(p), stream, p, pdl));
+    const bool one = p.M == 1 && !p.big_share, tp = p.tp.size > 1;
+    const size_t smem = chain_linear_smem(p);
+    cudaError_t e;
+    if (one && !tp) e = launch_chain_k(chain_linear_kernel<true, false>, p.grid, kCLinearThreads, smem, stream, p, pdl);
+    else if (!tp) e = launch_chain_k(chain_linear_kernel<false, false>, p.grid, kCLinearThreads, smem, stream, p, pdl);
+    else if (one) e = launch_chain_k(chain_linear_kernel<true, true>, p.grid, kCLinearThreads, smem, stream, p, pdl);
+    else e = launch_chain_k(chain_linear_kernel<false, true>, p.grid, kCLinearThreads, smem, stream, p, pdl);
+    return check_cuda(e);
 }
 
 int launch_embed(const EmbedParams& p, cudaStream_t stream, bool pdl) {
