@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kCLinearThreads, 2) chain_linear_kernel(const 
             }
         }
     };
-    if (n_chunks <= p.ring_stages) {
+    if (kOneToken || n_chunks <= p.ring_stages) {     // (the one-token form is only launched for resident shares)
         // The CTA's whole share sits in the ring (the usual case up to a few billion parameters):
         // every warp takes one contiguous run of it, nothing is released or refilled.
         const int lo_t = n_tiles * warp / kCWarps, hi_t = n_tiles * (warp + 1) / kCWarps;
