@@ -896,8 +896,19 @@ constexpr int kHeadMaxLoads = 10;   // 16-byte loads per lane per pass over a ro
 // (value, index) per token in part_val / part_idx[cta].
 // kCompact: the normalised activations (bf16 values) are kept as bf16 instead of f32, for batch x
 // hidden sizes whose f32 form does not fit shared memory; the products are the same.
-template <bool kCompact, class Sync>
-__device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, int cta, int n_cta, int tid, Sync sync) {
+// kRing: the weight rows arrive in shared memory by bulk copies - two row slots per warp, the first
+// two rows requested by the calling kernel - instead of being loaded by the warps' threads;
+// `ring` points at the slots ([warp][2][K] bf16), `bars` at one mbarrier per slot.  Same sums either way.
+constexpr int kHeadRingRows = 16;     // rows in flight per slot set: one per warp
+// One row of the projection into a warp's slot (one thread).
+__device__ __forceinline__ void head_request_row(const HeadParams& p, int row, uint8_t* dst, uint64_t* bar, uint64_t policy) {
+    const uint32_t bytes = (uint32_t)((size_t)p.K * sizeof(__nv_bfloat16));
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(dst, p.w + (int64_t)row * p.K, bytes, bar, policy);
+}
+template <bool kCompact, bool kRing, class Sync>
+__device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, int cta, int n_cta, int tid, Sync sync,
+                                          const uint8_t* ring = nullptr, uint64_t* bars = nullptr) {
     using XT = typename std::conditional<kCompact, __nv_bfloat16, float>::type;
     XT* xs = reinterpret_cast<XT*>(smem);                         // [M][K]
     double* red_d = reinterpret_cast<double*>(xs + (size_t)p.M * p.K);   // [16] (K is a multiple of 8)
@@ -942,8 +953,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
     for (int m = 0; m < 8; ++m) { bv[m] = -INFINITY; bi[m] = 0x7fffffff; }
     const int vec_per_row = p.K / 8;     // 16-byte pieces
     const uint64_t w_policy = l2_evict_first_policy();    // the projection is read once per step: first out of L2
-    for (int row = r0 + warp; row < r1; row += kHeadThreads / 32) {
-        const uint4* wr = reinterpret_cast<const uint4*>(p.w + (int64_t)row * p.K);
+    auto do_row = [&](int row, auto fetch) {      // fetch(v): 16-byte piece v of the row's weights
         float dot[8];
 #pragma unroll
         for (int m = 0; m < 8; ++m) dot[m] = 0.f;
@@ -952,7 +962,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
 #pragma unroll
             for (int u = 0; u < kHeadMaxLoads; ++u) {
                 const int v = base + u * 32 + lane;
-                if (v < vec_per_row) wv[u] = ldg_stream_hint(wr + v, w_policy);
+                if (v < vec_per_row) wv[u] = fetch(v);
             }
 #pragma unroll
             for (int u = 0; u < kHeadMaxLoads; ++u) {
@@ -988,6 +998,32 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
                 if (lane == 0 && p.logits) p.logits[(int64_t)m * p.V + row] = d;
                 if (d > bv[m]) { bv[m] = d; bi[m] = row + p.row_offset; }     // rows ascend: first maximum wins
             }
+        }
+    };
+    if constexpr (kRing) {
+        // every warp owns two row slots and refills a slot itself as soon as it has used it up: two
+        // rows per warp are in flight or in use at any time, and no warp waits for another
+        const size_t row_bytes = (size_t)p.K * sizeof(__nv_bfloat16);
+        const uint8_t* slot = ring + (size_t)warp * 2 * row_bytes;
+        uint64_t* full = bars + 2 * warp;
+        bool ok = true;
+        int k = 0;
+#pragma unroll 1
+        for (int row = r0 + warp; row < r1 && ok; row += kHeadThreads / 32, ++k) {
+            ok = mbar_wait(&full[k & 1], (k >> 1) & 1);
+            if (ok) {
+                const uint4* src = reinterpret_cast<const uint4*>(slot + (k & 1) * row_bytes);
+                do_row(row, [&](int v) { return src[v]; });
+            }
+            __syncwarp();
+            const int next = row + 2 * (kHeadThreads / 32);
+            if (lane == 0 && ok && next < r1) head_request_row(p, next, const_cast<uint8_t*>(slot) + (k & 1) * row_bytes, &full[k & 1], w_policy);
+        }
+        if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, kErrConsumerWait);
+    } else {
+        for (int row = r0 + warp; row < r1; row += kHeadThreads / 32) {
+            const uint4* wr = reinterpret_cast<const uint4*>(p.w + (int64_t)row * p.K);
+            do_row(row, [&](int v) { return ldg_stream_hint(wr + v, w_policy); });
         }
     }
     if (lane == 0) {

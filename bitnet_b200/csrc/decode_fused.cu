@@ -348,7 +348,39 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const Head
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
-    head_body<kCompact>(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
+    head_body<kCompact, false>(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
+}
+
+// The same with the projection's rows brought into shared memory by bulk copies: every warp owns
+// two row slots, requests its first two rows before the dependency wait (weights are constants) and
+// refills a slot as soon as it has used it up.  Bulk copies keep two rows per warp in flight with a
+// handful of instructions, which 512 threads issuing 16-byte loads do not.  For hidden sizes whose
+// 32 row slots fit shared memory beside the activations.
+template <bool kCompact>
+__global__ void __launch_bounds__(kHeadThreads, 1) output_head_ring_kernel(const HeadParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const size_t x_bytes = (kCompact ? 2 : 4) * (size_t)p.M * p.K + sizeof(float) * (32 + 16 * 8 * 2) + 64;
+    const size_t ring_off = (x_bytes + 127) / 128 * 128;
+    const size_t row_bytes = (size_t)p.K * sizeof(__nv_bfloat16);
+    uint8_t* ring = smem + ring_off;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + 2 * kHeadRingRows * row_bytes);     // [warp][2]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (lane == 0) {
+        mbar_init(&bars[2 * warp], 1);
+        mbar_init(&bars[2 * warp + 1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        const int cta = blockIdx.x, n_cta = gridDim.x;
+        const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
+        const uint64_t policy = l2_evict_first_policy();
+        for (int k = 0; k < 2; ++k) {
+            const int row = r0 + warp + k * (kHeadThreads / 32);
+            if (row < r1) head_request_row(p, row, ring + ((size_t)warp * 2 + k) * row_bytes, &bars[2 * warp + k], policy);
+        }
+    }
+    __syncwarp();
+    pdl_launch_dependents();
+    pdl_wait();
+    head_body<kCompact, true>(p, smem, blockIdx.x, gridDim.x, tid, [] { __syncthreads(); }, ring, bars);
 }
 
 // Greedy choice over the per-CTA maxima; writes the chosen ids, feeds them back as the next
@@ -457,6 +489,8 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     SET_SMEM(attention_decode_mma_kernel<16>, max_attn_smem)
     SET_SMEM(output_head_kernel<false>, max_head_smem)
     SET_SMEM(output_head_kernel<true>, max_head_smem)
+    SET_SMEM(output_head_ring_kernel<false>, max_head_smem)
+    SET_SMEM(output_head_ring_kernel<true>, max_head_smem)
 #undef SET_SMEM
     return kOk;
 }
@@ -494,15 +528,37 @@ int launch_attention(const AttentionParams& p, int batch, cudaStream_t stream, b
     return check_cuda(e);
 }
 
-// The activations of all tokens as f32 where that fits well into shared memory, else as bf16.
-static bool head_compact(const HeadParams& p) { return (size_t)p.M * p.K * sizeof(float) > 160 * 1024; }
-size_t head_smem(const HeadParams& p) {
-    return (head_compact(p) ? 2 : 4) * (size_t)p.M * p.K + sizeof(float) * (32 + 16 * 8 * 2) + 64;
+// Shared memory of the output head.  The activations of all tokens are kept as f32 where that
+// fits, else as bf16; the two 16-row stages of the ring-fed form are added where they fit too.
+static size_t head_x_bytes(const HeadParams& p, bool compact) {
+    return (compact ? 2 : 4) * (size_t)p.M * p.K + sizeof(float) * (32 + 16 * 8 * 2) + 64;
 }
+static size_t head_ring_bytes(const HeadParams& p, bool compact) {
+    return (head_x_bytes(p, compact) + 127) / 128 * 128 + 2 * (size_t)kHeadRingRows * p.K * sizeof(__nv_bfloat16) + 2 * kHeadRingRows * 8 + 64;
+}
+struct HeadPlan {
+    bool compact, ring;
+    size_t smem;
+};
+static HeadPlan head_plan(const HeadParams& p) {
+    const size_t cap = 227 * 1024;       // opt-in shared memory per CTA on sm_100
+    if (p.K % 8 == 0) {
+        for (bool compact : {false, true})
+            if (head_ring_bytes(p, compact) <= cap) return {compact, true, head_ring_bytes(p, compact)};
+    }
+    const bool compact = head_x_bytes(p, false) > 160 * 1024;
+    return {compact, false, head_x_bytes(p, compact)};
+}
+size_t head_smem(const HeadParams& p) { return head_plan(p).smem; }
 
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl) {
-    if (head_compact(p)) return check_cuda(launch_k(output_head_kernel<true>, grid, kHeadThreads, head_smem(p), stream, p, pdl));
-    return check_cuda(launch_k(output_head_kernel<false>, grid, kHeadThreads, head_smem(p), stream, p, pdl));
+    const HeadPlan h = head_plan(p);
+    if (h.ring) {
+        if (h.compact) return check_cuda(launch_k(output_head_ring_kernel<true>, grid, kHeadThreads, h.smem, stream, p, pdl));
+        return check_cuda(launch_k(output_head_ring_kernel<false>, grid, kHeadThreads, h.smem, stream, p, pdl));
+    }
+    if (h.compact) return check_cuda(launch_k(output_head_kernel<true>, grid, kHeadThreads, h.smem, stream, p, pdl));
+    return check_cuda(launch_k(output_head_kernel<false>, grid, kHeadThreads, h.smem, stream, p, pdl));
 }
 
 int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl) {

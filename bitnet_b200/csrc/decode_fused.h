@@ -213,6 +213,7 @@ struct HeadParams {
     TpPeers tp;                      // tensor parallel: the per-CTA maxima go to packets [size][grid][8] of every area
     size_t tp_val_off, tp_idx_off;
     TpTag tp_tag_out;
+    int* error_flag;                 // set when a bounded wait for weight rows runs out (may be null)
 };
 
 struct ArgmaxParams {

@@ -502,6 +502,7 @@ static HeadParams head_params(const Decoder* d, float* logits) {
     hp.h = d->h; hp.logits = logits; hp.part_val = d->part_val; hp.part_idx = d->part_idx;
     hp.stats_in = d->slot(d->cfg.n_layers - 1, kSlotH2);
     hp.M = d->cfg.batch; hp.K = d->cfg.dim; hp.V = d->loc.vocab_size;
+    hp.error_flag = d->error_flag;
     if (d->tp.size > 1) {
         const TpLayout lay = tp_layout(d->cfg, d->tp.size, kTpHeadGridMax);
         hp.row_offset = d->tp.rank * d->loc.vocab_size;
