@@ -906,7 +906,9 @@ __device__ __forceinline__ void head_request_row(const HeadParams& p, int row, u
     mbar_expect_tx(bar, bytes);
     bulk_g2s(dst, p.w + (int64_t)row * p.K, bytes, bar, policy);
 }
-template <bool kCompact, bool kRing, class Sync>
+// kOne: one token.  The token loops of the row code are unrolled; with one token their eight-fold
+// copy would be straight-line code that is jumped over but still fetched, row after row.
+template <bool kCompact, bool kRing, bool kOne, class Sync>
 __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, int cta, int n_cta, int tid, Sync sync,
                                           const uint8_t* ring = nullptr, uint64_t* bars = nullptr) {
     using XT = typename std::conditional<kCompact, __nv_bfloat16, float>::type;
@@ -947,6 +949,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
             put((size_t)m * p.K + k, bf16_round(get((size_t)m * p.K + k) * __bfloat162float(p.gamma[k]) * rinv));
     }
     const int r0 = (int)((int64_t)p.V * cta / n_cta), r1 = (int)((int64_t)p.V * (cta + 1) / n_cta);
+    constexpr int MM = kOne ? 1 : 8;     // tokens the row code is unrolled for
     float bv[8];
     int bi[8];
 #pragma unroll
@@ -954,9 +957,9 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
     const int vec_per_row = p.K / 8;     // 16-byte pieces
     const uint64_t w_policy = l2_evict_first_policy();    // the projection is read once per step: first out of L2
     auto do_row = [&](int row, auto fetch) {      // fetch(v): 16-byte piece v of the row's weights
-        float dot[8];
+        float dot[MM];
 #pragma unroll
-        for (int m = 0; m < 8; ++m) dot[m] = 0.f;
+        for (int m = 0; m < MM; ++m) dot[m] = 0.f;
         for (int base = 0; base < vec_per_row; base += 32 * kHeadMaxLoads) {
             uint4 wv[kHeadMaxLoads];
 #pragma unroll
@@ -970,7 +973,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
                 if (v < vec_per_row) {
                     const Vec8 wf = unpack_bf16x8(wv[u]);
 #pragma unroll
-                    for (int m = 0; m < 8; ++m) {
+                    for (int m = 0; m < MM; ++m) {
                         if (m < p.M) {
                             Vec8 xf;
                             if constexpr (kCompact) {
@@ -989,7 +992,7 @@ __device__ __forceinline__ void head_body(const HeadParams& p, uint8_t* smem, in
             }
         }
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
+        for (int m = 0; m < MM; ++m) {
             if (m < p.M) {
                 float d = dot[m];
 #pragma unroll

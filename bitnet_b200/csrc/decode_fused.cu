@@ -343,12 +343,12 @@ __global__ void __launch_bounds__(128, ROWS == 8 ? 3 : 1) attention_decode_mma_k
 // (bf16 weights, f32 accumulation, bf16-rounded result as gpu/model.py:280-281) and the
 // slice's argmax.  One warp per vocabulary row, all loads of a row in flight.
 // ---------------------------------------------------------------------------------------
-template <bool kCompact>
+template <bool kCompact, bool kOne>
 __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const HeadParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     pdl_wait();
-    head_body<kCompact, false>(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
+    head_body<kCompact, false, kOne>(p, smem, blockIdx.x, gridDim.x, threadIdx.x, [] { __syncthreads(); });
 }
 
 // The same with the projection's rows brought into shared memory by bulk copies: every warp owns
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_kernel(const Head
 // refills a slot as soon as it has used it up.  Bulk copies keep two rows per warp in flight with a
 // handful of instructions, which 512 threads issuing 16-byte loads do not.  For hidden sizes whose
 // 32 row slots fit shared memory beside the activations.
-template <bool kCompact>
+template <bool kCompact, bool kOne>
 __global__ void __launch_bounds__(kHeadThreads, 1) output_head_ring_kernel(const HeadParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const size_t x_bytes = (kCompact ? 2 : 4) * (size_t)p.M * p.K + sizeof(float) * (32 + 16 * 8 * 2) + 64;
@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(kHeadThreads, 1) output_head_ring_kernel(const
     __syncwarp();
     pdl_launch_dependents();
     pdl_wait();
-    head_body<kCompact, true>(p, smem, blockIdx.x, gridDim.x, tid, [] { __syncthreads(); }, ring, bars);
+    head_body<kCompact, true, kOne>(p, smem, blockIdx.x, gridDim.x, tid, [] { __syncthreads(); }, ring, bars);
 }
 
 // Greedy choice over the per-CTA maxima; writes the chosen ids, feeds them back as the next
@@ -487,10 +487,14 @@ int prepare_fused_kernels(size_t max_linear_smem, size_t max_attn_smem, size_t m
     SET_SMEM(attention_decode_kernel<16>, max_attn_smem)
     SET_SMEM(attention_decode_mma_kernel<8>, max_attn_smem)
     SET_SMEM(attention_decode_mma_kernel<16>, max_attn_smem)
-    SET_SMEM(output_head_kernel<false>, max_head_smem)
-    SET_SMEM(output_head_kernel<true>, max_head_smem)
-    SET_SMEM(output_head_ring_kernel<false>, max_head_smem)
-    SET_SMEM(output_head_ring_kernel<true>, max_head_smem)
+    SET_SMEM((output_head_kernel<false, false>), max_head_smem)
+    SET_SMEM((output_head_kernel<true, false>), max_head_smem)
+    SET_SMEM((output_head_kernel<false, true>), max_head_smem)
+    SET_SMEM((output_head_kernel<true, true>), max_head_smem)
+    SET_SMEM((output_head_ring_kernel<false, false>), max_head_smem)
+    SET_SMEM((output_head_ring_kernel<true, false>), max_head_smem)
+    SET_SMEM((output_head_ring_kernel<false, true>), max_head_smem)
+    SET_SMEM((output_head_ring_kernel<true, true>), max_head_smem)
 #undef SET_SMEM
     return kOk;
 }
@@ -553,12 +557,14 @@ size_t head_smem(const HeadParams& p) { return head_plan(p).smem; }
 
 int launch_head(const HeadParams& p, int grid, cudaStream_t stream, bool pdl) {
     const HeadPlan h = head_plan(p);
+    const bool one = p.M == 1;
+    auto go = [&](auto kernel) { return check_cuda(launch_k(kernel, grid, kHeadThreads, h.smem, stream, p, pdl)); };
     if (h.ring) {
-        if (h.compact) return check_cuda(launch_k(output_head_ring_kernel<true>, grid, kHeadThreads, h.smem, stream, p, pdl));
-        return check_cuda(launch_k(output_head_ring_kernel<false>, grid, kHeadThreads, h.smem, stream, p, pdl));
+        if (h.compact) return one ? go(output_head_ring_kernel<true, true>) : go(output_head_ring_kernel<true, false>);
+        return one ? go(output_head_ring_kernel<false, true>) : go(output_head_ring_kernel<false, false>);
     }
-    if (h.compact) return check_cuda(launch_k(output_head_kernel<true>, grid, kHeadThreads, h.smem, stream, p, pdl));
-    return check_cuda(launch_k(output_head_kernel<false>, grid, kHeadThreads, h.smem, stream, p, pdl));
+    if (h.compact) return one ? go(output_head_kernel<true, true>) : go(output_head_kernel<true, false>);
+    return one ? go(output_head_kernel<false, true>) : go(output_head_kernel<false, false>);
 }
 
 int launch_argmax(const ArgmaxParams& p, cudaStream_t stream, bool pdl) {
