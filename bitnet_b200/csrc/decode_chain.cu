@@ -659,17 +659,25 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpReduceParams p) 
         if (row < p.N) {
             int v = 0;
             bool ok = true;
-            // every thread takes its own packets: all requested first, those still missing waited for;
-            // integer sums: any order
-            unsigned int xv[kMaxTp], xt[kMaxTp];
-#pragma unroll
-            for (int r = 0; r < kMaxTp; ++r)
-                if (r < p.T) tp_peek(p.part + ((size_t)r * p.M + m) * p.N + row, xv[r], xt[r]);
+            // every thread takes its own packets: a pass that requests them all without waiting, then -
+            // only if one was missing - a pass that waits packet by packet; integer sums: any order
+            bool all = true;
 #pragma unroll
             for (int r = 0; r < kMaxTp; ++r) {
                 if (r < p.T) {
-                    if (xt[r] != tag) ok = tp_get(p.part + ((size_t)r * p.M + m) * p.N + row, tag, limit, xv[r]) && ok;
-                    v += (int)xv[r];
+                    unsigned int x, t;
+                    tp_peek(p.part + ((size_t)r * p.M + m) * p.N + row, x, t);
+                    all = all && t == tag;
+                    v += (int)x;
+                }
+            }
+            if (!all) {
+                v = 0;
+#pragma unroll 1
+                for (int r = 0; r < p.T; ++r) {
+                    unsigned int x;
+                    ok = tp_get(p.part + ((size_t)r * p.M + m) * p.N + row, tag, limit, x) && ok;
+                    v += (int)x;
                 }
             }
             if (!ok) {

@@ -136,33 +136,41 @@ __device__ __forceinline__ void tp_peek(const void* addr, unsigned int& value, u
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(value), "=r"(tag) : "l"(addr) : "memory");
 }
 // All ranks' statistics of token m from this rank's area, added in the order of the ranks (the same
-// sum on every rank).  All packets are requested first - one memory latency when they have all
-// arrived, instead of one per packet - and only those that have not are waited for.  False if a
-// packet did not arrive in time.
-__device__ __noinline__ bool tp_get_stats(const TpStatPackets* slots, int size, int M, int m, unsigned int tag,
+// sum on every rank).  First a pass that requests every packet without waiting - one memory
+// latency when they have all arrived, the usual case for all but the last rank to finish - and,
+// only if a tag was missing, a second pass that waits packet by packet.  False if a packet did not
+// arrive in time.
+__device__ __forceinline__ bool tp_get_stats(const TpStatPackets* slots, int size, int M, int m, unsigned int tag,
                                              long long limit_cycles, double& ss, float& mx) {
-    unsigned int v[kMaxTp][3], t[kMaxTp][3];
-#pragma unroll
-    for (int r = 0; r < kMaxTp; ++r) {
-        if (r < size) {
-            const TpStatPackets* src = slots + (size_t)r * M + m;
-#pragma unroll
-            for (int i = 0; i < 3; ++i) tp_peek(&src->w[2 * i], v[r][i], t[r][i]);
-        }
-    }
-    bool ok = true;
+    bool all = true;
     ss = 0.0;
     mx = 0.f;
 #pragma unroll
     for (int r = 0; r < kMaxTp; ++r) {
         if (r < size) {
             const TpStatPackets* src = slots + (size_t)r * M + m;
-#pragma unroll
-            for (int i = 0; i < 3; ++i)
-                if (t[r][i] != tag) ok = tp_get(&src->w[2 * i], tag, limit_cycles, v[r][i]) && ok;
-            ss += __longlong_as_double((long long)(((unsigned long long)v[r][1] << 32) | v[r][0]));
-            mx = fmaxf(mx, __uint_as_float(v[r][2]));
+            unsigned int lo, hi, mb, t0, t1, t2;
+            tp_peek(&src->w[0], lo, t0);
+            tp_peek(&src->w[2], hi, t1);
+            tp_peek(&src->w[4], mb, t2);
+            all = all && t0 == tag && t1 == tag && t2 == tag;
+            ss += __longlong_as_double((long long)(((unsigned long long)hi << 32) | lo));
+            mx = fmaxf(mx, __uint_as_float(mb));
         }
+    }
+    if (all) return true;
+    bool ok = true;
+    ss = 0.0;
+    mx = 0.f;
+#pragma unroll 1
+    for (int r = 0; r < size; ++r) {
+        const TpStatPackets* src = slots + (size_t)r * M + m;
+        unsigned int lo, hi, mb;
+        ok = tp_get(&src->w[0], tag, limit_cycles, lo) && ok;
+        ok = tp_get(&src->w[2], tag, limit_cycles, hi) && ok;
+        ok = tp_get(&src->w[4], tag, limit_cycles, mb) && ok;
+        ss += __longlong_as_double((long long)(((unsigned long long)hi << 32) | lo));
+        mx = fmaxf(mx, __uint_as_float(mb));
     }
     return ok;
 }
