@@ -28,6 +28,7 @@ SIGNATURES = {
     "bitnet_last_cuda_error": (ctypes.c_char_p, []),
     "bitnet_init": (_i, []),
     "bitnet_attention_decode": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "bitnet_sample_top_p": (_i, [_vp, _i64, _i, _i, _f, _f, ctypes.c_uint64, _vp, _vp, _vp, _vp, _vp]),
     "bitlinear_int8xint2": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bitlinear_int8xint2_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "bitlinear_int8xint2_noalloc_error": (_i, [_i]),

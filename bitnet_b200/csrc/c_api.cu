@@ -179,6 +179,15 @@ size_t bitnet_w2t_bytes(int N, int K) {
     return (size_t)(round_up(N, 16) * round_up(K, 128) / 4);
 }
 
+int bitnet_sample_top_p(const float* logits, int64_t ld, int batch, int vocab, float temperature, float top_p,
+                        uint64_t seed, const int64_t* pos, const float* uniforms, int64_t* out, int64_t* tokens,
+                        void* stream) {
+    set_status(kOk);
+    return sample_top_p(logits, ld, batch, vocab, temperature, top_p, seed, reinterpret_cast<const long long*>(pos),
+                        uniforms, reinterpret_cast<long long*>(out), reinterpret_cast<long long*>(tokens),
+                        static_cast<cudaStream_t>(stream));
+}
+
 int bitnet_pack_ternary(const int8_t* q, void* w2t, int N, int K, void* stream) {
     g_status = kOk;
     if (!q || !w2t || N < 1 || K < 1) return fail(kBadArgument);

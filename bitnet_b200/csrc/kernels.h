@@ -80,4 +80,9 @@ struct QuantArgs {
 };
 int act_quant(const QuantArgs& a, cudaStream_t stream);
 
+// Temperature + top-p sampling of one token per sequence from f32 logits [batch, ld] (sample.cu).
+int sample_top_p(const float* logits, long long ld, int batch, int vocab, float temperature, float top_p,
+                 unsigned long long seed, const long long* pos, const float* uniforms, long long* out,
+                 long long* tokens, cudaStream_t stream);
+
 }  // namespace bitnet

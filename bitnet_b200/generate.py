@@ -11,7 +11,7 @@ from typing import List, Optional
 
 import torch
 
-from . import _lib
+from . import _lib, ops
 from .model import BitLinearKernel, Transformer, make_cache
 
 
@@ -103,15 +103,21 @@ class FusedDecoder:
 
 
 class Generator:
-    AUTO_FUSED_MAX_BATCH = 2
+    AUTO_FUSED_MAX_BATCH = 4
 
     def __init__(self, model: Transformer, batch: int, max_seq_len: int, use_cuda_graph: bool = True,
-                 fused: Optional[bool] = None):
+                 fused: Optional[bool] = None, temperature: float = 0.0, top_p: float = 1.0, seed: int = 0):
         """fused=None picks the in-library decode step where it is the faster path (kernel model,
-        batch <= AUTO_FUSED_MAX_BATCH); fused=True asks for it up to batch 8."""
+        batch <= AUTO_FUSED_MAX_BATCH); fused=True asks for it up to batch 8.
+        temperature > 0 draws every next token from softmax(logits / temperature) cut at top_p
+        (gpu/generate.py:250-257) on the device, reproducibly for a given seed; 0 is greedy."""
         self.model, self.batch, self.max_seq_len = model, batch, max_seq_len
         dev = model.tok_embeddings.weight.device
         self.device = dev
+        self.temperature, self.top_p, self.seed = float(temperature), float(top_p), int(seed)
+        self.sampling = self.temperature > 0.0
+        self.logits = (torch.zeros((batch, model.args.vocab_size), dtype=torch.float32, device=dev)
+                       if self.sampling else None)
         self.cache = make_cache(model.args, batch, max_seq_len, device=dev)
         self.tokens = torch.zeros((batch, 1), dtype=torch.int64, device=dev)     # input of the next step
         self.pos = torch.zeros((batch,), dtype=torch.int64, device=dev)         # tokens already cached
@@ -128,10 +134,10 @@ class Generator:
         if fused and not can_fuse:
             raise ValueError("the fused decode chain needs the kernel model and batch <= 8")
         self.fused: Optional[FusedDecoder] = None
-        # fused=None: the in-library step where it is the faster path.  It repeats the activation
-        # prologue of every token in every CTA, so beyond two sequences one launch per operation
-        # wins (measured on B200, 2B architecture: batch 2: 1.66 vs 1.96 ms; batch 4: 2.38 vs
-        # 2.02 ms; batch 8: 3.94 vs 2.08 ms per step).
+        # fused=None: the in-library step where it is the faster path.  Its kernels repeat the
+        # activation prologue of every token in every CTA, so at eight sequences one launch per
+        # operation wins (measured on B200, 2B architecture, ms per step in-library vs per
+        # operation: batch 1: 0.82 vs 1.69; 2: 1.12 vs 1.71; 4: 1.55 vs 1.79; 8: 2.42 vs 1.92).
         if can_fuse and (fused or (fused is None and batch <= self.AUTO_FUSED_MAX_BATCH)):
             if model.rope is None or model.rope.shape[0] < max_seq_len:
                 from .model import rope_table
@@ -145,15 +151,26 @@ class Generator:
                 if fused:
                     raise
 
+    def _draw(self, logits: torch.Tensor, out: torch.Tensor, tokens: Optional[torch.Tensor]):
+        """The sampled ids for f32 logits [B, V]; the random numbers are a function of the seed,
+        the sequence and self.pos (already advanced), so a replayed graph draws afresh each step."""
+        ops.sample_top_p(logits, self.temperature, self.top_p, self.seed, pos=self.pos, out=out, tokens=tokens)
+
     def _step(self):
         if self.fused is not None:
-            self.fused.step(self.tokens, self.pos, self.out)
+            self.fused.step(self.tokens, self.pos, self.out, self.logits)
+            if self.sampling:
+                self._draw(self.logits, self.out, self.tokens)
             return
         logits = self.model(self.tokens, self.pos, self.cache)
+        self.pos.add_(1)
+        if self.sampling:
+            self.logits.copy_(logits[:, -1])
+            self._draw(self.logits, self.out, self.tokens)
+            return
         nxt = logits[:, -1].argmax(-1)
         self.out.copy_(nxt)
         self.tokens.copy_(nxt[:, None])
-        self.pos.add_(1)
 
     @torch.no_grad()
     def prefill(self, prompt: torch.Tensor):
@@ -164,10 +181,14 @@ class Generator:
         self._pos_host = T                      # host mirror of the positions (all sequences advance together)
         self.pos.zero_()
         logits = self.model(prompt, self.pos, self.cache, kv_len=T, last_only=True)
+        self.pos.fill_(T)
+        if self.sampling:
+            self.logits.copy_(logits[:, -1])
+            self._draw(self.logits, self.out, self.tokens)
+            return self.out.clone()
         nxt = logits[:, -1].argmax(-1)
         self.out.copy_(nxt)
         self.tokens.copy_(nxt[:, None])
-        self.pos.fill_(T)
         return nxt
 
     @torch.no_grad()
@@ -191,7 +212,9 @@ class Generator:
             self.graph_host = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph_host, stream=self.stream):
                 if self.fused is not None:
-                    self.fused.step(self.host_in, self.pos, self.host_out)
+                    self.fused.step(self.host_in, self.pos, self.host_out, self.logits)
+                    if self.sampling:
+                        self._draw(self.logits, self.host_out, self.host_in)
                 else:
                     self.tokens.copy_(self.host_in, non_blocking=True)
                     self._step()
@@ -244,7 +267,8 @@ class Generator:
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_new: int) -> torch.Tensor:
-        """Greedy decode; returns int64 [B, n_new] (first column = the token the prefill chose)."""
+        """Greedy (or, with a temperature, sampled) decode; returns int64 [B, n_new] (first column =
+        the token the prefill chose)."""
         first = self.prefill(prompt)
         self.capture()
         outs: List[torch.Tensor] = [first.clone()]

@@ -121,3 +121,22 @@ def attention_decode(xqkv: torch.Tensor, pos: torch.Tensor, rope: torch.Tensor, 
                                                 _lib.ptr(cache_k), _lib.ptr(cache_v), _lib.ptr(out), b, n_heads,
                                                 n_kv_heads, head_dim, length, _lib.stream_ptr()))
     return out
+
+
+def sample_top_p(logits: torch.Tensor, temperature: float, top_p: float, seed: int = 0,
+                 pos: Optional[torch.Tensor] = None, uniforms: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of f32 logits [B, V] with temperature and top-p, on the device (the
+    sampling branch of gpu/generate.py:250-257, gpu/sample_utils.py:8-30).  `uniforms` f32 [B] are
+    the random numbers to use; without them row b draws from a hash of (seed, b, pos[b]).  The ids
+    go to `out` (int64 [B], created if absent) and, if given, to `tokens` as well."""
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    b, v = logits.shape
+    if out is None:
+        out = torch.empty((b,), dtype=torch.int64, device=logits.device)
+    assert uniforms is None or (uniforms.dtype == torch.float32 and uniforms.numel() == b)
+    assert pos is None or (pos.dtype == torch.int64 and pos.numel() == b)
+    _lib.check(_lib.lib.bitnet_sample_top_p(_lib.ptr(logits), logits.stride(0), b, v, float(temperature), float(top_p),
+                                            int(seed) & 0xFFFFFFFFFFFFFFFF, _lib.ptr(pos), _lib.ptr(uniforms),
+                                            _lib.ptr(out), _lib.ptr(tokens), _lib.stream_ptr()))
+    return out

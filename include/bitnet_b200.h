@@ -186,6 +186,21 @@ int bitnet_decoder_step_sync(void* decoder, int64_t* tokens, int64_t* pos, int64
 int bitnet_attention_decode(const void* xqkv, int64_t ld_qkv, const int64_t* pos, const float* rope, void* cache_k,
                             void* cache_v, void* out, int batch, int n_heads, int n_kv_heads, int head_dim,
                             int max_seq_len, void* stream);
+/* The next token of every sequence drawn from its logits with a temperature and a top-p cut, on
+ * the device: what the reference's decode loop does between two steps (gpu/generate.py:250-257
+ * with gpu/sample_utils.py:8-30) - probs = softmax(logits / temperature), keep the most probable
+ * entries whose exclusive cumulative probability does not exceed top_p, draw one of them in
+ * proportion to its probability.  (temperature == 0 is the reference's argmax branch: that is
+ * what bitnet_decoder_step's `out` already holds.)
+ *   logits f32 [batch, ld], vocab <= ld; temperature > 0; top_p >= 0 (>= 1 keeps every entry)
+ *   uniforms f32 [batch] in [0, 1), the caller's random numbers, or NULL: then sequence b draws
+ *     from a counter hash of (seed, b, pos[b]) (pos int64 [batch] or NULL), which gives a new
+ *     number every step when the call is replayed inside a captured graph
+ *   out, tokens int64 [batch]: the chosen ids are written to both (either may be NULL)
+ * One kernel, no allocation, no synchronisation. */
+int bitnet_sample_top_p(const float* logits, int64_t ld, int batch, int vocab, float temperature, float top_p,
+                        uint64_t seed, const int64_t* pos, const float* uniforms, int64_t* out, int64_t* tokens,
+                        void* stream);
 /* The decoder's error word (synchronises the device): 0, or the code of what a kernel of this
  * decoder met - 1, 2: a bounded wait for weight tiles ran out; 4: a position outside the KV
  * cache; 5: a token id outside the vocabulary. */

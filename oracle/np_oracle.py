@@ -361,6 +361,61 @@ class RefLib:
 
 
 # ----------------------------------------------------------------------------------------
+# sampling of the next token (temperature + top-p)
+# ----------------------------------------------------------------------------------------
+
+
+def top_p_weights(logits: np.ndarray, temperature: float, top_p: float):
+    """The nucleus of gpu/sample_utils.py:8-30 applied to softmax(logits / temperature)
+    (gpu/generate.py:250-257), in exact (f64) arithmetic over f32 exponentials: sort descending
+    (ties in index order), drop every entry whose exclusive cumulative mass exceeds top_p times
+    the total.  Returns (e f32 [V] unnormalised probabilities, kept bool [V], margin f64 [V]):
+    margin is the distance of each entry's exclusive cumulative share from top_p, so that a
+    checker can excuse entries that sit on the cut within rounding."""
+    lg = np.asarray(logits, dtype=np.float32)
+    e = np.exp((lg - lg.max()) * np.float32(1.0 / temperature)).astype(np.float32)
+    order = np.argsort(-e, kind="stable")
+    es = e[order].astype(np.float64)
+    total = es.sum()
+    excl = np.cumsum(es) - es
+    kept = np.zeros(e.shape, dtype=bool)
+    kept[order] = excl <= top_p * total
+    margin = np.empty(e.shape, dtype=np.float64)
+    margin[order] = np.abs(excl / total - top_p)
+    return e, kept, margin
+
+
+def top_p_draw(e: np.ndarray, kept: np.ndarray, u: float) -> int:
+    """The kept entry, in index order, at which the running kept mass first exceeds u times the
+    kept mass: a draw from the renormalised nucleus (what torch.multinomial does to the sorted,
+    masked probabilities in gpu/sample_utils.py:27-29, with the entries taken in another order)."""
+    m = np.where(kept, e.astype(np.float64), 0.0)
+    cum = np.cumsum(m)
+    return int(np.searchsorted(cum, u * cum[-1], side="right"))
+
+
+def top_p_interval(e: np.ndarray, kept: np.ndarray, token: int):
+    """[lo, hi): the values of u for which top_p_draw returns `token` (empty if it is not kept)."""
+    m = np.where(kept, e.astype(np.float64), 0.0)
+    cum = np.cumsum(m)
+    return (cum[token] - m[token]) / cum[-1], cum[token] / cum[-1]
+
+
+def counter_uniform(seed: int, row: int, pos: int) -> np.float32:
+    """The library's counter-based random number for (seed, sequence, position): a splitmix64
+    finaliser (Steele, Lea, Flood 2014) over the three, top 24 bits as a fraction."""
+    mask = (1 << 64) - 1
+    x = (seed + 0x9E3779B97F4A7C15 * (row + 1)) & mask
+    x ^= (pos * 0xD1B54A32D192ED03) & mask
+    x ^= x >> 30
+    x = (x * 0xBF58476D1CE4E5B9) & mask
+    x ^= x >> 27
+    x = (x * 0x94D049BB133111EB) & mask
+    x ^= x >> 31
+    return np.float32((x >> 40) / 16777216.0)
+
+
+# ----------------------------------------------------------------------------------------
 # seeded synthetic inputs with the shapes and value distributions of the kernel sweep
 # ----------------------------------------------------------------------------------------
 
