@@ -34,8 +34,18 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+FLAVOUR = os.path.join(PKG, "build", "flavour")     # "plain" or "trace": what the library on disk was built as
+
+
+def _flavour() -> str:
+    try:
+        return open(FLAVOUR).read().strip()
+    except OSError:
+        return "plain"
+
+
 def is_stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or _flavour() != "plain":
         return True
     t = os.path.getmtime(LIB)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
@@ -69,6 +79,8 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> st
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+    with open(FLAVOUR, "w") as f:
+        f.write("trace" if trace else "plain")
     return LIB
 
 
