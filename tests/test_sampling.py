@@ -158,7 +158,9 @@ def test_generator_samples_reproducibly(fused):
 
     args = preset("tiny", n_layers=2)
     model = build_synthetic(args, seed=5, device="cuda", max_seq_len=64)
-    prompt = torch.randint(0, args.vocab_size, (2, 8), device="cuda")
+    # a fixed prompt: with a random one the tiny model now and then falls into a loop whose next
+    # token has probability > top_p, where sampling and argmax rightly agree on every token
+    prompt = torch.randint(0, args.vocab_size, (2, 8), device="cuda", generator=torch.Generator("cuda").manual_seed(0))
     runs = []
     for seed, graph in ((3, True), (3, False), (4, True)):
         gen = Generator(model, batch=2, max_seq_len=64, use_cuda_graph=graph, fused=fused, temperature=0.8, top_p=0.9, seed=seed)
