@@ -25,3 +25,18 @@ def test_quant_weight_int8_equals_oracle_ternarize():
     q_want, s_want = O.ternarize(w0)
     assert not q.any() and np.array_equal(q.numpy(), q_want)
     assert float(s.float()) == float(O.to_bf16(np.array([s_want], dtype=np.float32))[0]) == float(O.to_bf16(np.array([1e-5], dtype=np.float32))[0])
+
+
+def test_plain_build_after_trace_build_is_stale(tmp_path, monkeypatch):
+    """The library on disk may be the measurement build (phase time stamps compiled in): a plain
+    build request must then rebuild instead of returning it as up to date."""
+    from bitnet_b200 import build as b
+
+    flavour = tmp_path / "flavour"
+    monkeypatch.setattr(b, "FLAVOUR", str(flavour))
+    flavour.write_text("plain")
+    fresh = b.is_stale()            # whatever the time stamps say with a plain library on disk
+    flavour.write_text("trace")
+    assert b.is_stale()
+    flavour.unlink()
+    assert b.is_stale() == fresh    # no record: taken as plain
