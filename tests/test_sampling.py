@@ -170,3 +170,31 @@ def test_generator_samples_reproducibly(fused):
     assert (runs[0] != runs[2]).any()          # another seed, another continuation
     greedy = Generator(model, batch=2, max_seq_len=64, fused=fused).generate(prompt, 24).cpu().numpy()
     assert (greedy != runs[0]).any()
+
+
+# ----------------------------------------------------------------------------------------------
+# properties of the checker itself (any logits)
+# ----------------------------------------------------------------------------------------------
+
+def test_checker_properties_on_random_rows():
+    from hypothesis import given, settings, strategies as st
+    from hypothesis.extra import numpy as hnp
+
+    @settings(max_examples=60, deadline=None)
+    @given(hnp.arrays(np.float32, st.integers(1, 300), elements=st.floats(-30, 30, width=32)),
+           st.floats(0.05, 2.0), st.floats(0.0, 1.0), st.floats(0.0, 0.999))
+    def check(logits, temperature, top_p, u):
+        e, kept, _ = o.top_p_weights(logits, temperature, top_p)
+        # the most probable entry is always kept; what is kept is a prefix of the descending order
+        assert kept[np.argmax(e)]
+        assert e[kept].min() >= e[~kept].max() if (~kept).any() else True
+        # the kept mass reaches top_p of the total as soon as anything is dropped
+        if (~kept).any():
+            assert e[kept].astype(np.float64).sum() >= top_p * e.astype(np.float64).sum() * (1 - 1e-12)
+        # a draw is a kept entry of positive mass whose interval holds u
+        t = o.top_p_draw(e, kept, u)
+        assert kept[t] and e[t] > 0
+        lo, hi = o.top_p_interval(e, kept, t)
+        assert lo <= u < hi or abs(u - lo) < 1e-12 or abs(u - hi) < 1e-12
+
+    check()
